@@ -1,0 +1,414 @@
+"""Benchmark of the paged decode-attention hot path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload NAME]
+
+Workload (default `dense_fp16_b16_16k`): Qwen2.5-1.5B attention shape — 12 query
+/ 2 KV heads, head_dim 128, page 16 — batch 16, every sequence at 16 384 tokens
+of context, 28 layers each with its own K/V pools of ceil(1.2 x needed) blocks
+and one shuffled block table; synthetic N(0,1) fp16 values. A STEP is one decode
+step's attention: the 28 layer calls (split-KV kernel + merge each), i.e. one
+pass over 7.5 GB of KV, far more than the 126 MB L2, so nothing is flushed
+between steps.
+
+One JSON line comes out:
+  value      KV bytes the step must read / step time, GB/s, steps replayed from
+             one CUDA graph with everything resident in HBM (all ranks summed).
+  e2e        the same metric through the public Python API with HOST buffers:
+             each step copies the queries and the new K/V rows of all layers
+             from pinned host memory, runs cache.advance() (block tables,
+             lengths and slots shipped to the device), cache.write() and
+             paged_decode_attention() per layer, eagerly, and reads the
+             outputs back to the host.
+  roofline   the split-KV kernel alone (no merge), timed with CUDA events.
+  cpu_baseline  the numpy oracle on the host cores, one layer call.
+`--impl reference` times that CPU oracle instead (rank 0 only).
+
+With N > 1 (launched by torchrun, one rank per GPU) every rank runs the same
+workload on its own GPU — sequences shard across GPUs with no exchange step —
+and the time is the max over ranks; `torch.distributed` is used for that
+barrier and max only.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import pathlib
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = pathlib.Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+WORKLOADS = {
+    # name: (batch, context, layers)
+    "dense_fp16_b16_16k": (16, 16384, 28),
+    "dense_fp16_b4_2k": (4, 2048, 4),          # small case for profiler captures
+    "dense_fp16_b16_4k": (16, 4096, 8),
+}
+METRIC = "paged decode-attn HBM GB/s"
+FALLBACK_HBM_GBS = 6650.0
+# DRAM bytes per launch of the split-KV kernel on the default workload, from the
+# Nsight Compute capture summarised under profiles/ (null until captured).
+NCU_TRAFFIC_BYTES = None
+
+
+def measured_peak():
+    path = ROOT / "MEASURED_PEAKS.json"
+    if path.exists():
+        try:
+            return float(json.loads(path.read_text())["hbm_gbs"]), "measured"
+        except Exception:
+            pass
+    return FALLBACK_HBM_GBS, "fallback"
+
+
+class ClockSampler:
+    """nvidia-smi clocks and throttle reasons, every 100 ms, while it runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.rows, self.proc, self.thread = [], None, None
+        self.index = index
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}",
+                 "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            return
+        self.thread = threading.Thread(target=self._read, daemon=True)
+        self.thread.start()
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append((time.time(), [x.strip() for x in line.split(",")]))
+
+    def stop(self):
+        if self.proc is not None:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=2)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+
+    def summary(self, t0: float, t1: float) -> dict:
+        rows = [r for t, r in self.rows if t0 <= t <= t1 and len(r) >= 6] or \
+               [r for _, r in self.rows if len(r) >= 6]
+        if not rows:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+        reasons = [n for i, n in enumerate(names) if any(r[2 + i].lower() == "active" for r in rows)]
+        mhz = [float(r[0]) for r in rows if r[0].replace(".", "").isdigit()]
+        mx = [float(r[1]) for r in rows if r[1].replace(".", "").isdigit()]
+        return {"sm_mhz": statistics.median(mhz) if mhz else None,
+                "sm_max_mhz": max(mx) if mx else None, "reasons": reasons, "samples": len(rows)}
+
+
+def cpu_oracle_layer(q, k_pool, v_pool, tables, lens, repeats=1):
+    """One layer call on the host cores (torch CPU ops, every thread) with the
+    oracle's gather-then-softmax restatement; numpy arrays in, seconds out."""
+    import torch
+
+    from oracle import paged_attention_oracle as orc
+
+    args = [torch.from_numpy(x) for x in (q, k_pool, v_pool, tables, lens)]
+    best = float("inf")
+    for _ in range(repeats):
+        t0 = time.perf_counter()
+        orc.paged_decode_torch_cpu(*args)
+        best = min(best, time.perf_counter() - t0)
+    return best
+
+
+def host_threads() -> int:
+    import torch
+
+    return torch.get_num_threads()
+
+
+def run_reference(args, workload):
+    """The CPU restatement of the reference's torch path, on the host cores.
+    Each step is a bounded sample of the workload: one layer call over
+    `sample_seqs` sequences at the workload's context."""
+    import numpy as np
+
+    from latentserve_b200 import synthetic
+
+    batch, context, layers = workload
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    sample_seqs = 4
+    case = synthetic.dense_case([context] * sample_seqs, seed=0, spare=0)
+    nbytes = synthetic.kv_bytes_fp16([context] * sample_seqs)
+    for _ in range(max(1, min(args.warmup, 2))):
+        cpu_oracle_layer(case["q"], case["k_pool"], case["v_pool"], case["block_tables"], case["seq_lens"])
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        cpu_oracle_layer(case["q"], case["k_pool"], case["v_pool"], case["block_tables"], case["seq_lens"])
+    dt = (time.perf_counter() - t0) / args.steps
+    value = nbytes / dt / 1e9
+    cores = host_threads()
+    sample = (f"one layer call over {sample_seqs} of the workload's {batch} sequences at context "
+              f"{context} ({nbytes / 1e6:.0f} MB of KV) per step, torch CPU fp32 gather-then-softmax")
+    print(json.dumps({
+        "impl": "reference", "metric": METRIC, "value": round(value, 3), "unit": "GB/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": round(dt * 1e3, 3), "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": args.workload, "batch": batch, "context": context, "layers": layers,
+                   "note": "CPU path, bounded sample per step"},
+        "cpu_baseline": {"value": round(value, 3), "unit": "GB/s", "cores": cores, "kind": "port",
+                         "sample": sample},
+        "e2e": {"value": round(value, 3), "unit": "GB/s", "h2d_bytes_per_step": 0,
+                "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=10)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="dense_fp16_b16_16k", choices=sorted(WORKLOADS))
+    ap.add_argument("--kernel", default="mma", choices=["mma", "simt"],
+                    help="split-KV kernel variant (simt = CUDA-core kernel, for profiling)")
+    ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    args = ap.parse_args()
+    workload = WORKLOADS[args.workload]
+    if args.impl == "reference":
+        run_reference(args, workload)
+        return
+
+    import numpy as np
+    import torch
+
+    from latentserve_b200 import _lib, cache as lc, paged_decode as pd, paged_decode_cuda as pdc
+    from latentserve_b200 import synthetic
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py measures the CUDA path and there is no CUDA device")
+    _lib.lib()                                    # fail here, loudly, if the library is missing
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    dev = torch.device("cuda", local)
+    torch.cuda.set_device(dev)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=dev)
+
+    batch, context, layers = workload
+    impl = pdc.IMPL_SIMT if args.kernel == "simt" else pdc.IMPL_MMA
+    w = synthetic.dense_pools_on_device(batch, context, layers, dev, seed=rank)
+    tables, lens = w["block_tables"], w["seq_lens"]
+    step_bytes = synthetic.kv_bytes_fp16([context] * batch) * layers
+
+    def layer_call(i, merge=True):
+        k, v = w["pools"][i]
+        return pdc.paged_decode_cuda(w["q"][i], k, v, tables, lens, context, impl=impl, merge=merge)
+
+    # One step = the 28 layer calls, captured once.
+    side = torch.cuda.Stream()
+    with torch.cuda.stream(side):
+        for _ in range(3):
+            for i in range(layers):
+                layer_call(i)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        for i in range(layers):
+            layer_call(i)
+
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    sampler = ClockSampler(torch.cuda.current_device() if "CUDA_VISIBLE_DEVICES" not in os.environ
+                           else int(os.environ["CUDA_VISIBLE_DEVICES"].split(",")[local]))
+    sampler.start()
+    for _ in range(max(3, args.warmup)):
+        graph.replay()
+    barrier()
+    t_wall0 = time.time()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        graph.replay()
+    e1.record()
+    barrier()
+    ms_total = e0.elapsed_time(e1)
+    # Keep the same load running briefly if the timed region was too short for
+    # the 100 ms clock sampler to see it.
+    extra_until = t_wall0 + 1.2
+    while time.time() < extra_until:
+        for _ in range(20):
+            graph.replay()
+        torch.cuda.synchronize()
+    t_wall1 = time.time()
+    if dist is not None:
+        t = torch.tensor([ms_total], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms_total = float(t.item())
+    ms_step = ms_total / args.steps
+    value = world * step_bytes / (ms_step * 1e-3) / 1e9
+
+    # Roofline: the split-KV kernel alone, one launch per layer, CUDA events on
+    # the launching (current) stream.
+    for i in range(layers):
+        layer_call(i, merge=False)
+    torch.cuda.synchronize()
+    reps = max(3, min(20, args.steps))
+    k0, k1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    k0.record()
+    for _ in range(reps):
+        for i in range(layers):
+            layer_call(i, merge=False)
+    k1.record()
+    torch.cuda.synchronize()
+    kernel_ms = k0.elapsed_time(k1) / (reps * layers)
+    clocks = sampler.summary(t_wall0, t_wall1)
+    peak, peak_kind = measured_peak()
+    layer_bytes = step_bytes // layers
+    achieved = layer_bytes / (kernel_ms * 1e-3) / 1e9
+    roofline = {"bound": "hbm", "achieved": round(achieved, 1), "peak": peak, "unit": "GB/s",
+                "frac": round(achieved / peak, 4), "traffic": NCU_TRAFFIC_BYTES,
+                "peak_kind": f"of {peak_kind}", "kernel": f"decode_kernel<{args.kernel}> (no merge)",
+                "kernel_us": round(kernel_ms * 1e3, 2), "algorithmic_bytes_per_launch": layer_bytes,
+                "frac_of_8TBs": round(achieved / 8000.0, 4)}
+
+    # End to end through the public API with host buffers.
+    e2e = None
+    if not args.no_e2e:
+        e2e = run_e2e(args, workload, dev, dist, world)
+
+    cpu = None
+    if rank == 0 and world == 1 and not args.no_cpu:
+        k, v = w["pools"][0]
+        blocks = tables.long()
+        seqs = min(batch, 4)
+        # The sample's blocks, renumbered into a compact pool on the host.
+        kb = k[blocks[:seqs].reshape(-1)].cpu().numpy()
+        vb = v[blocks[:seqs].reshape(-1)].cpu().numpy()
+        tb = np.arange(kb.shape[0], dtype=np.int32).reshape(seqs, -1)
+        secs = cpu_oracle_layer(w["q"][0][:seqs].cpu().numpy(), kb, vb, tb,
+                                lens[:seqs].cpu().numpy(), repeats=3)
+        nbytes = synthetic.kv_bytes_fp16([context] * seqs)
+        cpu = {"value": round(nbytes / secs / 1e9, 3), "unit": "GB/s", "cores": host_threads(),
+               "kind": "port",
+               "sample": f"one layer call over {seqs} of the {batch} sequences "
+                         f"({nbytes / 1e6:.0f} MB of KV), torch CPU fp32 gather-then-softmax, best of 3"}
+    sampler.stop()
+
+    if rank == 0:
+        line = {
+            "metric": METRIC, "value": round(value, 1), "unit": "GB/s", "n_gpus": world,
+            "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": round(ms_step, 4),
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f16",
+            "data": "synthetic",
+            "config": {"workload": args.workload, "batch_per_gpu": batch, "context": context,
+                       "layers_per_step": layers, "q_heads": 12, "kv_heads": 2, "head_dim": 128,
+                       "page": 16, "pool_blocks": w["num_blocks"], "kernel": args.kernel,
+                       "parallelism": f"replicas x{world} (sequence-sharded, no collective)",
+                       "l2": f"no flush: each step reads {step_bytes / 1e9:.2f} GB, L2 is 126 MB",
+                       "step": "28 layer calls (split-KV kernel + merge) replayed from one CUDA graph"},
+            "pct_of_8TBs": round(100.0 * value / world / 8000.0, 2),
+            "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e,
+            "gpu_launches": 2 * layers * args.steps, "clocks": clocks,
+        }
+        print(json.dumps(line))
+    if dist is not None:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def run_e2e(args, workload, dev, dist, world):
+    """Steps through PagedKVCache + paged_decode_attention with host buffers."""
+    import torch
+
+    from latentserve_b200 import cache as lc, paged_decode as pd, synthetic
+
+    batch, context, layers = workload
+    h, r, d = 2, 6, 128
+    steps = max(3, min(args.steps, 30))
+    warm = 3
+    need = -(-(context + steps + warm + 1) // 16)
+    spec = lc.KVCacheSpec(num_layers=layers, num_kv_heads=h, head_dim=d,
+                          max_seq_len=need * 16, max_batch_size=batch, device=str(dev))
+    cache = lc.PagedKVCache(spec, num_blocks=int(1.2 * batch * need) + 1)
+    g = torch.Generator(device=dev).manual_seed(1)
+    for layer in range(layers):
+        cache.k_pool[layer].normal_(generator=g)
+        cache.v_pool[layer].normal_(generator=g)
+    # Context already in the cache: grow the tables without writing (the pools
+    # hold synthetic values everywhere).
+    import random
+    random.Random(0).shuffle(cache.allocator._free)      # shuffled block tables, as in `value`
+    for i in range(batch):
+        cache.tables[i].append(context - 1)
+    host_q = torch.randn(layers, batch, h, r, d).half().pin_memory()
+    host_k = torch.randn(layers, batch, h, 1, d).half().pin_memory()
+    host_v = torch.randn(layers, batch, h, 1, d).half().pin_memory()
+    host_out = torch.empty(layers, batch, h, r, d, dtype=torch.float16).pin_memory()
+    dq, dk, dv = (torch.empty_like(x, device=dev) for x in (host_q, host_k, host_v))
+    dout = torch.empty(layers, batch, h, r, d, dtype=torch.float16, device=dev)
+
+    def step():
+        dq.copy_(host_q, non_blocking=True)
+        dk.copy_(host_k, non_blocking=True)
+        dv.copy_(host_v, non_blocking=True)
+        cache.advance(1, batch_size=batch)
+        tables, lens = cache.block_tables_tensor(batch), cache.seq_lens_tensor(batch)
+        for layer in range(layers):
+            cache.write(layer, dk[layer], dv[layer])
+            out = pd.paged_decode_attention(dq[layer], cache.k_pool[layer], cache.v_pool[layer],
+                                            tables, lens, max_seq_len=cache.max_len)
+            dout[layer].copy_(out)
+        host_out.copy_(dout, non_blocking=True)
+        torch.cuda.current_stream().synchronize()        # the step's result is on the host
+
+    for _ in range(warm):
+        step()
+    if dist is not None:
+        dist.barrier()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        step()
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1)
+    if dist is not None:
+        t = torch.tensor([ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    ms /= steps
+    mean_len = context + warm + (steps + 1) / 2
+    step_bytes = synthetic.kv_bytes_fp16([mean_len] * batch) * layers
+    h2d = (host_q.numel() + host_k.numel() + host_v.numel()) * 2 + batch * (8 + 4)
+    d2h = host_out.numel() * 2
+    return {"value": round(world * step_bytes / (ms * 1e-3) / 1e9, 1), "unit": "GB/s",
+            "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h),
+            "ms_per_step": round(ms, 4), "steps": steps,
+            "gpu_launches_per_step": 3 * layers,
+            "path": "PagedKVCache.advance + write + paged_decode_attention per layer, eager"}
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,191 @@
+/* latentserve_b200 — C ABI of the sm_100a paged decode-attention kernels.
+ *
+ * One shared library (libls_b200.so), plain pointers and sizes, no PyTorch
+ * types. Every pointer is a DEVICE pointer unless stated; every stride is in
+ * ELEMENTS of the tensor it belongs to; `stream` is a cudaStream_t passed as
+ * void* (0 = the default stream). Every entry point only validates and
+ * launches: no allocation, no host synchronisation, no device-to-host copy, so
+ * all of them can be recorded into a CUDA graph. The caller owns every buffer.
+ *
+ * Return value: 0 on success; < 0 an argument error (LS_ERR_*), nothing was
+ * launched; > 0 the cudaError_t of a failed launch.
+ *
+ * Shapes use B = sequences in the batch, H = KV heads, R = query rows per KV
+ * head (GQA ratio, <= 8), D = 128 (head_dim), P = 16 (tokens per page),
+ * NB = blocks in the pool, MP = block-table width. Each declaration cites the
+ * reference interface (path inside the LatentServe tree : lines) it replaces.
+ */
+#ifndef LATENTSERVE_B200_H
+#define LATENTSERVE_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define LS_OK 0
+#define LS_ERR_NULL_POINTER (-1)
+#define LS_ERR_BAD_SHAPE (-2)
+#define LS_ERR_BAD_STRIDE (-3)
+#define LS_ERR_MISALIGNED (-4)
+#define LS_ERR_TOO_LARGE (-5)
+#define LS_ERR_UNSUPPORTED (-6)
+#define LS_ERR_SCRATCH_TOO_SMALL (-7)
+
+#define LS_IMPL_MMA 0  /* tensor-core kernel (the product path) */
+#define LS_IMPL_SIMT 1 /* CUDA-core kernel, fp16 pools only (kept for profiling) */
+
+/* Partial-state scratch shared by the three decode entry points.
+ *
+ * The batch's pages are cut into `num_chunks` equal chunks; each (chunk,
+ * sequence) piece writes one partial softmax state. With
+ * slots = ls_decode_slots(B, num_chunks) the caller provides
+ *   part_acc  float [slots, H, 8, 128]
+ *   part_m    float [slots, H, 8]        running maxima, log2 domain
+ *   part_l    float [slots, H, 8]
+ *   seg_range int32 [2*B + 2]            written by the kernel: first slot and
+ *                                        slot count of each sequence; element
+ *                                        [2*B] is set to 1 if a block id or a
+ *                                        residual row outside its pool was met
+ *                                        (that page is skipped, never read).
+ *                                        Zero it once before first use.
+ * None of it needs filling between calls. `num_chunks` x H is the grid: the
+ * kernels are sized for 2 resident CTAs per SM, so num_chunks = 2*SMs / H is
+ * the natural choice; `min_chunk` (>= 1) is the fewest pages a chunk may hold.
+ * If `out` is non-NULL the merge (ls_combine) is launched as well and `out`
+ * receives fp16 [B, H, R, 128] with the given strides.
+ */
+int ls_decode_slots(int batch, int num_chunks);
+
+/* Dense fp16 paged GQA decode attention, split-KV partials (+ merge).
+ * Replaces kernels/cuda/paged_decode_fp16.cu:55-200 (kernel `paged_decode_fp16`)
+ * as launched by kernels/cuda/paged_decode_cuda.py:202-252.
+ *   q [B,H,R,128] fp16 (sq_*), k_pool/v_pool [NB,16,H,128] fp16 (sk_b, sk_p, sk_h; same for both),
+ *   block_tables int32 rows of stride max_pages, seq_lens int32 [B].
+ * Rows need 16-byte alignment. B <= 1024. */
+int ls_paged_decode_fp16(const void* q, const void* k_pool, const void* v_pool,
+                         const int32_t* block_tables, const int32_t* seq_lens, float* part_acc,
+                         float* part_m, float* part_l, int32_t* seg_range, void* out, int batch,
+                         int kv_heads, int n_rep, int head_dim, int page, int max_pages,
+                         int num_blocks, int num_chunks, int min_chunk, int impl, int64_t sq_b,
+                         int64_t sq_h, int64_t sq_m, int64_t sk_b, int64_t sk_p, int64_t sk_h,
+                         int64_t so_b, int64_t so_h, int64_t so_m, float softmax_scale,
+                         void* stream);
+
+/* INT8 paged GQA decode attention.
+ * Replaces kernels/cuda/paged_decode_int8.cu:87-280 (kernel `paged_decode_int8`,
+ * variants ASYM / HAS_RES) as launched by kernels/cuda/paged_decode_cuda.py:202-252.
+ *   k_pool/v_pool [NB,16,H,128] int8; k_scale (and k_zero) float [NB,H,128] (ks_b, ks_h);
+ *   v_scale (and v_zero) float [NB,16,H] (vs_b, vs_p, vs_h); k_zero/v_zero both NULL = symmetric;
+ *   k_res fp16 [rows,16,H,128] (sr_r, sr_p, sr_h) with res_rows int32 [B]: each sequence's LAST
+ *   page of K is read from k_res[res_rows[b]] instead of the pool (both NULL = no residual). */
+int ls_paged_decode_int8(const void* q, const void* k_pool, const void* v_pool,
+                         const int32_t* block_tables, const int32_t* seq_lens, const float* k_scale,
+                         const float* v_scale, const float* k_zero, const float* v_zero,
+                         const void* k_res, const int32_t* res_rows, float* part_acc, float* part_m,
+                         float* part_l, int32_t* seg_range, void* out, int batch, int kv_heads,
+                         int n_rep, int head_dim, int page, int max_pages, int num_blocks,
+                         int num_res_rows, int num_chunks, int min_chunk, int64_t sq_b, int64_t sq_h,
+                         int64_t sq_m, int64_t sk_b, int64_t sk_p, int64_t sk_h, int64_t ks_b,
+                         int64_t ks_h, int64_t vs_b, int64_t vs_p, int64_t vs_h, int64_t sr_r,
+                         int64_t sr_p, int64_t sr_h, int64_t so_b, int64_t so_h, int64_t so_m,
+                         float softmax_scale, void* stream);
+
+/* Attention over selected pages only.
+ * Replaces kernels/cuda/paged_sparse_fp16.cu:205-364 (kernel `paged_sparse_fp16`)
+ * as launched by kernels/cuda/paged_sparse.py:185-219.
+ *   sel int32 [B,H,num_sel] (sl_b, sl_h): page indices, best first. With ratio > 0 each sequence
+ *   attends the first n = min(max(recent+1, ceil(ratio*pages)), pages, num_sel) entries
+ *   (pages = its own page count; ratio >= 1: all its pages); ratio <= 0: every entry.
+ *   Entries < 0 or >= pages are skipped. */
+int ls_paged_sparse_fp16(const void* q, const void* k_pool, const void* v_pool,
+                         const int32_t* block_tables, const int32_t* seq_lens, const int32_t* sel,
+                         float ratio, int recent, float* part_acc, float* part_m, float* part_l,
+                         int32_t* seg_range, void* out, int batch, int kv_heads, int n_rep,
+                         int head_dim, int page, int max_pages, int num_blocks, int num_sel,
+                         int num_chunks, int min_chunk, int64_t sq_b, int64_t sq_h, int64_t sq_m,
+                         int64_t sk_b, int64_t sk_p, int64_t sk_h, int64_t sl_b, int64_t sl_h,
+                         int64_t so_b, int64_t so_h, int64_t so_m, float softmax_scale,
+                         void* stream);
+
+/* Merge of the split partials into out fp16 [B,H,R,128].
+ * Replaces the Triton `_combine_kernel`, kernels/gqa/paged_decode.py:421-471
+ * (torch form `combine_splits`, :689-706). Reads seg_range as a decode entry
+ * point left it. */
+int ls_combine(const float* part_acc, const float* part_m, const float* part_l,
+               const int32_t* seg_range, void* out, int batch, int kv_heads, int n_rep,
+               int64_t so_b, int64_t so_h, int64_t so_m, void* stream);
+
+/* fp16 cache append for one new token per sequence: K and V rows scattered to
+ * flat slot `slots[b]` of the pools and, if kmin/kmax are given, the page's
+ * per-channel K bounds reset (slot % 16 == 0) or widened.
+ * Replaces PagedKVCache.write, cache/paged_cache.py:398-417 (two index_copy_) and
+ * `page_bounds_update`, kernels/cuda/paged_sparse_fp16.cu:54-72.
+ *   k, v fp16 rows [B,H,128] (sk_b, sk_h / sv_b, sv_h); slots int64 [B];
+ *   k_pool/v_pool viewed flat [num_slots,H,128] (sp_t, sp_h); kmin/kmax fp16 [NB,H,128] (sb_b, sb_h).
+ *   k_pool == v_pool == NULL: bounds only. */
+int ls_kv_append_fp16(const void* k, const void* v, const int64_t* slots, void* k_pool, void* v_pool,
+                      void* kmin, void* kmax, int batch, int kv_heads, int head_dim, int page,
+                      int64_t num_slots, int64_t sk_b, int64_t sk_h, int64_t sv_b, int64_t sv_h,
+                      int64_t sp_t, int64_t sp_h, int64_t sb_b, int64_t sb_h, void* stream);
+
+/* INT8 cache decode-step write: V quantised per (token, head) and scattered,
+ * K copied into the fp16 residual. Bit-exact with the reference.
+ * Replaces `int8_decode_write`, kernels/cuda/int8_write.cu:45-78
+ * (host side kernels/cuda/int8_write.py:61-81).
+ *   flat_v int8 [num_slots,H,128], flat_v_scale / flat_v_zero float [num_slots,H],
+ *   k_res fp16 [num_res,H,128], all contiguous; res_idx int64 [B] rows of k_res.
+ *   inv_qmax = (float)1 / (float)qmax and inv_levels likewise, formed by the caller. */
+int ls_int8_decode_write(const void* k, const void* v, const int64_t* slots, const int64_t* res_idx,
+                         void* flat_v, float* flat_v_scale, float* flat_v_zero, void* k_res,
+                         int batch, int kv_heads, int head_dim, int64_t num_slots, int64_t num_res,
+                         int64_t sk_b, int64_t sk_h, int64_t sv_b, int64_t sv_h, int asym, float eps,
+                         float qmax, float inv_qmax, float levels, float inv_levels, float offset,
+                         void* stream);
+
+/* INT8 cache: quantise completed K pages out of the residual, one step per
+ * (block, head, channel). Bit-exact with the reference's torch ops on a GPU.
+ * Replaces Int8PagedKVCache._finalize_blocks, cache/int8_paged_cache.py:670-699.
+ *   k_res fp16 [num_rows,16,H,128] (sr_*); res_rows / block_ids int64 [count];
+ *   k_pool int8 [NB,16,H,128] (sk_*); k_scale / k_zero float [NB,H,128] (ss_b, ss_h). */
+int ls_int8_finalize_blocks(const void* k_res, const int64_t* res_rows, const int64_t* block_ids,
+                            void* k_pool, float* k_scale, float* k_zero, int count, int kv_heads,
+                            int head_dim, int page, int64_t num_rows, int64_t num_blocks,
+                            int64_t sr_r, int64_t sr_p, int64_t sr_h, int64_t sk_b, int64_t sk_p,
+                            int64_t sk_h, int64_t ss_b, int64_t ss_h, int asym, float eps, float qmax,
+                            float inv_qmax, float levels, float inv_levels, float offset,
+                            void* stream);
+
+/* Page scores for sparse selection: Quest upper bound from per-page K min/max,
+ * maximised over the R query rows; +inf for page 0 and the `recent` last
+ * pages, -inf past the sequence's end. fp32 evaluation order as the reference.
+ * Replaces `page_index`, kernels/cuda/paged_sparse_fp16.cu:78-130
+ * (host side kernels/cuda/paged_sparse.py:104-123).
+ *   kmin/kmax fp16 [NB,H,128] (sb_b, sb_h); scores float [B,H,max_pages] (ss_b, ss_h);
+ *   table_stride = block-table row stride >= max_pages. */
+int ls_page_index(const void* q, const void* kmin, const void* kmax, const int32_t* block_tables,
+                  const int32_t* seq_lens, float* scores, int batch, int kv_heads, int n_rep,
+                  int head_dim, int page, int max_pages, int table_stride, int num_blocks,
+                  int recent, int64_t sq_b, int64_t sq_h, int64_t sq_m, int64_t sb_b, int64_t sb_h,
+                  int64_t ss_b, int64_t ss_h, void* stream);
+
+/* Per-query-row bounds float [B,H,R,max_pages] (sh_b, sh_h, sh_r), 0 past the end.
+ * Replaces `page_index_heads`, kernels/cuda/paged_sparse_fp16.cu:141-190. */
+int ls_page_index_heads(const void* q, const void* kmin, const void* kmax,
+                        const int32_t* block_tables, const int32_t* seq_lens, float* heads_out,
+                        int batch, int kv_heads, int n_rep, int head_dim, int page, int max_pages,
+                        int table_stride, int num_blocks, int64_t sq_b, int64_t sq_h, int64_t sq_m,
+                        int64_t sb_b, int64_t sb_h, int64_t sh_b, int64_t sh_h, int64_t sh_r,
+                        void* stream);
+
+/* Top-k pages per (sequence, KV head): sel int32 [B,H,k] (sl_b, sl_h), score
+ * descending, ties to the lower page index.
+ * Replaces torch.topk(..., sorted=True) in `select`, kernels/cuda/paged_sparse.py:164-168. */
+int ls_topk_pages(const float* scores, int32_t* sel, int batch, int kv_heads, int num_pages, int k,
+                  int64_t ss_b, int64_t ss_h, int64_t sl_b, int64_t sl_h, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* LATENTSERVE_B200_H */

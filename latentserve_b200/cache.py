@@ -1,0 +1,483 @@
+"""Block-paged KV caches whose decode-step device work runs on this library's
+kernels — the host-side mirror of the reference's cache layer.
+
+    KVCacheSpec        cache/kv_cache.py:71-109         (fields used by the paged caches)
+    BlockAllocator     cache/block_allocator.py:40-162  (LIFO free list, reference counts)
+    BlockTable         cache/block_allocator.py:165-229 (blocks, length, version)
+    PagedKVCache       cache/paged_cache.py:57-566      (fp16 pools, page bounds)
+    Int8PagedKVCache   cache/int8_paged_cache.py:143-1028 (int8 pools, fp32 scales,
+                       fp16 K residual, deferred finalize)
+
+Same storage layout (`[num_blocks, 16, H, D]` pools per layer, `[max_batch,
+max_pages]` int32 block tables at capacity width, persistent decode buffers
+whose addresses never change), same call order (`advance` outside a captured
+graph, `write` and attention inside), same invariants (every K page but a
+sequence's last is in the INT8 pool, the last is exact in the residual;
+shared prefix blocks are full and read-only).
+
+What is different is the hot part: `write()` for one token per sequence is one
+launch (`ls_kv_append_fp16` / `ls_int8_decode_write`), INT8 page finalisation
+is one launch per layer (`ls_int8_finalize_blocks`) instead of a dozen torch
+ops, and `advance()` stages the step's indices in pinned host memory and ships
+them with one copy per buffer. Prefill writes (more than one token per
+sequence) are set-up, not the hot path; they reuse the same kernels row by row.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Optional, Sequence
+
+import numpy as np
+import torch
+
+from latentserve_b200 import int8_write as iw
+from latentserve_b200 import kv_write
+
+_EPS = 1e-8
+
+
+class OutOfBlocks(RuntimeError):
+    """The pool cannot supply the blocks asked for: backpressure, not a crash."""
+
+
+@dataclass
+class KVCacheSpec:
+    num_layers: int
+    num_kv_heads: int
+    head_dim: int
+    max_seq_len: int
+    max_batch_size: int
+    dtype: torch.dtype = torch.float16
+    device: str = "cuda"
+
+
+class BlockAllocator:
+    """Fixed pool of block ids with reference counts; most recently freed
+    block is handed out first."""
+
+    def __init__(self, num_blocks: int, block_size: int):
+        if num_blocks <= 0 or block_size <= 0:
+            raise ValueError("num_blocks and block_size must be positive")
+        self.num_blocks, self.block_size = num_blocks, block_size
+        self._free = list(range(num_blocks - 1, -1, -1))
+        self._refs = [0] * num_blocks
+
+    @property
+    def num_free(self) -> int:
+        return len(self._free)
+
+    @property
+    def num_used(self) -> int:
+        return self.num_blocks - len(self._free)
+
+    def blocks_for_tokens(self, num_tokens: int) -> int:
+        return -(-num_tokens // self.block_size)
+
+    def allocate(self, n: int) -> list[int]:
+        if n > len(self._free):
+            raise OutOfBlocks(f"need {n} blocks, {len(self._free)} free of {self.num_blocks}")
+        out = [self._free.pop() for _ in range(n)]
+        for b in out:
+            self._refs[b] = 1
+        return out
+
+    def incref(self, blocks) -> None:
+        for b in blocks:
+            if self._refs[b] <= 0:
+                raise ValueError(f"increfing block {b} that is not allocated")
+            self._refs[b] += 1
+
+    def free(self, blocks) -> None:
+        for b in blocks:
+            if self._refs[b] <= 0:
+                raise ValueError(f"freeing block {b} that is not allocated")
+            self._refs[b] -= 1
+            if self._refs[b] == 0:
+                self._free.append(b)
+
+    def ref_count(self, block: int) -> int:
+        return self._refs[block]
+
+    def reset(self) -> None:
+        self._free = list(range(self.num_blocks - 1, -1, -1))
+        self._refs = [0] * self.num_blocks
+
+
+class BlockTable:
+    """One sequence: its physical blocks in logical order, its length, and a
+    version that changes whenever the block list does."""
+
+    def __init__(self, allocator: BlockAllocator):
+        self.allocator = allocator
+        self.blocks: list[int] = []
+        self.length = 0
+        self.version = 0
+
+    def append(self, num_tokens: int) -> None:
+        need = self.allocator.blocks_for_tokens(self.length + num_tokens) - len(self.blocks)
+        if need > 0:
+            self.blocks.extend(self.allocator.allocate(need))
+            self.version += 1
+        self.length += num_tokens
+
+    def slot(self, position: int) -> int:
+        if not 0 <= position < self.length:
+            raise IndexError(f"position {position} beyond length {self.length}")
+        bs = self.allocator.block_size
+        return self.blocks[position // bs] * bs + position % bs
+
+    def free(self) -> None:
+        self.allocator.free(self.blocks)
+        self.blocks, self.length = [], 0
+        self.version += 1
+
+
+class _PagedBase:
+    """Bookkeeping shared by the two caches: tables, active set, and the
+    persistent device buffers a decode step reads."""
+
+    def __init__(self, spec: KVCacheSpec, block_size: int, num_blocks: Optional[int]):
+        if block_size != 16 or spec.head_dim != 128:
+            raise ValueError("the sm_100a kernels need block_size 16 and head_dim 128")
+        self.spec, self.block_size = spec, block_size
+        self.device = torch.device(spec.device)
+        if self.device.type != "cuda":
+            raise RuntimeError("latentserve_b200 caches live on a CUDA device; there is no CPU path")
+        per_seq = -(-spec.max_seq_len // block_size)
+        self.num_blocks = num_blocks if num_blocks is not None else per_seq * spec.max_batch_size
+        self.allocator = BlockAllocator(self.num_blocks, block_size)
+        mb = spec.max_batch_size
+        self.tables = [BlockTable(self.allocator) for _ in range(mb)]
+        self._active = list(range(mb))
+        self._capacity_pages = max(1, per_seq)
+        dev = self.device
+        self._block_tables_buf = torch.zeros((mb, self._capacity_pages), dtype=torch.int32, device=dev)
+        self._seq_lens_buf = torch.zeros(mb, dtype=torch.int32, device=dev)
+        self._write_slots_buf = torch.zeros((mb, 1), dtype=torch.int64, device=dev)
+        # Pinned staging: one host copy of each buffer, filled with numpy.
+        self._h_lens = torch.zeros(mb, dtype=torch.int32).pin_memory()
+        self._h_slots = torch.zeros(mb, dtype=torch.int64).pin_memory()
+        self._h_row = torch.zeros(self._capacity_pages, dtype=torch.int32).pin_memory()
+        self._table_state: list = [None] * mb
+        self._block_tables = self._seq_lens_tensor = self._write_slots = None
+        self._prefill_slots: Optional[torch.Tensor] = None
+
+    # -- state ---------------------------------------------------------
+    @property
+    def seq_lens(self) -> list[int]:
+        return [self.tables[i].length for i in self._active]
+
+    @property
+    def max_len(self) -> int:
+        return max((self.tables[i].length for i in self._active), default=0)
+
+    def active_slots(self) -> list[int]:
+        return list(self._active)
+
+    def set_active(self, slots: Sequence[int]) -> None:
+        slots = list(slots)
+        if len(set(slots)) != len(slots) or any(not 0 <= s < len(self.tables) for s in slots):
+            raise ValueError(f"bad active set {slots}")
+        self._active = slots
+
+    def can_admit(self, num_tokens: int) -> bool:
+        return self.allocator.blocks_for_tokens(num_tokens) <= self.allocator.num_free
+
+    def free_sequence(self, index: int) -> None:
+        self.tables[index].free()
+
+    def attach_prefix(self, index: int, blocks: Sequence[int], num_tokens: int) -> None:
+        """Start sequence `index` on already-written, full, shared blocks."""
+        table = self.tables[index]
+        if table.length or table.blocks:
+            raise ValueError(f"slot {index} is not empty")
+        if num_tokens != len(blocks) * self.block_size:
+            raise ValueError("a cached prefix is a whole number of full blocks")
+        self.allocator.incref(blocks)
+        table.blocks, table.length = list(blocks), num_tokens
+        table.version += 1
+
+    def block_tables_tensor(self, batch_size: Optional[int] = None) -> torch.Tensor:
+        if self._block_tables is None:
+            raise RuntimeError("call advance() before block_tables_tensor()")
+        return self._block_tables if batch_size is None else self._block_tables[:batch_size]
+
+    def seq_lens_tensor(self, batch_size: Optional[int] = None) -> torch.Tensor:
+        if self._seq_lens_tensor is None:
+            raise RuntimeError("call advance() before seq_lens_tensor()")
+        return self._seq_lens_tensor if batch_size is None else self._seq_lens_tensor[:batch_size]
+
+    # -- per-step staging ------------------------------------------------
+    def _grow(self, n: int, batch_size, slots):
+        if slots is not None:
+            self.set_active(slots)
+        elif batch_size is not None:
+            self.set_active(range(batch_size))
+        active = self._active
+        starts = [self.tables[i].length for i in active]
+        for i in active:
+            self.tables[i].append(n)
+        return active, starts
+
+    def _ship_tables(self, active: list[int]) -> None:
+        """Block-table rows that changed, and every active length."""
+        for row, i in enumerate(active):
+            t = self.tables[i]
+            state = (i, t.version)
+            if self._table_state[row] != state:
+                if len(t.blocks) > self._capacity_pages:
+                    raise RuntimeError(f"sequence in slot {i} needs {len(t.blocks)} pages, past the "
+                                       f"cache's capacity of {self._capacity_pages}")
+                if t.blocks:
+                    # A fresh pinned row each time: the copy below is asynchronous.
+                    src = torch.tensor(t.blocks, dtype=torch.int32)
+                    self._block_tables_buf[row, : len(t.blocks)].copy_(src)
+                self._table_state[row] = state
+        b = len(active)
+        self._h_lens[:b] = torch.tensor([self.tables[i].length for i in active], dtype=torch.int32)
+        self._seq_lens_buf[:b].copy_(self._h_lens[:b], non_blocking=False)
+        self._block_tables = self._block_tables_buf[:b]
+        self._seq_lens_tensor = self._seq_lens_buf[:b]
+
+    def _ship_decode_slots(self, active, starts) -> None:
+        b = len(active)
+        self._h_slots[:b] = torch.tensor([self.tables[i].slot(s) for i, s in zip(active, starts)],
+                                         dtype=torch.int64)
+        self._write_slots_buf[:b, 0].copy_(self._h_slots[:b], non_blocking=False)
+        self._write_slots = self._write_slots_buf[:b]
+
+
+class PagedKVCache(_PagedBase):
+    """fp16 block-paged KV cache."""
+
+    def __init__(self, spec: KVCacheSpec, block_size: int = 16, num_blocks: Optional[int] = None):
+        super().__init__(spec, block_size, num_blocks)
+        shape = (self.num_blocks, block_size, spec.num_kv_heads, spec.head_dim)
+        self.k_pool = [torch.zeros(shape, dtype=spec.dtype, device=self.device)
+                       for _ in range(spec.num_layers)]
+        self.v_pool = [torch.zeros(shape, dtype=spec.dtype, device=self.device)
+                       for _ in range(spec.num_layers)]
+        self._flat_k = [t.view(-1, spec.num_kv_heads, spec.head_dim) for t in self.k_pool]
+        self._flat_v = [t.view(-1, spec.num_kv_heads, spec.head_dim) for t in self.v_pool]
+        self._bounds_on = False
+        self.kmin: list = []
+        self.kmax: list = []
+
+    def reset(self) -> None:
+        """Free every sequence; storage and buffer addresses stay."""
+        for t in self.tables:
+            if t.blocks:
+                t.free()
+        self._table_state = [None] * len(self.tables)
+        self._active = list(range(len(self.tables)))
+
+    def shareable_blocks(self, index: int) -> int:
+        return self.tables[index].length // self.block_size
+
+    def advance(self, n: int, batch_size: Optional[int] = None,
+                slots: Optional[Sequence[int]] = None) -> None:
+        active, starts = self._grow(n, batch_size, slots)
+        if n == 1:
+            self._ship_decode_slots(active, starts)
+            self._prefill_slots = None
+        else:
+            self._prefill_slots = torch.tensor(
+                [[self.tables[i].slot(p) for p in range(s, s + n)] for i, s in zip(active, starts)],
+                dtype=torch.int64, device=self.device)
+            self._write_slots = self._prefill_slots
+        self._ship_tables(active)
+
+    def write(self, layer_idx: int, k: torch.Tensor, v: torch.Tensor, start_pos: int = 0) -> None:
+        """k, v [B, kv_heads, n, head_dim] -> the pools, at the slots `advance` reserved."""
+        b, h, n, d = k.shape
+        slots = self._write_slots
+        if slots is None or slots.shape[0] < b or slots.shape[1] != n:
+            raise RuntimeError("call advance(n, batch_size) before write()")
+        kmin = self.kmin[layer_idx] if self._bounds_on else None
+        kmax = self.kmax[layer_idx] if self._bounds_on else None
+        if n == 1:
+            kv_write.append_fp16(k, v, slots[:b, 0], self._flat_k[layer_idx],
+                                 self._flat_v[layer_idx], kmin, kmax, self.block_size)
+            return
+        # Prefill: the same kernel, one launch per position (bounds stay exact
+        # because positions are written in order).
+        for j in range(n):
+            kv_write.append_fp16(k[:, :, j], v[:, :, j], slots[:b, j].contiguous(),
+                                 self._flat_k[layer_idx], self._flat_v[layer_idx], kmin, kmax,
+                                 self.block_size)
+
+    def enable_page_bounds(self) -> None:
+        """Keep each block's per-channel min / max of K for the sparse indexer.
+        Bounds of blocks already written are rebuilt over their written rows."""
+        if self._bounds_on:
+            return
+        nb, _, h, d = self.k_pool[0].shape
+        self.kmin = [torch.zeros(nb, h, d, dtype=self.spec.dtype, device=self.device)
+                     for _ in self.k_pool]
+        self.kmax = [torch.zeros_like(t) for t in self.kmin]
+        self._bounds_on = True
+        bs = self.block_size
+        for t in self.tables:
+            for p, blk in enumerate(t.blocks):
+                rows = min(bs, t.length - p * bs)
+                if rows <= 0:
+                    continue
+                for layer in range(len(self.k_pool)):
+                    self.kmin[layer][blk] = self.k_pool[layer][blk, :rows].amin(dim=0)
+                    self.kmax[layer][blk] = self.k_pool[layer][blk, :rows].amax(dim=0)
+
+    def page_bounds(self, layer_idx: int):
+        return (self.kmin[layer_idx], self.kmax[layer_idx]) if self._bounds_on else None
+
+
+class Int8PagedKVCache(_PagedBase):
+    """INT8 block-paged KV cache: V quantised per (token, head) on write; K
+    quantised per (block, head, channel) when its 16-token page completes, the
+    still-filling page held exact in an fp16 residual per sequence slot."""
+
+    def __init__(self, spec: KVCacheSpec, block_size: int = 16, num_blocks: Optional[int] = None,
+                 asymmetric: bool = False):
+        super().__init__(spec, block_size, num_blocks)
+        nb, h, d, mb = self.num_blocks, spec.num_kv_heads, spec.head_dim, spec.max_batch_size
+        dev, layers = self.device, range(spec.num_layers)
+        self.asymmetric = asymmetric
+        self.k_qmax = self.v_qmax = 127
+        self.k_levels = self.v_levels = 255
+        self.k_offset = self.v_offset = 128
+        self.k_pool = [torch.zeros(nb, block_size, h, d, dtype=torch.int8, device=dev) for _ in layers]
+        self.v_pool = [torch.zeros(nb, block_size, h, d, dtype=torch.int8, device=dev) for _ in layers]
+        self.k_scale_pool = [torch.ones(nb, h, d, dtype=torch.float32, device=dev) for _ in layers]
+        self.v_scale_pool = [torch.ones(nb, block_size, h, dtype=torch.float32, device=dev)
+                             for _ in layers]
+        self.k_zero_pool = [torch.zeros_like(t) for t in self.k_scale_pool] if asymmetric else []
+        self.v_zero_pool = [torch.zeros_like(t) for t in self.v_scale_pool] if asymmetric else []
+        self._flat_v = [t.view(-1, h, d) for t in self.v_pool]
+        self._flat_v_scale = [t.view(-1, h) for t in self.v_scale_pool]
+        self._flat_v_zero = [t.view(-1, h) for t in self.v_zero_pool]
+        self._k_residual = [torch.zeros(mb, block_size, h, d, dtype=spec.dtype, device=dev)
+                            for _ in layers]
+        self._k_res_flat = [r.view(mb * block_size, h, d) for r in self._k_residual]
+        self._k_res_idx_buf = torch.zeros(mb, dtype=torch.int64, device=dev)
+        self._res_rows_buf = torch.zeros(mb, dtype=torch.int32, device=dev)
+        self._res_rows = None
+        self._fin = [0] * mb            # K pages already quantised, per slot (all layers at once)
+        self.deferred_finalize = True   # the only mode: pages finalise in the next advance()
+
+    def reset(self) -> None:
+        for t in self.tables:
+            if t.blocks:
+                t.free()
+        self._table_state = [None] * len(self.tables)
+        self._active = list(range(len(self.tables)))
+        self._fin = [0] * len(self.tables)
+
+    def free_sequence(self, index: int) -> None:
+        super().free_sequence(index)
+        self._fin[index] = 0
+
+    def shareable_blocks(self, index: int) -> int:
+        """Full blocks whose K is final in the pool (quantised), safe to share."""
+        return self._fin[index]
+
+    def attach_prefix(self, index: int, blocks: Sequence[int], num_tokens: int) -> None:
+        super().attach_prefix(index, blocks, num_tokens)
+        self._fin[index] = len(blocks)
+
+    def residual(self, layer_idx: int) -> torch.Tensor:
+        return self._k_residual[layer_idx]
+
+    def residual_rows_tensor(self, batch_size: Optional[int] = None) -> torch.Tensor:
+        if self._res_rows is None:
+            raise RuntimeError("residual rows exist only after a decode advance(1)")
+        return self._res_rows if batch_size is None else self._res_rows[:batch_size]
+
+    def _quant_consts(self) -> dict:
+        return dict(eps=_EPS, qmax=float(self.k_qmax), levels=float(self.k_levels),
+                    offset=float(self.k_offset))
+
+    def _finalize_pending(self, seqs: Sequence[int]) -> None:
+        """Quantise, in every layer, the page each of `seqs` completed since
+        its last finalisation. At most one per sequence: the residual holds one."""
+        bs = self.block_size
+        rows, ids = [], []
+        for s in seqs:
+            done = self.tables[s].length // bs
+            pending = done - self._fin[s]
+            if pending <= 0:
+                continue
+            if pending > 1:
+                raise RuntimeError(f"sequence in slot {s} has {pending} unquantized blocks; the "
+                                   "residual holds one, so the earlier ones are already lost")
+            rows.append(s)
+            ids.append(self.tables[s].blocks[done - 1])
+            self._fin[s] = done
+        if not rows:
+            return
+        r = torch.tensor(rows, dtype=torch.int64, device=self.device)
+        i = torch.tensor(ids, dtype=torch.int64, device=self.device)
+        for layer in range(self.spec.num_layers):
+            iw.finalize_blocks(self._k_residual[layer], r, i, self.k_pool[layer],
+                               self.k_scale_pool[layer],
+                               self.k_zero_pool[layer] if self.asymmetric else None,
+                               **self._quant_consts())
+
+    def advance(self, n: int, batch_size: Optional[int] = None,
+                slots: Optional[Sequence[int]] = None) -> None:
+        if slots is not None:
+            self.set_active(slots)
+        elif batch_size is not None:
+            self.set_active(range(batch_size))
+        self._finalize_pending(self._active)
+        active, starts = self._grow(n, None, None)
+        self._starts = starts
+        if n == 1:
+            b, bs = len(active), self.block_size
+            self._ship_decode_slots(active, starts)
+            self._k_res_idx_buf[:b].copy_(torch.tensor(
+                [i * bs + st % bs for i, st in zip(active, starts)], dtype=torch.int64))
+            self._res_rows_buf[:b].copy_(torch.tensor(active, dtype=torch.int32))
+            self._res_rows = self._res_rows_buf[:b]
+            self._prefill_slots = None
+        else:
+            self._prefill_slots = torch.tensor(
+                [[self.tables[i].slot(p) for p in range(s, s + n)] for i, s in zip(active, starts)],
+                dtype=torch.int64, device=self.device)
+            self._write_slots = self._prefill_slots
+        self._ship_tables(active)
+
+    def write(self, layer_idx: int, k: torch.Tensor, v: torch.Tensor, start_pos: int = 0) -> None:
+        b, h, n, d = k.shape
+        slots = self._write_slots
+        if slots is None or slots.shape[0] < b or slots.shape[1] != n:
+            raise RuntimeError("call advance(n, batch_size) before write()")
+        zero = self._flat_v_zero[layer_idx] if self.asymmetric else None
+        consts = dict(asym=self.asymmetric, eps=_EPS, qmax=float(self.v_qmax),
+                      levels=float(self.v_levels), offset=float(self.v_offset))
+        if n == 1:
+            iw.decode_write(k, v, slots[:b, 0], self._k_res_idx_buf[:b], self._flat_v[layer_idx],
+                            self._flat_v_scale[layer_idx], zero, self._k_res_flat[layer_idx], **consts)
+            return
+        # Prefill (set-up path): token by token through the same two kernels,
+        # finalising a sequence's page as soon as a position completes it.
+        bs = self.block_size
+        active, starts = self._active[:b], self._starts[:b]
+        for j in range(n):
+            res_idx = torch.tensor([i * bs + (s + j) % bs for i, s in zip(active, starts)],
+                                   dtype=torch.int64, device=self.device)
+            iw.decode_write(k[:, :, j:j + 1], v[:, :, j:j + 1], slots[:b, j].contiguous(), res_idx,
+                            self._flat_v[layer_idx], self._flat_v_scale[layer_idx], zero,
+                            self._k_res_flat[layer_idx], **consts)
+            rows = [i for i, s in zip(active, starts) if (s + j + 1) % bs == 0]
+            if rows:
+                ids = [self.tables[i].blocks[(s + j) // bs] for i, s in zip(active, starts)
+                       if (s + j + 1) % bs == 0]
+                iw.finalize_blocks(self._k_residual[layer_idx],
+                                   torch.tensor(rows, dtype=torch.int64, device=self.device),
+                                   torch.tensor(ids, dtype=torch.int64, device=self.device),
+                                   self.k_pool[layer_idx], self.k_scale_pool[layer_idx],
+                                   self.k_zero_pool[layer_idx] if self.asymmetric else None,
+                                   **self._quant_consts())
+        if layer_idx == self.spec.num_layers - 1:
+            for i, s in zip(active, starts):
+                self._fin[i] = (s + n) // bs

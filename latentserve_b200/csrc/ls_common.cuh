@@ -1,0 +1,129 @@
+// Shared device helpers for the paged decode-attention kernels (sm_100a).
+//
+// Everything here is warp-synchronous, register- or shared-memory-level
+// plumbing: cp.async (16-byte global->shared copies with zero-fill), ldmatrix,
+// the m16n8k16 fp16 tensor-core MMA with fp32 accumulation, the 8x8 register
+// transpose (movmatrix), ex2, and the status codes the C-ABI returns.
+//
+// None of the kernels built on this header spin on a flag, an mbarrier or a
+// peer: data arrives through cp.async groups, which complete on their own, so
+// there is no wait that could hang a GPU.
+#pragma once
+
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#define LS_HEAD_DIM 128
+#define LS_PAGE 16
+#define LS_FULL_MASK 0xffffffffu
+
+// Status codes returned by every extern "C" entry point (0 = ok, > 0 is a
+// cudaError_t from the launch, < 0 is an argument-validation failure).
+#define LS_OK 0
+#define LS_ERR_NULL_POINTER (-1)
+#define LS_ERR_BAD_SHAPE (-2)
+#define LS_ERR_BAD_STRIDE (-3)
+#define LS_ERR_MISALIGNED (-4)
+#define LS_ERR_TOO_LARGE (-5)
+#define LS_ERR_UNSUPPORTED (-6)
+#define LS_ERR_SCRATCH_TOO_SMALL (-7)
+
+namespace ls {
+
+__device__ __forceinline__ float neg_inf() { return __int_as_float(0xff800000); }
+__device__ __forceinline__ float pos_inf() { return __int_as_float(0x7f800000); }
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+    return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+
+// 16-byte asynchronous copy, L1-bypassing. src_bytes == 0 writes 16 zero bytes
+// and reads nothing, which is how rows past a sequence's end are kept free of
+// whatever bit patterns (NaN included) the pool holds there.
+__device__ __forceinline__ void cp_async_16(uint32_t dst, const void* src, int src_bytes) {
+    asm volatile("cp.async.cg.shared.global.L2::128B [%0], [%1], 16, %2;\n" ::"r"(dst), "l"(src),
+                 "r"(src_bytes)
+                 : "memory");
+}
+
+// 4-byte asynchronous copy (scalars such as a per-token V scale).
+__device__ __forceinline__ void cp_async_4(uint32_t dst, const void* src, int src_bytes) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;\n" ::"r"(dst), "l"(src),
+                 "r"(src_bytes)
+                 : "memory");
+}
+
+__device__ __forceinline__ void cp_async_commit() {
+    asm volatile("cp.async.commit_group;\n" ::: "memory");
+}
+
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+    asm volatile("cp.async.wait_group %0;\n" ::"n"(N) : "memory");
+}
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2,
+                                            uint32_t& r3) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
+                 : "r"(addr));
+}
+
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t addr, uint32_t& r0, uint32_t& r1,
+                                                  uint32_t& r2, uint32_t& r3) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
+                 : "r"(addr));
+}
+
+// D = A(16x16, fp16, row) * B(16x8, fp16, col) + D, fp32 accumulators.
+__device__ __forceinline__ void mma_16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2,
+                                          uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+        "{%0,%1,%2,%3};\n"
+        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// Transpose an 8x8 matrix of 16-bit values held one row-pair per lane.
+__device__ __forceinline__ uint32_t movmatrix_trans(uint32_t x) {
+    uint32_t y;
+    asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;\n" : "=r"(y) : "r"(x));
+    return y;
+}
+
+__device__ __forceinline__ float ex2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
+    return y;
+}
+
+__device__ __forceinline__ uint32_t pack_half2(float lo, float hi) {
+    const __half2 h = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<const uint32_t*>(&h);
+}
+
+__device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
+    uint32_t r;
+    asm("prmt.b32 %0, %1, %2, %3;\n" : "=r"(r) : "r"(a), "r"(b), "r"(sel));
+    return r;
+}
+
+// Four bytes already biased to unsigned (x ^ 0x80) -> two half2 registers
+// holding the signed values exactly: bytes (0,1) and bytes (2,3).
+// 0x6400 | u is the fp16 number 1024 + u; subtracting 1152 = 1024 + 128
+// undoes the bias. Every step is exact.
+__device__ __forceinline__ void bytes4_to_half2x2(uint32_t biased, uint32_t& lo, uint32_t& hi) {
+    const uint32_t magic = 0x64646464u;
+    uint32_t a = prmt(biased, magic, 0x4140u);   // [b0, 0x64, b1, 0x64]
+    uint32_t b = prmt(biased, magic, 0x4342u);   // [b2, 0x64, b3, 0x64]
+    const __half2 off = __floats2half2_rn(1152.f, 1152.f);
+    __half2 ha = __hsub2(*reinterpret_cast<__half2*>(&a), off);
+    __half2 hb = __hsub2(*reinterpret_cast<__half2*>(&b), off);
+    lo = *reinterpret_cast<uint32_t*>(&ha);
+    hi = *reinterpret_cast<uint32_t*>(&hb);
+}
+
+}  // namespace ls

@@ -1,0 +1,1006 @@
+// Paged GQA decode attention for B200 (sm_100a): dense fp16, INT8 and
+// page-sparse fp16, plus the log-sum-exp merge of the split partials.
+//
+// Replaces the reference's one-warp-per-program CUDA-core kernels
+//   kernels/cuda/paged_decode_fp16.cu:55-200   (dense fp16)
+//   kernels/cuda/paged_decode_int8.cu:87-280   (INT8 pools, fp16 K residual)
+//   kernels/cuda/paged_sparse_fp16.cu:205-364  (attention over selected pages)
+// and the Triton merge kernels/gqa/paged_decode.py:421-471.
+//
+// Design (see decode_sched.cuh for the partitioning):
+//   * grid = (chunks, KV heads); a CTA of W warps owns one chunk of the
+//     batch's page axis for one KV head, so every CTA streams the same number
+//     of bytes whatever the sequence lengths are.
+//   * each warp is its own cp.async pipeline over its pages (fp16 page-head =
+//     16 K rows + 16 V rows of 256 B): STAGES-deep ring in shared memory, rows
+//     stored with a 16-byte-chunk XOR swizzle so that shared-memory reads are
+//     free of bank conflicts. No warp waits on another warp inside the page
+//     loop, and nothing spins: cp.async groups complete on their own.
+//   * all query heads of the GQA group share each page load: scores are
+//     S[16 tokens x 8 rows] = K_page . Q^T on the tensor cores (m16n8k16,
+//     fp32 accumulation), the page's weights are transposed in registers
+//     (movmatrix) and O^T[128 x 8] += V_page^T . P^T accumulates in fp32.
+//     The CUDA-core variant (LS_IMPL_SIMT) does the same arithmetic with fp32
+//     FMAs and is kept to show where the issue-slot limit sits.
+//   * INT8 pages are expanded to fp16 in registers (exactly: |x| <= 128) on
+//     their way into the MMA fragments; K's per-(block, head, channel) scale
+//     is folded into the query once per page, V's per-token scale into the
+//     softmax weight, so neither pool is ever dequantised element by element.
+//   * rows past a sequence's end are zero-filled on the way in (cp.async with
+//     a zero source size) and their scores forced to -inf: stale pool bytes,
+//     NaN patterns included, never reach the arithmetic.
+//   * at the end of a segment the CTA's warps merge their states through
+//     shared memory and write ONE partial (m, l, acc) per (chunk, sequence,
+//     head); every slot a sequence owns is written, so nothing is pre-filled.
+#include "decode_sched.cuh"
+
+namespace ls {
+
+#define LS_IMPL_MMA 0
+#define LS_IMPL_SIMT 1
+
+constexpr int kWarps = 4;
+constexpr int kThreads = kWarps * 32;
+constexpr int kMergeStride = LS_HEAD_DIM + 4;   // floats per merged row (bank-conflict pad)
+constexpr int kRP = 8;                          // query rows held per partial
+
+// What the load side knows about the page it is about to fetch; the block id
+// is read one iteration ahead of its use so its latency hides behind compute.
+struct PageItem {
+    int blk;
+    int valid;      // tokens of the page that exist (0 = skip)
+    int last;       // 1 if this is the sequence's last page
+};
+
+template <int MODE>
+__device__ __forceinline__ PageItem fetch_item(const DecodeParams& p, const Cursor& c, int h,
+                                               int& cached_b, int& cached_len) {
+    PageItem it = {0, 0, 0};
+    if (c.done) return it;
+    if (c.b != cached_b) {
+        cached_b = c.b;
+        cached_len = max(p.seq_lens[c.b], 0);
+    }
+    const int np = min((cached_len + LS_PAGE - 1) / LS_PAGE, p.max_pages);
+    int page = c.u;
+    if (MODE == LS_MODE_SPARSE) page = p.sel[c.b * p.sl_b + h * p.sl_h + c.u];
+    if (page >= 0 && page < np) {
+        it.blk = p.block_tables[(long long)c.b * p.max_pages + page];
+        it.valid = min(LS_PAGE, cached_len - page * LS_PAGE);
+        it.last = page == np - 1;
+    }
+    return it;
+}
+
+// ---------------------------------------------------------------------------
+// Online softmax on MMA accumulator fragments. Lane (g = lane / 4, t = lane % 4)
+// holds scores of tokens g and g + 8 for query rows 2t and 2t + 1:
+// s[0] = (g, 2t), s[1] = (g, 2t+1), s[2] = (g+8, 2t), s[3] = (g+8, 2t+1).
+// On return s holds the weights 2^(s - m_new); m, l and the output
+// accumulators o[8][4] are rescaled. Scores are in the log2 domain.
+__device__ __forceinline__ void softmax_update(float (&s)[4], float (&m)[2], float (&l)[2],
+                                               float (&o)[8][4], float& a0, float& a1) {
+    float mx0 = fmaxf(s[0], s[2]);
+    float mx1 = fmaxf(s[1], s[3]);
+#pragma unroll
+    for (int off = 4; off < 32; off <<= 1) {
+        mx0 = fmaxf(mx0, __shfl_xor_sync(LS_FULL_MASK, mx0, off));
+        mx1 = fmaxf(mx1, __shfl_xor_sync(LS_FULL_MASK, mx1, off));
+    }
+    const float mn0 = fmaxf(m[0], mx0), mn1 = fmaxf(m[1], mx1);
+    // A row that has seen no valid token keeps m = -inf; subtracting a finite
+    // stand-in keeps exp2 away from (-inf) - (-inf).
+    const float ms0 = (mn0 == neg_inf()) ? 0.f : mn0;
+    const float ms1 = (mn1 == neg_inf()) ? 0.f : mn1;
+    a0 = ex2(m[0] - ms0);
+    a1 = ex2(m[1] - ms1);
+    s[0] = ex2(s[0] - ms0);
+    s[1] = ex2(s[1] - ms1);
+    s[2] = ex2(s[2] - ms0);
+    s[3] = ex2(s[3] - ms1);
+    m[0] = mn0;
+    m[1] = mn1;
+    l[0] = l[0] * a0 + (s[0] + s[2]);
+    l[1] = l[1] * a1 + (s[1] + s[3]);
+#pragma unroll
+    for (int mt = 0; mt < 8; ++mt) {
+        o[mt][0] *= a0;
+        o[mt][1] *= a1;
+        o[mt][2] *= a0;
+        o[mt][3] *= a1;
+    }
+}
+
+__device__ __forceinline__ void mask_and_scale(float (&s)[4], int valid, float scale_log2, int lane) {
+    const int g = lane >> 2;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) s[i] *= scale_log2;
+    if (g >= valid) s[0] = s[1] = neg_inf();
+    if (g + 8 >= valid) s[2] = s[3] = neg_inf();
+}
+
+// S[16 tokens x 8 rows] += K_page(fp16, swizzled at `kaddr`) . Q^T, with Q^T
+// given as B fragments over natural 16-dim k-steps.
+__device__ __forceinline__ void qk_fp16(float (&s)[4], uint32_t kaddr, const uint32_t (&qb)[8][2],
+                                        int lane) {
+    const int row = (lane & 7) + ((lane >> 3) & 1) * 8;
+    const uint32_t base = kaddr + row * 256;
+    const int sw = row & 7, hi = lane >> 4;
+#pragma unroll
+    for (int ks = 0; ks < 8; ++ks) {
+        uint32_t a0, a1, a2, a3;
+        ldmatrix_x4(base + (((2 * ks + hi) ^ sw) << 4), a0, a1, a2, a3);
+        mma_16816(s, a0, a1, a2, a3, qb[ks][0], qb[ks][1]);
+    }
+}
+
+// B fragments of Q^T over natural k-steps: lane (g, t) holds
+// Q[row g][16 ks + 2t, +1] and [16 ks + 8 + 2t, +1]; rows >= n_rep are zero.
+__device__ __forceinline__ void load_q_fragments(const DecodeParams& p, int b, int h, int lane,
+                                                 uint32_t (&qb)[8][2]) {
+    const int g = lane >> 2, t = lane & 3;
+    const __half* src = p.q + b * p.sq_b + h * p.sq_h + g * p.sq_m + 2 * t;
+#pragma unroll
+    for (int ks = 0; ks < 8; ++ks) {
+        uint32_t x0 = 0, x1 = 0;
+        if (g < p.n_rep) {
+            x0 = *reinterpret_cast<const uint32_t*>(src + ks * 16);
+            x1 = *reinterpret_cast<const uint32_t*>(src + ks * 16 + 8);
+        }
+        qb[ks][0] = x0;
+        qb[ks][1] = x1;
+    }
+}
+
+// ---------------------------------------------------------------------------
+// fp16 pools: page loads.
+struct PoolFp16 {
+    static constexpr int STAGE_BYTES = 8192;       // K 4096 | V 4096
+
+    // 256 16-byte chunks of K and of V per page-head, 8 + 8 per lane.
+    static __device__ __forceinline__ int issue(const DecodeParams& p, int, int h,
+                                                const PageItem& it, uint32_t stage, int lane) {
+        const __half* kb = static_cast<const __half*>(p.k_pool) + it.blk * p.sk_b + h * p.sk_h;
+        const __half* vb = static_cast<const __half*>(p.v_pool) + it.blk * p.sk_b + h * p.sk_h;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const int ci = i * 32 + lane;
+            const int row = ci >> 4, col = ci & 15;
+            const uint32_t dst = stage + row * 256 + ((col ^ (row & 7)) << 4);
+            const int nbytes = row < it.valid ? 16 : 0;
+            const long long off = nbytes ? row * p.sk_p + col * 8 : 0;
+            cp_async_16(dst, kb + off, nbytes);
+            cp_async_16(dst + 4096, vb + off, nbytes);
+        }
+        return it.valid;
+    }
+};
+
+// Tensor-core state for fp16 pools.
+struct MmaFp16 {
+    using Pool = PoolFp16;
+    uint32_t qb[8][2];
+    float o[8][4];             // O^T: tile mt = dims 16 mt + g (+8), rows 2t, 2t+1
+    float m[2], l[2];
+
+    __device__ __forceinline__ void begin(const DecodeParams& p, int b, int h, int lane) {
+        m[0] = m[1] = neg_inf();
+        l[0] = l[1] = 0.f;
+#pragma unroll
+        for (int mt = 0; mt < 8; ++mt)
+#pragma unroll
+            for (int i = 0; i < 4; ++i) o[mt][i] = 0.f;
+        load_q_fragments(p, b, h, lane, qb);
+    }
+
+    __device__ __forceinline__ void compute(const DecodeParams& p, uint32_t stage, int meta,
+                                            int lane) {
+        float s[4] = {0.f, 0.f, 0.f, 0.f};
+        qk_fp16(s, stage, qb, lane);
+        mask_and_scale(s, meta, p.scale_log2, lane);
+        float a0, a1;
+        softmax_update(s, m, l, o, a0, a1);
+        // (token g, rows 2t..2t+1) -> (tokens 2t..2t+1, row g): the B fragment
+        // layout of P^T for the second MMA.
+        const uint32_t pb0 = movmatrix_trans(pack_half2(s[0], s[1]));
+        const uint32_t pb1 = movmatrix_trans(pack_half2(s[2], s[3]));
+        const int j = lane >> 3;
+        const int row = (lane & 7) + (j >> 1) * 8;
+        const uint32_t base = stage + 4096 + row * 256;
+        const int sw = row & 7, odd = j & 1;
+#pragma unroll
+        for (int mt = 0; mt < 8; ++mt) {
+            uint32_t a0r, a1r, a2r, a3r;
+            ldmatrix_x4_trans(base + (((2 * mt + odd) ^ sw) << 4), a0r, a1r, a2r, a3r);
+            mma_16816(o[mt], a0r, a1r, a2r, a3r, pb0, pb1);
+        }
+    }
+
+    // Reduce row sums over the token lanes, then warp state -> shared memory.
+    __device__ __forceinline__ void finish(float* mo, float* mm, float* ml, int n_rep, int lane) {
+#pragma unroll
+        for (int off = 4; off < 32; off <<= 1) {
+            l[0] += __shfl_xor_sync(LS_FULL_MASK, l[0], off);
+            l[1] += __shfl_xor_sync(LS_FULL_MASK, l[1], off);
+        }
+        const int g = lane >> 2, t = lane & 3;
+        const int r0 = 2 * t, r1 = r0 + 1;
+#pragma unroll
+        for (int mt = 0; mt < 8; ++mt) {
+            const int d = mt * 16 + g;
+            if (r0 < n_rep) {
+                mo[r0 * kMergeStride + d] = o[mt][0];
+                mo[r0 * kMergeStride + d + 8] = o[mt][2];
+            }
+            if (r1 < n_rep) {
+                mo[r1 * kMergeStride + d] = o[mt][1];
+                mo[r1 * kMergeStride + d + 8] = o[mt][3];
+            }
+        }
+        if (g == 0) {
+            if (r0 < n_rep) { mm[r0] = m[0]; ml[r0] = l[0]; }
+            if (r1 < n_rep) { mm[r1] = m[1]; ml[r1] = l[1]; }
+        }
+    }
+};
+
+// ---------------------------------------------------------------------------
+// CUDA-core version of the same page step (fp16 pools only). A half-warp owns
+// a token: 16 lanes x 8 dims; the two halves take alternate tokens. R is the
+// compile-time bound on query rows.
+template <int R>
+struct SimtFp16 {
+    using Pool = PoolFp16;
+    float qf[R][8];
+    float acc[R][8];
+    float m[R], l[R];
+
+    __device__ __forceinline__ void begin(const DecodeParams& p, int b, int h, int lane) {
+        const int d0 = (lane & 15) * 8;
+#pragma unroll
+        for (int r = 0; r < R; ++r) {
+            m[r] = neg_inf();
+            l[r] = 0.f;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) acc[r][j] = 0.f;
+            if (r < p.n_rep) {
+                const uint4 raw =
+                    *reinterpret_cast<const uint4*>(p.q + b * p.sq_b + h * p.sq_h + r * p.sq_m + d0);
+                const __half2* h2 = reinterpret_cast<const __half2*>(&raw);
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const float2 f = __half22float2(h2[i]);
+                    qf[r][2 * i] = f.x * p.scale_log2;
+                    qf[r][2 * i + 1] = f.y * p.scale_log2;
+                }
+            } else {
+#pragma unroll
+                for (int j = 0; j < 8; ++j) qf[r][j] = 0.f;
+            }
+        }
+    }
+
+    static __device__ __forceinline__ void lds_row8(uint32_t addr, float (&f)[8]) {
+        uint4 raw;
+        asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];\n"
+                     : "=r"(raw.x), "=r"(raw.y), "=r"(raw.z), "=r"(raw.w)
+                     : "r"(addr));
+        const __half2* h2 = reinterpret_cast<const __half2*>(&raw);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const float2 t = __half22float2(h2[i]);
+            f[2 * i] = t.x;
+            f[2 * i + 1] = t.y;
+        }
+    }
+
+    __device__ __forceinline__ void compute(const DecodeParams&, uint32_t stage, int valid,
+                                            int lane) {
+        const int half_id = lane >> 4, li = lane & 15;
+        // Two rounds of four tokens per half keep the score registers modest.
+#pragma unroll
+        for (int round = 0; round < 2; ++round) {
+            float s[4][R];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const int tok = 2 * (round * 4 + i) + half_id;
+                float kf[8];
+                lds_row8(stage + tok * 256 + ((li ^ (tok & 7)) << 4), kf);
+#pragma unroll
+                for (int r = 0; r < R; ++r) {
+                    float dot = 0.f;
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) dot = fmaf(qf[r][j], kf[j], dot);
+                    s[i][r] = dot;
+                }
+            }
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+#pragma unroll
+                for (int r = 0; r < R; ++r) {
+#pragma unroll
+                    for (int off = 8; off > 0; off >>= 1)
+                        s[i][r] += __shfl_xor_sync(LS_FULL_MASK, s[i][r], off);
+                    if (2 * (round * 4 + i) + half_id >= valid) s[i][r] = neg_inf();
+                }
+#pragma unroll
+            for (int r = 0; r < R; ++r) {
+                float mx = m[r];
+#pragma unroll
+                for (int i = 0; i < 4; ++i) mx = fmaxf(mx, s[i][r]);
+                const float ms = (mx == neg_inf()) ? 0.f : mx;
+                const float a = ex2(m[r] - ms);
+                m[r] = mx;
+                l[r] *= a;
+#pragma unroll
+                for (int j = 0; j < 8; ++j) acc[r][j] *= a;
+#pragma unroll
+                for (int i = 0; i < 4; ++i) s[i][r] = ex2(s[i][r] - ms);
+            }
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const int tok = 2 * (round * 4 + i) + half_id;
+                float vf[8];
+                lds_row8(stage + 4096 + tok * 256 + ((li ^ (tok & 7)) << 4), vf);
+#pragma unroll
+                for (int r = 0; r < R; ++r) {
+                    l[r] += s[i][r];
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) acc[r][j] = fmaf(s[i][r], vf[j], acc[r][j]);
+                }
+            }
+        }
+    }
+
+    // Fold the odd-token half into the even-token half, then store.
+    __device__ __forceinline__ void finish(float* mo, float* mm, float* ml, int n_rep, int lane) {
+#pragma unroll
+        for (int r = 0; r < R; ++r) {
+            const float mo_ = __shfl_xor_sync(LS_FULL_MASK, m[r], 16);
+            const float lo_ = __shfl_xor_sync(LS_FULL_MASK, l[r], 16);
+            const float mn = fmaxf(m[r], mo_);
+            const float ms = (mn == neg_inf()) ? 0.f : mn;
+            const float ea = ex2(m[r] - ms), eb = ex2(mo_ - ms);
+            l[r] = l[r] * ea + lo_ * eb;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const float ao = __shfl_xor_sync(LS_FULL_MASK, acc[r][j], 16);
+                acc[r][j] = acc[r][j] * ea + ao * eb;
+            }
+            m[r] = mn;
+        }
+        if (lane >= 16) return;
+        const int d0 = lane * 8;
+#pragma unroll
+        for (int r = 0; r < R; ++r) {
+            if (r < n_rep) {
+#pragma unroll
+                for (int j = 0; j < 8; ++j) mo[r * kMergeStride + d0 + j] = acc[r][j];
+                if (lane == 0) { mm[r] = m[r]; ml[r] = l[r]; }
+            }
+        }
+    }
+};
+
+// ---------------------------------------------------------------------------
+// INT8 pools. Stage layout (bytes):
+//   [0, 4096)     K: int8 page = 16 rows x 128 B (8 swizzled 16-B chunks), or, for a
+//                 sequence's last page, the fp16 residual rows (16 x 256 B)
+//   [4096, 6144)  V: int8, 16 rows x 128 B
+//   [6144, 6656)  K scale, 128 fp32     [6656, 7168)  K zero point (asymmetric only)
+//   [7168, 7232)  V scale, 16 fp32      [7232, 7296)  V zero point (asymmetric only)
+template <int ASYM>
+struct PoolInt8 {
+    static constexpr int STAGE_BYTES = 7424;
+    static constexpr int OFF_V = 4096, OFF_KS = 6144, OFF_KZ = 6656, OFF_VS = 7168, OFF_VZ = 7232;
+
+    // meta = valid tokens | (K came from the residual) << 8
+    static __device__ __forceinline__ int issue(const DecodeParams& p, int b, int h,
+                                                const PageItem& it, uint32_t stage, int lane) {
+        bool from_res = p.k_res != nullptr && it.last && it.valid > 0;
+        int rr = from_res ? p.res_rows[b] : 0;
+        if (rr < 0 || rr >= p.num_res_rows) {             // corrupt row index: read nothing, flag it
+            if (lane == 0) p.seg_range[2 * p.batch] = 1;
+            rr = 0;
+        }
+        if (from_res) {
+            const __half* kr = p.k_res + (long long)rr * p.sr_r + h * p.sr_h;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const int ci = i * 32 + lane;
+                const int row = ci >> 4, col = ci & 15;
+                const int nbytes = row < it.valid ? 16 : 0;
+                cp_async_16(stage + row * 256 + ((col ^ (row & 7)) << 4),
+                            kr + (nbytes ? row * p.sr_p + col * 8 : 0), nbytes);
+            }
+        } else {
+            const signed char* kb =
+                static_cast<const signed char*>(p.k_pool) + it.blk * p.sk_b + h * p.sk_h;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const int ci = i * 32 + lane;
+                const int row = ci >> 3, col = ci & 7;
+                const int nbytes = row < it.valid ? 16 : 0;
+                cp_async_16(stage + row * 128 + ((col ^ (row & 7)) << 4),
+                            kb + (nbytes ? row * p.sk_p + col * 16 : 0), nbytes);
+            }
+            const int nb = it.valid > 0 ? 16 : 0;
+            cp_async_16(stage + OFF_KS + lane * 16,
+                        p.k_scale + (nb ? it.blk * p.ks_b + h * p.ks_h + lane * 4 : 0), nb);
+            if (ASYM)
+                cp_async_16(stage + OFF_KZ + lane * 16,
+                            p.k_zero + (nb ? it.blk * p.ks_b + h * p.ks_h + lane * 4 : 0), nb);
+        }
+        const signed char* vb =
+            static_cast<const signed char*>(p.v_pool) + it.blk * p.sk_b + h * p.sk_h;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int ci = i * 32 + lane;
+            const int row = ci >> 3, col = ci & 7;
+            const int nbytes = row < it.valid ? 16 : 0;
+            cp_async_16(stage + OFF_V + row * 128 + ((col ^ (row & 7)) << 4),
+                        vb + (nbytes ? row * p.sk_p + col * 16 : 0), nbytes);
+        }
+        {
+            const int tok = lane & 15;
+            const int nbytes = tok < it.valid ? 4 : 0;
+            const long long off = nbytes ? it.blk * p.vs_b + tok * p.vs_p + h * p.vs_h : 0;
+            if (lane < 16)
+                cp_async_4(stage + OFF_VS + tok * 4, p.v_scale + off, nbytes);
+            else if (ASYM)
+                cp_async_4(stage + OFF_VZ + tok * 4, p.v_zero + off, nbytes);
+        }
+        return it.valid | (from_res ? 256 : 0);
+    }
+};
+
+__device__ __forceinline__ uint4 lds128(uint32_t addr) {
+    uint4 r;
+    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w)
+                 : "r"(addr));
+    return r;
+}
+__device__ __forceinline__ float lds32f(uint32_t addr) {
+    float r;
+    asm volatile("ld.shared.f32 %0, [%1];\n" : "=f"(r) : "r"(addr));
+    return r;
+}
+
+// Tensor-core state for INT8 pools.
+//
+// The MMA's k index is a free permutation as long as both operands agree, so
+// for the int8 K page lane (g, t) takes dims 32t .. 32t+31 of rows g and g+8
+// (two 16-byte shared loads per row) and k-step ks uses dims 32t + 4ks .. +3;
+// the query fragments are built in the same order. For V the m index (output
+// dim) is permuted instead: lane (g, t) takes dims 16g .. 16g+15 of tokens
+// 2t, 2t+1, 2t+8, 2t+9, and tile mt holds dims 16g + 2mt and 16g + 2mt + 1.
+template <int ASYM>
+struct MmaInt8 {
+    using Pool = PoolInt8<ASYM>;
+    float qf[32];              // Q[row g][32t .. 32t+31] in fp32 (row g < n_rep, else 0)
+    float o[8][4];             // O^T: tile mt = dims 16g + 2mt (regs 0,1) and +1 (regs 2,3)
+    float m[2], l[2];
+    float zacc[2];             // asymmetric V: sum_t w * zero_t, added to every dim
+    int b_, h_;
+
+    __device__ __forceinline__ void begin(const DecodeParams& p, int b, int h, int lane) {
+        b_ = b;
+        h_ = h;
+        m[0] = m[1] = neg_inf();
+        l[0] = l[1] = 0.f;
+        zacc[0] = zacc[1] = 0.f;
+#pragma unroll
+        for (int mt = 0; mt < 8; ++mt)
+#pragma unroll
+            for (int i = 0; i < 4; ++i) o[mt][i] = 0.f;
+        const int g = lane >> 2, t = lane & 3;
+        const __half* src = p.q + b * p.sq_b + h * p.sq_h + g * p.sq_m + 32 * t;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            uint4 raw = make_uint4(0, 0, 0, 0);
+            if (g < p.n_rep) raw = *reinterpret_cast<const uint4*>(src + 8 * i);
+            const __half2* h2 = reinterpret_cast<const __half2*>(&raw);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const float2 f = __half22float2(h2[j]);
+                qf[8 * i + 2 * j] = f.x;
+                qf[8 * i + 2 * j + 1] = f.y;
+            }
+        }
+    }
+
+    __device__ __forceinline__ void compute(const DecodeParams& p, uint32_t stage, int meta,
+                                            int lane) {
+        const int valid = meta & 255;
+        const int g = lane >> 2, t = lane & 3;
+        float s[4] = {0.f, 0.f, 0.f, 0.f};
+        if (meta & 256) {
+            // Last page: K is exact fp16 in the residual. Its query fragments
+            // are fetched on the spot; this happens once per (sequence, head).
+            uint32_t qb[8][2];
+            load_q_fragments(p, b_, h_, lane, qb);
+            qk_fp16(s, stage, qb, lane);
+        } else {
+            // q' = fp16(q * k_scale), one rounding, in this lane's dim order.
+            uint32_t qk[8][2];
+            float zq = 0.f;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const uint4 sc = lds128(stage + Pool::OFF_KS + (32 * t + 4 * i) * 4);
+                qk[i][0] = pack_half2(qf[4 * i] * __uint_as_float(sc.x),
+                                      qf[4 * i + 1] * __uint_as_float(sc.y));
+                qk[i][1] = pack_half2(qf[4 * i + 2] * __uint_as_float(sc.z),
+                                      qf[4 * i + 3] * __uint_as_float(sc.w));
+                if (ASYM) {
+                    const uint4 z = lds128(stage + Pool::OFF_KZ + (32 * t + 4 * i) * 4);
+                    zq = fmaf(qf[4 * i], __uint_as_float(z.x), zq);
+                    zq = fmaf(qf[4 * i + 1], __uint_as_float(z.y), zq);
+                    zq = fmaf(qf[4 * i + 2], __uint_as_float(z.z), zq);
+                    zq = fmaf(qf[4 * i + 3], __uint_as_float(z.w), zq);
+                }
+            }
+            const uint32_t r0 = stage + g * 128, r1 = stage + (g + 8) * 128;
+            uint4 w0[2], w1[2];
+            w0[0] = lds128(r0 + (((2 * t) ^ g) << 4));
+            w0[1] = lds128(r0 + (((2 * t + 1) ^ g) << 4));
+            w1[0] = lds128(r1 + (((2 * t) ^ g) << 4));
+            w1[1] = lds128(r1 + (((2 * t + 1) ^ g) << 4));
+            const uint32_t* k0 = reinterpret_cast<const uint32_t*>(w0);
+            const uint32_t* k1 = reinterpret_cast<const uint32_t*>(w1);
+#pragma unroll
+            for (int ks = 0; ks < 8; ++ks) {
+                uint32_t a0, a1, a2, a3;
+                bytes4_to_half2x2(k0[ks] ^ 0x80808080u, a0, a2);
+                bytes4_to_half2x2(k1[ks] ^ 0x80808080u, a1, a3);
+                mma_16816(s, a0, a1, a2, a3, qk[ks][0], qk[ks][1]);
+            }
+            if (ASYM) {
+                // + q . k_zero: the same for every token of the page, per row.
+                zq += __shfl_xor_sync(LS_FULL_MASK, zq, 1);
+                zq += __shfl_xor_sync(LS_FULL_MASK, zq, 2);      // lanes (g, *) hold row g's sum
+                const float z0 = __shfl_sync(LS_FULL_MASK, zq, (2 * t) * 4);
+                const float z1 = __shfl_sync(LS_FULL_MASK, zq, (2 * t + 1) * 4);
+                s[0] += z0; s[1] += z1; s[2] += z0; s[3] += z1;
+            }
+        }
+        mask_and_scale(s, valid, p.scale_log2, lane);
+        float a0, a1;
+        softmax_update(s, m, l, o, a0, a1);
+        // V's per-token scale rides on the weight (zero for rows past the end:
+        // the scale slots of those rows were zero-filled).
+        const float vs0 = lds32f(stage + Pool::OFF_VS + g * 4);
+        const float vs1 = lds32f(stage + Pool::OFF_VS + (g + 8) * 4);
+        if (ASYM) {
+            const float vz0 = lds32f(stage + Pool::OFF_VZ + g * 4);
+            const float vz1 = lds32f(stage + Pool::OFF_VZ + (g + 8) * 4);
+            zacc[0] = zacc[0] * a0 + (s[0] * vz0 + s[2] * vz1);
+            zacc[1] = zacc[1] * a1 + (s[1] * vz0 + s[3] * vz1);
+        }
+        const uint32_t pb0 = movmatrix_trans(pack_half2(s[0] * vs0, s[1] * vs0));
+        const uint32_t pb1 = movmatrix_trans(pack_half2(s[2] * vs1, s[3] * vs1));
+
+        // V fragments: tokens 2t, 2t+1, 2t+8, 2t+9, dims 16g .. 16g+15.
+        const uint32_t vbase = stage + Pool::OFF_V;
+        uint4 v[4];
+        v[0] = lds128(vbase + (2 * t) * 128 + ((g ^ ((2 * t) & 7)) << 4));
+        v[1] = lds128(vbase + (2 * t + 1) * 128 + ((g ^ ((2 * t + 1) & 7)) << 4));
+        v[2] = lds128(vbase + (2 * t + 8) * 128 + ((g ^ ((2 * t) & 7)) << 4));
+        v[3] = lds128(vbase + (2 * t + 9) * 128 + ((g ^ ((2 * t + 1) & 7)) << 4));
+        const uint32_t* vw0 = reinterpret_cast<const uint32_t*>(&v[0]);
+        const uint32_t* vw1 = reinterpret_cast<const uint32_t*>(&v[1]);
+        const uint32_t* vw2 = reinterpret_cast<const uint32_t*>(&v[2]);
+        const uint32_t* vw3 = reinterpret_cast<const uint32_t*>(&v[3]);
+        const uint32_t magic = 0x64646464u;
+        const __half2 off = __floats2half2_rn(1152.f, 1152.f);
+#pragma unroll
+        for (int mt = 0; mt < 8; ++mt) {
+            const int j = mt >> 1;
+            const uint32_t sel = (mt & 1) ? 0x7632u : 0x5410u;
+            // [T0.dA, T0.dB, T1.dA, T1.dB] and the same for tokens T2, T3
+            const uint32_t x01 = prmt(vw0[j], vw1[j], sel) ^ 0x80808080u;
+            const uint32_t x23 = prmt(vw2[j], vw3[j], sel) ^ 0x80808080u;
+            uint32_t f[4];
+            f[0] = prmt(x01, magic, 0x4240u);   // dim A, tokens T0 T1
+            f[1] = prmt(x01, magic, 0x4341u);   // dim B, tokens T0 T1
+            f[2] = prmt(x23, magic, 0x4240u);   // dim A, tokens T2 T3
+            f[3] = prmt(x23, magic, 0x4341u);   // dim B, tokens T2 T3
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const __half2 hv = __hsub2(*reinterpret_cast<__half2*>(&f[i]), off);
+                f[i] = *reinterpret_cast<const uint32_t*>(&hv);
+            }
+            mma_16816(o[mt], f[0], f[1], f[2], f[3], pb0, pb1);
+        }
+    }
+
+    __device__ __forceinline__ void finish(float* mo, float* mm, float* ml, int n_rep, int lane) {
+#pragma unroll
+        for (int off = 4; off < 32; off <<= 1) {
+            l[0] += __shfl_xor_sync(LS_FULL_MASK, l[0], off);
+            l[1] += __shfl_xor_sync(LS_FULL_MASK, l[1], off);
+            if (ASYM) {
+                zacc[0] += __shfl_xor_sync(LS_FULL_MASK, zacc[0], off);
+                zacc[1] += __shfl_xor_sync(LS_FULL_MASK, zacc[1], off);
+            }
+        }
+        const int g = lane >> 2, t = lane & 3;
+        const int r0 = 2 * t, r1 = r0 + 1;
+        const float z0 = ASYM ? zacc[0] : 0.f, z1 = ASYM ? zacc[1] : 0.f;
+#pragma unroll
+        for (int mt = 0; mt < 8; ++mt) {
+            const int d = 16 * g + 2 * mt;
+            if (r0 < n_rep) {
+                mo[r0 * kMergeStride + d] = o[mt][0] + z0;
+                mo[r0 * kMergeStride + d + 1] = o[mt][2] + z0;
+            }
+            if (r1 < n_rep) {
+                mo[r1 * kMergeStride + d] = o[mt][1] + z1;
+                mo[r1 * kMergeStride + d + 1] = o[mt][3] + z1;
+            }
+        }
+        if (g == 0) {
+            if (r0 < n_rep) { mm[r0] = m[0]; ml[r0] = l[0]; }
+            if (r1 < n_rep) { mm[r1] = m[1]; ml[r1] = l[1]; }
+        }
+    }
+};
+
+// ---------------------------------------------------------------------------
+template <class State, int MODE, int STAGES>
+__global__ void __launch_bounds__(kThreads, 2) decode_kernel(const DecodeParams p) {
+    extern __shared__ __align__(1024) unsigned char smem[];
+    using Pool = typename State::Pool;
+    constexpr int STAGE_BYTES = Pool::STAGE_BYTES;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int chunk_id = blockIdx.x, h = blockIdx.y;
+
+    float* merge_o = reinterpret_cast<float*>(smem + kWarps * STAGES * STAGE_BYTES);
+    float* merge_m = merge_o + kWarps * p.n_rep * kMergeStride;
+    float* merge_l = merge_m + kWarps * kRP;
+    int* meta = reinterpret_cast<int*>(merge_l + kWarps * kRP);   // [kWarps][STAGES]
+    int* scan = meta + kWarps * STAGES;                           // [kWarps]
+    int* cum = scan + kWarps;                                     // [batch + 1]
+
+    const int total = build_prefix<MODE, kThreads>(p, cum, scan);
+    const int chunk = chunk_size(p, total);
+    if (chunk_id == 0 && h == 0) write_seg_ranges<kThreads>(p, cum, chunk);
+    const int g0 = chunk_id * chunk;
+    if (g0 >= total) return;
+    const int g1 = min(total, g0 + chunk);
+    const int b0 = find_seq(cum, p.batch, g0);
+
+    const uint32_t ring = smem_u32(smem + warp * (STAGES * STAGE_BYTES));
+    int* my_meta = meta + warp * STAGES;
+
+    // Load side.
+    Cursor lc = cursor_begin<kWarps>(cum, p.batch, b0, g0, g1, warp);
+    int cached_b = -1, cached_len = 0;
+    PageItem item = fetch_item<MODE>(p, lc, h, cached_b, cached_len);
+    auto issue = [&](int stage) {
+        if (!lc.done) {
+            if (item.blk < 0 || item.blk >= p.num_blocks) {   // corrupt table: read nothing, flag it
+                if (item.valid > 0 && lane == 0) p.seg_range[2 * p.batch] = 1;
+                item.blk = 0;
+                item.valid = 0;
+            }
+            const int mt = Pool::issue(p, lc.b, h, item, ring + stage * STAGE_BYTES, lane);
+            if (lane == 0) my_meta[stage] = mt;
+            cursor_next<kWarps>(lc, cum, p.batch, warp);
+            item = fetch_item<MODE>(p, lc, h, cached_b, cached_len);
+        }
+        cp_async_commit();
+    };
+#pragma unroll
+    for (int s = 0; s < STAGES - 1; ++s) issue(s);
+
+    // Compute side: segment by segment.
+    State st;
+    int it = 0;            // pages this warp has consumed
+    int b = b0;
+    int first_u = g0 - cum[b0];
+    for (int guard = 0; guard <= p.batch; ++guard) {
+        const int hi = min(g1, cum[b + 1]) - cum[b];
+        st.begin(p, b, h, lane);
+        for (int u = first_u + warp; u < hi; u += kWarps, ++it) {
+            cp_async_wait<STAGES - 2>();
+            __syncwarp();
+            issue((it + STAGES - 1) % STAGES);
+            const int stage = it % STAGES;
+            st.compute(p, ring + stage * STAGE_BYTES, my_meta[stage], lane);
+        }
+        st.finish(merge_o + warp * p.n_rep * kMergeStride, merge_m + warp * kRP,
+                  merge_l + warp * kRP, p.n_rep, lane);
+        __syncthreads();
+        {
+            // CTA merge: thread = one of the 128 dims, all rows.
+            const int slot = chunk_id + b;
+            float* pa = p.part_acc + ((long long)slot * p.heads + h) * kRP * LS_HEAD_DIM;
+            float* pm = p.part_m + ((long long)slot * p.heads + h) * kRP;
+            float* pl = p.part_l + ((long long)slot * p.heads + h) * kRP;
+            for (int r = 0; r < p.n_rep; ++r) {
+                float mg = neg_inf();
+#pragma unroll
+                for (int w = 0; w < kWarps; ++w) mg = fmaxf(mg, merge_m[w * kRP + r]);
+                const float ms = (mg == neg_inf()) ? 0.f : mg;
+                float lsum = 0.f;
+                float wgt[kWarps];
+#pragma unroll
+                for (int w = 0; w < kWarps; ++w) {
+                    wgt[w] = ex2(merge_m[w * kRP + r] - ms);
+                    lsum += wgt[w] * merge_l[w * kRP + r];
+                }
+                for (int d = tid; d < LS_HEAD_DIM; d += kThreads) {
+                    float a = 0.f;
+#pragma unroll
+                    for (int w = 0; w < kWarps; ++w)
+                        a += wgt[w] * merge_o[(w * p.n_rep + r) * kMergeStride + d];
+                    pa[r * LS_HEAD_DIM + d] = a;
+                }
+                if (tid == 0) {
+                    pm[r] = mg;
+                    pl[r] = lsum;
+                }
+            }
+        }
+        if (cum[b + 1] >= g1) break;
+        __syncthreads();
+        ++b;
+        while (b < p.batch - 1 && cum[b + 1] == cum[b]) ++b;
+        first_u = 0;
+    }
+    cp_async_wait<0>();
+}
+
+// ---------------------------------------------------------------------------
+// Merge of a sequence's partials:
+//   out = sum_s acc_s 2^(m_s - M) / max(sum_s l_s 2^(m_s - M), 1e-20),
+// the reference combine (kernels/gqa/paged_decode.py:421-471, torch form
+// :689-706) with m held in the log2 domain. grid (B, H), thread = head dim.
+__global__ void __launch_bounds__(LS_HEAD_DIM)
+merge_kernel(const float* __restrict__ part_acc, const float* __restrict__ part_m,
+             const float* __restrict__ part_l, const int* __restrict__ seg_range,
+             __half* __restrict__ out, int heads, int n_rep, long long so_b, long long so_h,
+             long long so_m) {
+    const int b = blockIdx.x, h = blockIdx.y, d = threadIdx.x;
+    const int first = seg_range[2 * b], count = seg_range[2 * b + 1];
+    for (int r = 0; r < n_rep; ++r) {
+        float mg = neg_inf();
+        for (int s = 0; s < count; ++s)
+            mg = fmaxf(mg, part_m[((long long)(first + s) * heads + h) * kRP + r]);
+        const float ms = (mg == neg_inf()) ? 0.f : mg;
+        float lsum = 0.f, a = 0.f;
+        for (int s = 0; s < count; ++s) {
+            const long long row = ((long long)(first + s) * heads + h) * kRP + r;
+            const float w = ex2(part_m[row] - ms);
+            lsum += w * part_l[row];
+            a += w * part_acc[row * LS_HEAD_DIM + d];
+        }
+        out[b * so_b + h * so_h + r * so_m + d] = __float2half_rn(a / fmaxf(lsum, 1e-20f));
+    }
+}
+
+// ---------------------------------------------------------------------------
+static int validate_common(const DecodeParams& p) {
+    if (!p.q || !p.k_pool || !p.v_pool || !p.block_tables || !p.seq_lens || !p.part_acc ||
+        !p.part_m || !p.part_l || !p.seg_range)
+        return LS_ERR_NULL_POINTER;
+    if (p.batch <= 0 || p.heads <= 0 || p.n_rep <= 0 || p.max_pages <= 0 || p.num_chunks <= 0 ||
+        p.num_blocks <= 0 || p.min_chunk <= 0)
+        return LS_ERR_BAD_SHAPE;
+    if (p.batch > LS_MAX_BATCH || p.heads > 65535) return LS_ERR_TOO_LARGE;
+    if (p.n_rep > kRP) return LS_ERR_UNSUPPORTED;
+    if ((reinterpret_cast<uintptr_t>(p.q) & 15) || (p.sq_b % 8) || (p.sq_h % 8) || (p.sq_m % 8))
+        return LS_ERR_MISALIGNED;
+    return LS_OK;
+}
+
+template <class State, int MODE, int STAGES>
+static int launch_decode(const DecodeParams& p, cudaStream_t stream) {
+    const size_t smem = (size_t)kWarps * STAGES * State::Pool::STAGE_BYTES +
+                        sizeof(float) * ((size_t)kWarps * p.n_rep * kMergeStride + 2 * kWarps * kRP) +
+                        sizeof(int) * ((size_t)kWarps * STAGES + kWarps + p.batch + 1);
+    auto kern = decode_kernel<State, MODE, STAGES>;
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+    kern<<<dim3(p.num_chunks, p.heads), kThreads, smem, stream>>>(p);
+    return (int)cudaGetLastError();
+}
+
+static int run_merge(const DecodeParams& p, void* out, long long so_b, long long so_h, long long so_m,
+                     cudaStream_t stream) {
+    if (!out) return LS_OK;
+    merge_kernel<<<dim3(p.batch, p.heads), LS_HEAD_DIM, 0, stream>>>(
+        p.part_acc, p.part_m, p.part_l, p.seg_range, static_cast<__half*>(out), p.heads, p.n_rep, so_b,
+        so_h, so_m);
+    return (int)cudaGetLastError();
+}
+
+}  // namespace ls
+
+using ls::DecodeParams;
+
+static int check_pool_fp16(const DecodeParams& p) {
+    if ((reinterpret_cast<uintptr_t>(p.k_pool) & 15) || (reinterpret_cast<uintptr_t>(p.v_pool) & 15) ||
+        (p.sk_b % 8) || (p.sk_p % 8) || (p.sk_h % 8))
+        return LS_ERR_MISALIGNED;
+    return LS_OK;
+}
+
+extern "C" {
+
+int ls_decode_slots(int batch, int num_chunks) { return batch + num_chunks; }
+
+int ls_paged_decode_fp16(const void* q, const void* k_pool, const void* v_pool,
+                         const int32_t* block_tables, const int32_t* seq_lens, float* part_acc,
+                         float* part_m, float* part_l, int32_t* seg_range, void* out, int batch,
+                         int kv_heads, int n_rep, int head_dim, int page, int max_pages,
+                         int num_blocks, int num_chunks, int min_chunk, int impl, int64_t sq_b,
+                         int64_t sq_h, int64_t sq_m, int64_t sk_b, int64_t sk_p, int64_t sk_h,
+                         int64_t so_b, int64_t so_h, int64_t so_m, float softmax_scale,
+                         void* stream) {
+    if (head_dim != LS_HEAD_DIM || page != LS_PAGE) return LS_ERR_UNSUPPORTED;
+    DecodeParams p = {};
+    p.q = static_cast<const __half*>(q);
+    p.k_pool = k_pool;
+    p.v_pool = v_pool;
+    p.block_tables = block_tables;
+    p.seq_lens = seq_lens;
+    p.part_acc = part_acc;
+    p.part_m = part_m;
+    p.part_l = part_l;
+    p.seg_range = seg_range;
+    p.batch = batch;
+    p.heads = kv_heads;
+    p.n_rep = n_rep;
+    p.max_pages = max_pages;
+    p.num_blocks = num_blocks;
+    p.num_chunks = num_chunks;
+    p.min_chunk = min_chunk;
+    p.sq_b = sq_b; p.sq_h = sq_h; p.sq_m = sq_m;
+    p.sk_b = sk_b; p.sk_p = sk_p; p.sk_h = sk_h;
+    p.scale_log2 = softmax_scale * 1.4426950408889634f;
+    int rc = ls::validate_common(p);
+    if (rc) return rc;
+    rc = check_pool_fp16(p);
+    if (rc) return rc;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (impl == LS_IMPL_SIMT) {
+        if (n_rep <= 6)
+            rc = ls::launch_decode<ls::SimtFp16<6>, LS_MODE_DENSE, 3>(p, s);
+        else
+            rc = ls::launch_decode<ls::SimtFp16<8>, LS_MODE_DENSE, 3>(p, s);
+    } else if (impl == LS_IMPL_MMA) {
+        rc = ls::launch_decode<ls::MmaFp16, LS_MODE_DENSE, 3>(p, s);
+    } else {
+        return LS_ERR_UNSUPPORTED;
+    }
+    if (rc) return rc;
+    return ls::run_merge(p, out, so_b, so_h, so_m, s);
+}
+
+int ls_paged_sparse_fp16(const void* q, const void* k_pool, const void* v_pool,
+                         const int32_t* block_tables, const int32_t* seq_lens, const int32_t* sel,
+                         float ratio, int recent, float* part_acc, float* part_m, float* part_l,
+                         int32_t* seg_range, void* out, int batch, int kv_heads, int n_rep,
+                         int head_dim, int page, int max_pages, int num_blocks, int num_sel,
+                         int num_chunks, int min_chunk, int64_t sq_b, int64_t sq_h, int64_t sq_m,
+                         int64_t sk_b, int64_t sk_p, int64_t sk_h, int64_t sl_b, int64_t sl_h,
+                         int64_t so_b, int64_t so_h, int64_t so_m, float softmax_scale,
+                         void* stream) {
+    if (head_dim != LS_HEAD_DIM || page != LS_PAGE) return LS_ERR_UNSUPPORTED;
+    if (!sel) return LS_ERR_NULL_POINTER;
+    if (num_sel <= 0) return LS_ERR_BAD_SHAPE;
+    DecodeParams p = {};
+    p.q = static_cast<const __half*>(q);
+    p.k_pool = k_pool;
+    p.v_pool = v_pool;
+    p.block_tables = block_tables;
+    p.seq_lens = seq_lens;
+    p.sel = sel;
+    p.ratio = ratio;
+    p.recent = recent;
+    p.num_sel = num_sel;
+    p.sl_b = sl_b; p.sl_h = sl_h;
+    p.part_acc = part_acc;
+    p.part_m = part_m;
+    p.part_l = part_l;
+    p.seg_range = seg_range;
+    p.batch = batch;
+    p.heads = kv_heads;
+    p.n_rep = n_rep;
+    p.max_pages = max_pages;
+    p.num_blocks = num_blocks;
+    p.num_chunks = num_chunks;
+    p.min_chunk = min_chunk;
+    p.sq_b = sq_b; p.sq_h = sq_h; p.sq_m = sq_m;
+    p.sk_b = sk_b; p.sk_p = sk_p; p.sk_h = sk_h;
+    p.scale_log2 = softmax_scale * 1.4426950408889634f;
+    int rc = ls::validate_common(p);
+    if (rc) return rc;
+    rc = check_pool_fp16(p);
+    if (rc) return rc;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    rc = ls::launch_decode<ls::MmaFp16, LS_MODE_SPARSE, 3>(p, s);
+    if (rc) return rc;
+    return ls::run_merge(p, out, so_b, so_h, so_m, s);
+}
+
+int ls_paged_decode_int8(const void* q, const void* k_pool, const void* v_pool,
+                         const int32_t* block_tables, const int32_t* seq_lens, const float* k_scale,
+                         const float* v_scale, const float* k_zero, const float* v_zero,
+                         const void* k_res, const int32_t* res_rows, float* part_acc, float* part_m,
+                         float* part_l, int32_t* seg_range, void* out, int batch, int kv_heads,
+                         int n_rep, int head_dim, int page, int max_pages, int num_blocks,
+                         int num_res_rows, int num_chunks, int min_chunk, int64_t sq_b, int64_t sq_h,
+                         int64_t sq_m, int64_t sk_b, int64_t sk_p, int64_t sk_h, int64_t ks_b, int64_t ks_h,
+                         int64_t vs_b, int64_t vs_p, int64_t vs_h, int64_t sr_r, int64_t sr_p,
+                         int64_t sr_h, int64_t so_b, int64_t so_h, int64_t so_m, float softmax_scale,
+                         void* stream) {
+    if (head_dim != LS_HEAD_DIM || page != LS_PAGE) return LS_ERR_UNSUPPORTED;
+    if (!k_scale || !v_scale) return LS_ERR_NULL_POINTER;
+    if ((k_zero == nullptr) != (v_zero == nullptr)) return LS_ERR_NULL_POINTER;
+    if ((k_res == nullptr) != (res_rows == nullptr)) return LS_ERR_NULL_POINTER;
+    DecodeParams p = {};
+    p.q = static_cast<const __half*>(q);
+    p.k_pool = k_pool;
+    p.v_pool = v_pool;
+    p.block_tables = block_tables;
+    p.seq_lens = seq_lens;
+    p.k_scale = k_scale;
+    p.v_scale = v_scale;
+    p.k_zero = k_zero;
+    p.v_zero = v_zero;
+    p.k_res = static_cast<const __half*>(k_res);
+    p.res_rows = res_rows;
+    p.num_res_rows = k_res ? num_res_rows : 1;
+    if (k_res && num_res_rows <= 0) return LS_ERR_BAD_SHAPE;
+    p.part_acc = part_acc;
+    p.part_m = part_m;
+    p.part_l = part_l;
+    p.seg_range = seg_range;
+    p.batch = batch;
+    p.heads = kv_heads;
+    p.n_rep = n_rep;
+    p.max_pages = max_pages;
+    p.num_blocks = num_blocks;
+    p.num_chunks = num_chunks;
+    p.min_chunk = min_chunk;
+    p.sq_b = sq_b; p.sq_h = sq_h; p.sq_m = sq_m;
+    p.sk_b = sk_b; p.sk_p = sk_p; p.sk_h = sk_h;
+    p.ks_b = ks_b; p.ks_h = ks_h;
+    p.vs_b = vs_b; p.vs_p = vs_p; p.vs_h = vs_h;
+    p.sr_r = sr_r; p.sr_p = sr_p; p.sr_h = sr_h;
+    p.scale_log2 = softmax_scale * 1.4426950408889634f;
+    int rc = ls::validate_common(p);
+    if (rc) return rc;
+    // 16-byte rows for the int8 pools, the K scales / zero points and the residual.
+    if ((reinterpret_cast<uintptr_t>(k_pool) & 15) || (reinterpret_cast<uintptr_t>(v_pool) & 15) ||
+        (sk_b % 16) || (sk_p % 16) || (sk_h % 16))
+        return LS_ERR_MISALIGNED;
+    if ((reinterpret_cast<uintptr_t>(k_scale) & 15) || (ks_b % 4) || (ks_h % 4)) return LS_ERR_MISALIGNED;
+    if (k_zero && (reinterpret_cast<uintptr_t>(k_zero) & 15)) return LS_ERR_MISALIGNED;
+    if (k_res && ((reinterpret_cast<uintptr_t>(k_res) & 15) || (sr_r % 8) || (sr_p % 8) || (sr_h % 8)))
+        return LS_ERR_MISALIGNED;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (k_zero)
+        rc = ls::launch_decode<ls::MmaInt8<1>, LS_MODE_DENSE, 3>(p, s);
+    else
+        rc = ls::launch_decode<ls::MmaInt8<0>, LS_MODE_DENSE, 3>(p, s);
+    if (rc) return rc;
+    return ls::run_merge(p, out, so_b, so_h, so_m, s);
+}
+
+int ls_combine(const float* part_acc, const float* part_m, const float* part_l,
+               const int32_t* seg_range, void* out, int batch, int kv_heads, int n_rep,
+               int64_t so_b, int64_t so_h, int64_t so_m, void* stream) {
+    if (!part_acc || !part_m || !part_l || !seg_range || !out) return LS_ERR_NULL_POINTER;
+    if (batch <= 0 || kv_heads <= 0 || n_rep <= 0 || n_rep > ls::kRP) return LS_ERR_BAD_SHAPE;
+    if (kv_heads > 65535) return LS_ERR_TOO_LARGE;
+    ls::merge_kernel<<<dim3(batch, kv_heads), LS_HEAD_DIM, 0, static_cast<cudaStream_t>(stream)>>>(
+        part_acc, part_m, part_l, seg_range, static_cast<__half*>(out), kv_heads, n_rep, so_b, so_h,
+        so_m);
+    return (int)cudaGetLastError();
+}
+
+}  // extern "C"

@@ -1,0 +1,72 @@
+"""Entry point of the decode-attention path.
+
+Mirrors the reference dispatcher `kernels/gqa/paged_decode.py`
+(`set_decode_backend` :491-494, `decode_backend` :497-498,
+`paged_decode_attention` :709-829) with one backend: the sm_100a kernels of
+this library. There is no Triton backend and no CPU path here; a CPU tensor,
+`force_reference=True`, or an ineligible layout raises instead of quietly
+running something else.
+"""
+
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from latentserve_b200 import paged_decode_cuda as pdc
+
+_BACKEND = {"decode": "cuda"}
+
+
+def set_decode_backend(name: str) -> None:
+    if name != "cuda":
+        raise ValueError(f"unknown decode backend {name!r}: this library has only 'cuda'")
+    _BACKEND["decode"] = name
+
+
+def decode_backend() -> str:
+    return _BACKEND["decode"]
+
+
+def paged_decode_attention(
+    q: torch.Tensor,
+    k_pool: torch.Tensor,
+    v_pool: torch.Tensor,
+    block_tables: torch.Tensor,
+    seq_lens: torch.Tensor,
+    k_scale: Optional[torch.Tensor] = None,
+    v_scale: Optional[torch.Tensor] = None,
+    k_zero: Optional[torch.Tensor] = None,
+    v_zero: Optional[torch.Tensor] = None,
+    num_splits: Optional[int] = None,
+    softmax_scale: Optional[float] = None,
+    max_seq_len: Optional[int] = None,
+    force_reference: bool = False,
+    k_residual: Optional[torch.Tensor] = None,
+    res_rows: Optional[torch.Tensor] = None,
+    pages_per_iter: Optional[int] = None,
+    num_warps: Optional[int] = None,
+    num_stages: Optional[int] = None,
+) -> torch.Tensor:
+    """q [B, H_kv, N_REP, D]; pools [num_blocks, PAGE, H_kv, D]; block_tables
+    [B, max_pages] int32; seq_lens [B] int32 -> [B, H_kv, N_REP, D].
+
+    `num_splits` is ignored, as the reference's "cuda" backend ignores it
+    (kernels/gqa/paged_decode.py:750-762); `pages_per_iter`, `num_warps` and
+    `num_stages` tuned the reference's Triton kernels and have no meaning here.
+    """
+    if force_reference:
+        raise RuntimeError("latentserve_b200 carries no reference implementation to force")
+    if not q.is_cuda:
+        raise RuntimeError("latentserve_b200 has no CPU path: tensors must be on a CUDA device")
+    if not pdc.eligible(q, k_pool, k_scale, k_residual, v_scale=v_scale, k_zero=k_zero,
+                        v_zero=v_zero, res_rows=res_rows):
+        raise ValueError(
+            "layout not supported by the sm_100a kernels: need fp16 q with head_dim 128, <= 8 query "
+            "rows per KV head, page 16, fp16 or INT8 pools with 16-byte aligned rows")
+    return pdc.paged_decode_cuda(q, k_pool, v_pool, block_tables, seq_lens,
+                                 max_seq_len if max_seq_len is not None else 0,
+                                 softmax_scale=softmax_scale, k_scale=k_scale, v_scale=v_scale,
+                                 k_zero=k_zero, v_zero=v_zero, k_residual=k_residual,
+                                 res_rows=res_rows)

@@ -1,0 +1,188 @@
+"""Dense fp16 paged decode on the GPU against the CPU oracle and the golden
+fixtures (cases follow the reference's tests/test_cuda_decode.py:69-122 and
+tests/test_phase11_kernel.py:87-135)."""
+
+import numpy as np
+import pytest
+import torch
+
+from latentserve_b200 import paged_decode as pd
+from latentserve_b200 import paged_decode_cuda as pdc
+from latentserve_b200 import synthetic
+from oracle import paged_attention_oracle as orc
+from tests.gpu_util import close, device, on_device
+
+pytestmark = pytest.mark.gpu
+IMPLS = [pdc.IMPL_MMA, pdc.IMPL_SIMT]
+
+
+def _run(t, impl=pdc.IMPL_MMA, splits=None, **kw):
+    return pdc.paged_decode_cuda(t["q"], t["k_pool"], t["v_pool"], t["block_tables"], t["seq_lens"],
+                                 int(t["seq_lens"].max()), num_splits=splits, impl=impl, **kw)
+
+
+@pytest.mark.parametrize("impl", IMPLS)
+@pytest.mark.parametrize("splits", [None, 1, 3, 64])
+def test_matches_the_oracle_on_ragged_lengths(impl, splits):
+    case = synthetic.dense_case([1024, 300, 61, 17, 1], seed=0)
+    want = orc.paged_decode(case["q"], case["k_pool"], case["v_pool"], case["block_tables"],
+                            case["seq_lens"])
+    close(_run(on_device(case), impl, splits), want)
+
+
+@pytest.mark.parametrize("impl", IMPLS)
+@pytest.mark.parametrize("name,make", [
+    ("dense_ragged", lambda: synthetic.dense_case([1024, 300, 61, 17, 1], seed=0)),
+    ("dense_config1", lambda: synthetic.config1(seed=0)),
+    ("dense_edges", lambda: synthetic.dense_case([15, 16, 17, 31, 32, 33, 1], seed=3)),
+])
+def test_matches_the_reference_golden_outputs(impl, name, make, golden_dir):
+    g = np.load(golden_dir / f"{name}.npz")
+    close(_run(on_device(make()), impl), g["out_splits1"])
+
+
+@pytest.mark.parametrize("impl", IMPLS)
+def test_final_page_lengths_and_empty_sequences(impl):
+    lens = [1, 15, 16, 17, 31, 32, 33, 0, 48, 0]
+    case = synthetic.dense_case(lens, seed=4)
+    want = orc.paged_decode(case["q"], case["k_pool"], case["v_pool"], case["block_tables"],
+                            case["seq_lens"])
+    got = _run(on_device(case), impl)
+    close(got, want)
+    assert (got[7] == 0).all() and (got[9] == 0).all()          # empty sequences give zeros
+
+
+def test_no_cross_sequence_leak_and_stale_rows_are_never_read():
+    """Rows past each sequence's end, and every block no table names, hold NaN."""
+    lens = [100, 37, 260]
+    case = synthetic.dense_case(lens, seed=6)
+    want = orc.paged_decode(case["q"], case["k_pool"], case["v_pool"], case["block_tables"],
+                            case["seq_lens"])
+    k, v = case["k_pool"].copy(), case["v_pool"].copy()
+    used = np.zeros(k.shape[:2], dtype=bool)
+    for b, L in enumerate(lens):
+        for pos in range(L):
+            used[case["block_tables"][b, pos // 16], pos % 16] = True
+    k[~used] = np.nan
+    v[~used] = np.nan
+    case.update(k_pool=k, v_pool=v)
+    for impl in IMPLS:
+        close(_run(on_device(case), impl), want)
+
+
+def test_other_group_sizes():
+    for n_rep in (1, 4, 8):
+        case = synthetic.dense_case([200, 33], n_rep=n_rep, seed=8)
+        want = orc.paged_decode(case["q"], case["k_pool"], case["v_pool"], case["block_tables"],
+                                case["seq_lens"])
+        for impl in IMPLS:
+            close(_run(on_device(case), impl), want)
+
+
+def test_four_kv_heads_and_a_strided_query_view():
+    case = synthetic.dense_case([500, 130], n_rep=6, h=4, seed=9)
+    want = orc.paged_decode(case["q"], case["k_pool"], case["v_pool"], case["block_tables"],
+                            case["seq_lens"])
+    t = on_device(case)
+    # q as the model hands it over: a reshape of a [B, 1, Hq*D] projection slice.
+    wide = torch.zeros(2, 1, 4 * 6 * 128 + 512, dtype=torch.float16, device=device())
+    wide[:, 0, : 4 * 6 * 128] = t["q"].reshape(2, -1)
+    t["q"] = wide[:, 0, : 4 * 6 * 128].view(2, 4, 6, 128)
+    assert not t["q"].is_contiguous()
+    close(_run(t), want)
+
+
+def test_dispatch_through_the_entry_point():
+    case = synthetic.dense_case([700, 33], seed=10)
+    want = orc.paged_decode(case["q"], case["k_pool"], case["v_pool"], case["block_tables"],
+                            case["seq_lens"])
+    t = on_device(case)
+    pd.set_decode_backend("cuda")
+    got = pd.paged_decode_attention(t["q"], t["k_pool"], t["v_pool"], t["block_tables"],
+                                    t["seq_lens"], max_seq_len=700)
+    close(got, want)
+
+
+def test_softmax_scale_is_honoured():
+    case = synthetic.dense_case([300, 90], seed=12)
+    want = orc.paged_decode(case["q"], case["k_pool"], case["v_pool"], case["block_tables"],
+                            case["seq_lens"], softmax_scale=0.05)
+    close(_run(on_device(case), softmax_scale=0.05), want)
+
+
+def test_survives_cuda_graph_capture_and_reads_current_inputs():
+    case = synthetic.dense_case([500, 200], seed=13)
+    t = on_device(case)
+    _run(t)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        out = _run(t)
+    # New query and a longer second sequence after capture: replay must see both.
+    q2 = (np.random.default_rng(1).standard_normal(case["q"].shape)).astype(np.float16)
+    t["q"].copy_(torch.from_numpy(q2))
+    t["seq_lens"].copy_(torch.tensor([480, 230], dtype=torch.int32))
+    graph.replay()
+    torch.cuda.synchronize()
+    want = orc.paged_decode(q2, case["k_pool"], case["v_pool"], case["block_tables"],
+                            np.asarray([480, 230], dtype=np.int32))
+    close(out, want)
+
+
+def test_long_uniform_batch_property_checks():
+    """Full-size shape of the benchmark workload (batch 16 x 16K), checked by
+    properties that need no CPU pass over 268 MB: (1) permuting which physical
+    blocks hold the pages changes nothing; (2) V = const gives that constant;
+    (3) one sequence of it against the oracle."""
+    dev = device()
+    w = synthetic.dense_pools_on_device(16, 16384, 1, dev, seed=2)
+    k, v = w["pools"][0]
+    q = w["q"][0]
+    out = pdc.paged_decode_cuda(q, k, v, w["block_tables"], w["seq_lens"], 16384).clone()
+    assert torch.isfinite(out).all()
+    # (3) sequence 5 on the CPU
+    b = 5
+    blocks = w["block_tables"][b].long()
+    case_k = k[blocks].cpu().numpy()
+    case_v = v[blocks].cpu().numpy()
+    tables = np.arange(1024, dtype=np.int32)[None]
+    want = orc.paged_decode(q[b:b + 1].cpu().numpy(), case_k, case_v, tables,
+                            np.asarray([16384], dtype=np.int32))
+    close(out[b:b + 1], want)
+    # (1) move every page to a different physical block
+    perm = torch.randperm(w["num_blocks"], device=dev)
+    inv = torch.empty_like(perm)
+    inv[perm] = torch.arange(w["num_blocks"], device=dev)
+    k2, v2 = k[perm], v[perm]                      # block i of the new pool = old block perm[i]
+    tables2 = inv[w["block_tables"].long()].to(torch.int32)
+    out2 = pdc.paged_decode_cuda(q, k2, v2, tables2, w["seq_lens"], 16384)
+    assert torch.equal(out, out2)
+    # (2) constant V
+    v.fill_(0.25)
+    out3 = pdc.paged_decode_cuda(q, k, v, w["block_tables"], w["seq_lens"], 16384)
+    assert torch.allclose(out3.float(), torch.full_like(out3.float(), 0.25), atol=1e-3)
+
+
+def test_corrupt_block_ids_are_skipped_and_flagged_not_read():
+    case = synthetic.dense_case([64, 64], seed=14)
+    t = on_device(case)
+    t["block_tables"][1, 2] = 10_000_000          # far outside the pool
+    out = _run(t)
+    torch.cuda.synchronize()
+    assert torch.isfinite(out).all()
+    assert pdc.error_flag(device(), 2) == 1
+
+
+def test_layout_violations_raise_value_error():
+    case = synthetic.dense_case([64], seed=15)
+    t = on_device(case)
+    with pytest.raises(ValueError):
+        pdc.paged_decode_cuda(t["q"], t["k_pool"], t["v_pool"], t["block_tables"].long(),
+                              t["seq_lens"], 64)
+    with pytest.raises(ValueError):
+        pdc.paged_decode_cuda(t["q"], t["k_pool"], t["v_pool"][:, :, :1], t["block_tables"],
+                              t["seq_lens"], 64)
+    q9 = torch.zeros(1, 2, 9, 128, dtype=torch.float16, device=device())
+    assert not pdc.eligible(q9, t["k_pool"])
+    with pytest.raises(ValueError):
+        pd.paged_decode_attention(q9, t["k_pool"], t["v_pool"], t["block_tables"], t["seq_lens"])

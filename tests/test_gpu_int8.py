@@ -1,0 +1,262 @@
+"""INT8 path on the GPU: quantize-on-write and page finalisation bit-exact,
+INT8 decode attention against the oracle on the dequantised cache (cases follow
+the reference's tests/test_phase16_int8.py:70-141, tests/test_cuda_decode.py:174-212,
+tests/test_phase14_int8_graph.py:73-167)."""
+
+import numpy as np
+import pytest
+import torch
+
+from latentserve_b200 import cache as lc
+from latentserve_b200 import int8_write as iw
+from latentserve_b200 import paged_decode_cuda as pdc
+from oracle import paged_attention_oracle as orc
+from tests.gpu_util import close, device
+
+pytestmark = pytest.mark.gpu
+CONSTS = dict(eps=1e-8, qmax=127.0, levels=255.0, offset=128.0)
+
+
+def _torch_formula(v, asym):
+    """The reference cache's V arithmetic as torch ops, run ON THE GPU
+    (cache/int8_paged_cache.py:738-766): the second oracle for bit-exactness."""
+    v_f = v.to(torch.float32)
+    if asym:
+        lo, hi = v_f.amin(dim=-1, keepdim=True), v_f.amax(dim=-1, keepdim=True)
+        step = ((hi - lo) / 255).clamp_min(1e-8)
+        u = torch.clamp(torch.round((v_f - lo) / step), 0, 255)
+        return (u - 128).to(torch.int8), step.squeeze(-1), (lo + 128 * step).squeeze(-1)
+    step = v_f.abs().amax(dim=-1, keepdim=True).clamp_min(1e-8) / 127
+    return torch.clamp(torch.round(v_f / step), -127, 127).to(torch.int8), step.squeeze(-1), None
+
+
+@pytest.mark.parametrize("asym", [False, True])
+def test_decode_write_is_bit_exact(asym):
+    dev = device()
+    rng = np.random.default_rng(5)
+    b, h, d = 256, 2, 128
+    mag = np.logspace(-3, 2, b)[:, None, None, None]
+    v_np = (rng.standard_normal((b, h, 1, d)) * mag).astype(np.float16)
+    v_np[3] = 0                                              # all-zero rows: the eps floor
+    k_np = rng.standard_normal((b, h, 1, d)).astype(np.float16)
+    slots_np = rng.permutation(4 * b)[:b].astype(np.int64)
+    v, k = torch.from_numpy(v_np).to(dev), torch.from_numpy(k_np).to(dev)
+    slots = torch.from_numpy(slots_np).to(dev)
+    res_idx = torch.arange(b, device=dev)
+    flat_v = torch.zeros(4 * b, h, d, dtype=torch.int8, device=dev)
+    flat_s = torch.zeros(4 * b, h, device=dev)
+    flat_z = torch.zeros(4 * b, h, device=dev) if asym else None
+    k_res = torch.zeros(b, h, d, dtype=torch.float16, device=dev)
+    iw.decode_write(k, v, slots, res_idx, flat_v, flat_s, flat_z, k_res, asym=asym, **CONSTS)
+    torch.cuda.synchronize()
+    # Oracle 1: the numpy restatement with the GPU's reciprocal multiply.
+    want_q, want_s, want_z = orc.quantize_v_rows(v_np[:, :, 0], asym=asym, reciprocal=True)
+    assert np.array_equal(flat_v[slots].cpu().numpy(), want_q)
+    assert np.array_equal(flat_s[slots].cpu().numpy(), want_s), "scales differ: check the reciprocal"
+    if asym:
+        assert np.array_equal(flat_z[slots].cpu().numpy(), want_z)
+    assert torch.equal(k_res, k[:, :, 0])
+    # Oracle 2: the reference's torch ops on this GPU.
+    tq, ts, tz = _torch_formula(v[:, :, 0], asym)
+    assert torch.equal(flat_v[slots], tq) and torch.equal(flat_s[slots], ts)
+    if asym:
+        assert torch.equal(flat_z[slots], tz)
+    # Slots nothing wrote stay untouched.
+    mask = torch.ones(4 * b, dtype=torch.bool, device=dev)
+    mask[slots] = False
+    assert (flat_v[mask] == 0).all()
+
+
+@pytest.mark.parametrize("asym", [False, True])
+def test_decode_write_takes_strided_projection_views(asym):
+    dev = device()
+    g = torch.Generator(device=dev).manual_seed(2)
+    qkv = torch.randn(5, 1, 2 * 2 * 128 + 64, dtype=torch.float16, device=dev, generator=g)
+    k = qkv[:, :, :256].view(5, 1, 2, 128).transpose(1, 2)      # [B, H, 1, D], non-contiguous
+    v = qkv[:, :, 256:512].view(5, 1, 2, 128).transpose(1, 2)
+    assert iw.eligible(k, v)
+    slots = torch.tensor([9, 3, 0, 31, 17], device=dev)
+    flat_v = torch.zeros(32, 2, 128, dtype=torch.int8, device=dev)
+    flat_s = torch.zeros(32, 2, device=dev)
+    flat_z = torch.zeros(32, 2, device=dev) if asym else None
+    k_res = torch.zeros(8, 2, 128, dtype=torch.float16, device=dev)
+    iw.decode_write(k, v, slots, torch.arange(5, device=dev), flat_v, flat_s, flat_z, k_res,
+                    asym=asym, **CONSTS)
+    want_q, want_s, _ = orc.quantize_v_rows(v[:, :, 0].cpu().numpy(), asym=asym)
+    assert np.array_equal(flat_v[slots].cpu().numpy(), want_q)
+    assert np.array_equal(flat_s[slots].cpu().numpy(), want_s)
+    assert torch.equal(k_res[:5], k[:, :, 0])
+
+
+@pytest.mark.parametrize("asym", [False, True])
+def test_finalize_blocks_is_bit_exact(asym):
+    dev = device()
+    rng = np.random.default_rng(9)
+    rows, h, d, nb = 12, 2, 128, 40
+    res_np = (rng.standard_normal((rows, 16, h, d)) * np.logspace(-2, 1.5, rows)[:, None, None, None]
+              ).astype(np.float16)
+    res_np[2, :, 0, 5] = 0                                   # an all-zero channel
+    res = torch.from_numpy(res_np).to(dev)
+    pick = torch.tensor([7, 0, 11, 2, 5], device=dev)
+    ids = torch.tensor([3, 39, 17, 0, 21], device=dev)
+    k_pool = torch.zeros(nb, 16, h, d, dtype=torch.int8, device=dev)
+    k_scale = torch.ones(nb, h, d, device=dev)
+    k_zero = torch.zeros(nb, h, d, device=dev) if asym else None
+    iw.finalize_blocks(res, pick, ids, k_pool, k_scale, k_zero, **CONSTS)
+    torch.cuda.synchronize()
+    want_q, want_s, want_z = orc.quantize_k_blocks(res_np[pick.cpu().numpy()], asym=asym)
+    assert np.array_equal(k_pool[ids].cpu().numpy(), want_q)
+    assert np.array_equal(k_scale[ids].cpu().numpy(), want_s)
+    if asym:
+        assert np.array_equal(k_zero[ids].cpu().numpy(), want_z)
+    # Second oracle: the reference's torch ops on this GPU (cache/int8_paged_cache.py:683-699).
+    f = res[pick].to(torch.float32)
+    if asym:
+        lo, hi = f.amin(dim=1), f.amax(dim=1)
+        step = ((hi - lo) / 255).clamp_min(1e-8)
+        q = (torch.clamp(torch.round((f - lo.unsqueeze(1)) / step.unsqueeze(1)), 0, 255) - 128).to(torch.int8)
+        assert torch.equal(k_zero[ids], lo + 128 * step)
+    else:
+        step = f.abs().amax(dim=1).clamp_min(1e-8) / 127
+        q = torch.clamp(torch.round(f / step.unsqueeze(1)), -127, 127).to(torch.int8)
+    assert torch.equal(k_pool[ids], q) and torch.equal(k_scale[ids], step)
+    untouched = torch.ones(nb, dtype=torch.bool, device=dev)
+    untouched[ids] = False
+    assert (k_pool[untouched] == 0).all() and (k_scale[untouched] == 1).all()
+
+
+def _golden_state(g, asym, dev):
+    t = {k: torch.from_numpy(np.ascontiguousarray(g[k])).to(dev)
+         for k in ("q", "k_pool", "v_pool", "k_scale", "v_scale", "k_residual", "res_rows",
+                   "block_tables", "seq_lens")}
+    if asym:
+        t["k_zero"] = torch.from_numpy(g["k_zero"]).to(dev)
+        t["v_zero"] = torch.from_numpy(g["v_zero"]).to(dev)
+    return t
+
+
+@pytest.mark.parametrize("name,asym", [("int8_sym", False), ("int8_asym", True)])
+def test_int8_decode_matches_the_reference_on_its_own_cache_state(name, asym, golden_dir):
+    """Pools, scales, residual and tables exactly as the reference cache left
+    them; expected output from the reference's paged_decode_reference."""
+    g = np.load(golden_dir / f"{name}.npz")
+    t = _golden_state(g, asym, device())
+    got = pdc.paged_decode_cuda(
+        t["q"], t["k_pool"], t["v_pool"], t["block_tables"], t["seq_lens"], int(g["seq_lens"].max()),
+        k_scale=t["k_scale"], v_scale=t["v_scale"], k_zero=t.get("k_zero"), v_zero=t.get("v_zero"),
+        k_residual=t["k_residual"], res_rows=t["res_rows"])
+    close(got, g["out"])
+
+
+def _random_int8_case(lens, asym, residual, seed):
+    rng = np.random.default_rng(seed)
+    h, d = 2, 128
+    pages = max(1, -(-max(lens) // 16))
+    nb = len(lens) * pages + 3
+    k_f = (rng.standard_normal((nb, 16, h, d)) + (0.7 if asym else 0.0)).astype(np.float16)
+    v_f = (rng.standard_normal((nb, 16, h, d)) * 1.5).astype(np.float16)
+    kq, ks, kz = orc.quantize_k_blocks(k_f, asym=asym)
+    vq, vs, vz = orc.quantize_v_rows(v_f.transpose(0, 1, 2, 3), asym=asym)     # per (blk, tok, head)
+    case = dict(k_pool=kq, v_pool=vq, k_scale=ks, v_scale=vs)
+    if asym:
+        case.update(k_zero=kz, v_zero=vz)
+    case["block_tables"] = rng.permutation(nb)[: len(lens) * pages].reshape(len(lens), pages).astype(np.int32)
+    case["seq_lens"] = np.asarray(lens, dtype=np.int32)
+    case["q"] = rng.standard_normal((len(lens), h, 6, d)).astype(np.float16)
+    if residual:
+        case["k_residual"] = rng.standard_normal((len(lens) + 2, 16, h, d)).astype(np.float16)
+        case["res_rows"] = rng.permutation(len(lens) + 2)[: len(lens)].astype(np.int32)   # not the identity
+    return case
+
+
+@pytest.mark.parametrize("asym", [False, True])
+@pytest.mark.parametrize("residual", [False, True])
+@pytest.mark.parametrize("splits", [None, 1, 3])
+def test_int8_decode_matches_the_oracle(asym, residual, splits):
+    lens = [1024, 300, 61, 17, 1, 32, 0]
+    case = _random_int8_case(lens, asym, residual, seed=21)
+    extra = {k: case[k] for k in ("k_scale", "v_scale", "k_zero", "v_zero", "k_residual", "res_rows")
+             if k in case}
+    want = orc.paged_decode(case["q"], case["k_pool"], case["v_pool"], case["block_tables"],
+                            case["seq_lens"], **extra)
+    dev = device()
+    t = {k: torch.from_numpy(np.ascontiguousarray(v)).to(dev) for k, v in case.items()}
+    got = pdc.paged_decode_cuda(
+        t["q"], t["k_pool"], t["v_pool"], t["block_tables"], t["seq_lens"], max(lens),
+        num_splits=splits, k_scale=t["k_scale"], v_scale=t["v_scale"], k_zero=t.get("k_zero"),
+        v_zero=t.get("v_zero"), k_residual=t.get("k_residual"), res_rows=t.get("res_rows"))
+    close(got, want)
+
+
+def test_int8_stale_scales_and_rows_are_never_read():
+    lens = [100, 37]
+    case = _random_int8_case(lens, False, True, seed=22)
+    extra = {k: case[k] for k in ("k_scale", "v_scale", "k_residual", "res_rows")}
+    want = orc.paged_decode(case["q"], case["k_pool"], case["v_pool"], case["block_tables"],
+                            case["seq_lens"], **extra)
+    vs = case["v_scale"].copy()
+    res = case["k_residual"].copy()
+    for b, L in enumerate(lens):
+        last = (L - 1) // 16
+        blk = case["block_tables"][b, last]
+        vs[blk, L - last * 16:] = np.nan                       # V scales of unwritten tokens
+        res[case["res_rows"][b], L - last * 16:] = np.nan      # residual rows past the end
+    case.update(v_scale=vs, k_residual=res)
+    dev = device()
+    t = {k: torch.from_numpy(np.ascontiguousarray(v)).to(dev) for k, v in case.items()}
+    got = pdc.paged_decode_cuda(t["q"], t["k_pool"], t["v_pool"], t["block_tables"], t["seq_lens"],
+                                max(lens), k_scale=t["k_scale"], v_scale=t["v_scale"],
+                                k_residual=t["k_residual"], res_rows=t["res_rows"])
+    close(got, want)
+
+
+@pytest.mark.parametrize("asym", [False, True])
+def test_cache_decode_steps_reproduce_the_reference_cache_bytes(asym, golden_dir):
+    """Int8PagedKVCache driven exactly as make_golden.py drove the reference's
+    cache (prefill 37 / 80 / 16 tokens, then 21 decode steps): attention output
+    against the reference's, and the K residual byte for byte. Pool bytes are
+    compared through the oracle (GPU arithmetic), since the fixture's were
+    produced with CPU division."""
+    name = "int8_asym" if asym else "int8_sym"
+    g = np.load(golden_dir / f"{name}.npz")
+    dev = device()
+    spec = lc.KVCacheSpec(num_layers=1, num_kv_heads=2, head_dim=128, max_seq_len=160,
+                          max_batch_size=3, device="cuda")
+    cache = lc.Int8PagedKVCache(spec, num_blocks=40, asymmetric=asym)
+    prompt, steps = [int(x) for x in g["prompt"]], int(g["steps"])
+    fed = [(torch.from_numpy(g[f"fed_k{i}"]).to(dev), torch.from_numpy(g[f"fed_v{i}"]).to(dev))
+           for i in range(3)]
+    for i, n in enumerate(prompt):
+        cache.advance(n, slots=[i])
+        cache.write(0, fed[i][0][None, :, :n], fed[i][1][None, :, :n])
+    for s in range(steps):
+        cache.advance(1, slots=[0, 1, 2])
+        k = torch.stack([fed[i][0][:, prompt[i] + s] for i in range(3)])[:, :, None]
+        v = torch.stack([fed[i][1][:, prompt[i] + s] for i in range(3)])[:, :, None]
+        cache.write(0, k, v)
+    q = torch.from_numpy(g["q"]).to(dev)
+    got = pdc.paged_decode_cuda(
+        q, cache.k_pool[0], cache.v_pool[0], cache.block_tables_tensor(3), cache.seq_lens_tensor(3),
+        cache.max_len, k_scale=cache.k_scale_pool[0], v_scale=cache.v_scale_pool[0],
+        k_zero=cache.k_zero_pool[0] if asym else None, v_zero=cache.v_zero_pool[0] if asym else None,
+        k_residual=cache.residual(0), res_rows=cache.residual_rows_tensor(3))
+    close(got, g["out"])
+    assert cache.seq_lens == [int(x) for x in g["seq_lens"]]
+    tables = cache.block_tables_tensor(3).cpu().numpy()
+    for i, L in enumerate(cache.seq_lens):
+        fk, fv = g[f"fed_k{i}"], g[f"fed_v{i}"]
+        vq, vstep, _ = orc.quantize_v_rows(fv, asym=asym, reciprocal=True)
+        for pos in range(L):
+            blk, off = int(tables[i, pos // 16]), pos % 16
+            assert np.array_equal(cache.v_pool[0][blk, off].cpu().numpy(), vq[:, pos])
+            assert np.array_equal(cache.v_scale_pool[0][blk, off].cpu().numpy(), vstep[:, pos])
+        done = L // 16 if L % 16 else L // 16 - 1
+        for p in range(done):
+            kq, kstep, _ = orc.quantize_k_blocks(fk[:, p * 16:(p + 1) * 16].transpose(1, 0, 2)[None],
+                                                 asym=asym, reciprocal=True)
+            blk = int(tables[i, p])
+            assert np.array_equal(cache.k_pool[0][blk].cpu().numpy(), kq[0])
+            assert np.array_equal(cache.k_scale_pool[0][blk].cpu().numpy(), kstep[0])
+        tail0 = (L - 1) // 16 * 16
+        assert np.array_equal(cache.residual(0)[i, :L - tail0].cpu().numpy(),
+                              fk[:, tail0:L].transpose(1, 0, 2))

@@ -1,0 +1,257 @@
+"""Page-sparse path on the GPU: page bounds, indexer scores and top-k bit-exact
+against the oracle; attention over selected pages within tolerance (cases
+follow the reference's tests/test_phase14_sparse_kernels.py:73-217 and
+tests/test_phase17_policy.py:108-143)."""
+
+import numpy as np
+import pytest
+import torch
+
+from latentserve_b200 import cache as lc
+from latentserve_b200 import kv_write
+from latentserve_b200 import paged_decode_cuda as pdc
+from latentserve_b200 import paged_sparse as ps
+from latentserve_b200 import synthetic
+from oracle import paged_attention_oracle as orc
+from tests.gpu_util import close, device, on_device
+
+pytestmark = pytest.mark.gpu
+
+
+def _with_bounds(case):
+    t = on_device(case)
+    nb, _, h, d = t["k_pool"].shape
+    t["kmin"] = torch.empty(nb, h, d, dtype=torch.float16, device=device())
+    t["kmax"] = torch.empty_like(t["kmin"])
+    ps.rebuild_bounds(t["k_pool"], t["kmin"], t["kmax"])
+    return t
+
+
+def test_bounds_updated_token_by_token_equal_the_true_min_and_max():
+    dev = device()
+    rng = np.random.default_rng(1)
+    h, d, nb = 2, 128, 8
+    kmin = torch.full((nb, h, d), 99.0, dtype=torch.float16, device=dev)
+    kmax = torch.full_like(kmin, -99.0)
+    k_pool = torch.zeros(nb, 16, h, d, dtype=torch.float16, device=dev)
+    v_pool = torch.zeros_like(k_pool)
+    blocks, rows = [5, 2], {}
+    for pos in range(27):
+        slot = blocks[pos // 16] * 16 + pos % 16
+        k_new = torch.from_numpy(rng.standard_normal((1, h, 1, d)).astype(np.float16)).to(dev)
+        v_new = torch.from_numpy(rng.standard_normal((1, h, 1, d)).astype(np.float16)).to(dev)
+        kv_write.append_fp16(k_new, v_new, torch.tensor([slot], device=dev), k_pool.view(-1, h, d),
+                             v_pool.view(-1, h, d), kmin, kmax)
+        rows.setdefault(blocks[pos // 16], []).append((pos % 16, k_new[0, :, 0], v_new[0, :, 0]))
+    torch.cuda.synchronize()
+    for blk, items in rows.items():
+        stack = torch.stack([k for _, k, _ in items])
+        assert torch.equal(kmin[blk], stack.amin(0)) and torch.equal(kmax[blk], stack.amax(0))
+        for off, k, v in items:
+            assert torch.equal(k_pool[blk, off], k) and torch.equal(v_pool[blk, off], v)
+    # Stand-alone bounds update (rows scattered by someone else) gives the same.
+    kmin2 = torch.full((nb, h, d), 99.0, dtype=torch.float16, device=dev)
+    kmax2 = torch.full_like(kmin2, -99.0)
+    for blk, items in rows.items():
+        for off, k, _ in items:
+            ps.update_bounds(k[None], torch.tensor([blk * 16 + off], device=dev), kmin2, kmax2)
+    assert torch.equal(kmin2[blocks], kmin[blocks]) and torch.equal(kmax2[blocks], kmax[blocks])
+
+
+@pytest.mark.parametrize("lens", [[700, 333], [32768, 4096, 17, 1, 0]])
+def test_indexer_scores_are_bit_exact(lens):
+    case = synthetic.dense_case(lens, seed=11, page_offset_std=0.5)
+    t = _with_bounds(case)
+    got = ps.page_scores(t["q"], t["kmin"], t["kmax"], t["block_tables"], t["seq_lens"], recent=2)
+    want = orc.page_scores(case["q"], t["kmin"].cpu().numpy(), t["kmax"].cpu().numpy(),
+                           case["block_tables"], case["seq_lens"], recent=2)
+    assert np.array_equal(got.cpu().numpy().view(np.uint32), want.view(np.uint32))
+
+
+def test_indexer_scores_against_the_reference_bounds(golden_dir):
+    g = np.load(golden_dir / "sparse.npz")
+    lens = [int(x) for x in g["seq_lens"]]
+    t = _with_bounds(synthetic.dense_case(lens, seed=11, page_offset_std=0.5))
+    scores = ps.page_scores(t["q"], t["kmin"], t["kmax"], t["block_tables"], t["seq_lens"]).cpu().numpy()
+    for b, L in enumerate(lens):
+        np_ = -(-L // 16)
+        mid = slice(1, np_ - 2)
+        np.testing.assert_allclose(scores[b, :, mid], g[f"bounds{b}"][:, mid], rtol=1e-4, atol=1e-3)
+        assert np.isposinf(scores[b, :, 0]).all() and np.isposinf(scores[b, :, np_ - 2:np_]).all()
+        assert np.isneginf(scores[b, :, np_:]).all()
+
+
+@pytest.mark.parametrize("n,k", [(2048, 1024), (2048, 2048), (700, 44), (33, 3), (1, 1), (257, 256)])
+def test_topk_is_bit_exact_with_ties_to_the_lower_index(n, k):
+    rng = np.random.default_rng(n + k)
+    s = rng.standard_normal((3, 2, n)).astype(np.float32)
+    s[..., 0] = np.inf
+    if n > 40:
+        s[0, 0, 10:30] = s[0, 0, 10]                          # runs of exact ties
+        s[1, 1, :] = np.round(s[1, 1, :], 1)                  # many ties everywhere
+        s[..., n - n // 4:] = -np.inf                         # pages past the end
+        s[..., n - n // 4 - 2:n - n // 4] = np.inf            # recent pages
+        s[2, 0, 5] = -0.0
+        s[2, 0, 6] = 0.0
+    got = ps.select(torch.from_numpy(s).to(device()), k)
+    assert np.array_equal(got.cpu().numpy(), orc.select(s, k))
+
+
+def test_selection_end_to_end_is_bit_exact_on_the_sparse_workload_shape():
+    """Scores from the kernel, selection from the kernel, against the oracle
+    chain, at 2048 pages and a 50 % budget."""
+    lens = [32768, 32768]
+    case = synthetic.dense_case(lens, seed=17, page_offset_std=0.5)
+    t = _with_bounds(case)
+    scores = ps.page_scores(t["q"], t["kmin"], t["kmax"], t["block_tables"], t["seq_lens"])
+    k = ps.budget(0.5, 2048)
+    assert k == 1024
+    sel = ps.select(scores, k).cpu().numpy()
+    want_scores = orc.page_scores(case["q"], t["kmin"].cpu().numpy(), t["kmax"].cpu().numpy(),
+                                  case["block_tables"], case["seq_lens"])
+    assert np.array_equal(sel, orc.select(want_scores, k))
+    assert (sel[..., :3] == np.asarray([0, 2046, 2047])).all()  # forced pages first, index order
+
+
+@pytest.mark.parametrize("num_splits", [None, 1, 3])
+def test_sparse_kernel_attends_exactly_the_given_pages(num_splits, golden_dir):
+    g = np.load(golden_dir / "sparse.npz")
+    lens = [int(x) for x in g["seq_lens"]]
+    case = synthetic.dense_case(lens, seed=11, page_offset_std=0.5)
+    t = on_device(case)
+    sel = np.stack([np.stack([p, p[::-1]]) for p in g["picks"]]).astype(np.int32)
+    got = ps.sparse_decode(t["q"], t["k_pool"], t["v_pool"], t["block_tables"], t["seq_lens"],
+                           torch.from_numpy(sel).to(device()), num_splits=num_splits)
+    close(got, g["attend_picks"])
+
+
+def test_selection_with_invalid_entries_and_per_sequence_budgets():
+    lens = [4096, 700, 40, 0]
+    ratio = 0.375
+    case = synthetic.dense_case(lens, seed=19, page_offset_std=0.5)
+    t = _with_bounds(case)
+    scores = ps.page_scores(t["q"], t["kmin"], t["kmax"], t["block_tables"], t["seq_lens"])
+    k = ps.budget(ratio, 256)
+    sel = ps.select(scores, k)
+    got = ps.sparse_decode(t["q"], t["k_pool"], t["v_pool"], t["block_tables"], t["seq_lens"], sel,
+                           ratio=ratio)
+    assert ps.budgets(t["seq_lens"], ratio).tolist() == [96, 17, 3, 0]
+    want = orc.sparse_decode(case["q"], case["k_pool"], case["v_pool"], case["block_tables"],
+                             case["seq_lens"], sel.cpu().numpy(), ratio=ratio)
+    close(got, want)
+    # A hand-made list with negative and past-the-end entries is skipped, not read.
+    bad = sel.clone()
+    bad[:, :, 1] = -1
+    bad[:, :, 2] = 1_000_000
+    got = ps.sparse_decode(t["q"], t["k_pool"], t["v_pool"], t["block_tables"], t["seq_lens"], bad)
+    want = orc.sparse_decode(case["q"], case["k_pool"], case["v_pool"], case["block_tables"],
+                             case["seq_lens"], bad.cpu().numpy())
+    close(got, want)
+
+
+def test_full_budget_reproduces_the_dense_kernel():
+    case = synthetic.dense_case([1024, 300], seed=3)
+    t = _with_bounds(case)
+    dense = pdc.paged_decode_cuda(t["q"], t["k_pool"], t["v_pool"], t["block_tables"], t["seq_lens"],
+                                  1024).clone()
+    sparse = ps.sparse_attention(t["q"], t["k_pool"], t["v_pool"], t["block_tables"], t["seq_lens"],
+                                 t["kmin"], t["kmax"], ratio=1.0)
+    close(sparse, dense.float().cpu().numpy(), atol=1e-3)
+
+
+@pytest.mark.parametrize("scoring", ["bounds", "mass"])
+def test_sparse_attention_pipeline_at_quarter_budget(scoring):
+    lens = [2048, 900]
+    case = synthetic.dense_case(lens, seed=23, page_offset_std=0.5)
+    t = _with_bounds(case)
+    got = ps.sparse_attention(t["q"], t["k_pool"], t["v_pool"], t["block_tables"], t["seq_lens"],
+                              t["kmin"], t["kmax"], ratio=0.25, max_seq_len=2048, scoring=scoring)
+    if scoring == "bounds":
+        scores = orc.page_scores(case["q"], t["kmin"].cpu().numpy(), t["kmax"].cpu().numpy(),
+                                 case["block_tables"], case["seq_lens"])
+    else:
+        scores = ps.page_scores_mass(t["q"], t["kmin"], t["kmax"], t["block_tables"],
+                                     t["seq_lens"]).cpu().numpy()
+    sel = orc.select(scores, ps.budget(0.25, 128))
+    for b, L in enumerate(lens):
+        np_ = -(-L // 16)
+        n = int(orc.budgets([L], 0.25)[0])
+        assert {0, np_ - 2, np_ - 1} <= set(sel[b, 0, :n].tolist())
+    want = orc.sparse_decode(case["q"], case["k_pool"], case["v_pool"], case["block_tables"],
+                             case["seq_lens"], sel, ratio=0.25)
+    close(got, want)
+
+
+def test_sparse_pipeline_survives_graph_capture():
+    case = synthetic.dense_case([1500, 640], seed=29, page_offset_std=0.5)
+    t = _with_bounds(case)
+    args = (t["q"], t["k_pool"], t["v_pool"], t["block_tables"], t["seq_lens"], t["kmin"], t["kmax"])
+    ps.sparse_attention(*args, ratio=0.25)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        out = ps.sparse_attention(*args, ratio=0.25)
+    q2 = np.random.default_rng(2).standard_normal(case["q"].shape).astype(np.float16)
+    t["q"].copy_(torch.from_numpy(q2))
+    graph.replay()
+    torch.cuda.synchronize()
+    scores = orc.page_scores(q2, t["kmin"].cpu().numpy(), t["kmax"].cpu().numpy(),
+                             case["block_tables"], case["seq_lens"])
+    sel = orc.select(scores, ps.budget(0.25, 94))
+    want = orc.sparse_decode(q2, case["k_pool"], case["v_pool"], case["block_tables"],
+                             case["seq_lens"], sel, ratio=0.25)
+    close(out, want)
+
+
+def test_fp16_cache_decode_steps_with_bounds_and_prefix_sharing():
+    """PagedKVCache end to end: prefill, a shared ref-counted prefix, decode
+    steps with page bounds on; dense and sparse attention against the oracle
+    over the cache's own pools."""
+    dev = device()
+    rng = np.random.default_rng(31)
+    spec = lc.KVCacheSpec(num_layers=2, num_kv_heads=2, head_dim=128, max_seq_len=512,
+                          max_batch_size=3, device="cuda")
+    cache = lc.PagedKVCache(spec, num_blocks=80)
+    cache.enable_page_bounds()
+
+    def rows(b, n):
+        return (torch.from_numpy(rng.standard_normal((b, 2, n, 128)).astype(np.float16)).to(dev),
+                torch.from_numpy(rng.standard_normal((b, 2, n, 128)).astype(np.float16)).to(dev))
+
+    cache.advance(64, slots=[0])
+    for layer in range(2):
+        cache.write(layer, *rows(1, 64))
+    shared = cache.tables[0].blocks[:2]                        # 32 tokens = 2 full blocks
+    cache.attach_prefix(1, shared, 32)
+    assert cache.allocator.ref_count(shared[0]) == 2
+    cache.advance(21, slots=[1])
+    for layer in range(2):
+        cache.write(layer, *rows(1, 21))
+    for _ in range(19):
+        cache.advance(1, slots=[0, 1])
+        for layer in range(2):
+            cache.write(layer, *rows(2, 1))
+    assert cache.seq_lens == [83, 72]
+    tables, lens = cache.block_tables_tensor(2), cache.seq_lens_tensor(2)
+    assert tables[0, :2].tolist() == tables[1, :2].tolist() == shared
+    q = torch.from_numpy(rng.standard_normal((2, 2, 6, 128)).astype(np.float16)).to(dev)
+    for layer in range(2):
+        k, v = cache.k_pool[layer], cache.v_pool[layer]
+        want = orc.paged_decode(q.cpu().numpy(), k.cpu().numpy(), v.cpu().numpy(),
+                                tables.cpu().numpy(), lens.cpu().numpy())
+        close(pdc.paged_decode_cuda(q, k, v, tables, lens, cache.max_len), want)
+        kmin, kmax = cache.page_bounds(layer)
+        for b, L in enumerate(cache.seq_lens):
+            for p in range(-(-L // 16)):
+                blk = int(tables[b, p])
+                n = min(16, L - p * 16)
+                assert torch.equal(kmin[blk], k[blk, :n].amin(0)) and torch.equal(kmax[blk], k[blk, :n].amax(0))
+        got = ps.sparse_attention(q, k, v, tables, lens, kmin, kmax, ratio=0.5, max_seq_len=cache.max_len)
+        scores = orc.page_scores(q.cpu().numpy(), kmin.cpu().numpy(), kmax.cpu().numpy(),
+                                 tables.cpu().numpy(), lens.cpu().numpy())
+        sel = orc.select(scores, ps.budget(0.5, -(-cache.max_len // 16)))
+        want = orc.sparse_decode(q.cpu().numpy(), k.cpu().numpy(), v.cpu().numpy(),
+                                 tables.cpu().numpy(), lens.cpu().numpy(), sel, ratio=0.5)
+        close(got, want)
+    cache.free_sequence(0)
+    assert cache.allocator.ref_count(shared[0]) == 1           # still held by sequence 1
