@@ -6,7 +6,7 @@ Workload (default `dense_fp16_b16_16k`): Qwen2.5-1.5B attention shape — 12 que
 / 2 KV heads, head_dim 128, page 16 — batch 16, every sequence at 16 384 tokens
 of context, 28 layers each with its own K/V pools of ceil(1.2 x needed) blocks
 and one shuffled block table; synthetic N(0,1) fp16 values. A STEP is one decode
-step's attention: the 28 layer calls (split-KV kernel + merge each), i.e. one
+step's attention: the 28 layer calls (one launch each: split-KV + merge), i.e. one
 pass over 7.5 GB of KV, far more than the 126 MB L2, so nothing is flushed
 between steps.
 
@@ -19,7 +19,7 @@ One JSON line comes out:
              lengths and slots shipped to the device), cache.write() and
              paged_decode_attention() per layer, eagerly, and reads the
              outputs back to the host.
-  roofline   the split-KV kernel alone (no merge), timed with CUDA events.
+  roofline   the decode kernel, launched eagerly layer by layer, timed with CUDA events.
   cpu_baseline  the numpy oracle on the host cores, one layer call.
 `--impl reference` times that CPU oracle instead (rank 0 only).
 
@@ -45,10 +45,15 @@ ROOT = pathlib.Path(__file__).resolve().parent
 sys.path.insert(0, str(ROOT))
 
 WORKLOADS = {
-    # name: (batch, context, layers)
+    # name: (batch, context, layers); the first is the benchmark, the rest exist for
+    # profiler captures and for the other kernels of the path.
     "dense_fp16_b16_16k": (16, 16384, 28),
-    "dense_fp16_b4_2k": (4, 2048, 4),          # small case for profiler captures
-    "dense_fp16_b16_4k": (16, 4096, 8),
+    "dense_fp16_b16_4k": (16, 4096, 8),        # small case for profiler captures
+    "dense_fp16_b64_ragged": (64, "loguniform_1k_32k", 8),
+    "int8_b32_8k_32k": (32, "uniform_8k_32k", 8),
+    "int8_b16_4k": (16, 4096, 8),              # small case for profiler captures
+    "sparse50_b8_32k": (8, 32768, 8),
+    "sparse50_b8_8k": (8, 8192, 8),            # small case for profiler captures
 }
 METRIC = "paged decode-attn HBM GB/s"
 FALLBACK_HBM_GBS = 6650.0
@@ -187,8 +192,12 @@ def main():
                     help="split-KV kernel variant (simt = CUDA-core kernel, for profiling)")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--quick", action="store_true",
+                    help="profiler runs: no e2e / CPU legs, no extension of the load for clock sampling")
     args = ap.parse_args()
     workload = WORKLOADS[args.workload]
+    if args.quick:
+        args.no_e2e = args.no_cpu = True
     if args.impl == "reference":
         run_reference(args, workload)
         return
@@ -214,13 +223,55 @@ def main():
 
     batch, context, layers = workload
     impl = pdc.IMPL_SIMT if args.kernel == "simt" else pdc.IMPL_MMA
-    w = synthetic.dense_pools_on_device(batch, context, layers, dev, seed=rank)
-    tables, lens = w["block_tables"], w["seq_lens"]
-    step_bytes = synthetic.kv_bytes_fp16([context] * batch) * layers
+    rng = np.random.default_rng(1234 + rank)
+    if context == "loguniform_1k_32k":
+        seq_lens = np.exp(rng.uniform(np.log(1024), np.log(32768), size=batch)).astype(int).tolist()
+    elif context == "uniform_8k_32k":
+        seq_lens = rng.integers(8192, 32769, size=batch).tolist()
+    else:
+        seq_lens = [context] * batch
+    kind = args.workload.split("_")[0]
+    if kind == "int8":
+        w = synthetic.int8_pools_on_device(seq_lens, layers, dev, seed=rank)
+        tables, lens = w["block_tables"], w["seq_lens"]
+        step_bytes = synthetic.kv_bytes_int8(seq_lens) * layers
 
-    def layer_call(i, merge=True):
-        k, v = w["pools"][i]
-        return pdc.paged_decode_cuda(w["q"][i], k, v, tables, lens, context, impl=impl, merge=merge)
+        def layer_call(i, merge=True):
+            L = w["layers"][i]
+            return pdc.paged_decode_cuda(w["q"][i], L["k_pool"], L["v_pool"], tables, lens, max(seq_lens),
+                                         k_scale=L["k_scale"], v_scale=L["v_scale"],
+                                         k_residual=L["k_residual"], res_rows=w["res_rows"], merge=merge)
+        launches_per_layer, kernel_name = 1, "decode_kernel<int8>"
+    elif kind.startswith("sparse"):
+        from latentserve_b200 import paged_sparse as ps
+
+        w = synthetic.sparse_pools_on_device(batch, context, layers, dev, seed=rank)
+        tables, lens = w["block_tables"], w["seq_lens"]
+        pages = -(-context // 16)
+        keep = ps.budget(0.5, pages)
+        # indexer reads kmin+kmax of every page-head, writes and re-reads the scores,
+        # attention reads the selected pages
+        layer_bytes = batch * 2 * (pages * 512 + pages * 8 + keep * 16 * 512)
+        step_bytes = layer_bytes * layers
+
+        def layer_call(i, merge=True):
+            k, v = w["pools"][i]
+            kmin, kmax = w["bounds"][i]
+            return ps.sparse_attention(w["q"][i], k, v, tables, lens, kmin, kmax, ratio=0.5,
+                                       max_seq_len=context)
+        launches_per_layer, kernel_name = 3, "page_index + topk_pages + decode_kernel<sparse>"
+    else:
+        w = synthetic.dense_pools_on_device(batch, seq_lens, layers, dev, seed=rank)
+        tables, lens = w["block_tables"], w["seq_lens"]
+        step_bytes = synthetic.kv_bytes_fp16(seq_lens) * layers
+
+        def layer_call(i, merge=True):
+            k, v = w["pools"][i]
+            return pdc.paged_decode_cuda(w["q"][i], k, v, tables, lens, max(seq_lens), impl=impl,
+                                         merge=merge)
+        launches_per_layer = 1
+        kernel_name = f"decode_kernel<{args.kernel}> (split-KV + in-kernel merge)"
+    default_workload = args.workload == "dense_fp16_b16_16k"
 
     # One step = the 28 layer calls, captured once.
     side = torch.cuda.Stream()
@@ -255,7 +306,7 @@ def main():
     ms_total = e0.elapsed_time(e1)
     # Keep the same load running briefly if the timed region was too short for
     # the 100 ms clock sampler to see it.
-    extra_until = t_wall0 + 1.2
+    extra_until = t_wall0 + (0.0 if args.quick else 1.2)
     while time.time() < extra_until:
         for _ in range(20):
             graph.replay()
@@ -268,17 +319,17 @@ def main():
     ms_step = ms_total / args.steps
     value = world * step_bytes / (ms_step * 1e-3) / 1e9
 
-    # Roofline: the split-KV kernel alone, one launch per layer, CUDA events on
-    # the launching (current) stream.
+    # Roofline: the decode kernel, one eager launch per layer, CUDA events on the
+    # launching (current) stream.
     for i in range(layers):
-        layer_call(i, merge=False)
+        layer_call(i)
     torch.cuda.synchronize()
     reps = max(3, min(20, args.steps))
     k0, k1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     k0.record()
     for _ in range(reps):
         for i in range(layers):
-            layer_call(i, merge=False)
+            layer_call(i)
     k1.record()
     torch.cuda.synchronize()
     kernel_ms = k0.elapsed_time(k1) / (reps * layers)
@@ -288,17 +339,17 @@ def main():
     achieved = layer_bytes / (kernel_ms * 1e-3) / 1e9
     roofline = {"bound": "hbm", "achieved": round(achieved, 1), "peak": peak, "unit": "GB/s",
                 "frac": round(achieved / peak, 4), "traffic": NCU_TRAFFIC_BYTES,
-                "peak_kind": f"of {peak_kind}", "kernel": f"decode_kernel<{args.kernel}> (no merge)",
+                "peak_kind": f"of {peak_kind}", "kernel": kernel_name,
                 "kernel_us": round(kernel_ms * 1e3, 2), "algorithmic_bytes_per_launch": layer_bytes,
                 "frac_of_8TBs": round(achieved / 8000.0, 4)}
 
     # End to end through the public API with host buffers.
     e2e = None
-    if not args.no_e2e:
+    if not args.no_e2e and default_workload:
         e2e = run_e2e(args, workload, dev, dist, world)
 
     cpu = None
-    if rank == 0 and world == 1 and not args.no_cpu:
+    if rank == 0 and world == 1 and not args.no_cpu and default_workload:
         k, v = w["pools"][0]
         blocks = tables.long()
         seqs = min(batch, 4)
@@ -319,17 +370,19 @@ def main():
         line = {
             "metric": METRIC, "value": round(value, 1), "unit": "GB/s", "n_gpus": world,
             "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": round(ms_step, 4),
-            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f16",
-            "data": "synthetic",
-            "config": {"workload": args.workload, "batch_per_gpu": batch, "context": context,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "i8" if kind == "int8" else "f16", "data": "synthetic",
+            "config": {"workload": args.workload, "batch_per_gpu": batch,
+                       "context": context if isinstance(context, int) else
+                       f"{context}: min {min(seq_lens)}, mean {int(np.mean(seq_lens))}, max {max(seq_lens)}",
                        "layers_per_step": layers, "q_heads": 12, "kv_heads": 2, "head_dim": 128,
                        "page": 16, "pool_blocks": w["num_blocks"], "kernel": args.kernel,
                        "parallelism": f"replicas x{world} (sequence-sharded, no collective)",
                        "l2": f"no flush: each step reads {step_bytes / 1e9:.2f} GB, L2 is 126 MB",
-                       "step": "28 layer calls (split-KV kernel + merge) replayed from one CUDA graph"},
+                       "step": f"{layers} layer calls (one launch each) replayed from one CUDA graph"},
             "pct_of_8TBs": round(100.0 * value / world / 8000.0, 2),
             "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e,
-            "gpu_launches": 2 * layers * args.steps, "clocks": clocks,
+            "gpu_launches": launches_per_layer * layers * args.steps, "clocks": clocks,
         }
         print(json.dumps(line))
     if dist is not None:
@@ -406,7 +459,7 @@ def run_e2e(args, workload, dev, dist, world):
     return {"value": round(world * step_bytes / (ms * 1e-3) / 1e9, 1), "unit": "GB/s",
             "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h),
             "ms_per_step": round(ms, 4), "steps": steps,
-            "gpu_launches_per_step": 3 * layers,
+            "gpu_launches_per_step": 2 * layers,
             "path": "PagedKVCache.advance + write + paged_decode_attention per layer, eager"}
 
 

@@ -44,17 +44,23 @@ extern "C" {
  *   part_acc  float [slots, H, 8, 128]
  *   part_m    float [slots, H, 8]        running maxima, log2 domain
  *   part_l    float [slots, H, 8]
- *   seg_range int32 [2*B + 2]            written by the kernel: first slot and
- *                                        slot count of each sequence; element
- *                                        [2*B] is set to 1 if a block id or a
+ *   seg_range int32 [2*B + 2 + B*H]      [0, 2B): first slot and slot count of
+ *                                        each sequence, written by the kernel;
+ *                                        [2B]: set to 1 if a block id or a
  *                                        residual row outside its pool was met
- *                                        (that page is skipped, never read).
- *                                        Zero it once before first use.
+ *                                        (that page is skipped, never read);
+ *                                        [2B+2, ...): one arrival counter per
+ *                                        (sequence, head), left at zero by
+ *                                        every launch. ZERO THE BUFFER ONCE
+ *                                        before first use.
  * None of it needs filling between calls. `num_chunks` x H is the grid: the
  * kernels are sized for 2 resident CTAs per SM, so num_chunks = 2*SMs / H is
  * the natural choice; `min_chunk` (>= 1) is the fewest pages a chunk may hold.
- * If `out` is non-NULL the merge (ls_combine) is launched as well and `out`
- * receives fp16 [B, H, R, 128] with the given strides.
+ * If `out` is non-NULL the same launch also merges the partials — the CTA that
+ * delivers a sequence's last partial does it, nobody waits — and `out`
+ * receives fp16 [B, H, R, 128] with the given strides; sequences of length 0
+ * get zeros. If `out` is NULL only the partials are produced (ls_combine
+ * merges them). Launches that share one scratch must not overlap on the GPU.
  */
 int ls_decode_slots(int batch, int num_chunks);
 

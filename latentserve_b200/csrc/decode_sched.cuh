@@ -31,7 +31,10 @@ struct DecodeParams {
     float* part_acc;               // [slots, H, RP, 128]
     float* part_m;                 // [slots, H, RP]   (log2 domain)
     float* part_l;                 // [slots, H, RP]
-    int* seg_range;                // [B, 2] first slot, count; [2B] = error flag
+    int* seg_range;                // [B, 2] first slot, count; [2B] = error flag;
+                                   // [2B+2 ..) one arrival counter per (sequence, head)
+    __half* out;                   // [B, H, R, 128] final output, or null: partials only
+    long long so_b, so_h, so_m;
     // INT8 pools
     const float* k_scale;
     const float* v_scale;

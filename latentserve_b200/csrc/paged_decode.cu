@@ -32,6 +32,9 @@
 //   * at the end of a segment the CTA's warps merge their states through
 //     shared memory and write ONE partial (m, l, acc) per (chunk, sequence,
 //     head); every slot a sequence owns is written, so nothing is pre-filled.
+//   * the CTA that delivers a sequence's last outstanding partial (an atomic
+//     arrival count per (sequence, head), no waiting) merges them and writes
+//     the fp16 output, so a layer call is ONE launch.
 #include "decode_sched.cuh"
 
 namespace ls {
@@ -647,6 +650,34 @@ struct MmaInt8 {
 };
 
 // ---------------------------------------------------------------------------
+// Merge of a sequence's partials:
+//   out = sum_s acc_s 2^(m_s - M) / max(sum_s l_s 2^(m_s - M), 1e-20),
+// the reference combine (kernels/gqa/paged_decode.py:421-471, torch form
+// :689-706) with m held in the log2 domain. Called by 128 threads (thread =
+// head dim); loads bypass L1 because other CTAs of the same launch may have
+// written the partials.
+__device__ __forceinline__ void merge_partials(const float* part_acc, const float* part_m,
+                                               const float* part_l, int first, int count,
+                                               __half* out, int heads, int n_rep, int b, int h,
+                                               int d, long long so_b, long long so_h,
+                                               long long so_m) {
+    for (int r = 0; r < n_rep; ++r) {
+        float mg = neg_inf();
+        for (int s = 0; s < count; ++s)
+            mg = fmaxf(mg, __ldcg(part_m + ((long long)(first + s) * heads + h) * kRP + r));
+        const float ms = (mg == neg_inf()) ? 0.f : mg;
+        float lsum = 0.f, a = 0.f;
+        for (int s = 0; s < count; ++s) {
+            const long long row = ((long long)(first + s) * heads + h) * kRP + r;
+            const float w = ex2(__ldcg(part_m + row) - ms);
+            lsum += w * __ldcg(part_l + row);
+            a += w * __ldcg(part_acc + row * LS_HEAD_DIM + d);
+        }
+        out[b * so_b + h * so_h + r * so_m + d] = __float2half_rn(a / fmaxf(lsum, 1e-20f));
+    }
+}
+
+// ---------------------------------------------------------------------------
 template <class State, int MODE, int STAGES>
 __global__ void __launch_bounds__(kThreads, 2) decode_kernel(const DecodeParams p) {
     extern __shared__ __align__(1024) unsigned char smem[];
@@ -660,11 +691,20 @@ __global__ void __launch_bounds__(kThreads, 2) decode_kernel(const DecodeParams 
     float* merge_l = merge_m + kWarps * kRP;
     int* meta = reinterpret_cast<int*>(merge_l + kWarps * kRP);   // [kWarps][STAGES]
     int* scan = meta + kWarps * STAGES;                           // [kWarps]
-    int* cum = scan + kWarps;                                     // [batch + 1]
+    int* flag = scan + kWarps;                                    // [1]
+    int* cum = flag + 1;                                          // [batch + 1]
 
     const int total = build_prefix<MODE, kThreads>(p, cum, scan);
     const int chunk = chunk_size(p, total);
     if (chunk_id == 0 && h == 0) write_seg_ranges<kThreads>(p, cum, chunk);
+    if (chunk_id == 0 && p.out != nullptr) {
+        // Sequences with nothing to attend produce zeros (nobody else writes them).
+        for (int b = 0; b < p.batch; ++b) {
+            if (cum[b + 1] != cum[b]) continue;
+            for (int i = tid; i < p.n_rep * LS_HEAD_DIM; i += kThreads)
+                p.out[b * p.so_b + h * p.so_h + (i >> 7) * p.so_m + (i & 127)] = __float2half_rn(0.f);
+        }
+    }
     const int g0 = chunk_id * chunk;
     if (g0 >= total) return;
     const int g1 = min(total, g0 + chunk);
@@ -712,9 +752,9 @@ __global__ void __launch_bounds__(kThreads, 2) decode_kernel(const DecodeParams 
         st.finish(merge_o + warp * p.n_rep * kMergeStride, merge_m + warp * kRP,
                   merge_l + warp * kRP, p.n_rep, lane);
         __syncthreads();
+        const int slot = chunk_id + b;
         {
             // CTA merge: thread = one of the 128 dims, all rows.
-            const int slot = chunk_id + b;
             float* pa = p.part_acc + ((long long)slot * p.heads + h) * kRP * LS_HEAD_DIM;
             float* pm = p.part_m + ((long long)slot * p.heads + h) * kRP;
             float* pl = p.part_l + ((long long)slot * p.heads + h) * kRP;
@@ -743,6 +783,29 @@ __global__ void __launch_bounds__(kThreads, 2) decode_kernel(const DecodeParams 
                 }
             }
         }
+        if (p.out != nullptr) {
+            // Whoever brings a sequence's last partial merges them all. Arrival is
+            // counted with one atomic per segment; nobody waits for anybody.
+            const int c_lo = cum[b] / chunk, c_hi = (cum[b + 1] - 1) / chunk;
+            const int nseg = c_hi - c_lo + 1;
+            int* counter = p.seg_range + 2 * p.batch + 2 + b * p.heads + h;
+            __threadfence();
+            __syncthreads();
+            if (tid == 0) {
+                int last = 1;
+                if (nseg > 1) {
+                    last = atomicAdd(counter, 1) == nseg - 1;
+                    if (last) *counter = 0;                  // ready for the next launch
+                }
+                *flag = last;
+            }
+            __syncthreads();
+            if (*flag) {
+                __threadfence();
+                merge_partials(p.part_acc, p.part_m, p.part_l, c_lo + b, nseg, p.out, p.heads,
+                               p.n_rep, b, h, tid, p.so_b, p.so_h, p.so_m);
+            }
+        }
         if (cum[b + 1] >= g1) break;
         __syncthreads();
         ++b;
@@ -753,31 +816,15 @@ __global__ void __launch_bounds__(kThreads, 2) decode_kernel(const DecodeParams 
 }
 
 // ---------------------------------------------------------------------------
-// Merge of a sequence's partials:
-//   out = sum_s acc_s 2^(m_s - M) / max(sum_s l_s 2^(m_s - M), 1e-20),
-// the reference combine (kernels/gqa/paged_decode.py:421-471, torch form
-// :689-706) with m held in the log2 domain. grid (B, H), thread = head dim.
+// Stand-alone merge (see merge_partials). grid (B, H), thread = head dim.
 __global__ void __launch_bounds__(LS_HEAD_DIM)
 merge_kernel(const float* __restrict__ part_acc, const float* __restrict__ part_m,
              const float* __restrict__ part_l, const int* __restrict__ seg_range,
              __half* __restrict__ out, int heads, int n_rep, long long so_b, long long so_h,
              long long so_m) {
-    const int b = blockIdx.x, h = blockIdx.y, d = threadIdx.x;
-    const int first = seg_range[2 * b], count = seg_range[2 * b + 1];
-    for (int r = 0; r < n_rep; ++r) {
-        float mg = neg_inf();
-        for (int s = 0; s < count; ++s)
-            mg = fmaxf(mg, part_m[((long long)(first + s) * heads + h) * kRP + r]);
-        const float ms = (mg == neg_inf()) ? 0.f : mg;
-        float lsum = 0.f, a = 0.f;
-        for (int s = 0; s < count; ++s) {
-            const long long row = ((long long)(first + s) * heads + h) * kRP + r;
-            const float w = ex2(part_m[row] - ms);
-            lsum += w * part_l[row];
-            a += w * part_acc[row * LS_HEAD_DIM + d];
-        }
-        out[b * so_b + h * so_h + r * so_m + d] = __float2half_rn(a / fmaxf(lsum, 1e-20f));
-    }
+    const int b = blockIdx.x, h = blockIdx.y;
+    merge_partials(part_acc, part_m, part_l, seg_range[2 * b], seg_range[2 * b + 1], out, heads,
+                   n_rep, b, h, threadIdx.x, so_b, so_h, so_m);
 }
 
 // ---------------------------------------------------------------------------
@@ -799,20 +846,11 @@ template <class State, int MODE, int STAGES>
 static int launch_decode(const DecodeParams& p, cudaStream_t stream) {
     const size_t smem = (size_t)kWarps * STAGES * State::Pool::STAGE_BYTES +
                         sizeof(float) * ((size_t)kWarps * p.n_rep * kMergeStride + 2 * kWarps * kRP) +
-                        sizeof(int) * ((size_t)kWarps * STAGES + kWarps + p.batch + 1);
+                        sizeof(int) * ((size_t)kWarps * STAGES + kWarps + 1 + p.batch + 1);
     auto kern = decode_kernel<State, MODE, STAGES>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
     kern<<<dim3(p.num_chunks, p.heads), kThreads, smem, stream>>>(p);
-    return (int)cudaGetLastError();
-}
-
-static int run_merge(const DecodeParams& p, void* out, long long so_b, long long so_h, long long so_m,
-                     cudaStream_t stream) {
-    if (!out) return LS_OK;
-    merge_kernel<<<dim3(p.batch, p.heads), LS_HEAD_DIM, 0, stream>>>(
-        p.part_acc, p.part_m, p.part_l, p.seg_range, static_cast<__half*>(out), p.heads, p.n_rep, so_b,
-        so_h, so_m);
     return (int)cudaGetLastError();
 }
 
@@ -850,6 +888,8 @@ int ls_paged_decode_fp16(const void* q, const void* k_pool, const void* v_pool,
     p.part_m = part_m;
     p.part_l = part_l;
     p.seg_range = seg_range;
+    p.out = static_cast<__half*>(out);
+    p.so_b = so_b; p.so_h = so_h; p.so_m = so_m;
     p.batch = batch;
     p.heads = kv_heads;
     p.n_rep = n_rep;
@@ -875,8 +915,7 @@ int ls_paged_decode_fp16(const void* q, const void* k_pool, const void* v_pool,
     } else {
         return LS_ERR_UNSUPPORTED;
     }
-    if (rc) return rc;
-    return ls::run_merge(p, out, so_b, so_h, so_m, s);
+    return rc;
 }
 
 int ls_paged_sparse_fp16(const void* q, const void* k_pool, const void* v_pool,
@@ -906,6 +945,8 @@ int ls_paged_sparse_fp16(const void* q, const void* k_pool, const void* v_pool,
     p.part_m = part_m;
     p.part_l = part_l;
     p.seg_range = seg_range;
+    p.out = static_cast<__half*>(out);
+    p.so_b = so_b; p.so_h = so_h; p.so_m = so_m;
     p.batch = batch;
     p.heads = kv_heads;
     p.n_rep = n_rep;
@@ -922,8 +963,7 @@ int ls_paged_sparse_fp16(const void* q, const void* k_pool, const void* v_pool,
     if (rc) return rc;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     rc = ls::launch_decode<ls::MmaFp16, LS_MODE_SPARSE, 3>(p, s);
-    if (rc) return rc;
-    return ls::run_merge(p, out, so_b, so_h, so_m, s);
+    return rc;
 }
 
 int ls_paged_decode_int8(const void* q, const void* k_pool, const void* v_pool,
@@ -959,6 +999,8 @@ int ls_paged_decode_int8(const void* q, const void* k_pool, const void* v_pool,
     p.part_m = part_m;
     p.part_l = part_l;
     p.seg_range = seg_range;
+    p.out = static_cast<__half*>(out);
+    p.so_b = so_b; p.so_h = so_h; p.so_m = so_m;
     p.batch = batch;
     p.heads = kv_heads;
     p.n_rep = n_rep;
@@ -987,8 +1029,7 @@ int ls_paged_decode_int8(const void* q, const void* k_pool, const void* v_pool,
         rc = ls::launch_decode<ls::MmaInt8<1>, LS_MODE_DENSE, 3>(p, s);
     else
         rc = ls::launch_decode<ls::MmaInt8<0>, LS_MODE_DENSE, 3>(p, s);
-    if (rc) return rc;
-    return ls::run_merge(p, out, so_b, so_h, so_m, s);
+    return rc;
 }
 
 int ls_combine(const float* part_acc, const float* part_m, const float* part_l,

@@ -37,7 +37,7 @@ def append_fp16(k: torch.Tensor, v: torch.Tensor, slots: torch.Tensor, flat_k: t
         raise RuntimeError("latentserve_b200 has no CPU path: tensors must be on a CUDA device")
     kr, vr = _rows(k), _rows(v)
     b, h, d = kr.shape
-    if slots.dtype != torch.int64 or slots.numel() < b or slots.stride(-1) != 1:
+    if slots.dtype != torch.int64 or slots.numel() < b or (slots.numel() > 1 and slots.stride(-1) != 1):
         raise ValueError("slots must be a contiguous int64 vector with one entry per sequence")
     if flat_k.stride() != flat_v.stride() or flat_k.stride(-1) != 1:
         raise ValueError("K and V pools must share one layout with unit-stride channels")

@@ -102,20 +102,27 @@ def choose_splits(batch: int, kv_heads: int, num_pages: int) -> int:
     return max(1, min(num_pages, 128))
 
 
+def seg_len(batch: int, kv_heads: int) -> int:
+    """int32 entries of the bookkeeping scratch: per-sequence slot ranges, the
+    error flag, and one arrival counter per (sequence, KV head)."""
+    return 2 * batch + 2 + batch * kv_heads
+
+
 def _partials(q: torch.Tensor, chunks: int, tag: str):
     b, h = q.shape[0], q.shape[1]
     slots = b + chunks
     acc = scratch(tag + "_acc", (slots, h, ROWS_PER_PARTIAL, 128), torch.float32, q.device)
     m = scratch(tag + "_m", (slots, h, ROWS_PER_PARTIAL), torch.float32, q.device)
     l = scratch(tag + "_l", (slots, h, ROWS_PER_PARTIAL), torch.float32, q.device)
-    seg = scratch(tag + "_seg", (2 * MAX_BATCH + 2,), torch.int32, q.device, zero=True)
+    seg = scratch(tag + "_seg", (seg_len(b, h),), torch.int32, q.device, zero=True)
     return acc, m, l, seg
 
 
-def error_flag(device, batch: int, tag: str = "cuda") -> int:
+def error_flag(device, batch: int, kv_heads: int = 2, tag: str = "cuda") -> int:
     """1 if a launch at this batch size met a block id (or residual row)
     outside its pool and skipped it. Reading it synchronises; for tests."""
-    seg = _SCRATCH.get((tag + "_seg", (2 * MAX_BATCH + 2,), torch.int32, str(torch.device(device))))
+    seg = _SCRATCH.get((tag + "_seg", (seg_len(batch, kv_heads),), torch.int32,
+                        str(torch.device(device))))
     return 0 if seg is None else int(seg[2 * batch].item())
 
 
@@ -132,7 +139,7 @@ def paged_decode_cuda(q, k_pool, v_pool, block_tables, seq_lens, max_seq_len: in
     `max_seq_len` and `min_blocks` are accepted for signature parity; extents
     come from `seq_lens` on the device. The returned tensor is persistent
     scratch, valid until the next call with the same shapes. `merge=False`
-    launches the partial kernel alone (for timing it) and returns None.
+    stops at the partial states (no output is written) and returns None.
     """
     if not q.is_cuda:
         raise RuntimeError("latentserve_b200 has no CPU path: tensors must be on a CUDA device")
@@ -141,7 +148,7 @@ def paged_decode_cuda(q, k_pool, v_pool, block_tables, seq_lens, max_seq_len: in
         raise ValueError("the CUDA kernel needs unit-stride head dims and matching K/V pools")
     if block_tables.dtype != torch.int32 or seq_lens.dtype != torch.int32:
         raise ValueError("block tables and sequence lengths must be int32")
-    if block_tables.stride(-1) != 1 or seq_lens.stride(0) != 1:
+    if block_tables.stride(-1) != 1 or (seq_lens.numel() > 1 and seq_lens.stride(0) != 1):
         raise ValueError("block tables and sequence lengths must be contiguous rows")
     scale = softmax_scale if softmax_scale is not None else 1.0 / math.sqrt(d)
     chunks = choose_chunks(q.device, h_kv, num_splits, b)

@@ -96,3 +96,69 @@ def kv_bytes_int8(lens, h=2, d=128) -> int:
         x = int(x)
         total += x * h * (d + d + 4) + (-(-x // PAGE)) * h * d * 4
     return total
+
+
+def int8_pools_on_device(lens, layers, device, h=2, d=128, n_rep=6, slack=1.2, seed=0):
+    """INT8 pools for a ragged batch, produced the way a serving cache produces
+    them: N(0,1) fp16 K/V pushed through this library's quantize-on-write kernel
+    (V, per token) and page-finalize kernel (K, per completed page); each
+    sequence's last page of K stays exact in an fp16 residual row."""
+    import torch
+
+    from latentserve_b200 import int8_write as iw
+
+    g = torch.Generator(device=device).manual_seed(seed)
+    lens = [int(x) for x in lens]
+    batch = len(lens)
+    pages = [-(-x // PAGE) for x in lens]
+    width = max(pages)
+    nb = int(np.ceil(slack * sum(pages)))
+    perm = torch.randperm(nb, device=device, generator=g)
+    tables = torch.zeros((batch, width), dtype=torch.int32, device=device)
+    at = 0
+    for i, n in enumerate(pages):
+        tables[i, :n] = perm[at:at + n].to(torch.int32)
+        at += n
+    consts = dict(eps=1e-8, qmax=127.0, levels=255.0, offset=128.0)
+    out = []
+    chunk = 2048                                     # blocks quantised per kernel call
+    for _ in range(layers):
+        k_pool = torch.zeros((nb, PAGE, h, d), dtype=torch.int8, device=device)
+        v_pool = torch.zeros_like(k_pool)
+        k_scale = torch.ones((nb, h, d), dtype=torch.float32, device=device)
+        v_scale = torch.ones((nb, PAGE, h), dtype=torch.float32, device=device)
+        residual = torch.randn((batch, PAGE, h, d), dtype=torch.float16, device=device, generator=g)
+        scratch_res = torch.empty((chunk * PAGE, h, d), dtype=torch.float16, device=device)
+        for lo in range(0, nb, chunk):
+            n = min(chunk, nb - lo)
+            ids = torch.arange(lo, lo + n, device=device)
+            data = torch.randn((n, PAGE, h, d), dtype=torch.float16, device=device, generator=g)
+            iw.finalize_blocks(data, torch.arange(n, device=device), ids, k_pool, k_scale, None, **consts)
+            vals = torch.randn((n * PAGE, h, 1, d), dtype=torch.float16, device=device, generator=g)
+            slots = torch.arange(lo * PAGE, (lo + n) * PAGE, device=device)
+            iw.decode_write(vals, vals, slots, torch.arange(n * PAGE, device=device),
+                            v_pool.view(-1, h, d), v_scale.view(-1, h), None, scratch_res,
+                            asym=False, **consts)
+        out.append(dict(k_pool=k_pool, v_pool=v_pool, k_scale=k_scale, v_scale=v_scale,
+                        k_residual=residual))
+    q = torch.randn((layers, batch, h, n_rep, d), dtype=torch.float16, device=device, generator=g)
+    return {"q": q, "layers": out, "block_tables": tables,
+            "seq_lens": torch.tensor(lens, dtype=torch.int32, device=device),
+            "res_rows": torch.arange(batch, dtype=torch.int32, device=device), "num_blocks": nb}
+
+
+def sparse_pools_on_device(batch, context, layers, device, h=2, d=128, n_rep=6, slack=1.2, seed=0,
+                           offset_std=0.5):
+    """fp16 pools whose K carries a per-(page, head) mean offset, so page scores
+    are well separated, plus the per-page K bounds the indexer reads."""
+    import torch
+
+    w = dense_pools_on_device(batch, context, layers, device, n_rep, h, d, slack, seed)
+    g = torch.Generator(device=device).manual_seed(seed + 1)
+    bounds = []
+    for k, _ in w["pools"]:
+        off = torch.randn((k.shape[0], 1, h, d), dtype=torch.float16, device=device, generator=g)
+        k.add_(off * offset_std)
+        bounds.append((k.amin(dim=1), k.amax(dim=1)))
+    w["bounds"] = bounds
+    return w
