@@ -53,6 +53,8 @@ def build(force: bool = False, verbose: bool = False, ptxas_verbose: bool = Fals
            *ARCH_FLAGS, "-I", str(CSRC)]
     if ptxas_verbose:
         cmd += ["-Xptxas", "-v"]
+    # Developer knob for tuning runs, e.g. LS_NVCC_EXTRA='-DLS_STAGES=2'.
+    cmd += os.environ.get("LS_NVCC_EXTRA", "").split()
     cmd += [str(s) for s in sources()] + ["-o", str(LIB)]
     if verbose:
         print(" ".join(cmd), file=sys.stderr)

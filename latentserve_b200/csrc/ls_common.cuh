@@ -14,6 +14,12 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+// L2 prefetch granularity asked of the 16-byte page loads (rows are 256 B
+// contiguous for fp16 pools, 128 B for INT8 pools).
+#ifndef LS_CP_L2_HINT
+#define LS_CP_L2_HINT ".L2::128B"
+#endif
+
 #define LS_HEAD_DIM 128
 #define LS_PAGE 16
 #define LS_FULL_MASK 0xffffffffu
@@ -42,7 +48,7 @@ __device__ __forceinline__ uint32_t smem_u32(const void* p) {
 // and reads nothing, which is how rows past a sequence's end are kept free of
 // whatever bit patterns (NaN included) the pool holds there.
 __device__ __forceinline__ void cp_async_16(uint32_t dst, const void* src, int src_bytes) {
-    asm volatile("cp.async.cg.shared.global.L2::128B [%0], [%1], 16, %2;\n" ::"r"(dst), "l"(src),
+    asm volatile("cp.async.cg.shared.global" LS_CP_L2_HINT " [%0], [%1], 16, %2;\n" ::"r"(dst), "l"(src),
                  "r"(src_bytes)
                  : "memory");
 }

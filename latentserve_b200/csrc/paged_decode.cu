@@ -42,7 +42,11 @@ namespace ls {
 #define LS_IMPL_MMA 0
 #define LS_IMPL_SIMT 1
 
+#ifndef LS_STAGES
+#define LS_STAGES 3                 // cp.async ring depth per warp
+#endif
 constexpr int kWarps = 4;
+constexpr int kStages = LS_STAGES;
 constexpr int kThreads = kWarps * 32;
 constexpr int kMergeStride = LS_HEAD_DIM + 4;   // floats per merged row (bank-conflict pad)
 constexpr int kRP = 8;                          // query rows held per partial
@@ -653,27 +657,53 @@ struct MmaInt8 {
 // Merge of a sequence's partials:
 //   out = sum_s acc_s 2^(m_s - M) / max(sum_s l_s 2^(m_s - M), 1e-20),
 // the reference combine (kernels/gqa/paged_decode.py:421-471, torch form
-// :689-706) with m held in the log2 domain. Called by 128 threads (thread =
-// head dim); loads bypass L1 because other CTAs of the same launch may have
-// written the partials.
+// :689-706) with m held in the log2 domain. Called by the 4 warps of a CTA:
+// warp w takes query rows w, w + 4; lane s holds partial s's (m, l) and weight,
+// and the 32 lanes cover the 128 dims as float4, so a row of one partial is one
+// coalesced 512-byte load and the loads of a row's partials are independent
+// (issued back to back, not one L2 round trip after another). Loads bypass L1
+// because other CTAs of the same launch may have written the partials.
 __device__ __forceinline__ void merge_partials(const float* part_acc, const float* part_m,
                                                const float* part_l, int first, int count,
                                                __half* out, int heads, int n_rep, int b, int h,
-                                               int d, long long so_b, long long so_h,
+                                               int tid, long long so_b, long long so_h,
                                                long long so_m) {
-    for (int r = 0; r < n_rep; ++r) {
+    const int warp = tid >> 5, lane = tid & 31;
+    for (int r = warp; r < n_rep; r += kWarps) {
+        const long long row0 = ((long long)first * heads + h) * kRP + r;
+        const long long step = (long long)heads * kRP;               // rows between partials
         float mg = neg_inf();
-        for (int s = 0; s < count; ++s)
-            mg = fmaxf(mg, __ldcg(part_m + ((long long)(first + s) * heads + h) * kRP + r));
+        for (int s = lane; s < count; s += 32) mg = fmaxf(mg, __ldcg(part_m + row0 + s * step));
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1)
+            mg = fmaxf(mg, __shfl_xor_sync(LS_FULL_MASK, mg, off));
         const float ms = (mg == neg_inf()) ? 0.f : mg;
-        float lsum = 0.f, a = 0.f;
-        for (int s = 0; s < count; ++s) {
-            const long long row = ((long long)(first + s) * heads + h) * kRP + r;
-            const float w = ex2(__ldcg(part_m + row) - ms);
-            lsum += w * __ldcg(part_l + row);
-            a += w * __ldcg(part_acc + row * LS_HEAD_DIM + d);
+        float lsum = 0.f;
+        float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int s0 = 0; s0 < count; s0 += 32) {
+            const int s = s0 + lane;
+            float w = 0.f;
+            if (s < count) {
+                w = ex2(__ldcg(part_m + row0 + s * step) - ms);
+                lsum += w * __ldcg(part_l + row0 + s * step);
+            }
+            const int n = min(32, count - s0);
+            const float4* src =
+                reinterpret_cast<const float4*>(part_acc + (row0 + s0 * step) * LS_HEAD_DIM) + lane;
+#pragma unroll 8
+            for (int j = 0; j < n; ++j) {
+                const float wj = __shfl_sync(LS_FULL_MASK, w, j);
+                const float4 v = __ldcg(src + j * step * (LS_HEAD_DIM / 4));
+                a.x += wj * v.x; a.y += wj * v.y; a.z += wj * v.z; a.w += wj * v.w;
+            }
         }
-        out[b * so_b + h * so_h + r * so_m + d] = __float2half_rn(a / fmaxf(lsum, 1e-20f));
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) lsum += __shfl_xor_sync(LS_FULL_MASK, lsum, off);
+        const float inv = 1.f / fmaxf(lsum, 1e-20f);
+        uint2 packed;
+        packed.x = pack_half2(a.x * inv, a.y * inv);
+        packed.y = pack_half2(a.z * inv, a.w * inv);
+        *reinterpret_cast<uint2*>(out + b * so_b + h * so_h + r * so_m + lane * 4) = packed;
     }
 }
 
@@ -839,6 +869,8 @@ static int validate_common(const DecodeParams& p) {
     if (p.n_rep > kRP) return LS_ERR_UNSUPPORTED;
     if ((reinterpret_cast<uintptr_t>(p.q) & 15) || (p.sq_b % 8) || (p.sq_h % 8) || (p.sq_m % 8))
         return LS_ERR_MISALIGNED;
+    if (p.out && ((reinterpret_cast<uintptr_t>(p.out) & 7) || (p.so_b % 4) || (p.so_h % 4) || (p.so_m % 4)))
+        return LS_ERR_MISALIGNED;
     return LS_OK;
 }
 
@@ -907,11 +939,11 @@ int ls_paged_decode_fp16(const void* q, const void* k_pool, const void* v_pool,
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     if (impl == LS_IMPL_SIMT) {
         if (n_rep <= 6)
-            rc = ls::launch_decode<ls::SimtFp16<6>, LS_MODE_DENSE, 3>(p, s);
+            rc = ls::launch_decode<ls::SimtFp16<6>, LS_MODE_DENSE, ls::kStages>(p, s);
         else
-            rc = ls::launch_decode<ls::SimtFp16<8>, LS_MODE_DENSE, 3>(p, s);
+            rc = ls::launch_decode<ls::SimtFp16<8>, LS_MODE_DENSE, ls::kStages>(p, s);
     } else if (impl == LS_IMPL_MMA) {
-        rc = ls::launch_decode<ls::MmaFp16, LS_MODE_DENSE, 3>(p, s);
+        rc = ls::launch_decode<ls::MmaFp16, LS_MODE_DENSE, ls::kStages>(p, s);
     } else {
         return LS_ERR_UNSUPPORTED;
     }
@@ -962,7 +994,7 @@ int ls_paged_sparse_fp16(const void* q, const void* k_pool, const void* v_pool,
     rc = check_pool_fp16(p);
     if (rc) return rc;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    rc = ls::launch_decode<ls::MmaFp16, LS_MODE_SPARSE, 3>(p, s);
+    rc = ls::launch_decode<ls::MmaFp16, LS_MODE_SPARSE, ls::kStages>(p, s);
     return rc;
 }
 
@@ -1026,9 +1058,9 @@ int ls_paged_decode_int8(const void* q, const void* k_pool, const void* v_pool,
         return LS_ERR_MISALIGNED;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     if (k_zero)
-        rc = ls::launch_decode<ls::MmaInt8<1>, LS_MODE_DENSE, 3>(p, s);
+        rc = ls::launch_decode<ls::MmaInt8<1>, LS_MODE_DENSE, ls::kStages>(p, s);
     else
-        rc = ls::launch_decode<ls::MmaInt8<0>, LS_MODE_DENSE, 3>(p, s);
+        rc = ls::launch_decode<ls::MmaInt8<0>, LS_MODE_DENSE, ls::kStages>(p, s);
     return rc;
 }
 
@@ -1038,6 +1070,8 @@ int ls_combine(const float* part_acc, const float* part_m, const float* part_l,
     if (!part_acc || !part_m || !part_l || !seg_range || !out) return LS_ERR_NULL_POINTER;
     if (batch <= 0 || kv_heads <= 0 || n_rep <= 0 || n_rep > ls::kRP) return LS_ERR_BAD_SHAPE;
     if (kv_heads > 65535) return LS_ERR_TOO_LARGE;
+    if ((reinterpret_cast<uintptr_t>(out) & 7) || (so_b % 4) || (so_h % 4) || (so_m % 4))
+        return LS_ERR_MISALIGNED;
     ls::merge_kernel<<<dim3(batch, kv_heads), LS_HEAD_DIM, 0, static_cast<cudaStream_t>(stream)>>>(
         part_acc, part_m, part_l, seg_range, static_cast<__half*>(out), kv_heads, n_rep, so_b, so_h,
         so_m);
