@@ -32,6 +32,8 @@ extern "C" {
 #define LS_ERR_TOO_LARGE (-5)
 #define LS_ERR_UNSUPPORTED (-6)
 #define LS_ERR_SCRATCH_TOO_SMALL (-7)
+#define LS_ERR_NOALLOC_LIMIT (-8) /* ls_paged_decode_fp16_noalloc: shape past its fixed scratch */
+#define LS_NOALLOC_SCRATCH_BYTES 4264704
 
 #define LS_IMPL_MMA 0  /* tensor-core kernel (the product path) */
 #define LS_IMPL_SIMT 1 /* CUDA-core kernel, fp16 pools only (kept for profiling) */
@@ -78,6 +80,32 @@ int ls_paged_decode_fp16(const void* q, const void* k_pool, const void* v_pool,
                          int64_t sq_h, int64_t sq_m, int64_t sk_b, int64_t sk_p, int64_t sk_h,
                          int64_t so_b, int64_t so_h, int64_t so_m, float softmax_scale,
                          void* stream);
+
+/* Dense fp16 decode for callers that cannot allocate device memory. No
+ * counterpart in the reference (its scratch comes from torch's allocator,
+ * kernels/gqa/paged_decode.py:501-517, and every caller there has one).
+ *
+ * Same computation and arguments as ls_paged_decode_fp16 with the tensor-core
+ * kernel, minus the four scratch pointers: the partial states live in a fixed
+ * array inside the library image (LS_NOALLOC_SCRATCH_BYTES, about 4.1 MiB of
+ * device memory on every GPU that loads the library, held until exit). Meant
+ * for hosts that reach this ABI through an FFI and own no device allocator,
+ * and for processes that gave all device memory away at start-up, where a
+ * cudaMalloc on the decode path may fail and stalls the device while it runs.
+ *   Limits: batch <= 64 and (batch + num_chunks) * kv_heads <= 1024, else
+ *   LS_ERR_NOALLOC_LIMIT and nothing is launched. `out` is required.
+ *   The first call on a device resolves the array's device address
+ *   (cudaGetSymbolAddress, with that device current): make it before any
+ *   stream capture starts. Calls share the array: its bookkeeping part is
+ *   cleared on `stream` at the start of every call, and calls whose kernels
+ *   overlap on one GPU race — keep them ordered. Allocates nothing. */
+int ls_paged_decode_fp16_noalloc(const void* q, const void* k_pool, const void* v_pool,
+                                 const int32_t* block_tables, const int32_t* seq_lens, void* out,
+                                 int batch, int kv_heads, int n_rep, int head_dim, int page,
+                                 int max_pages, int num_blocks, int num_chunks, int min_chunk,
+                                 int64_t sq_b, int64_t sq_h, int64_t sq_m, int64_t sk_b, int64_t sk_p,
+                                 int64_t sk_h, int64_t so_b, int64_t so_h, int64_t so_m,
+                                 float softmax_scale, void* stream);
 
 /* INT8 paged GQA decode attention.
  * Replaces kernels/cuda/paged_decode_int8.cu:87-280 (kernel `paged_decode_int8`,

@@ -26,6 +26,8 @@ STATUS = {
     -5: "size past what the kernel supports",
     -6: "unsupported configuration (needs head_dim 128, page 16, <= 8 query rows per KV head)",
     -7: "scratch buffer too small",
+    -8: "shape past the fixed scratch of the allocation-free entry point "
+        "(needs batch <= 64 and (batch + num_chunks) * kv_heads <= 1024)",
 }
 
 P, I, L, F = c_void_p, c_int, c_int64, c_float
@@ -35,6 +37,7 @@ _PROTOTYPES = {
     "ls_paged_decode_fp16": [P, P, P, P, P, P, P, P, P, P] + [I] * 10 + [L] * 9 + [F, P],
     "ls_paged_sparse_fp16": [P, P, P, P, P, P, F, I, P, P, P, P, P] + [I] * 10 + [L] * 11 + [F, P],
     "ls_paged_decode_int8": [P] * 16 + [I] * 10 + [L] * 17 + [F, P],
+    "ls_paged_decode_fp16_noalloc": [P, P, P, P, P, P] + [I] * 9 + [L] * 9 + [F, P],
     "ls_combine": [P, P, P, P, P, I, I, I, L, L, L, P],
     "ls_kv_append_fp16": [P, P, P, P, P, P, P, I, I, I, I] + [L] * 9 + [P],
     "ls_int8_decode_write": [P, P, P, P, P, P, P, P, I, I, I] + [L] * 6 + [I] + [F] * 6 + [P],

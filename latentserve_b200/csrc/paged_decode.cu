@@ -37,6 +37,8 @@
 //     the fp16 output, so a layer call is ONE launch.
 #include "decode_sched.cuh"
 
+#include <mutex>
+
 namespace ls {
 
 #define LS_IMPL_MMA 0
@@ -1076,6 +1078,135 @@ int ls_combine(const float* part_acc, const float* part_m, const float* part_l,
         part_acc, part_m, part_l, seg_range, static_cast<__half*>(out), kv_heads, n_rep, so_b, so_h,
         so_m);
     return (int)cudaGetLastError();
+}
+
+}  // extern "C"
+
+// ---------------------------------------------------------------------------
+// ls_paged_decode_fp16_noalloc: dense fp16 decode for callers that cannot
+// allocate device memory.
+//
+// Who that is: a host that embeds this library from C, Go or Java through its
+// foreign-function interface and owns no device allocator of its own; or a
+// serving process whose device memory was handed out in full at start-up (KV
+// pools sized to fill the GPU), where a later cudaMalloc can simply fail, and
+// would in any case stall every stream of the device while it runs. Such a
+// caller can still provide its inputs and its output, but has nowhere to put
+// the partial softmax states the split-KV kernel needs between its CTAs.
+//
+// This entry point keeps that scratch inside the library image instead: a
+// fixed array in device global memory, LS_NOALLOC_SCRATCH_BYTES (about 4.1 MiB)
+// on every GPU that loads the library, held until the process exits. The price
+// of a fixed array is a fixed ceiling:
+//     batch <= LS_NOALLOC_MAX_BATCH (64)   and
+//     (batch + num_chunks) * kv_heads <= LS_NOALLOC_MAX_ROWS (1024);
+// anything larger is refused with LS_ERR_NOALLOC_LIMIT and nothing is launched.
+//
+// The array's name is only a handle on the host side, not a device address.
+// The first call on each device (with that device current) asks the runtime
+// for the address with cudaGetSymbolAddress and remembers it; make that first
+// call before any stream capture begins. Every later call does no set-up.
+//
+// All calls on a device share the one array, and it keeps whatever the last
+// call left in it. The bookkeeping part (slot ranges, error flag, arrival
+// counters, whose positions depend on the batch size) is therefore cleared on
+// the caller's stream at the start of every call; the partial states need no
+// clearing because every slot that is read has been written by the same
+// launch. Two calls whose kernels overlap on the GPU (different streams, no
+// ordering between them) race on the array: keep calls on one device ordered.
+//
+// No cudaMalloc, cudaFree or allocating library routine is called here.
+#define LS_NOALLOC_MAX_BATCH 64
+#define LS_NOALLOC_MAX_ROWS 1024
+#define LS_ERR_NOALLOC_LIMIT (-8)
+
+namespace ls {
+
+constexpr size_t kNaAccBytes = (size_t)LS_NOALLOC_MAX_ROWS * kRP * LS_HEAD_DIM * sizeof(float);
+constexpr size_t kNaMlBytes = (size_t)LS_NOALLOC_MAX_ROWS * kRP * sizeof(float);
+constexpr size_t kNaSegInts = 2 * LS_NOALLOC_MAX_BATCH + 2 + LS_NOALLOC_MAX_ROWS;
+constexpr size_t kNaSegBytes = (kNaSegInts * sizeof(int) + 255) / 256 * 256;
+constexpr size_t kNaTotalBytes = kNaAccBytes + 2 * kNaMlBytes + kNaSegBytes;
+
+static_assert(kNaTotalBytes == 4264704, "keep LS_NOALLOC_SCRATCH_BYTES in the header in step");
+
+static __device__ __align__(256) unsigned char g_noalloc_scratch[kNaTotalBytes];
+
+constexpr int kMaxDevices = 64;
+static std::mutex g_noalloc_mutex;
+static unsigned char* g_noalloc_base[kMaxDevices] = {};
+
+// Device address of the scratch array on the current device (looked up once).
+static int noalloc_scratch_base(unsigned char** base) {
+    int dev = -1;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return (int)e;
+    if (dev < 0 || dev >= kMaxDevices) return LS_ERR_UNSUPPORTED;
+    std::lock_guard<std::mutex> lock(g_noalloc_mutex);
+    if (g_noalloc_base[dev] == nullptr) {
+        unsigned char* ptr = nullptr;
+        e = cudaGetSymbolAddress((void**)&ptr, g_noalloc_scratch);
+        if (e != cudaSuccess) return (int)e;
+        if (ptr == nullptr) return LS_ERR_NULL_POINTER;
+        g_noalloc_base[dev] = ptr;
+    }
+    *base = g_noalloc_base[dev];
+    return LS_OK;
+}
+
+}  // namespace ls
+
+extern "C" {
+
+int ls_paged_decode_fp16_noalloc(const void* q, const void* k_pool, const void* v_pool,
+                                 const int32_t* block_tables, const int32_t* seq_lens, void* out,
+                                 int batch, int kv_heads, int n_rep, int head_dim, int page,
+                                 int max_pages, int num_blocks, int num_chunks, int min_chunk,
+                                 int64_t sq_b, int64_t sq_h, int64_t sq_m, int64_t sk_b, int64_t sk_p,
+                                 int64_t sk_h, int64_t so_b, int64_t so_h, int64_t so_m,
+                                 float softmax_scale, void* stream) {
+    if (head_dim != LS_HEAD_DIM || page != LS_PAGE) return LS_ERR_UNSUPPORTED;
+    if (!out) return LS_ERR_NULL_POINTER;
+    if (batch <= 0 || kv_heads <= 0 || num_chunks <= 0) return LS_ERR_BAD_SHAPE;
+    if (batch > LS_NOALLOC_MAX_BATCH ||
+        ((long long)batch + num_chunks) * kv_heads > LS_NOALLOC_MAX_ROWS)
+        return LS_ERR_NOALLOC_LIMIT;
+    unsigned char* base = nullptr;
+    int rc = ls::noalloc_scratch_base(&base);
+    if (rc) return rc;
+    DecodeParams p = {};
+    p.q = static_cast<const __half*>(q);
+    p.k_pool = k_pool;
+    p.v_pool = v_pool;
+    p.block_tables = block_tables;
+    p.seq_lens = seq_lens;
+    p.part_acc = reinterpret_cast<float*>(base);
+    p.part_m = reinterpret_cast<float*>(base + ls::kNaAccBytes);
+    p.part_l = reinterpret_cast<float*>(base + ls::kNaAccBytes + ls::kNaMlBytes);
+    p.seg_range = reinterpret_cast<int*>(base + ls::kNaAccBytes + 2 * ls::kNaMlBytes);
+    p.out = static_cast<__half*>(out);
+    p.so_b = so_b; p.so_h = so_h; p.so_m = so_m;
+    p.batch = batch;
+    p.heads = kv_heads;
+    p.n_rep = n_rep;
+    p.max_pages = max_pages;
+    p.num_blocks = num_blocks;
+    p.num_chunks = num_chunks;
+    p.min_chunk = min_chunk;
+    p.sq_b = sq_b; p.sq_h = sq_h; p.sq_m = sq_m;
+    p.sk_b = sk_b; p.sk_p = sk_p; p.sk_h = sk_h;
+    p.scale_log2 = softmax_scale * 1.4426950408889634f;
+    rc = ls::validate_common(p);
+    if (rc) return rc;
+    rc = check_pool_fp16(p);
+    if (rc) return rc;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    // Bookkeeping of the previous call (possibly another batch size) must not
+    // be mistaken for this call's arrival counters.
+    const size_t seg_bytes = sizeof(int) * (2 * (size_t)batch + 2 + (size_t)batch * kv_heads);
+    cudaError_t e = cudaMemsetAsync(p.seg_range, 0, seg_bytes, s);
+    if (e != cudaSuccess) return (int)e;
+    return ls::launch_decode<ls::MmaFp16, LS_MODE_DENSE, ls::kStages>(p, s);
 }
 
 }  // extern "C"
