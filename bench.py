@@ -48,7 +48,9 @@ WORKLOADS = {
     # name: (batch, context, layers); the first is the benchmark, the rest exist for
     # profiler captures and for the other kernels of the path.
     "dense_fp16_b16_16k": (16, 16384, 28),
-    "dense_fp16_b16_4k": (16, 4096, 8),        # small case for profiler captures
+    "dense_fp16_b16_4k": (16, 4096, 8),        # small cases for profiler captures
+    "dense_fp16_b16_8k": (16, 8192, 8),
+    "int8_b32_8k": (32, 8192, 8),
     "dense_fp16_b64_ragged": (64, "loguniform_1k_32k", 8),
     "int8_b32_8k_32k": (32, "uniform_8k_32k", 8),
     "int8_b16_4k": (16, 4096, 8),              # small case for profiler captures
@@ -192,6 +194,8 @@ def main():
                     help="split-KV kernel variant (simt = CUDA-core kernel, for profiling)")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--no-pdl", action="store_true",
+                    help="ordinary launches instead of programmatic dependent launch")
     ap.add_argument("--quick", action="store_true",
                     help="profiler runs: no e2e / CPU legs, no extension of the load for clock sampling")
     args = ap.parse_args()
@@ -211,6 +215,7 @@ def main():
     if not torch.cuda.is_available():
         raise SystemExit("bench.py measures the CUDA path and there is no CUDA device")
     _lib.lib()                                    # fail here, loudly, if the library is missing
+    pdc.set_programmatic_launch(not args.no_pdl)
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
@@ -377,6 +382,7 @@ def main():
                        f"{context}: min {min(seq_lens)}, mean {int(np.mean(seq_lens))}, max {max(seq_lens)}",
                        "layers_per_step": layers, "q_heads": 12, "kv_heads": 2, "head_dim": 128,
                        "page": 16, "pool_blocks": w["num_blocks"], "kernel": args.kernel,
+                       "programmatic_launch": not args.no_pdl,
                        "parallelism": f"replicas x{world} (sequence-sharded, no collective)",
                        "l2": f"no flush: each step reads {step_bytes / 1e9:.2f} GB, L2 is 126 MB",
                        "step": f"{layers} layer calls (one launch each) replayed from one CUDA graph"},

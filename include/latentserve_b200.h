@@ -35,8 +35,16 @@ extern "C" {
 #define LS_ERR_NOALLOC_LIMIT (-8) /* ls_paged_decode_fp16_noalloc: shape past its fixed scratch */
 #define LS_NOALLOC_SCRATCH_BYTES 4264704
 
+/* `flags` of the decode entry points. The low byte of ls_paged_decode_fp16's
+ * flags picks the kernel variant. */
 #define LS_IMPL_MMA 0  /* tensor-core kernel (the product path) */
 #define LS_IMPL_SIMT 1 /* CUDA-core kernel, fp16 pools only (kept for profiling) */
+/* Launch with programmatic stream serialization: the kernel may be scheduled
+ * while the previous kernel of the stream is still draining, and it reads
+ * seq_lens and block_tables (nothing else) before it synchronises on that
+ * kernel. Only set it when the kernel launched just before on the stream does
+ * not write seq_lens or block_tables (in LatentServe it is the KV append). */
+#define LS_LAUNCH_PROGRAMMATIC 0x100
 
 /* Partial-state scratch shared by the three decode entry points.
  *
@@ -76,7 +84,7 @@ int ls_paged_decode_fp16(const void* q, const void* k_pool, const void* v_pool,
                          const int32_t* block_tables, const int32_t* seq_lens, float* part_acc,
                          float* part_m, float* part_l, int32_t* seg_range, void* out, int batch,
                          int kv_heads, int n_rep, int head_dim, int page, int max_pages,
-                         int num_blocks, int num_chunks, int min_chunk, int impl, int64_t sq_b,
+                         int num_blocks, int num_chunks, int min_chunk, int flags, int64_t sq_b,
                          int64_t sq_h, int64_t sq_m, int64_t sk_b, int64_t sk_p, int64_t sk_h,
                          int64_t so_b, int64_t so_h, int64_t so_m, float softmax_scale,
                          void* stream);
@@ -120,11 +128,11 @@ int ls_paged_decode_int8(const void* q, const void* k_pool, const void* v_pool,
                          const void* k_res, const int32_t* res_rows, float* part_acc, float* part_m,
                          float* part_l, int32_t* seg_range, void* out, int batch, int kv_heads,
                          int n_rep, int head_dim, int page, int max_pages, int num_blocks,
-                         int num_res_rows, int num_chunks, int min_chunk, int64_t sq_b, int64_t sq_h,
-                         int64_t sq_m, int64_t sk_b, int64_t sk_p, int64_t sk_h, int64_t ks_b,
-                         int64_t ks_h, int64_t vs_b, int64_t vs_p, int64_t vs_h, int64_t sr_r,
-                         int64_t sr_p, int64_t sr_h, int64_t so_b, int64_t so_h, int64_t so_m,
-                         float softmax_scale, void* stream);
+                         int num_res_rows, int num_chunks, int min_chunk, int flags, int64_t sq_b,
+                         int64_t sq_h, int64_t sq_m, int64_t sk_b, int64_t sk_p, int64_t sk_h,
+                         int64_t ks_b, int64_t ks_h, int64_t vs_b, int64_t vs_p, int64_t vs_h,
+                         int64_t sr_r, int64_t sr_p, int64_t sr_h, int64_t so_b, int64_t so_h,
+                         int64_t so_m, float softmax_scale, void* stream);
 
 /* Attention over selected pages only.
  * Replaces kernels/cuda/paged_sparse_fp16.cu:205-364 (kernel `paged_sparse_fp16`)
@@ -138,9 +146,9 @@ int ls_paged_sparse_fp16(const void* q, const void* k_pool, const void* v_pool,
                          float ratio, int recent, float* part_acc, float* part_m, float* part_l,
                          int32_t* seg_range, void* out, int batch, int kv_heads, int n_rep,
                          int head_dim, int page, int max_pages, int num_blocks, int num_sel,
-                         int num_chunks, int min_chunk, int64_t sq_b, int64_t sq_h, int64_t sq_m,
-                         int64_t sk_b, int64_t sk_p, int64_t sk_h, int64_t sl_b, int64_t sl_h,
-                         int64_t so_b, int64_t so_h, int64_t so_m, float softmax_scale,
+                         int num_chunks, int min_chunk, int flags, int64_t sq_b, int64_t sq_h,
+                         int64_t sq_m, int64_t sk_b, int64_t sk_p, int64_t sk_h, int64_t sl_b,
+                         int64_t sl_h, int64_t so_b, int64_t so_h, int64_t so_m, float softmax_scale,
                          void* stream);
 
 /* Merge of the split partials into out fp16 [B,H,R,128].

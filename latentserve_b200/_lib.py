@@ -35,8 +35,8 @@ P, I, L, F = c_void_p, c_int, c_int64, c_float
 _PROTOTYPES = {
     "ls_decode_slots": [I, I],
     "ls_paged_decode_fp16": [P, P, P, P, P, P, P, P, P, P] + [I] * 10 + [L] * 9 + [F, P],
-    "ls_paged_sparse_fp16": [P, P, P, P, P, P, F, I, P, P, P, P, P] + [I] * 10 + [L] * 11 + [F, P],
-    "ls_paged_decode_int8": [P] * 16 + [I] * 10 + [L] * 17 + [F, P],
+    "ls_paged_sparse_fp16": [P, P, P, P, P, P, F, I, P, P, P, P, P] + [I] * 11 + [L] * 11 + [F, P],
+    "ls_paged_decode_int8": [P] * 16 + [I] * 11 + [L] * 17 + [F, P],
     "ls_paged_decode_fp16_noalloc": [P, P, P, P, P, P] + [I] * 9 + [L] * 9 + [F, P],
     "ls_combine": [P, P, P, P, P, I, I, I, L, L, L, P],
     "ls_kv_append_fp16": [P, P, P, P, P, P, P, I, I, I, I] + [L] * 9 + [P],

@@ -53,6 +53,25 @@ __device__ __forceinline__ void cp_async_16(uint32_t dst, const void* src, int s
                  : "memory");
 }
 
+// The same copy for rows known to exist (no source-size operand).
+__device__ __forceinline__ void cp_async_16_full(uint32_t dst, const void* src) {
+    asm volatile("cp.async.cg.shared.global" LS_CP_L2_HINT " [%0], [%1], 16;\n" ::"r"(dst), "l"(src)
+                 : "memory");
+}
+
+// KV pages are read once per decode step: marking them evict-first keeps the
+// small, re-read inputs (block tables, lengths, queries, partials) in L2.
+__device__ __forceinline__ uint64_t l2_policy_evict_first() {
+    uint64_t pol;
+    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;\n" : "=l"(pol));
+    return pol;
+}
+__device__ __forceinline__ void cp_async_16_stream(uint32_t dst, const void* src, uint64_t pol) {
+    asm volatile("cp.async.cg.shared.global.L2::cache_hint" LS_CP_L2_HINT " [%0], [%1], 16, 16, %2;\n" ::"r"(dst),
+                 "l"(src), "l"(pol)
+                 : "memory");
+}
+
 // 4-byte asynchronous copy (scalars such as a per-token V scale).
 __device__ __forceinline__ void cp_async_4(uint32_t dst, const void* src, int src_bytes) {
     asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;\n" ::"r"(dst), "l"(src),

@@ -19,7 +19,7 @@
 namespace ls {
 
 constexpr int kIndexWarps = 4;
-constexpr int kPagesPerWarp = 8;
+constexpr int kPagesPerWarp = 4;
 
 __device__ __forceinline__ void unpack4h(uint2 raw, float (&f)[4]) {
     const __half2* h2 = reinterpret_cast<const __half2*>(&raw);
@@ -27,18 +27,26 @@ __device__ __forceinline__ void unpack4h(uint2 raw, float (&f)[4]) {
     f[0] = a.x; f[1] = a.y; f[2] = b.x; f[3] = b.y;
 }
 
-__device__ __forceinline__ float bound_row(const float (&q)[4], const float (&lo)[4],
-                                           const float (&hi)[4]) {
-    float s = 0.f;
+// Bounds of all 8 (padded) query rows for one page. Every row keeps the order
+// "lane sum of 4 channels from 0, then xor butterfly 16, 8, 4, 2, 1"; the rows'
+// butterflies are interleaved so their shuffle latencies overlap.
+__device__ __forceinline__ void bound_rows(const float (&q)[8][4], const float (&lo)[4],
+                                           const float (&hi)[4], float (&s)[8]) {
 #pragma unroll
-    for (int j = 0; j < 4; ++j)
-        s = __fadd_rn(s, fmaxf(__fmul_rn(q[j], lo[j]), __fmul_rn(q[j], hi[j])));
+    for (int r = 0; r < 8; ++r) {
+        float t = 0.f;
 #pragma unroll
-    for (int off = 16; off > 0; off >>= 1) s = __fadd_rn(s, __shfl_xor_sync(LS_FULL_MASK, s, off));
-    return s;
+        for (int j = 0; j < 4; ++j)
+            t = __fadd_rn(t, fmaxf(__fmul_rn(q[r][j], lo[j]), __fmul_rn(q[r][j], hi[j])));
+        s[r] = t;
+    }
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1)
+#pragma unroll
+        for (int r = 0; r < 8; ++r) s[r] = __fadd_rn(s[r], __shfl_xor_sync(LS_FULL_MASK, s[r], off));
 }
 
-// grid (ceil(max_pages / 32), H, B), block 128. PER_HEAD = 0: scores [B,H,P];
+// grid (ceil(max_pages / 16), H, B), block 128. PER_HEAD = 0: scores [B,H,P];
 // PER_HEAD = 1: heads [B,H,R,P].
 template <int PER_HEAD>
 __global__ void __launch_bounds__(kIndexWarps * 32)
@@ -95,16 +103,19 @@ page_index_kernel(const __half* __restrict__ q, const __half* __restrict__ kmin,
         float lo[4], hi[4];
         unpack4h(lo_raw[k], lo);
         unpack4h(hi_raw[k], hi);
+        float s[8];
+        if (scored[k]) {                                // warp-uniform
+            bound_rows(qf, lo, hi, s);
+        } else {
+#pragma unroll
+            for (int r = 0; r < 8; ++r) s[r] = 0.f;
+        }
         if (PER_HEAD) {
             // Pages past the end get a finite 0: their token count of zero
             // removes them downstream, and a stale NaN here would not.
 #pragma unroll
-            for (int r = 0; r < 8; ++r) {
-                if (r < n_rep) {
-                    const float s = scored[k] ? bound_row(qf[r], lo, hi) : 0.f;
-                    if (lane == 0) out[b * ss_b + h * ss_h + r * ss_r + p] = s;
-                }
-            }
+            for (int r = 0; r < 8; ++r)
+                if (r < n_rep && lane == 0) out[b * ss_b + h * ss_h + r * ss_r + p] = s[r];
         } else {
             float best;
             if (p >= np) {
@@ -113,9 +124,11 @@ page_index_kernel(const __half* __restrict__ q, const __half* __restrict__ kmin,
                 best = pos_inf();                       // sink and recent pages: always kept
             } else {
                 best = neg_inf();
+                if (scored[k]) {
 #pragma unroll
-                for (int r = 0; r < 8; ++r)
-                    if (r < n_rep && scored[k]) best = fmaxf(best, bound_row(qf[r], lo, hi));
+                    for (int r = 0; r < 8; ++r)
+                        if (r < n_rep) best = fmaxf(best, s[r]);
+                }
             }
             if (lane == 0) out[b * ss_b + h * ss_h + p] = best;
         }
@@ -129,12 +142,16 @@ __device__ __forceinline__ uint32_t order_key(float x) {
     return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
 }
 
-constexpr int kTopkThreads = 256;
+constexpr int kTopkThreads = 128;
+constexpr int kTopkPerThread = 2;
+constexpr int kTopkTile = kTopkThreads * kTopkPerThread;
 
 // Rank by counting: rank(i) = #{j : s_j > s_i} + #{j < i : s_j == s_i}. The
 // entry of rank r < k lands at sel[r], which is the stable descending order.
-// grid (ceil(n / 256), B*H). O(n^2 / grid) compares against the row held in
-// shared memory; n is a block-table width (2048 pages for a 32K context).
+// grid (ceil(n / 256), B*H); a thread ranks two candidates (i and i + 128 of
+// the CTA's 256-entry tile) against the whole row held in shared memory, so
+// each 16-byte broadcast read of four keys serves eight comparisons.
+// O(n^2 / grid) compares; n is a block-table width (2048 pages at 32K context).
 __global__ void __launch_bounds__(kTopkThreads)
 topk_pages_kernel(const float* __restrict__ scores, int* __restrict__ sel, int n, int k, int heads,
                   long long ss_b, long long ss_h, long long sl_b, long long sl_h) {
@@ -144,27 +161,34 @@ topk_pages_kernel(const float* __restrict__ scores, int* __restrict__ sel, int n
     const int n4 = (n + 3) & ~3;
     for (int j = threadIdx.x; j < n4; j += kTopkThreads) keys[j] = j < n ? order_key(row[j]) : 0u;
     __syncthreads();
-    const int i = blockIdx.x * kTopkThreads + threadIdx.x;
-    const uint32_t mine = i < n ? keys[i] : 0xffffffffu;
-    const int tile_lo = blockIdx.x * kTopkThreads, tile_hi = min(n4, tile_lo + kTopkThreads);
-    int rank = 0;
+    const int tile_lo = blockIdx.x * kTopkTile, tile_hi = min(n4, tile_lo + kTopkTile);
+    const int i0 = tile_lo + threadIdx.x, i1 = i0 + kTopkThreads;
+    const uint32_t m0 = i0 < n ? keys[i0] : 0xffffffffu;
+    const uint32_t m1 = i1 < n ? keys[i1] : 0xffffffffu;
+    int rank0 = 0, rank1 = 0;
     const uint4* k4 = reinterpret_cast<const uint4*>(keys);
-    // Entries before this CTA's tile precede every i of the tile: ties count.
+    // Entries before this CTA's tile precede every candidate of the tile: ties count.
+#pragma unroll 4
     for (int j = 0; j < tile_lo / 4; ++j) {
         const uint4 v = k4[j];
-        rank += (v.x >= mine) + (v.y >= mine) + (v.z >= mine) + (v.w >= mine);
+        rank0 += (v.x >= m0) + (v.y >= m0) + (v.z >= m0) + (v.w >= m0);
+        rank1 += (v.x >= m1) + (v.y >= m1) + (v.z >= m1) + (v.w >= m1);
     }
     for (int j = tile_lo; j < tile_hi; ++j) {
         const uint32_t v = keys[j];
-        rank += (v > mine) || (v == mine && j < i);
+        rank0 += (v > m0) || (v == m0 && j < i0);
+        rank1 += (v > m1) || (v == m1 && j < i1);
     }
+#pragma unroll 4
     for (int j = tile_hi / 4; j < n4 / 4; ++j) {
         const uint4 v = k4[j];
-        rank += (v.x > mine) + (v.y > mine) + (v.z > mine) + (v.w > mine);
+        rank0 += (v.x > m0) + (v.y > m0) + (v.z > m0) + (v.w > m0);
+        rank1 += (v.x > m1) + (v.y > m1) + (v.z > m1) + (v.w > m1);
     }
     // Padding keys (0) never outrank a real entry: key(x) >= 1 for every
     // float except NaN patterns with the sign bit set, which sort last.
-    if (i < n && rank < k) sel[b * sl_b + h * sl_h + rank] = i;
+    if (i0 < n && rank0 < k) sel[b * sl_b + h * sl_h + rank0] = i0;
+    if (i1 < n && rank1 < k) sel[b * sl_b + h * sl_h + rank1] = i1;
 }
 
 }  // namespace ls
@@ -234,7 +258,7 @@ int ls_topk_pages(const float* scores, int32_t* sel, int batch, int kv_heads, in
     cudaError_t e = cudaFuncSetAttribute(ls::topk_pages_kernel,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
-    dim3 grid((num_pages + ls::kTopkThreads - 1) / ls::kTopkThreads, batch * kv_heads);
+    dim3 grid((num_pages + ls::kTopkTile - 1) / ls::kTopkTile, batch * kv_heads);
     ls::topk_pages_kernel<<<grid, ls::kTopkThreads, smem, static_cast<cudaStream_t>(stream)>>>(
         scores, sel, num_pages, k, kv_heads, ss_b, ss_h, sl_b, sl_h);
     return (int)cudaGetLastError();

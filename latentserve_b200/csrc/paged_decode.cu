@@ -43,9 +43,13 @@ namespace ls {
 
 #define LS_IMPL_MMA 0
 #define LS_IMPL_SIMT 1
+#define LS_LAUNCH_PROGRAMMATIC 0x100
 
 #ifndef LS_STAGES
 #define LS_STAGES 3                 // cp.async ring depth per warp
+#endif
+#ifndef LS_EVICT_FIRST
+#define LS_EVICT_FIRST 1            // L2 evict-first policy on the (read-once) KV page loads
 #endif
 constexpr int kWarps = 4;
 constexpr int kStages = LS_STAGES;
@@ -53,33 +57,94 @@ constexpr int kThreads = kWarps * 32;
 constexpr int kMergeStride = LS_HEAD_DIM + 4;   // floats per merged row (bank-conflict pad)
 constexpr int kRP = 8;                          // query rows held per partial
 
-// What the load side knows about the page it is about to fetch; the block id
-// is read one iteration ahead of its use so its latency hides behind compute.
+// What the load side knows about the page it is about to fetch.
 struct PageItem {
     int blk;
     int valid;      // tokens of the page that exist (0 = skip)
     int last;       // 1 if this is the sequence's last page
 };
 
+// Lookahead over a warp's page sequence. Lane j of the warp holds the block id
+// and extent of the j-th upcoming page of the current segment (up to 32 pages),
+// fetched with one round of independent loads (two for the sparse kernel:
+// selection entry, then block-table entry) instead of a dependent scalar load
+// per page. The next window is fetched while the last two pages of the current
+// one are still being handed out, so its latency hides behind compute.
 template <int MODE>
-__device__ __forceinline__ PageItem fetch_item(const DecodeParams& p, const Cursor& c, int h,
-                                               int& cached_b, int& cached_len) {
-    PageItem it = {0, 0, 0};
-    if (c.done) return it;
-    if (c.b != cached_b) {
-        cached_b = c.b;
-        cached_len = max(p.seq_lens[c.b], 0);
+struct PageWindow {
+    Cursor c;                       // first page of the current window
+    int n, i;                       // pages in the window, next one to hand out
+    int blk, valid, last;           // lane j: page j
+    Cursor nc;                      // the window after this one
+    int nn, nblk, nvalid, nlast;
+    bool have_next;
+    int cached_b, cached_len;
+
+    __device__ __forceinline__ void fill(const DecodeParams& p, const Cursor& cur, int h, int lane,
+                                         int& cnt, int& b_, int& v_, int& l_) {
+        cnt = 0; b_ = 0; v_ = 0; l_ = 0;
+        if (cur.done) return;
+        if (cur.b != cached_b) {
+            cached_b = cur.b;
+            cached_len = max(p.seq_lens[cur.b], 0);
+        }
+        const int np = min((cached_len + LS_PAGE - 1) / LS_PAGE, p.max_pages);
+        cnt = min(32, (cur.hi - cur.u + kWarps - 1) / kWarps);
+        const int u = cur.u + kWarps * lane;
+        const bool in = lane < cnt;
+        int page = u;
+        if (MODE == LS_MODE_SPARSE && in) page = p.sel[cur.b * p.sl_b + h * p.sl_h + u];
+        if (in && page >= 0 && page < np) {
+            const int id = p.block_tables[(long long)cur.b * p.max_pages + page];
+            if (id >= 0 && id < p.num_blocks) {
+                b_ = id;
+                v_ = min(LS_PAGE, cached_len - page * LS_PAGE);
+                l_ = page == np - 1;
+            } else {
+                p.seg_range[2 * p.batch] = 1;      // corrupt table: read nothing, flag it
+            }
+        }
     }
-    const int np = min((cached_len + LS_PAGE - 1) / LS_PAGE, p.max_pages);
-    int page = c.u;
-    if (MODE == LS_MODE_SPARSE) page = p.sel[c.b * p.sl_b + h * p.sl_h + c.u];
-    if (page >= 0 && page < np) {
-        it.blk = p.block_tables[(long long)c.b * p.max_pages + page];
-        it.valid = min(LS_PAGE, cached_len - page * LS_PAGE);
-        it.last = page == np - 1;
+
+    __device__ __forceinline__ void begin(const DecodeParams& p, const Cursor& first, int h,
+                                          int lane) {
+        cached_b = -1;
+        cached_len = 0;
+        c = first;
+        fill(p, c, h, lane, n, blk, valid, last);
+        i = 0;
+        have_next = false;
     }
-    return it;
-}
+
+    __device__ __forceinline__ void prefetch(const DecodeParams& p, const int* cum, int h, int warp,
+                                             int lane) {
+        nc = c;
+        nc.u += kWarps * n;
+        cursor_normalize<kWarps>(nc, cum, p.batch, warp);
+        fill(p, nc, h, lane, nn, nblk, nvalid, nlast);
+        have_next = true;
+    }
+
+    // Next page of this warp; false when the chunk is exhausted. `b` is its sequence.
+    __device__ __forceinline__ bool next(const DecodeParams& p, const int* cum, int h, int warp,
+                                         int lane, PageItem& it, int& b) {
+        if (i == n) {
+            if (n == 0) return false;
+            if (!have_next) prefetch(p, cum, h, warp, lane);
+            c = nc; n = nn; blk = nblk; valid = nvalid; last = nlast;
+            have_next = false;
+            i = 0;
+            if (n == 0) return false;
+        }
+        it.blk = __shfl_sync(LS_FULL_MASK, blk, i);
+        it.valid = __shfl_sync(LS_FULL_MASK, valid, i);
+        it.last = __shfl_sync(LS_FULL_MASK, last, i);
+        b = c.b;
+        ++i;
+        if (!have_next && i + 2 >= n) prefetch(p, cum, h, warp, lane);
+        return true;
+    }
+};
 
 // ---------------------------------------------------------------------------
 // Online softmax on MMA accumulator fragments. Lane (g = lane / 4, t = lane % 4)
@@ -111,12 +176,16 @@ __device__ __forceinline__ void softmax_update(float (&s)[4], float (&m)[2], flo
     m[1] = mn1;
     l[0] = l[0] * a0 + (s[0] + s[2]);
     l[1] = l[1] * a1 + (s[1] + s[3]);
+    // Once a row's running maximum has settled (the usual case after the first
+    // few pages) the factors are exactly 1 and the rescale is skipped.
+    if (a0 != 1.f || a1 != 1.f) {
 #pragma unroll
-    for (int mt = 0; mt < 8; ++mt) {
-        o[mt][0] *= a0;
-        o[mt][1] *= a1;
-        o[mt][2] *= a0;
-        o[mt][3] *= a1;
+        for (int mt = 0; mt < 8; ++mt) {
+            o[mt][0] *= a0;
+            o[mt][1] *= a1;
+            o[mt][2] *= a0;
+            o[mt][3] *= a1;
+        }
     }
 }
 
@@ -166,20 +235,43 @@ __device__ __forceinline__ void load_q_fragments(const DecodeParams& p, int b, i
 struct PoolFp16 {
     static constexpr int STAGE_BYTES = 8192;       // K 4096 | V 4096
 
-    // 256 16-byte chunks of K and of V per page-head, 8 + 8 per lane.
+    // 256 16-byte chunks of K and of V per page-head, 8 + 8 per lane: lane l
+    // takes chunk (l & 15) of rows 2i + (l >> 4), i = 0..7, so a warp-wide copy
+    // covers two whole 256-byte rows. Row r lands at r * 256 with its chunks
+    // XOR-swizzled by r & 7.
     static __device__ __forceinline__ int issue(const DecodeParams& p, int, int h,
                                                 const PageItem& it, uint32_t stage, int lane) {
-        const __half* kb = static_cast<const __half*>(p.k_pool) + it.blk * p.sk_b + h * p.sk_h;
-        const __half* vb = static_cast<const __half*>(p.v_pool) + it.blk * p.sk_b + h * p.sk_h;
+        const int hi = lane >> 4, col = lane & 15;
+        const long long lane_off = hi * p.sk_p + col * 8;
+        const long long row2 = 2 * p.sk_p;
+        const __half* kb = static_cast<const __half*>(p.k_pool) + it.blk * p.sk_b + h * p.sk_h + lane_off;
+        const __half* vb = static_cast<const __half*>(p.v_pool) + it.blk * p.sk_b + h * p.sk_h + lane_off;
+        const uint32_t dst0 = stage + hi * 256;
+        const uint32_t c0 = (uint32_t)(col ^ hi) << 4;      // ((2i + hi) & 7) = (2i & 7) | hi
+        if (it.valid == LS_PAGE) {
+#if LS_EVICT_FIRST
+            const uint64_t pol = l2_policy_evict_first();
+#endif
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
-            const int ci = i * 32 + lane;
-            const int row = ci >> 4, col = ci & 15;
-            const uint32_t dst = stage + row * 256 + ((col ^ (row & 7)) << 4);
-            const int nbytes = row < it.valid ? 16 : 0;
-            const long long off = nbytes ? row * p.sk_p + col * 8 : 0;
-            cp_async_16(dst, kb + off, nbytes);
-            cp_async_16(dst + 4096, vb + off, nbytes);
+            for (int i = 0; i < 8; ++i) {
+                const uint32_t dst = dst0 + i * 512 + (c0 ^ (((2 * i) & 7) << 4));
+#if LS_EVICT_FIRST
+                cp_async_16_stream(dst, kb + i * row2, pol);
+                cp_async_16_stream(dst + 4096, vb + i * row2, pol);
+#else
+                cp_async_16_full(dst, kb + i * row2);
+                cp_async_16_full(dst + 4096, vb + i * row2);
+#endif
+            }
+        } else {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const uint32_t dst = dst0 + i * 512 + (c0 ^ (((2 * i) & 7) << 4));
+                const int nbytes = 2 * i + hi < it.valid ? 16 : 0;
+                cp_async_16(dst, nbytes ? kb + i * row2 : static_cast<const __half*>(p.k_pool), nbytes);
+                cp_async_16(dst + 4096, nbytes ? vb + i * row2 : static_cast<const __half*>(p.v_pool),
+                            nbytes);
+            }
         }
         return it.valid;
     }
@@ -422,33 +514,63 @@ struct PoolInt8 {
                 cp_async_16(stage + row * 256 + ((col ^ (row & 7)) << 4),
                             kr + (nbytes ? row * p.sr_p + col * 8 : 0), nbytes);
             }
-        } else {
-            const signed char* kb =
-                static_cast<const signed char*>(p.k_pool) + it.blk * p.sk_b + h * p.sk_h;
+        }
+        // int8 rows: lane l takes chunk (l & 7) of rows 4i + (l >> 3), i = 0..3; a
+        // warp-wide copy covers four whole 128-byte rows.
+        const int r0 = lane >> 3, col = lane & 7;
+        const long long lane_off = r0 * p.sk_p + col * 16;
+        const long long row4 = 4 * p.sk_p;
+        const uint32_t dst0 = stage + r0 * 128;
+        const uint32_t c0 = (uint32_t)(col ^ r0) << 4;          // ((4i + r0) & 7) = (4i & 7) | r0
+        const signed char* kb =
+            static_cast<const signed char*>(p.k_pool) + it.blk * p.sk_b + h * p.sk_h + lane_off;
+        const signed char* vb =
+            static_cast<const signed char*>(p.v_pool) + it.blk * p.sk_b + h * p.sk_h + lane_off;
+        const bool full = it.valid == LS_PAGE;
+#if LS_EVICT_FIRST
+        const uint64_t pol = l2_policy_evict_first();
+#endif
+        if (!from_res) {
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
-                const int ci = i * 32 + lane;
-                const int row = ci >> 3, col = ci & 7;
-                const int nbytes = row < it.valid ? 16 : 0;
-                cp_async_16(stage + row * 128 + ((col ^ (row & 7)) << 4),
-                            kb + (nbytes ? row * p.sk_p + col * 16 : 0), nbytes);
+                const uint32_t dst = dst0 + i * 512 + (c0 ^ (((4 * i) & 7) << 4));
+                if (full) {
+#if LS_EVICT_FIRST
+                    cp_async_16_stream(dst, kb + i * row4, pol);
+#else
+                    cp_async_16_full(dst, kb + i * row4);
+#endif
+                } else {
+                    const int nbytes = 4 * i + r0 < it.valid ? 16 : 0;
+                    cp_async_16(dst, nbytes ? kb + i * row4 : static_cast<const signed char*>(p.k_pool),
+                                nbytes);
+                }
             }
+            // K scales (and zero points): float4 f = lane goes to slot
+            // (f & ~7) | ((f & 7) ^ (f >> 3)), so the four quarter-rows that one
+            // shared load touches sit in different banks.
             const int nb = it.valid > 0 ? 16 : 0;
-            cp_async_16(stage + OFF_KS + lane * 16,
+            const uint32_t slot = (uint32_t)((lane & ~7) | ((lane & 7) ^ (lane >> 3))) << 4;
+            cp_async_16(stage + OFF_KS + slot,
                         p.k_scale + (nb ? it.blk * p.ks_b + h * p.ks_h + lane * 4 : 0), nb);
             if (ASYM)
-                cp_async_16(stage + OFF_KZ + lane * 16,
+                cp_async_16(stage + OFF_KZ + slot,
                             p.k_zero + (nb ? it.blk * p.ks_b + h * p.ks_h + lane * 4 : 0), nb);
         }
-        const signed char* vb =
-            static_cast<const signed char*>(p.v_pool) + it.blk * p.sk_b + h * p.sk_h;
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
-            const int ci = i * 32 + lane;
-            const int row = ci >> 3, col = ci & 7;
-            const int nbytes = row < it.valid ? 16 : 0;
-            cp_async_16(stage + OFF_V + row * 128 + ((col ^ (row & 7)) << 4),
-                        vb + (nbytes ? row * p.sk_p + col * 16 : 0), nbytes);
+            const uint32_t dst = dst0 + OFF_V + i * 512 + (c0 ^ (((4 * i) & 7) << 4));
+            if (full) {
+#if LS_EVICT_FIRST
+                cp_async_16_stream(dst, vb + i * row4, pol);
+#else
+                cp_async_16_full(dst, vb + i * row4);
+#endif
+            } else {
+                const int nbytes = 4 * i + r0 < it.valid ? 16 : 0;
+                cp_async_16(dst, nbytes ? vb + i * row4 : static_cast<const signed char*>(p.v_pool),
+                            nbytes);
+            }
         }
         {
             const int tok = lane & 15;
@@ -536,13 +658,14 @@ struct MmaInt8 {
             float zq = 0.f;
 #pragma unroll
             for (int i = 0; i < 8; ++i) {
-                const uint4 sc = lds128(stage + Pool::OFF_KS + (32 * t + 4 * i) * 4);
+                const uint32_t slot = (uint32_t)(8 * t + (i ^ t)) << 4;   // see PoolInt8::issue
+                const uint4 sc = lds128(stage + Pool::OFF_KS + slot);
                 qk[i][0] = pack_half2(qf[4 * i] * __uint_as_float(sc.x),
                                       qf[4 * i + 1] * __uint_as_float(sc.y));
                 qk[i][1] = pack_half2(qf[4 * i + 2] * __uint_as_float(sc.z),
                                       qf[4 * i + 3] * __uint_as_float(sc.w));
                 if (ASYM) {
-                    const uint4 z = lds128(stage + Pool::OFF_KZ + (32 * t + 4 * i) * 4);
+                    const uint4 z = lds128(stage + Pool::OFF_KZ + slot);
                     zq = fmaf(qf[4 * i], __uint_as_float(z.x), zq);
                     zq = fmaf(qf[4 * i + 1], __uint_as_float(z.y), zq);
                     zq = fmaf(qf[4 * i + 2], __uint_as_float(z.z), zq);
@@ -670,42 +793,76 @@ __device__ __forceinline__ void merge_partials(const float* part_acc, const floa
                                                __half* out, int heads, int n_rep, int b, int h,
                                                int tid, long long so_b, long long so_h,
                                                long long so_m) {
+    constexpr int kBatch = 8;                                // partial rows loaded per round
     const int warp = tid >> 5, lane = tid & 31;
-    for (int r = warp; r < n_rep; r += kWarps) {
-        const long long row0 = ((long long)first * heads + h) * kRP + r;
-        const long long step = (long long)heads * kRP;               // rows between partials
-        float mg = neg_inf();
-        for (int s = lane; s < count; s += 32) mg = fmaxf(mg, __ldcg(part_m + row0 + s * step));
+    const long long step = (long long)heads * kRP;           // rows between partials
+    // Warp w merges rows w and w + 4 together, so both rows' loads are in flight at once.
+    const int r0 = warp, r1 = warp + kWarps;
+    const bool has0 = r0 < n_rep, has1 = r1 < n_rep;
+    if (!has0) return;
+    const long long base0 = ((long long)first * heads + h) * kRP + r0;
+    const long long base1 = base0 + kWarps;
+    float mg0 = neg_inf(), mg1 = neg_inf();
+    for (int s = lane; s < count; s += 32) {
+        mg0 = fmaxf(mg0, __ldcg(part_m + base0 + s * step));
+        if (has1) mg1 = fmaxf(mg1, __ldcg(part_m + base1 + s * step));
+    }
 #pragma unroll
-        for (int off = 16; off > 0; off >>= 1)
-            mg = fmaxf(mg, __shfl_xor_sync(LS_FULL_MASK, mg, off));
-        const float ms = (mg == neg_inf()) ? 0.f : mg;
-        float lsum = 0.f;
-        float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
-        for (int s0 = 0; s0 < count; s0 += 32) {
-            const int s = s0 + lane;
-            float w = 0.f;
-            if (s < count) {
-                w = ex2(__ldcg(part_m + row0 + s * step) - ms);
-                lsum += w * __ldcg(part_l + row0 + s * step);
-            }
-            const int n = min(32, count - s0);
-            const float4* src =
-                reinterpret_cast<const float4*>(part_acc + (row0 + s0 * step) * LS_HEAD_DIM) + lane;
-#pragma unroll 8
-            for (int j = 0; j < n; ++j) {
-                const float wj = __shfl_sync(LS_FULL_MASK, w, j);
-                const float4 v = __ldcg(src + j * step * (LS_HEAD_DIM / 4));
-                a.x += wj * v.x; a.y += wj * v.y; a.z += wj * v.z; a.w += wj * v.w;
+    for (int off = 16; off > 0; off >>= 1) {
+        mg0 = fmaxf(mg0, __shfl_xor_sync(LS_FULL_MASK, mg0, off));
+        mg1 = fmaxf(mg1, __shfl_xor_sync(LS_FULL_MASK, mg1, off));
+    }
+    const float ms0 = (mg0 == neg_inf()) ? 0.f : mg0;
+    const float ms1 = (mg1 == neg_inf()) ? 0.f : mg1;
+    float ls0 = 0.f, ls1 = 0.f;
+    float4 a0 = make_float4(0.f, 0.f, 0.f, 0.f), a1 = a0;
+    for (int s0 = 0; s0 < count; s0 += 32) {
+        const int s = s0 + lane;
+        float w0 = 0.f, w1 = 0.f;
+        if (s < count) {
+            w0 = ex2(__ldcg(part_m + base0 + s * step) - ms0);
+            ls0 += w0 * __ldcg(part_l + base0 + s * step);
+            if (has1) {
+                w1 = ex2(__ldcg(part_m + base1 + s * step) - ms1);
+                ls1 += w1 * __ldcg(part_l + base1 + s * step);
             }
         }
+        const int n = min(32, count - s0);
+        const float4* src0 =
+            reinterpret_cast<const float4*>(part_acc + (base0 + s0 * step) * LS_HEAD_DIM) + lane;
+        const float4* src1 = src0 + kWarps * (LS_HEAD_DIM / 4);
+        const long long pstep = step * (LS_HEAD_DIM / 4);
+        for (int j0 = 0; j0 < n; j0 += kBatch) {
+            float4 v0[kBatch], v1[kBatch];
 #pragma unroll
-        for (int off = 16; off > 0; off >>= 1) lsum += __shfl_xor_sync(LS_FULL_MASK, lsum, off);
-        const float inv = 1.f / fmaxf(lsum, 1e-20f);
-        uint2 packed;
-        packed.x = pack_half2(a.x * inv, a.y * inv);
-        packed.y = pack_half2(a.z * inv, a.w * inv);
-        *reinterpret_cast<uint2*>(out + b * so_b + h * so_h + r * so_m + lane * 4) = packed;
+            for (int j = 0; j < kBatch; ++j) {
+                const bool ok = j0 + j < n;
+                v0[j] = ok ? __ldcg(src0 + (j0 + j) * pstep) : make_float4(0.f, 0.f, 0.f, 0.f);
+                v1[j] = (ok && has1) ? __ldcg(src1 + (j0 + j) * pstep) : make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+#pragma unroll
+            for (int j = 0; j < kBatch; ++j) {
+                const float x0 = __shfl_sync(LS_FULL_MASK, w0, (j0 + j) & 31);
+                const float x1 = __shfl_sync(LS_FULL_MASK, w1, (j0 + j) & 31);
+                a0.x += x0 * v0[j].x; a0.y += x0 * v0[j].y; a0.z += x0 * v0[j].z; a0.w += x0 * v0[j].w;
+                a1.x += x1 * v1[j].x; a1.y += x1 * v1[j].y; a1.z += x1 * v1[j].z; a1.w += x1 * v1[j].w;
+            }
+        }
+    }
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) {
+        ls0 += __shfl_xor_sync(LS_FULL_MASK, ls0, off);
+        ls1 += __shfl_xor_sync(LS_FULL_MASK, ls1, off);
+    }
+    const float i0 = 1.f / fmaxf(ls0, 1e-20f), i1 = 1.f / fmaxf(ls1, 1e-20f);
+    uint2 packed;
+    packed.x = pack_half2(a0.x * i0, a0.y * i0);
+    packed.y = pack_half2(a0.z * i0, a0.w * i0);
+    *reinterpret_cast<uint2*>(out + b * so_b + h * so_h + r0 * so_m + lane * 4) = packed;
+    if (has1) {
+        packed.x = pack_half2(a1.x * i1, a1.y * i1);
+        packed.y = pack_half2(a1.z * i1, a1.w * i1);
+        *reinterpret_cast<uint2*>(out + b * so_b + h * so_h + r1 * so_m + lane * 4) = packed;
     }
 }
 
@@ -726,8 +883,28 @@ __global__ void __launch_bounds__(kThreads, 2) decode_kernel(const DecodeParams 
     int* flag = scan + kWarps;                                    // [1]
     int* cum = flag + 1;                                          // [batch + 1]
 
+    // Programmatic dependent launch: let the next kernel of the stream be
+    // scheduled as this one drains, and -- when this launch was itself made
+    // with the attribute -- do the part of the prologue that reads only
+    // seq_lens and block_tables while the previous kernel is still finishing.
+    // Without the attribute both instructions are no-ops.
+    asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
     const int total = build_prefix<MODE, kThreads>(p, cum, scan);
     const int chunk = chunk_size(p, total);
+    const int g0 = chunk_id * chunk;
+    const int g1 = min(total, g0 + chunk);
+    const bool has_work = g0 < total;
+    const int b0 = has_work ? find_seq(cum, p.batch, g0) : 0;
+    const uint32_t ring = smem_u32(smem + warp * (STAGES * STAGE_BYTES));
+    int* my_meta = meta + warp * STAGES;
+
+    // Load side. The dense walk needs nothing the previous kernel may have
+    // written; the sparse walk reads the selection, which it usually did write.
+    PageWindow<MODE> win;
+    if (MODE == LS_MODE_DENSE && has_work)
+        win.begin(p, cursor_begin<kWarps>(cum, p.batch, b0, g0, g1, warp), h, lane);
+    asm volatile("griddepcontrol.wait;\n" ::: "memory");
+
     if (chunk_id == 0 && h == 0) write_seg_ranges<kThreads>(p, cum, chunk);
     if (chunk_id == 0 && p.out != nullptr) {
         // Sequences with nothing to attend produce zeros (nobody else writes them).
@@ -737,29 +914,15 @@ __global__ void __launch_bounds__(kThreads, 2) decode_kernel(const DecodeParams 
                 p.out[b * p.so_b + h * p.so_h + (i >> 7) * p.so_m + (i & 127)] = __float2half_rn(0.f);
         }
     }
-    const int g0 = chunk_id * chunk;
-    if (g0 >= total) return;
-    const int g1 = min(total, g0 + chunk);
-    const int b0 = find_seq(cum, p.batch, g0);
-
-    const uint32_t ring = smem_u32(smem + warp * (STAGES * STAGE_BYTES));
-    int* my_meta = meta + warp * STAGES;
-
-    // Load side.
-    Cursor lc = cursor_begin<kWarps>(cum, p.batch, b0, g0, g1, warp);
-    int cached_b = -1, cached_len = 0;
-    PageItem item = fetch_item<MODE>(p, lc, h, cached_b, cached_len);
+    if (!has_work) return;
+    if (MODE != LS_MODE_DENSE)
+        win.begin(p, cursor_begin<kWarps>(cum, p.batch, b0, g0, g1, warp), h, lane);
     auto issue = [&](int stage) {
-        if (!lc.done) {
-            if (item.blk < 0 || item.blk >= p.num_blocks) {   // corrupt table: read nothing, flag it
-                if (item.valid > 0 && lane == 0) p.seg_range[2 * p.batch] = 1;
-                item.blk = 0;
-                item.valid = 0;
-            }
-            const int mt = Pool::issue(p, lc.b, h, item, ring + stage * STAGE_BYTES, lane);
+        PageItem item;
+        int lb;
+        if (win.next(p, cum, h, warp, lane, item, lb)) {
+            const int mt = Pool::issue(p, lb, h, item, ring + stage * STAGE_BYTES, lane);
             if (lane == 0) my_meta[stage] = mt;
-            cursor_next<kWarps>(lc, cum, p.batch, warp);
-            item = fetch_item<MODE>(p, lc, h, cached_b, cached_len);
         }
         cp_async_commit();
     };
@@ -821,11 +984,11 @@ __global__ void __launch_bounds__(kThreads, 2) decode_kernel(const DecodeParams 
             const int c_lo = cum[b] / chunk, c_hi = (cum[b + 1] - 1) / chunk;
             const int nseg = c_hi - c_lo + 1;
             int* counter = p.seg_range + 2 * p.batch + 2 + b * p.heads + h;
-            __threadfence();
-            __syncthreads();
+            __syncthreads();                                  // the CTA's partial is written
             if (tid == 0) {
                 int last = 1;
                 if (nseg > 1) {
+                    __threadfence();                          // ... and visible before we count
                     last = atomicAdd(counter, 1) == nseg - 1;
                     if (last) *counter = 0;                  // ready for the next launch
                 }
@@ -877,14 +1040,25 @@ static int validate_common(const DecodeParams& p) {
 }
 
 template <class State, int MODE, int STAGES>
-static int launch_decode(const DecodeParams& p, cudaStream_t stream) {
+static int launch_decode(const DecodeParams& p, cudaStream_t stream, bool programmatic = false) {
     const size_t smem = (size_t)kWarps * STAGES * State::Pool::STAGE_BYTES +
                         sizeof(float) * ((size_t)kWarps * p.n_rep * kMergeStride + 2 * kWarps * kRP) +
                         sizeof(int) * ((size_t)kWarps * STAGES + kWarps + 1 + p.batch + 1);
     auto kern = decode_kernel<State, MODE, STAGES>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
-    kern<<<dim3(p.num_chunks, p.heads), kThreads, smem, stream>>>(p);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(p.num_chunks, p.heads);
+    cfg.blockDim = dim3(kThreads);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = programmatic ? 1 : 0;
+    e = cudaLaunchKernelEx(&cfg, kern, p);
+    if (e != cudaSuccess) return (int)e;
     return (int)cudaGetLastError();
 }
 
@@ -907,7 +1081,7 @@ int ls_paged_decode_fp16(const void* q, const void* k_pool, const void* v_pool,
                          const int32_t* block_tables, const int32_t* seq_lens, float* part_acc,
                          float* part_m, float* part_l, int32_t* seg_range, void* out, int batch,
                          int kv_heads, int n_rep, int head_dim, int page, int max_pages,
-                         int num_blocks, int num_chunks, int min_chunk, int impl, int64_t sq_b,
+                         int num_blocks, int num_chunks, int min_chunk, int flags, int64_t sq_b,
                          int64_t sq_h, int64_t sq_m, int64_t sk_b, int64_t sk_p, int64_t sk_h,
                          int64_t so_b, int64_t so_h, int64_t so_m, float softmax_scale,
                          void* stream) {
@@ -939,13 +1113,16 @@ int ls_paged_decode_fp16(const void* q, const void* k_pool, const void* v_pool,
     rc = check_pool_fp16(p);
     if (rc) return rc;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const bool pdl = (flags & LS_LAUNCH_PROGRAMMATIC) != 0;
+    const int impl = flags & 0xff;
+    if (flags & ~(0xff | LS_LAUNCH_PROGRAMMATIC)) return LS_ERR_UNSUPPORTED;
     if (impl == LS_IMPL_SIMT) {
         if (n_rep <= 6)
-            rc = ls::launch_decode<ls::SimtFp16<6>, LS_MODE_DENSE, ls::kStages>(p, s);
+            rc = ls::launch_decode<ls::SimtFp16<6>, LS_MODE_DENSE, ls::kStages>(p, s, pdl);
         else
-            rc = ls::launch_decode<ls::SimtFp16<8>, LS_MODE_DENSE, ls::kStages>(p, s);
+            rc = ls::launch_decode<ls::SimtFp16<8>, LS_MODE_DENSE, ls::kStages>(p, s, pdl);
     } else if (impl == LS_IMPL_MMA) {
-        rc = ls::launch_decode<ls::MmaFp16, LS_MODE_DENSE, ls::kStages>(p, s);
+        rc = ls::launch_decode<ls::MmaFp16, LS_MODE_DENSE, ls::kStages>(p, s, pdl);
     } else {
         return LS_ERR_UNSUPPORTED;
     }
@@ -957,8 +1134,8 @@ int ls_paged_sparse_fp16(const void* q, const void* k_pool, const void* v_pool,
                          float ratio, int recent, float* part_acc, float* part_m, float* part_l,
                          int32_t* seg_range, void* out, int batch, int kv_heads, int n_rep,
                          int head_dim, int page, int max_pages, int num_blocks, int num_sel,
-                         int num_chunks, int min_chunk, int64_t sq_b, int64_t sq_h, int64_t sq_m,
-                         int64_t sk_b, int64_t sk_p, int64_t sk_h, int64_t sl_b, int64_t sl_h,
+                         int num_chunks, int min_chunk, int flags, int64_t sq_b, int64_t sq_h,
+                         int64_t sq_m, int64_t sk_b, int64_t sk_p, int64_t sk_h, int64_t sl_b, int64_t sl_h,
                          int64_t so_b, int64_t so_h, int64_t so_m, float softmax_scale,
                          void* stream) {
     if (head_dim != LS_HEAD_DIM || page != LS_PAGE) return LS_ERR_UNSUPPORTED;
@@ -996,7 +1173,9 @@ int ls_paged_sparse_fp16(const void* q, const void* k_pool, const void* v_pool,
     rc = check_pool_fp16(p);
     if (rc) return rc;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    rc = ls::launch_decode<ls::MmaFp16, LS_MODE_SPARSE, ls::kStages>(p, s);
+    if (flags & ~LS_LAUNCH_PROGRAMMATIC) return LS_ERR_UNSUPPORTED;
+    rc = ls::launch_decode<ls::MmaFp16, LS_MODE_SPARSE, ls::kStages>(p, s,
+                                                                     (flags & LS_LAUNCH_PROGRAMMATIC) != 0);
     return rc;
 }
 
@@ -1006,8 +1185,9 @@ int ls_paged_decode_int8(const void* q, const void* k_pool, const void* v_pool,
                          const void* k_res, const int32_t* res_rows, float* part_acc, float* part_m,
                          float* part_l, int32_t* seg_range, void* out, int batch, int kv_heads,
                          int n_rep, int head_dim, int page, int max_pages, int num_blocks,
-                         int num_res_rows, int num_chunks, int min_chunk, int64_t sq_b, int64_t sq_h,
-                         int64_t sq_m, int64_t sk_b, int64_t sk_p, int64_t sk_h, int64_t ks_b, int64_t ks_h,
+                         int num_res_rows, int num_chunks, int min_chunk, int flags, int64_t sq_b,
+                         int64_t sq_h, int64_t sq_m, int64_t sk_b, int64_t sk_p, int64_t sk_h, int64_t ks_b,
+                         int64_t ks_h,
                          int64_t vs_b, int64_t vs_p, int64_t vs_h, int64_t sr_r, int64_t sr_p,
                          int64_t sr_h, int64_t so_b, int64_t so_h, int64_t so_m, float softmax_scale,
                          void* stream) {
@@ -1059,10 +1239,12 @@ int ls_paged_decode_int8(const void* q, const void* k_pool, const void* v_pool,
     if (k_res && ((reinterpret_cast<uintptr_t>(k_res) & 15) || (sr_r % 8) || (sr_p % 8) || (sr_h % 8)))
         return LS_ERR_MISALIGNED;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (flags & ~LS_LAUNCH_PROGRAMMATIC) return LS_ERR_UNSUPPORTED;
+    const bool pdl = (flags & LS_LAUNCH_PROGRAMMATIC) != 0;
     if (k_zero)
-        rc = ls::launch_decode<ls::MmaInt8<1>, LS_MODE_DENSE, ls::kStages>(p, s);
+        rc = ls::launch_decode<ls::MmaInt8<1>, LS_MODE_DENSE, ls::kStages>(p, s, pdl);
     else
-        rc = ls::launch_decode<ls::MmaInt8<0>, LS_MODE_DENSE, ls::kStages>(p, s);
+        rc = ls::launch_decode<ls::MmaInt8<0>, LS_MODE_DENSE, ls::kStages>(p, s, pdl);
     return rc;
 }
 

@@ -16,6 +16,7 @@ cut; the result does not depend on it beyond fp32 rounding.
 from __future__ import annotations
 
 import math
+import os
 from typing import Optional
 
 import torch
@@ -23,6 +24,13 @@ import torch
 from latentserve_b200 import _lib
 
 IMPL_MMA, IMPL_SIMT = 0, 1          # tensor-core kernel / CUDA-core kernel (fp16 pools)
+LAUNCH_PROGRAMMATIC = 0x100         # see LS_LAUNCH_PROGRAMMATIC in the header
+# Decode launches use programmatic dependent launch when this is set: the
+# kernel's prologue (which reads only seq_lens and block_tables) overlaps the
+# tail of the previous kernel on the stream. Safe wherever that previous kernel
+# does not write those two tensors -- in a LatentServe layer it is the KV
+# append. Off unless asked for (LATENTSERVE_B200_PDL=1 or set_programmatic_launch).
+_PROGRAMMATIC = {"on": os.environ.get("LATENTSERVE_B200_PDL", "0") == "1"}
 ROWS_PER_PARTIAL = 8                # query rows a partial holds (GQA ratio <= 8)
 MIN_CHUNK_PAGES = 8                 # never cut the page axis finer than this
 CTAS_PER_SM = 2                     # resident CTAs per SM the kernels are sized for
@@ -30,6 +38,14 @@ MAX_BATCH = 1024
 
 _SCRATCH: dict = {}
 _SM_COUNT: dict = {}
+
+
+def set_programmatic_launch(on: bool) -> None:
+    _PROGRAMMATIC["on"] = bool(on)
+
+
+def launch_flags() -> int:
+    return LAUNCH_PROGRAMMATIC if _PROGRAMMATIC["on"] else 0
 
 
 def scratch(key, shape, dtype, device, zero: bool = False) -> torch.Tensor:
@@ -169,7 +185,7 @@ def paged_decode_cuda(q, k_pool, v_pool, block_tables, seq_lens, max_seq_len: in
             ptr(k_scale), ptr(v_scale), ptr(k_zero), ptr(v_zero), ptr(k_residual), ptr(res_rows),
             ptr(acc), ptr(m), ptr(l), ptr(seg), out_ptr,
             b, h_kv, n_rep, d, k_pool.shape[1], block_tables.stride(0), k_pool.shape[0],
-            0 if k_residual is None else k_residual.shape[0], chunks, MIN_CHUNK_PAGES,
+            0 if k_residual is None else k_residual.shape[0], chunks, MIN_CHUNK_PAGES, launch_flags(),
             q.stride(0), q.stride(1), q.stride(2),
             k_pool.stride(0), k_pool.stride(1), k_pool.stride(2),
             k_scale.stride(0), k_scale.stride(1),
@@ -182,7 +198,7 @@ def paged_decode_cuda(q, k_pool, v_pool, block_tables, seq_lens, max_seq_len: in
             ptr(q), ptr(k_pool), ptr(v_pool), ptr(block_tables), ptr(seq_lens),
             ptr(acc), ptr(m), ptr(l), ptr(seg), out_ptr,
             b, h_kv, n_rep, d, k_pool.shape[1], block_tables.stride(0), k_pool.shape[0],
-            chunks, MIN_CHUNK_PAGES, impl,
+            chunks, MIN_CHUNK_PAGES, impl | launch_flags(),
             q.stride(0), q.stride(1), q.stride(2),
             k_pool.stride(0), k_pool.stride(1), k_pool.stride(2),
             out.stride(0), out.stride(1), out.stride(2), scale, stream)

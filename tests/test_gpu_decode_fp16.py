@@ -131,6 +131,34 @@ def test_survives_cuda_graph_capture_and_reads_current_inputs():
     close(out, want)
 
 
+def test_programmatic_launch_eager_and_under_capture():
+    """Back-to-back layer calls launched with programmatic stream serialization
+    (each kernel's prologue overlapping the previous kernel's tail, shared
+    partial scratch) give the same bits as ordinary launches."""
+    dev = device()
+    cases = [synthetic.dense_case([3000, 1200, 64, 5], seed=50 + i) for i in range(4)]
+    ts = [on_device(c) for c in cases]
+    plain = [_run(t).clone() for t in ts]
+    pdc.set_programmatic_launch(True)
+    try:
+        eager = [_run(t).clone() for t in ts]
+        torch.cuda.synchronize()
+        outs = [torch.empty_like(plain[0]) for _ in ts]
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            for t, o in zip(ts, outs):
+                o.copy_(_run(t))
+        for _ in range(3):
+            graph.replay()
+        torch.cuda.synchronize()
+    finally:
+        pdc.set_programmatic_launch(False)
+    for a, b, c, case in zip(plain, eager, outs, cases):
+        assert torch.equal(a, b) and torch.equal(a, c)
+        close(a, orc.paged_decode(case["q"], case["k_pool"], case["v_pool"], case["block_tables"],
+                                  case["seq_lens"]))
+
+
 def test_long_uniform_batch_property_checks():
     """Full-size shape of the benchmark workload (batch 16 x 16K), checked by
     properties that need no CPU pass over 268 MB: (1) permuting which physical
