@@ -19,7 +19,7 @@ One JSON line comes out:
              lengths and slots shipped to the device), cache.write() and
              paged_decode_attention() per layer, eagerly, and reads the
              outputs back to the host.
-  roofline   the decode kernel, launched eagerly layer by layer, timed with CUDA events.
+  roofline   the decode kernel alone: CUDA events around replays of a graph of its launches.
   cpu_baseline  the numpy oracle on the host cores, one layer call.
 `--impl reference` times that CPU oracle instead (rank 0 only).
 
@@ -61,7 +61,7 @@ METRIC = "paged decode-attn HBM GB/s"
 FALLBACK_HBM_GBS = 6650.0
 # DRAM bytes per launch of the split-KV kernel on the default workload, from the
 # Nsight Compute capture summarised under profiles/ (null until captured).
-NCU_TRAFFIC_BYTES = None
+NCU_TRAFFIC_BYTES = 273_000_000     # profiles/decode_kernel_fp16_dense_b16_16k.md section 3
 
 
 def measured_peak():
@@ -324,29 +324,57 @@ def main():
     ms_step = ms_total / args.steps
     value = world * step_bytes / (ms_step * 1e-3) / 1e9
 
-    # Roofline: the decode kernel, one eager launch per layer, CUDA events on the
-    # launching (current) stream.
-    for i in range(layers):
-        layer_call(i)
-    torch.cuda.synchronize()
-    reps = max(3, min(20, args.steps))
-    k0, k1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    k0.record()
-    for _ in range(reps):
+    # Roofline: the dominant kernel's average launch duration, timed with CUDA
+    # events on the launching stream around replays of a graph that holds one
+    # launch per layer (so neither Python nor launch latency is in it).
+    def graph_us(fn, reps):
         for i in range(layers):
-            layer_call(i)
-    k1.record()
-    torch.cuda.synchronize()
-    kernel_ms = k0.elapsed_time(k1) / (reps * layers)
+            fn(i)
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            for i in range(layers):
+                fn(i)
+        for _ in range(3):
+            g.replay()
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(reps):
+            g.replay()
+        b.record()
+        torch.cuda.synchronize()
+        return a.elapsed_time(b) * 1e3 / (reps * layers)
+
+    reps = max(3, min(50, args.steps))
+    breakdown = None
+    if kind.startswith("sparse"):
+        pages_ = -(-context // 16)
+        keep_ = ps.budget(0.5, pages_)
+        sel_fixed = ps.select(ps.page_scores(w["q"][0], *w["bounds"][0], tables, lens), keep_).clone()
+        scores_fixed = ps.page_scores(w["q"][0], *w["bounds"][0], tables, lens).clone()
+        breakdown = {
+            "page_index_us": round(graph_us(lambda i: ps.page_scores(w["q"][i], *w["bounds"][i], tables, lens), reps), 2),
+            "topk_pages_us": round(graph_us(lambda i: ps.select(scores_fixed, keep_), reps), 2),
+            "sparse_decode_us": round(graph_us(lambda i: ps.sparse_decode(
+                w["q"][i], w["pools"][i][0], w["pools"][i][1], tables, lens, sel_fixed, ratio=0.5), reps), 2),
+        }
+        kernel_ms = breakdown["sparse_decode_us"] * 1e-3
+        roof_bytes = batch * 2 * keep_ * 16 * 512
+        kernel_name = "decode_kernel<sparse> (attention over the selected pages)"
+    else:
+        kernel_ms = graph_us(lambda i: layer_call(i), reps) * 1e-3
+        roof_bytes = step_bytes // layers
     clocks = sampler.summary(t_wall0, t_wall1)
     peak, peak_kind = measured_peak()
-    layer_bytes = step_bytes // layers
+    layer_bytes = roof_bytes
     achieved = layer_bytes / (kernel_ms * 1e-3) / 1e9
     roofline = {"bound": "hbm", "achieved": round(achieved, 1), "peak": peak, "unit": "GB/s",
-                "frac": round(achieved / peak, 4), "traffic": NCU_TRAFFIC_BYTES,
+                "frac": round(achieved / peak, 4),
+                "traffic": NCU_TRAFFIC_BYTES if default_workload and args.kernel == "mma" else None,
                 "peak_kind": f"of {peak_kind}", "kernel": kernel_name,
                 "kernel_us": round(kernel_ms * 1e3, 2), "algorithmic_bytes_per_launch": layer_bytes,
-                "frac_of_8TBs": round(achieved / 8000.0, 4)}
+                "frac_of_8TBs": round(achieved / 8000.0, 4), "breakdown": breakdown}
 
     # End to end through the public API with host buffers.
     e2e = None

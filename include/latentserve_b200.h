@@ -222,7 +222,7 @@ int ls_page_index_heads(const void* q, const void* kmin, const void* kmax,
                         void* stream);
 
 /* Top-k pages per (sequence, KV head): sel int32 [B,H,k] (sl_b, sl_h), score
- * descending, ties to the lower page index.
+ * descending, ties to the lower page index. num_pages <= 8192 (a 128K context).
  * Replaces torch.topk(..., sorted=True) in `select`, kernels/cuda/paged_sparse.py:164-168. */
 int ls_topk_pages(const float* scores, int32_t* sel, int batch, int kv_heads, int num_pages, int k,
                   int64_t ss_b, int64_t ss_h, int64_t sl_b, int64_t sl_h, void* stream);

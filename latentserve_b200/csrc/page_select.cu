@@ -11,15 +11,21 @@
 //                        whose tie order is unspecified; this one is fixed)
 //
 // The score arithmetic keeps the reference's fp32 evaluation order exactly --
-// lane l sums channels 4l..4l+3 left to right starting from 0, then an xor
-// butterfly over lanes with offsets 16, 8, 4, 2, 1 -- so that scores, and with
-// them the selected indices, are reproducible bit for bit on a CPU.
+// lane l sums channels 4l..4l+3 left to right starting from 0, then pairwise
+// sums over lanes at distance 16, 8, 4, 2, 1 -- so that scores, and with them
+// the selected indices, are reproducible bit for bit on a CPU. The reference
+// does that with an all-lanes butterfly per value (5 shuffles each); here 32
+// values (4 pages x 8 padded query rows) are reduced together, each step
+// keeping half of the values per lane, which forms exactly the same pairwise
+// sums with 31 shuffles for all 32.
 #include "ls_common.cuh"
 
 namespace ls {
 
 constexpr int kIndexWarps = 4;
-constexpr int kPagesPerWarp = 4;
+constexpr int kGroup = 4;                    // pages reduced together
+constexpr int kGroupsPerWarp = 4;
+constexpr int kPagesPerWarp = kGroup * kGroupsPerWarp;
 
 __device__ __forceinline__ void unpack4h(uint2 raw, float (&f)[4]) {
     const __half2* h2 = reinterpret_cast<const __half2*>(&raw);
@@ -27,27 +33,52 @@ __device__ __forceinline__ void unpack4h(uint2 raw, float (&f)[4]) {
     f[0] = a.x; f[1] = a.y; f[2] = b.x; f[3] = b.y;
 }
 
-// Bounds of all 8 (padded) query rows for one page. Every row keeps the order
-// "lane sum of 4 channels from 0, then xor butterfly 16, 8, 4, 2, 1"; the rows'
-// butterflies are interleaved so their shuffle latencies overlap.
-__device__ __forceinline__ void bound_rows(const float (&q)[8][4], const float (&lo)[4],
-                                           const float (&hi)[4], float (&s)[8]) {
+// One halving step of the joint reduction: N values per lane in, N/2 out.
+// Lanes with bit OFF clear keep values [0, N/2), the others [N/2, N); each
+// kept value becomes own + partner's, the same two operands the all-lanes
+// butterfly adds at this distance.
+template <int N, int OFF>
+__device__ __forceinline__ void halve(const float (&in)[N], float (&out)[N / 2], int lane) {
+    const bool upper = (lane & OFF) != 0;
 #pragma unroll
-    for (int r = 0; r < 8; ++r) {
-        float t = 0.f;
-#pragma unroll
-        for (int j = 0; j < 4; ++j)
-            t = __fadd_rn(t, fmaxf(__fmul_rn(q[r][j], lo[j]), __fmul_rn(q[r][j], hi[j])));
-        s[r] = t;
+    for (int k = 0; k < N / 2; ++k) {
+        const float keep = upper ? in[k + N / 2] : in[k];
+        const float send = upper ? in[k] : in[k + N / 2];
+        out[k] = __fadd_rn(keep, __shfl_xor_sync(LS_FULL_MASK, send, OFF));
     }
-#pragma unroll
-    for (int off = 16; off > 0; off >>= 1)
-#pragma unroll
-        for (int r = 0; r < 8; ++r) s[r] = __fadd_rn(s[r], __shfl_xor_sync(LS_FULL_MASK, s[r], off));
 }
 
-// grid (ceil(max_pages / 16), H, B), block 128. PER_HEAD = 0: scores [B,H,P];
-// PER_HEAD = 1: heads [B,H,R,P].
+// Bounds of 8 (padded) query rows x 4 pages. On return lane l holds the
+// complete bound of page (l >> 3) of the group, query row (l & 7).
+__device__ __forceinline__ float bounds_4x8(const float (&q)[8][4], const uint2 (&lo_raw)[kGroup],
+                                            const uint2 (&hi_raw)[kGroup], int lane) {
+    float x[32];
+#pragma unroll
+    for (int pg = 0; pg < kGroup; ++pg) {
+        float lo[4], hi[4];
+        unpack4h(lo_raw[pg], lo);
+        unpack4h(hi_raw[pg], hi);
+#pragma unroll
+        for (int r = 0; r < 8; ++r) {
+            float t = 0.f;
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+                t = __fadd_rn(t, fmaxf(__fmul_rn(q[r][j], lo[j]), __fmul_rn(q[r][j], hi[j])));
+            x[pg * 8 + r] = t;
+        }
+    }
+    float a[16], b[8], c[4], d[2], e[1];
+    halve<32, 16>(x, a, lane);
+    halve<16, 8>(a, b, lane);
+    halve<8, 4>(b, c, lane);
+    halve<4, 2>(c, d, lane);
+    halve<2, 1>(d, e, lane);
+    return e[0];
+}
+
+// grid (ceil(max_pages / 64), H, B), block 128: a warp scores 16 pages, four
+// groups of four.
+// PER_HEAD = 0: scores [B,H,P]; PER_HEAD = 1: heads [B,H,R,P].
 template <int PER_HEAD>
 __global__ void __launch_bounds__(kIndexWarps * 32)
 page_index_kernel(const __half* __restrict__ q, const __half* __restrict__ kmin,
@@ -63,6 +94,17 @@ page_index_kernel(const __half* __restrict__ q, const __half* __restrict__ kmin,
     const int L = max(seq_lens[b], 0);
     const int np = min((L + LS_PAGE - 1) / LS_PAGE, table_stride);
 
+    // Lane j < 16 fetches the block id of page first + j (-1: nothing to score).
+    int my_blk = -1;
+    {
+        const int p = first + lane;
+        bool need = lane < kPagesPerWarp && p < max_pages && p < np;
+        if (!PER_HEAD) need = need && !(p == 0 || p >= np - recent);
+        if (need) {
+            const int id = block_tables[(long long)b * table_stride + p];
+            if (id >= 0 && id < num_blocks) my_blk = id;
+        }
+    }
     float qf[8][4];
 #pragma unroll
     for (int r = 0; r < 8; ++r) {
@@ -75,62 +117,39 @@ page_index_kernel(const __half* __restrict__ q, const __half* __restrict__ kmin,
         }
     }
 
-    // Issue every page's loads before any arithmetic.
-    uint2 lo_raw[kPagesPerWarp], hi_raw[kPagesPerWarp];
-    bool scored[kPagesPerWarp];
+    auto fetch = [&](int g, uint2 (&lo_raw)[kGroup], uint2 (&hi_raw)[kGroup]) {
 #pragma unroll
-    for (int k = 0; k < kPagesPerWarp; ++k) {
-        const int p = first + k;
-        bool need = p < max_pages && p < np;
-        if (!PER_HEAD) need = need && !(p == 0 || p >= np - recent);
-        int blk = 0;
-        if (need) {
-            blk = block_tables[(long long)b * table_stride + p];
-            need = blk >= 0 && blk < num_blocks;
+        for (int k = 0; k < kGroup; ++k) {
+            const int blk = __shfl_sync(LS_FULL_MASK, my_blk, g * kGroup + k);
+            lo_raw[k] = make_uint2(0, 0);
+            hi_raw[k] = make_uint2(0, 0);
+            if (blk >= 0) {
+                lo_raw[k] = *reinterpret_cast<const uint2*>(kmin + blk * sb_b + h * sb_h + lane * 4);
+                hi_raw[k] = *reinterpret_cast<const uint2*>(kmax + blk * sb_b + h * sb_h + lane * 4);
+            }
         }
-        scored[k] = need;
-        lo_raw[k] = make_uint2(0, 0);
-        hi_raw[k] = make_uint2(0, 0);
-        if (need) {
-            lo_raw[k] = *reinterpret_cast<const uint2*>(kmin + blk * sb_b + h * sb_h + lane * 4);
-            hi_raw[k] = *reinterpret_cast<const uint2*>(kmax + blk * sb_b + h * sb_h + lane * 4);
-        }
-    }
+    };
+    // Every page's bounds are requested before anything is reduced: one DRAM
+    // round trip for the warp's 16 pages.
+    uint2 lo_all[kGroupsPerWarp][kGroup], hi_all[kGroupsPerWarp][kGroup];
 #pragma unroll
-    for (int k = 0; k < kPagesPerWarp; ++k) {
-        const int p = first + k;
-        if (p >= max_pages) break;
-        float lo[4], hi[4];
-        unpack4h(lo_raw[k], lo);
-        unpack4h(hi_raw[k], hi);
-        float s[8];
-        if (scored[k]) {                                // warp-uniform
-            bound_rows(qf, lo, hi, s);
-        } else {
+    for (int g = 0; g < kGroupsPerWarp; ++g) fetch(g, lo_all[g], hi_all[g]);
 #pragma unroll
-            for (int r = 0; r < 8; ++r) s[r] = 0.f;
-        }
+    for (int g = 0; g < kGroupsPerWarp; ++g) {
+        float s = bounds_4x8(qf, lo_all[g], hi_all[g], lane);
+        const int p = first + g * kGroup + (lane >> 3), r = lane & 7;
+        const int blk = __shfl_sync(LS_FULL_MASK, my_blk, g * kGroup + (lane >> 3));
         if (PER_HEAD) {
             // Pages past the end get a finite 0: their token count of zero
             // removes them downstream, and a stale NaN here would not.
-#pragma unroll
-            for (int r = 0; r < 8; ++r)
-                if (r < n_rep && lane == 0) out[b * ss_b + h * ss_h + r * ss_r + p] = s[r];
+            if (p < max_pages && r < n_rep) out[b * ss_b + h * ss_h + r * ss_r + p] = blk >= 0 ? s : 0.f;
         } else {
-            float best;
-            if (p >= np) {
-                best = neg_inf();                       // past the end: never chosen
-            } else if (p == 0 || p >= np - recent) {
-                best = pos_inf();                       // sink and recent pages: always kept
-            } else {
-                best = neg_inf();
-                if (scored[k]) {
+            if (r >= n_rep || blk < 0) s = neg_inf();
 #pragma unroll
-                    for (int r = 0; r < 8; ++r)
-                        if (r < n_rep) best = fmaxf(best, s[r]);
-                }
-            }
-            if (lane == 0) out[b * ss_b + h * ss_h + p] = best;
+            for (int off = 1; off < 8; off <<= 1) s = fmaxf(s, __shfl_xor_sync(LS_FULL_MASK, s, off));
+            if (p >= np) s = neg_inf();                                  // past the end: never chosen
+            else if (p == 0 || p >= np - recent) s = pos_inf();          // sink and recent: always kept
+            if (r == 0 && p < max_pages) out[b * ss_b + h * ss_h + p] = s;
         }
     }
 }
@@ -142,53 +161,79 @@ __device__ __forceinline__ uint32_t order_key(float x) {
     return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
 }
 
-constexpr int kTopkThreads = 128;
-constexpr int kTopkPerThread = 2;
-constexpr int kTopkTile = kTopkThreads * kTopkPerThread;
+constexpr int kTopkPerThread = 8;
+constexpr int kTopkMaxRow = 8192;              // 1024 threads x 8 keys
 
-// Rank by counting: rank(i) = #{j : s_j > s_i} + #{j < i : s_j == s_i}. The
-// entry of rank r < k lands at sel[r], which is the stable descending order.
-// grid (ceil(n / 256), B*H); a thread ranks two candidates (i and i + 128 of
-// the CTA's 256-entry tile) against the whole row held in shared memory, so
-// each 16-byte broadcast read of four keys serves eight comparisons.
-// O(n^2 / grid) compares; n is a block-table width (2048 pages at 32K context).
-__global__ void __launch_bounds__(kTopkThreads)
-topk_pages_kernel(const float* __restrict__ scores, int* __restrict__ sel, int n, int k, int heads,
-                  long long ss_b, long long ss_h, long long sl_b, long long sl_h) {
-    extern __shared__ uint32_t keys[];
-    const int bh = blockIdx.y, b = bh / heads, h = bh % heads;
+typedef unsigned long long u64;
+
+// One compare-exchange of a bitonic network on the key this lane holds for
+// position i, against the key `other` of position i ^ stride.
+__device__ __forceinline__ u64 bitonic_keep(u64 mine, u64 other, int i, int stride, int size) {
+    const bool lower = (i & stride) == 0, descending = (i & size) == 0;
+    const u64 mx = mine > other ? mine : other, mn = mine > other ? other : mine;
+    return (lower == descending) ? mx : mn;
+}
+
+// Deterministic top-k by a full sort of the row: one CTA per (sequence, head)
+// sorts 64-bit keys (order_key(score) << 32 | ~page) to descending order with a
+// bitonic network, so equal scores come out with the lower page first, and
+// writes the first k pages. Each thread holds 8 consecutive keys in registers:
+// exchanges at distance 1, 2, 4 stay inside the thread, distances 8..128 are
+// warp shuffles, and only distances >= 256 go through shared memory with a
+// barrier (6 of the 66 rounds for a 2048-page row).
+__global__ void __launch_bounds__(kTopkMaxRow / kTopkPerThread)
+topk_pages_kernel(const float* __restrict__ scores, int* __restrict__ sel, int n, int n_pow2, int k,
+                  int heads, long long ss_b, long long ss_h, long long sl_b, long long sl_h) {
+    extern __shared__ __align__(8) u64 keys[];
+    const int bh = blockIdx.x, b = bh / heads, h = bh % heads;
     const float* row = scores + b * ss_b + h * ss_h;
-    const int n4 = (n + 3) & ~3;
-    for (int j = threadIdx.x; j < n4; j += kTopkThreads) keys[j] = j < n ? order_key(row[j]) : 0u;
-    __syncthreads();
-    const int tile_lo = blockIdx.x * kTopkTile, tile_hi = min(n4, tile_lo + kTopkTile);
-    const int i0 = tile_lo + threadIdx.x, i1 = i0 + kTopkThreads;
-    const uint32_t m0 = i0 < n ? keys[i0] : 0xffffffffu;
-    const uint32_t m1 = i1 < n ? keys[i1] : 0xffffffffu;
-    int rank0 = 0, rank1 = 0;
-    const uint4* k4 = reinterpret_cast<const uint4*>(keys);
-    // Entries before this CTA's tile precede every candidate of the tile: ties count.
-#pragma unroll 4
-    for (int j = 0; j < tile_lo / 4; ++j) {
-        const uint4 v = k4[j];
-        rank0 += (v.x >= m0) + (v.y >= m0) + (v.z >= m0) + (v.w >= m0);
-        rank1 += (v.x >= m1) + (v.y >= m1) + (v.z >= m1) + (v.w >= m1);
+    const int base = threadIdx.x * kTopkPerThread;
+    u64 v[kTopkPerThread];
+#pragma unroll
+    for (int e = 0; e < kTopkPerThread; ++e) {
+        const int i = base + e;
+        v[e] = 0ull;                               // padding sorts after every real entry
+        if (i < n) v[e] = ((u64)order_key(row[i]) << 32) | (0xffffffffu - (uint32_t)i);
     }
-    for (int j = tile_lo; j < tile_hi; ++j) {
-        const uint32_t v = keys[j];
-        rank0 += (v > m0) || (v == m0 && j < i0);
-        rank1 += (v > m1) || (v == m1 && j < i1);
+    for (int size = 2; size <= n_pow2; size <<= 1) {
+        int stride = size >> 1;
+        for (; stride >= 32 * kTopkPerThread; stride >>= 1) {          // other warps: shared memory
+#pragma unroll
+            for (int e = 0; e < kTopkPerThread; ++e) keys[base + e] = v[e];
+            __syncthreads();
+#pragma unroll
+            for (int e = 0; e < kTopkPerThread; ++e)
+                v[e] = bitonic_keep(v[e], keys[(base + e) ^ stride], base + e, stride, size);
+            __syncthreads();
+        }
+        for (; stride >= kTopkPerThread; stride >>= 1) {               // same warp: shuffles
+            const int lane_mask = stride / kTopkPerThread;
+#pragma unroll
+            for (int e = 0; e < kTopkPerThread; ++e) {
+                const u64 other = __shfl_xor_sync(LS_FULL_MASK, v[e], lane_mask);
+                v[e] = bitonic_keep(v[e], other, base + e, stride, size);
+            }
+        }
+#pragma unroll
+        for (int st = kTopkPerThread / 2; st > 0; st >>= 1) {          // same thread: registers
+            if (st <= stride) {
+#pragma unroll
+                for (int e = 0; e < kTopkPerThread; ++e) {
+                    if ((e & st) == 0) {
+                        const bool descending = ((base + e) & size) == 0;
+                        const u64 a = v[e], c = v[e | st];
+                        const u64 mx = a > c ? a : c, mn = a > c ? c : a;
+                        v[e] = descending ? mx : mn;
+                        v[e | st] = descending ? mn : mx;
+                    }
+                }
+            }
+        }
     }
-#pragma unroll 4
-    for (int j = tile_hi / 4; j < n4 / 4; ++j) {
-        const uint4 v = k4[j];
-        rank0 += (v.x > m0) + (v.y > m0) + (v.z > m0) + (v.w > m0);
-        rank1 += (v.x > m1) + (v.y > m1) + (v.z > m1) + (v.w > m1);
-    }
-    // Padding keys (0) never outrank a real entry: key(x) >= 1 for every
-    // float except NaN patterns with the sign bit set, which sort last.
-    if (i0 < n && rank0 < k) sel[b * sl_b + h * sl_h + rank0] = i0;
-    if (i1 < n && rank1 < k) sel[b * sl_b + h * sl_h + rank1] = i1;
+    int* dst = sel + b * sl_b + h * sl_h;
+#pragma unroll
+    for (int e = 0; e < kTopkPerThread; ++e)
+        if (base + e < k) dst[base + e] = (int)(0xffffffffu - (uint32_t)(v[e] & 0xffffffffull));
 }
 
 }  // namespace ls
@@ -252,15 +297,17 @@ int ls_topk_pages(const float* scores, int32_t* sel, int batch, int kv_heads, in
     if (!scores || !sel) return LS_ERR_NULL_POINTER;
     if (batch <= 0 || kv_heads <= 0 || num_pages <= 0 || k <= 0 || k > num_pages)
         return LS_ERR_BAD_SHAPE;
-    const size_t smem = sizeof(uint32_t) * (size_t)((num_pages + 3) & ~3);
-    if (smem > 200 * 1024 || (long long)batch * kv_heads > 65535) return LS_ERR_TOO_LARGE;
+    int n_pow2 = 32 * ls::kTopkPerThread;           // at least one full warp of keys
+    while (n_pow2 < num_pages) n_pow2 <<= 1;
+    if (n_pow2 > ls::kTopkMaxRow || (long long)batch * kv_heads > 2147483647LL) return LS_ERR_TOO_LARGE;
     if (((uintptr_t)scores & 3) || ((uintptr_t)sel & 3)) return LS_ERR_MISALIGNED;
+    const size_t smem = sizeof(unsigned long long) * (size_t)n_pow2;
     cudaError_t e = cudaFuncSetAttribute(ls::topk_pages_kernel,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
-    dim3 grid((num_pages + ls::kTopkTile - 1) / ls::kTopkTile, batch * kv_heads);
-    ls::topk_pages_kernel<<<grid, ls::kTopkThreads, smem, static_cast<cudaStream_t>(stream)>>>(
-        scores, sel, num_pages, k, kv_heads, ss_b, ss_h, sl_b, sl_h);
+    ls::topk_pages_kernel<<<batch * kv_heads, n_pow2 / ls::kTopkPerThread, smem,
+                            static_cast<cudaStream_t>(stream)>>>(
+        scores, sel, num_pages, n_pow2, k, kv_heads, ss_b, ss_h, sl_b, sl_h);
     return (int)cudaGetLastError();
 }
 

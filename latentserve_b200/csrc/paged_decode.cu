@@ -48,6 +48,12 @@ namespace ls {
 #ifndef LS_STAGES
 #define LS_STAGES 3                 // cp.async ring depth per warp
 #endif
+#ifndef LS_INT8_STAGES
+#define LS_INT8_STAGES 2            // ring depth of the INT8 kernel (smaller stages, more CTAs)
+#endif
+#ifndef LS_INT8_CTAS
+#define LS_INT8_CTAS 3              // resident CTAs per SM the INT8 kernel is compiled for
+#endif
 #ifndef LS_EVICT_FIRST
 #define LS_EVICT_FIRST 1            // L2 evict-first policy on the (read-once) KV page loads
 #endif
@@ -280,6 +286,7 @@ struct PoolFp16 {
 // Tensor-core state for fp16 pools.
 struct MmaFp16 {
     using Pool = PoolFp16;
+    static constexpr int kMinCtas = 2;
     uint32_t qb[8][2];
     float o[8][4];             // O^T: tile mt = dims 16 mt + g (+8), rows 2t, 2t+1
     float m[2], l[2];
@@ -352,6 +359,7 @@ struct MmaFp16 {
 template <int R>
 struct SimtFp16 {
     using Pool = PoolFp16;
+    static constexpr int kMinCtas = 2;
     float qf[R][8];
     float acc[R][8];
     float m[R], l[R];
@@ -609,6 +617,7 @@ __device__ __forceinline__ float lds32f(uint32_t addr) {
 template <int ASYM>
 struct MmaInt8 {
     using Pool = PoolInt8<ASYM>;
+    static constexpr int kMinCtas = LS_INT8_CTAS;
     float qf[32];              // Q[row g][32t .. 32t+31] in fp32 (row g < n_rep, else 0)
     float o[8][4];             // O^T: tile mt = dims 16g + 2mt (regs 0,1) and +1 (regs 2,3)
     float m[2], l[2];
@@ -868,7 +877,7 @@ __device__ __forceinline__ void merge_partials(const float* part_acc, const floa
 
 // ---------------------------------------------------------------------------
 template <class State, int MODE, int STAGES>
-__global__ void __launch_bounds__(kThreads, 2) decode_kernel(const DecodeParams p) {
+__global__ void __launch_bounds__(kThreads, State::kMinCtas) decode_kernel(const DecodeParams p) {
     extern __shared__ __align__(1024) unsigned char smem[];
     using Pool = typename State::Pool;
     constexpr int STAGE_BYTES = Pool::STAGE_BYTES;
@@ -1242,9 +1251,9 @@ int ls_paged_decode_int8(const void* q, const void* k_pool, const void* v_pool,
     if (flags & ~LS_LAUNCH_PROGRAMMATIC) return LS_ERR_UNSUPPORTED;
     const bool pdl = (flags & LS_LAUNCH_PROGRAMMATIC) != 0;
     if (k_zero)
-        rc = ls::launch_decode<ls::MmaInt8<1>, LS_MODE_DENSE, ls::kStages>(p, s, pdl);
+        rc = ls::launch_decode<ls::MmaInt8<1>, LS_MODE_DENSE, LS_INT8_STAGES>(p, s, pdl);
     else
-        rc = ls::launch_decode<ls::MmaInt8<0>, LS_MODE_DENSE, ls::kStages>(p, s, pdl);
+        rc = ls::launch_decode<ls::MmaInt8<0>, LS_MODE_DENSE, LS_INT8_STAGES>(p, s, pdl);
     return rc;
 }
 

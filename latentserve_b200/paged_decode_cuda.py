@@ -34,6 +34,8 @@ _PROGRAMMATIC = {"on": os.environ.get("LATENTSERVE_B200_PDL", "0") == "1"}
 ROWS_PER_PARTIAL = 8                # query rows a partial holds (GQA ratio <= 8)
 MIN_CHUNK_PAGES = 8                 # never cut the page axis finer than this
 CTAS_PER_SM = 2                     # resident CTAs per SM the kernels are sized for
+# ... and for the INT8 kernel (must match LS_INT8_CTAS the library was built with)
+INT8_CTAS_PER_SM = int(os.environ.get("LATENTSERVE_B200_INT8_CTAS", "3"))
 MAX_BATCH = 1024
 
 _SCRATCH: dict = {}
@@ -102,11 +104,11 @@ def eligible(q: torch.Tensor, k_pool: torch.Tensor, k_scale=None, k_residual=Non
 
 
 def choose_chunks(device: torch.device, kv_heads: int, num_splits: Optional[int] = None,
-                  batch: int = 1) -> int:
+                  batch: int = 1, ctas_per_sm: int = CTAS_PER_SM) -> int:
     """Pieces the batch's page axis is cut into: one per resident CTA column
     (grid = chunks x KV heads fills every SM `CTAS_PER_SM` times). A caller's
     `num_splits` caps it at batch x num_splits."""
-    chunks = max(1, (CTAS_PER_SM * sm_count(device)) // max(1, kv_heads))
+    chunks = max(1, (ctas_per_sm * sm_count(device)) // max(1, kv_heads))
     if num_splits:
         chunks = max(1, min(chunks, batch * num_splits))
     return chunks
@@ -167,8 +169,8 @@ def paged_decode_cuda(q, k_pool, v_pool, block_tables, seq_lens, max_seq_len: in
     if block_tables.stride(-1) != 1 or (seq_lens.numel() > 1 and seq_lens.stride(0) != 1):
         raise ValueError("block tables and sequence lengths must be contiguous rows")
     scale = softmax_scale if softmax_scale is not None else 1.0 / math.sqrt(d)
-    chunks = choose_chunks(q.device, h_kv, num_splits, b)
     int8 = k_pool.dtype == torch.int8
+    chunks = choose_chunks(q.device, h_kv, num_splits, b, INT8_CTAS_PER_SM if int8 else CTAS_PER_SM)
     tag = "cuda_i8" if int8 else "cuda"
     acc, m, l, seg = _partials(q, chunks, tag)
     out = scratch(tag + "_out", (b, h_kv, n_rep, d), q.dtype, q.device)
