@@ -57,6 +57,15 @@ WORKLOADS = {
     "sparse50_b8_32k": (8, 32768, 8),
     "sparse50_b8_8k": (8, 8192, 8),            # small case for profiler captures
 }
+# Whole decode steps of a random-init Qwen2.5-1.5B-shaped model (28 layers) over the
+# paged caches: name -> (batch, context, kv cache kind, sparse ratio, shared prefix)
+STEP_WORKLOADS = {
+    "qwen_step_b16_16k": (16, 16384, "fp16", None, 0),
+    "qwen_step_b16_16k_int8": (16, 16384, "int8", None, 0),
+    "qwen_step_b16_16k_sparse50": (16, 16384, "fp16", 0.5, 0),
+    "qwen_step_b64_ragged": (64, "loguniform_1k_32k", "fp16", None, 4096),
+    "qwen_step_b64_ragged_int8": (64, "loguniform_1k_32k", "int8", None, 4096),
+}
 METRIC = "paged decode-attn HBM GB/s"
 FALLBACK_HBM_GBS = 6650.0
 # DRAM bytes per launch of the split-KV kernel on the default workload, from the
@@ -189,7 +198,8 @@ def main():
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="dense_fp16_b16_16k", choices=sorted(WORKLOADS))
+    ap.add_argument("--workload", default="dense_fp16_b16_16k",
+                    choices=sorted(WORKLOADS) + sorted(STEP_WORKLOADS))
     ap.add_argument("--kernel", default="mma", choices=["mma", "simt"],
                     help="split-KV kernel variant (simt = CUDA-core kernel, for profiling)")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg")
@@ -199,6 +209,9 @@ def main():
     ap.add_argument("--quick", action="store_true",
                     help="profiler runs: no e2e / CPU legs, no extension of the load for clock sampling")
     args = ap.parse_args()
+    if args.workload in STEP_WORKLOADS:
+        run_model_step(args)
+        return
     workload = WORKLOADS[args.workload]
     if args.quick:
         args.no_e2e = args.no_cpu = True
@@ -419,6 +432,140 @@ def main():
             "gpu_launches": launches_per_layer * layers * args.steps, "clocks": clocks,
         }
         print(json.dumps(line))
+    if dist is not None:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def run_model_step(args):
+    """Whole decode steps (all 28 layers: GEMMs, norms, RoPE, append, attention,
+    output head, greedy argmax) replayed from one CUDA graph. Reports ms per step
+    (graph replay only, and the full loop with cache.advance() on the host) and
+    tokens per second; with N ranks every rank serves its own sequences."""
+    import random
+
+    import numpy as np
+    import torch
+
+    from latentserve_b200 import _lib, cache as lc, decode_step as ds, paged_decode_cuda as pdc
+
+    _lib.lib()
+    pdc.set_programmatic_launch(not args.no_pdl)
+    batch, context, kind, ratio, prefix = STEP_WORKLOADS[args.workload]
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    dev = torch.device("cuda", local)
+    torch.cuda.set_device(dev)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=dev)
+    rng = np.random.default_rng(1234 + rank)
+    if context == "loguniform_1k_32k":
+        lens = np.exp(rng.uniform(np.log(1024), np.log(32768), size=batch)).astype(int).tolist()
+    else:
+        lens = [context] * batch
+    steps, warm = args.steps, max(3, args.warmup)
+    shape = ds.QwenShape()
+    room = steps + warm + 8
+    spec = lc.KVCacheSpec(num_layers=shape.num_layers, num_kv_heads=shape.kv_heads,
+                          head_dim=shape.head_dim, max_seq_len=max(lens) + room + 16,
+                          max_batch_size=batch, device=str(dev))
+    blocks = int(1.2 * sum(-(-(n + room) // 16) for n in lens)) + 64
+    cache = (lc.Int8PagedKVCache if kind == "int8" else lc.PagedKVCache)(spec, num_blocks=blocks)
+    g = torch.Generator(device=dev).manual_seed(rank)
+    for layer in range(shape.num_layers):          # synthetic history: random K/V everywhere
+        if kind == "int8":
+            cache.k_pool[layer].random_(-127, 128, generator=g)
+            cache.v_pool[layer].random_(-127, 128, generator=g)
+            cache.k_scale_pool[layer].uniform_(0.01, 0.03, generator=g)
+            cache.v_scale_pool[layer].uniform_(0.01, 0.03, generator=g)
+        else:
+            cache.k_pool[layer].normal_(generator=g)
+            cache.v_pool[layer].normal_(generator=g)
+    random.Random(rank).shuffle(cache.allocator._free)
+    shared, owners = [], []
+    if prefix:                                     # a quarter of the batch shares one ref-counted prefix
+        owners = [i for i in range(batch) if lens[i] > prefix][: max(1, batch // 4)]
+        if owners:
+            cache.tables[owners[0]].append(prefix)
+            shared = cache.tables[owners[0]].blocks[: prefix // 16]
+            for i in owners[1:]:
+                cache.attach_prefix(i, shared, prefix)
+            if kind == "int8":
+                cache._fin[owners[0]] = prefix // 16
+    for i, n in enumerate(lens):
+        have = cache.tables[i].length
+        cache.tables[i].append(n - 1 - have)
+        if kind == "int8":
+            cache._fin[i] = (n - 1) // 16
+    if ratio is not None:
+        cache.enable_page_bounds()
+    model = ds.DecodeModel(shape, dev, max_pos=max(lens) + room + 16, seed=rank)
+    model.set_sparse(ratio)
+    hint = max(lens) + room
+    runner = ds.GraphedStep(model, cache, batch, hint)
+    runner.tokens.random_(0, shape.vocab, generator=g)
+    cache.advance(1, batch_size=batch)
+    runner.positions.copy_(torch.tensor([n - 1 for n in cache.seq_lens], dtype=torch.long))
+    runner.capture()
+    for _ in range(warm):
+        cache.advance(1, batch_size=batch)
+        runner.step()
+    if dist is not None:
+        dist.barrier()
+    torch.cuda.synchronize()
+    sampler = ClockSampler(local)
+    sampler.start()
+    t_wall0 = time.time()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        cache.advance(1, batch_size=batch)
+        runner.step()
+    e1.record()
+    torch.cuda.synchronize()
+    loop_ms = e0.elapsed_time(e1) / steps
+    # Graph replay alone (lengths frozen), as the reference quotes its "graph-only" step.
+    r0, r1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    reps = max(10, min(steps, 100))
+    r0.record()
+    for _ in range(reps):
+        runner.graph.replay()
+    r1.record()
+    torch.cuda.synchronize()
+    graph_ms = r0.elapsed_time(r1) / reps
+    while time.time() < t_wall0 + 1.2:
+        runner.graph.replay()
+        torch.cuda.synchronize()
+    clocks = sampler.summary(t_wall0, time.time())
+    sampler.stop()
+    if dist is not None:
+        t = torch.tensor([loop_ms, graph_ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        loop_ms, graph_ms = float(t[0]), float(t[1])
+    mean_len = float(np.mean(lens)) + warm + steps / 2
+    kv_per_tok = shape.num_layers * shape.kv_heads * (292 if kind == "int8" else 512)
+    kv_bytes = mean_len * batch * kv_per_tok * (ratio if ratio else 1.0)
+    floor_ms = (kv_bytes + model.weight_bytes()) / (measured_peak()[0] * 1e9) * 1e3
+    if rank == 0:
+        print(json.dumps({
+            "metric": "Qwen2.5-1.5B decode step ms", "value": round(loop_ms, 4), "unit": "ms",
+            "n_gpus": world, "steps": steps, "warmup": warm, "ms_per_step": round(loop_ms, 4),
+            "higher_is_better": False, "scaling": "weak", "vs_baseline": None,
+            "dtype": "i8" if kind == "int8" else "f16", "data": "synthetic",
+            "config": {"workload": args.workload, "batch_per_gpu": batch,
+                       "context": f"min {min(lens)}, mean {int(np.mean(lens))}, max {max(lens)}",
+                       "kv_cache": kind, "sparse_ratio": ratio, "shared_prefix_tokens": prefix,
+                       "sequences_sharing_prefix": len(owners),
+                       "layers": shape.num_layers, "programmatic_launch": not args.no_pdl,
+                       "parallelism": f"replicas x{world} (sequence-sharded, no collective)"},
+            "graph_replay_ms": round(graph_ms, 4),
+            "tokens_per_s": round(world * batch / (loop_ms * 1e-3), 1),
+            "hbm_floor_ms": round(floor_ms, 4),
+            "frac_of_floor": round(floor_ms / graph_ms, 4), "clocks": clocks,
+        }))
     if dist is not None:
         dist.barrier()
         dist.destroy_process_group()

@@ -227,6 +227,49 @@ int ls_page_index_heads(const void* q, const void* kmin, const void* kmax,
 int ls_topk_pages(const float* scores, int32_t* sel, int batch, int kv_heads, int num_pages, int k,
                   int64_t ss_b, int64_t ss_h, int64_t sl_b, int64_t sl_h, void* stream);
 
+/* ---- The per-layer kernels around attention (the callers' side of the path) ---- */
+
+/* RMSNorm over fp16 rows, optionally fused with the residual add:
+ *   s = fp16(x + residual); res_out = s; y = fp16(weight * fp16(s * rsqrt(mean(s^2) + eps))).
+ * residual == res_out == NULL: plain RMSNorm of x. n % 8 == 0, rows 16-byte aligned.
+ * Replaces the Triton `_rms_norm_kernel`, kernels/fused_elementwise.py:118-137
+ * (torch forms `rms_norm_ref` / `fused_add_rms_norm_ref`, :75-86). */
+int ls_rms_norm(const void* x, const void* residual, const void* weight, void* y, void* res_out,
+                int rows, int n, float eps, int64_t sx, int64_t sr, int64_t sy, int64_t sro,
+                void* stream);
+
+/* out[r, i] = fp16(fp16(silu(gate_up[r, i])) * gate_up[r, inter + i]), fp16 rows.
+ * Replaces the Triton `_silu_mul_kernel`, kernels/fused_elementwise.py:140-151
+ * (torch form `silu_and_mul_ref`, :89-91). */
+int ls_silu_mul(const void* gate_up, void* out, int rows, int inter, int64_t sgu, int64_t sout,
+                void* stream);
+
+/* RoPE of the query and key heads of a fused QKV projection row, fused with the
+ * KV append of the fp16 cache: one launch writes q_out [B, q_heads, 128] (rotated),
+ * the rotated K row and the V row at flat slot slots[b] of the pools, and the
+ * page's K bounds when kmin/kmax are given.
+ *   qkv fp16 [B, (q_heads + 2 kv_heads) * 128] (row stride s_qkv), heads in q, k, v order;
+ *   cos, sin fp16 [max_pos, 128] (row stride s_cos), halves duplicated; positions int64 [B].
+ * Rounding as the reference's rope (three fp16 roundings per output).
+ * Replaces the Triton `_rope_kernel`, kernels/fused_elementwise.py:154-182 (torch form
+ * `rope_qk_ref`, :99-107) followed by PagedKVCache.write, cache/paged_cache.py:398-417. */
+int ls_rope_append_fp16(const void* qkv, const void* cos, const void* sin, const int64_t* positions,
+                        const int64_t* slots, void* q_out, void* k_pool, void* v_pool, void* kmin,
+                        void* kmax, int batch, int q_heads, int kv_heads, int head_dim, int page,
+                        int64_t max_pos, int64_t num_slots, int64_t s_qkv, int64_t s_cos, int64_t sq_b,
+                        int64_t sp_t, int64_t sp_h, int64_t sb_b, int64_t sb_h, void* stream);
+
+/* The same for the INT8 cache: rotated K into the fp16 residual (row res_idx[b]),
+ * V quantised per (token, head) and scattered, bit-exact with ls_int8_decode_write.
+ * Replaces `_rope_kernel` followed by `int8_decode_write`, kernels/cuda/int8_write.cu:45-78. */
+int ls_rope_append_int8(const void* qkv, const void* cos, const void* sin, const int64_t* positions,
+                        const int64_t* slots, const int64_t* res_idx, void* q_out, void* flat_v,
+                        float* flat_v_scale, float* flat_v_zero, void* k_res, int batch, int q_heads,
+                        int kv_heads, int head_dim, int64_t max_pos, int64_t num_slots,
+                        int64_t num_res, int64_t s_qkv, int64_t s_cos, int64_t sq_b, int asym,
+                        float eps, float qmax, float inv_qmax, float levels, float inv_levels,
+                        float offset, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -45,6 +45,10 @@ _PROTOTYPES = {
     "ls_page_index": [P, P, P, P, P, P] + [I] * 9 + [L] * 7 + [P],
     "ls_page_index_heads": [P, P, P, P, P, P] + [I] * 8 + [L] * 8 + [P],
     "ls_topk_pages": [P, P, I, I, I, I, L, L, L, L, P],
+    "ls_rms_norm": [P, P, P, P, P, I, I, F, L, L, L, L, P],
+    "ls_silu_mul": [P, P, I, I, L, L, P],
+    "ls_rope_append_fp16": [P] * 10 + [I] * 5 + [L] * 9 + [P],
+    "ls_rope_append_int8": [P] * 11 + [I] * 4 + [L] * 6 + [I] + [F] * 6 + [P],
 }
 
 

@@ -31,6 +31,7 @@ from typing import Optional, Sequence
 import numpy as np
 import torch
 
+from latentserve_b200 import fused_elementwise as fe
 from latentserve_b200 import int8_write as iw
 from latentserve_b200 import kv_write
 
@@ -307,6 +308,21 @@ class PagedKVCache(_PagedBase):
                                  self._flat_k[layer_idx], self._flat_v[layer_idx], kmin, kmax,
                                  self.block_size)
 
+    def rope_write(self, layer_idx: int, qkv: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor,
+                   positions: torch.Tensor, q_out: torch.Tensor, q_heads: int) -> None:
+        """One decode token per sequence, from the fused QKV projection row: rotate
+        q into `q_out`, rotate k and append it with v at the slots `advance(1)`
+        reserved (and update the page bounds) — one launch."""
+        b = qkv.shape[0]
+        slots = self._write_slots
+        if slots is None or slots.shape[0] < b or slots.shape[1] != 1:
+            raise RuntimeError("call advance(1, batch_size) before rope_write()")
+        kmin = self.kmin[layer_idx] if self._bounds_on else None
+        kmax = self.kmax[layer_idx] if self._bounds_on else None
+        fe.rope_append_fp16(qkv, cos, sin, positions, slots[:b, 0], q_out, self._flat_k[layer_idx],
+                            self._flat_v[layer_idx], kmin, kmax, q_heads, self.spec.num_kv_heads,
+                            self.block_size)
+
     def enable_page_bounds(self) -> None:
         """Keep each block's per-channel min / max of K for the sparse indexer.
         Bounds of blocks already written are rebuilt over their written rows."""
@@ -318,14 +334,16 @@ class PagedKVCache(_PagedBase):
         self.kmax = [torch.zeros_like(t) for t in self.kmin]
         self._bounds_on = True
         bs = self.block_size
-        for t in self.tables:
-            for p, blk in enumerate(t.blocks):
-                rows = min(bs, t.length - p * bs)
-                if rows <= 0:
-                    continue
-                for layer in range(len(self.k_pool)):
-                    self.kmin[layer][blk] = self.k_pool[layer][blk, :rows].amin(dim=0)
-                    self.kmax[layer][blk] = self.k_pool[layer][blk, :rows].amax(dim=0)
+        # Whole pool at once over all 16 rows, then the partly filled last page
+        # of each sequence again over its written rows only.
+        partial = [(t.blocks[(t.length - 1) // bs], t.length - (t.length - 1) // bs * bs)
+                   for t in self.tables if t.length % bs]
+        for layer in range(len(self.k_pool)):
+            self.kmin[layer].copy_(self.k_pool[layer].amin(dim=1))
+            self.kmax[layer].copy_(self.k_pool[layer].amax(dim=1))
+            for blk, rows in partial:
+                self.kmin[layer][blk] = self.k_pool[layer][blk, :rows].amin(dim=0)
+                self.kmax[layer][blk] = self.k_pool[layer][blk, :rows].amax(dim=0)
 
     def page_bounds(self, layer_idx: int):
         return (self.kmin[layer_idx], self.kmax[layer_idx]) if self._bounds_on else None
@@ -445,6 +463,21 @@ class Int8PagedKVCache(_PagedBase):
                 dtype=torch.int64, device=self.device)
             self._write_slots = self._prefill_slots
         self._ship_tables(active)
+
+    def rope_write(self, layer_idx: int, qkv: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor,
+                   positions: torch.Tensor, q_out: torch.Tensor, q_heads: int) -> None:
+        """As PagedKVCache.rope_write: rotated q out, rotated K into the residual,
+        V quantised on write, one launch."""
+        b = qkv.shape[0]
+        slots = self._write_slots
+        if slots is None or slots.shape[0] < b or slots.shape[1] != 1:
+            raise RuntimeError("call advance(1, batch_size) before rope_write()")
+        fe.rope_append_int8(qkv, cos, sin, positions, slots[:b, 0], self._k_res_idx_buf[:b], q_out,
+                            self._flat_v[layer_idx], self._flat_v_scale[layer_idx],
+                            self._flat_v_zero[layer_idx] if self.asymmetric else None,
+                            self._k_res_flat[layer_idx], q_heads, self.spec.num_kv_heads,
+                            asym=self.asymmetric, eps=_EPS, qmax=float(self.v_qmax),
+                            levels=float(self.v_levels), offset=float(self.v_offset))
 
     def write(self, layer_idx: int, k: torch.Tensor, v: torch.Tensor, start_pos: int = 0) -> None:
         b, h, n, d = k.shape

@@ -20,6 +20,8 @@
 // sums with 31 shuffles for all 32.
 #include "ls_common.cuh"
 
+#include <cstdlib>
+
 namespace ls {
 
 constexpr int kIndexWarps = 4;
@@ -50,7 +52,11 @@ __device__ __forceinline__ void halve(const float (&in)[N], float (&out)[N / 2],
 
 // Bounds of 8 (padded) query rows x 4 pages. On return lane l holds the
 // complete bound of page (l >> 3) of the group, query row (l & 7).
-__device__ __forceinline__ float bounds_4x8(const float (&q)[8][4], const uint2 (&lo_raw)[kGroup],
+// max(q * lo, q * hi) is evaluated as q * (q >= 0 ? hi : lo): with lo <= hi
+// (they are a page's channel minimum and maximum) that is the same product,
+// bit for bit, for one multiply instead of two and a max.
+__device__ __forceinline__ float bounds_4x8(const float (&q)[8][4], int n_rep,
+                                            const uint2 (&lo_raw)[kGroup],
                                             const uint2 (&hi_raw)[kGroup], int lane) {
     float x[32];
 #pragma unroll
@@ -61,9 +67,11 @@ __device__ __forceinline__ float bounds_4x8(const float (&q)[8][4], const uint2 
 #pragma unroll
         for (int r = 0; r < 8; ++r) {
             float t = 0.f;
+            if (r < n_rep) {
 #pragma unroll
-            for (int j = 0; j < 4; ++j)
-                t = __fadd_rn(t, fmaxf(__fmul_rn(q[r][j], lo[j]), __fmul_rn(q[r][j], hi[j])));
+                for (int j = 0; j < 4; ++j)
+                    t = __fadd_rn(t, __fmul_rn(q[r][j], q[r][j] >= 0.f ? hi[j] : lo[j]));
+            }
             x[pg * 8 + r] = t;
         }
     }
@@ -136,7 +144,7 @@ page_index_kernel(const __half* __restrict__ q, const __half* __restrict__ kmin,
     for (int g = 0; g < kGroupsPerWarp; ++g) fetch(g, lo_all[g], hi_all[g]);
 #pragma unroll
     for (int g = 0; g < kGroupsPerWarp; ++g) {
-        float s = bounds_4x8(qf, lo_all[g], hi_all[g], lane);
+        float s = bounds_4x8(qf, n_rep, lo_all[g], hi_all[g], lane);
         const int p = first + g * kGroup + (lane >> 3), r = lane & 7;
         const int blk = __shfl_sync(LS_FULL_MASK, my_blk, g * kGroup + (lane >> 3));
         if (PER_HEAD) {
@@ -161,27 +169,25 @@ __device__ __forceinline__ uint32_t order_key(float x) {
     return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
 }
 
-constexpr int kTopkPerThread = 8;
-constexpr int kTopkMaxRow = 8192;              // 1024 threads x 8 keys
+constexpr int kTopkMaxRow = 8192;              // longest row (a 128K context)
 
 typedef unsigned long long u64;
 
-// One compare-exchange of a bitonic network on the key this lane holds for
-// position i, against the key `other` of position i ^ stride.
-__device__ __forceinline__ u64 bitonic_keep(u64 mine, u64 other, int i, int stride, int size) {
-    const bool lower = (i & stride) == 0, descending = (i & size) == 0;
-    const u64 mx = mine > other ? mine : other, mn = mine > other ? other : mine;
-    return (lower == descending) ? mx : mn;
+// One compare-exchange of a bitonic network: keep the larger of (mine, other)
+// if `want_max`, else the smaller.
+__device__ __forceinline__ u64 bitonic_keep(u64 mine, u64 other, bool want_max) {
+    return ((other > mine) == want_max) ? other : mine;
 }
 
 // Deterministic top-k by a full sort of the row: one CTA per (sequence, head)
 // sorts 64-bit keys (order_key(score) << 32 | ~page) to descending order with a
 // bitonic network, so equal scores come out with the lower page first, and
-// writes the first k pages. Each thread holds 8 consecutive keys in registers:
-// exchanges at distance 1, 2, 4 stay inside the thread, distances 8..128 are
-// warp shuffles, and only distances >= 256 go through shared memory with a
-// barrier (6 of the 66 rounds for a 2048-page row).
-__global__ void __launch_bounds__(kTopkMaxRow / kTopkPerThread)
+// writes the first k pages. Each thread holds E consecutive keys in registers:
+// exchanges at distance < E stay inside the thread, distances E..16E are warp
+// shuffles, and only distances >= 32E go through shared memory with a barrier.
+// Fewer keys per thread means more warps to hide the network's latency.
+template <int kTopkPerThread>
+__global__ void __launch_bounds__(1024)
 topk_pages_kernel(const float* __restrict__ scores, int* __restrict__ sel, int n, int n_pow2, int k,
                   int heads, long long ss_b, long long ss_h, long long sl_b, long long sl_h) {
     extern __shared__ __align__(8) u64 keys[];
@@ -197,22 +203,24 @@ topk_pages_kernel(const float* __restrict__ scores, int* __restrict__ sel, int n
     }
     for (int size = 2; size <= n_pow2; size <<= 1) {
         int stride = size >> 1;
+        // For strides >= E every key of this thread sits on the same side of the
+        // exchange and in the same sorting direction: one decision per round.
         for (; stride >= 32 * kTopkPerThread; stride >>= 1) {          // other warps: shared memory
+            const bool want_max = ((base & stride) == 0) == ((base & size) == 0);
 #pragma unroll
             for (int e = 0; e < kTopkPerThread; ++e) keys[base + e] = v[e];
             __syncthreads();
 #pragma unroll
             for (int e = 0; e < kTopkPerThread; ++e)
-                v[e] = bitonic_keep(v[e], keys[(base + e) ^ stride], base + e, stride, size);
+                v[e] = bitonic_keep(v[e], keys[(base + e) ^ stride], want_max);
             __syncthreads();
         }
         for (; stride >= kTopkPerThread; stride >>= 1) {               // same warp: shuffles
+            const bool want_max = ((base & stride) == 0) == ((base & size) == 0);
             const int lane_mask = stride / kTopkPerThread;
 #pragma unroll
-            for (int e = 0; e < kTopkPerThread; ++e) {
-                const u64 other = __shfl_xor_sync(LS_FULL_MASK, v[e], lane_mask);
-                v[e] = bitonic_keep(v[e], other, base + e, stride, size);
-            }
+            for (int e = 0; e < kTopkPerThread; ++e)
+                v[e] = bitonic_keep(v[e], __shfl_xor_sync(LS_FULL_MASK, v[e], lane_mask), want_max);
         }
 #pragma unroll
         for (int st = kTopkPerThread / 2; st > 0; st >>= 1) {          // same thread: registers
@@ -222,9 +230,9 @@ topk_pages_kernel(const float* __restrict__ scores, int* __restrict__ sel, int n
                     if ((e & st) == 0) {
                         const bool descending = ((base + e) & size) == 0;
                         const u64 a = v[e], c = v[e | st];
-                        const u64 mx = a > c ? a : c, mn = a > c ? c : a;
-                        v[e] = descending ? mx : mn;
-                        v[e | st] = descending ? mn : mx;
+                        const bool swap = (c > a) == descending;
+                        v[e] = swap ? c : a;
+                        v[e | st] = swap ? a : c;
                     }
                 }
             }
@@ -297,17 +305,31 @@ int ls_topk_pages(const float* scores, int32_t* sel, int batch, int kv_heads, in
     if (!scores || !sel) return LS_ERR_NULL_POINTER;
     if (batch <= 0 || kv_heads <= 0 || num_pages <= 0 || k <= 0 || k > num_pages)
         return LS_ERR_BAD_SHAPE;
-    int n_pow2 = 32 * ls::kTopkPerThread;           // at least one full warp of keys
+    int n_pow2 = 256;
     while (n_pow2 < num_pages) n_pow2 <<= 1;
     if (n_pow2 > ls::kTopkMaxRow || (long long)batch * kv_heads > 2147483647LL) return LS_ERR_TOO_LARGE;
     if (((uintptr_t)scores & 3) || ((uintptr_t)sel & 3)) return LS_ERR_MISALIGNED;
     const size_t smem = sizeof(unsigned long long) * (size_t)n_pow2;
-    cudaError_t e = cudaFuncSetAttribute(ls::topk_pages_kernel,
-                                         cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) return (int)e;
-    ls::topk_pages_kernel<<<batch * kv_heads, n_pow2 / ls::kTopkPerThread, smem,
-                            static_cast<cudaStream_t>(stream)>>>(
-        scores, sel, num_pages, n_pow2, k, kv_heads, ss_b, ss_h, sl_b, sl_h);
+    // Keys per thread: 4 measured best at 2048 keys (512 threads); 8 beyond 4096.
+    int per_thread = n_pow2 <= 4096 ? 4 : 8;
+    if (const char* env = getenv("LS_TOPK_E")) {
+        const int e = atoi(env);
+        if ((e == 2 || e == 4 || e == 8) && n_pow2 / e <= 1024 && n_pow2 / e >= 32) per_thread = e;
+    }
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const int grid = batch * kv_heads;
+#define LS_LAUNCH_TOPK(E)                                                                          \
+    do {                                                                                           \
+        cudaError_t e_ = cudaFuncSetAttribute(ls::topk_pages_kernel<E>,                            \
+                                              cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+        if (e_ != cudaSuccess) return (int)e_;                                                     \
+        ls::topk_pages_kernel<E><<<grid, n_pow2 / E, smem, st>>>(scores, sel, num_pages, n_pow2, k, \
+                                                                 kv_heads, ss_b, ss_h, sl_b, sl_h); \
+    } while (0)
+    if (per_thread == 2) LS_LAUNCH_TOPK(2);
+    else if (per_thread == 4) LS_LAUNCH_TOPK(4);
+    else LS_LAUNCH_TOPK(8);
+#undef LS_LAUNCH_TOPK
     return (int)cudaGetLastError();
 }
 

@@ -349,3 +349,46 @@ def paged_decode_torch_cpu(q, k_pool, v_pool, tables, lens, softmax_scale=None):
     probs = torch.softmax(scores, dim=-1)
     v = torch.where(keep[:, None, :, None], v, torch.zeros_like(v))
     return torch.matmul(probs, v)
+
+
+# ---------------------------------------------------------------------------
+# The per-layer element-wise ops around attention, with the fp16 rounding
+# sequence of the reference's torch forms (kernels/fused_elementwise.py:75-107).
+F16 = np.float16
+
+
+def _r16(x):
+    """Round fp32 values to fp16 and return them as fp32: one model-dtype rounding."""
+    return np.asarray(x, dtype=F32).astype(F16).astype(F32)
+
+
+def rms_norm(x, weight, eps, residual=None):
+    """x, residual [rows, n] fp16, weight [n] fp16 -> (y fp16, summed residual fp16 or None).
+    kernels/fused_elementwise.py:75-86 (`rms_norm_ref`, `fused_add_rms_norm_ref`)."""
+    s = None
+    h = _f32(x)
+    if residual is not None:
+        s = _r16(_f32(residual) + h)
+        h = s
+    var = (h * h).mean(axis=-1, keepdims=True, dtype=F32)
+    normed = _r16(h * (F32(1) / np.sqrt(var + F32(eps))))
+    y = (_f32(weight) * normed).astype(F16)
+    return y, None if s is None else s.astype(F16)
+
+
+def silu_and_mul(gate_up):
+    """[rows, 2 * inter] fp16 -> [rows, inter] fp16. kernels/fused_elementwise.py:89-91."""
+    inter = gate_up.shape[-1] // 2
+    g, u = _f32(gate_up[..., :inter]), _f32(gate_up[..., inter:])
+    act = _r16(g / (F32(1) + np.exp(-g)))
+    return (act * u).astype(F16)
+
+
+def rope(x, cos, sin):
+    """x [..., heads, 128] fp16, cos / sin broadcastable [..., 1, 128] fp16 -> fp16:
+    x * cos + rotate_half(x) * sin with every product and the sum rounded to fp16.
+    kernels/fused_elementwise.py:94-107 (`rope_qk_ref`)."""
+    half = x.shape[-1] // 2
+    xf, c, s = _f32(x), _f32(cos), _f32(sin)
+    rot = np.concatenate([-xf[..., half:], xf[..., :half]], axis=-1)
+    return (_r16(xf * c) + _r16(rot * s)).astype(F16)

@@ -10,6 +10,8 @@ the same bytes everywhere); outputs come from the reference's own functions:
     int8_*.npz     cache.int8_paged_cache.Int8PagedKVCache driven through prefill and
                    deferred-finalize decode steps on CPU: pool bytes, scales, residual,
                    block tables, and paged_decode_reference over that state
+    elementwise.npz  kernels.fused_elementwise.{rms_norm_ref, fused_add_rms_norm_ref, silu_and_mul_ref,
+                   rope_qk_ref}
     sparse.npz     model.attention.sparse.page_bounds, kernels.cuda.paged_sparse.budget/budgets,
                    torch.topk on the scores, and the reference tests' masked-softmax attention
 
@@ -149,6 +151,30 @@ def sparse():
         **bounds)
 
 
+def elementwise():
+    """The per-layer ops around attention, from the reference's torch forms
+    (kernels/fused_elementwise.py:75-107): RMSNorm (+ residual), SiLU * up, RoPE."""
+    from kernels import fused_elementwise as ref_fe
+
+    rng = np.random.default_rng(21)
+    x = (rng.standard_normal((7, 1536)) * 3).astype(np.float16)
+    r = (rng.standard_normal((7, 1536)) * 2).astype(np.float16)
+    w = (1 + 0.1 * rng.standard_normal(1536)).astype(np.float16)
+    y = ref_fe.rms_norm_ref(t(x), t(w), 1e-6)
+    y2, s2 = ref_fe.fused_add_rms_norm_ref(t(x), t(r), t(w), 1e-6)
+    gu = (rng.standard_normal((5, 2 * 896)) * 2).astype(np.float16)
+    act = ref_fe.silu_and_mul_ref(t(gu))
+    q = rng.standard_normal((3, 1, 12 * 128)).astype(np.float16)
+    k = rng.standard_normal((3, 1, 2 * 128)).astype(np.float16)
+    ang = rng.uniform(0, 6.28, (3, 1, 1, 64)).astype(np.float32)
+    ang = np.concatenate([ang, ang], -1)
+    cos, sin = np.cos(ang).astype(np.float16), np.sin(ang).astype(np.float16)
+    qo, ko = ref_fe.rope_qk_ref(t(q), t(k), t(cos), t(sin), 12, 2, 128)
+    np.savez_compressed(HERE / "elementwise.npz", x=x, r=r, w=w, rms=y.numpy(), add_rms=y2.numpy(),
+                        add_rms_sum=s2.numpy(), gu=gu, silu_mul=act.numpy(), q=q, k=k, cos=cos, sin=sin,
+                        rope_q=qo.numpy(), rope_k=ko.numpy())
+
+
 def main():
     torch.manual_seed(0)
     dense("dense_ragged", synthetic.dense_case([1024, 300, 61, 17, 1], seed=0))
@@ -157,6 +183,7 @@ def main():
     int8_state("int8_sym", asym=False)
     int8_state("int8_asym", asym=True)
     sparse()
+    elementwise()
     for f in sorted(HERE.glob("*.npz")):
         print(f.name, f.stat().st_size)
 

@@ -168,3 +168,18 @@ def test_sparse_attention_oracle_matches_the_reference_tests_form(golden_dir):
     sel = np.stack([np.stack([p, p[::-1]]) for p in picks]).astype(np.int32)       # [B, H, 6]
     got = orc.sparse_decode(c["q"], c["k_pool"], c["v_pool"], c["block_tables"], c["seq_lens"], sel)
     np.testing.assert_allclose(got, g["attend_picks"], atol=2e-6, rtol=1e-5)
+
+
+def test_elementwise_restatements_match_the_reference_forms(golden_dir):
+    g = np.load(golden_dir / "elementwise.npz")
+    y, _ = orc.rms_norm(g["x"], g["w"], 1e-6)
+    assert np.array_equal(y, g["rms"])
+    y2, s2 = orc.rms_norm(g["x"], g["w"], 1e-6, residual=g["r"])
+    assert np.array_equal(y2, g["add_rms"]) and np.array_equal(s2, g["add_rms_sum"])
+    act = orc.silu_and_mul(g["gu"])
+    # exp() implementations differ in the last fp32 bit: at most one fp16 ulp, rarely.
+    assert np.mean(act != g["silu_mul"]) < 2e-3
+    np.testing.assert_allclose(act.astype(np.float32), g["silu_mul"].astype(np.float32), rtol=1e-3, atol=1e-6)
+    q = orc.rope(g["q"].reshape(3, 12, 128), g["cos"].reshape(3, 1, 128), g["sin"].reshape(3, 1, 128))
+    k = orc.rope(g["k"].reshape(3, 2, 128), g["cos"].reshape(3, 1, 128), g["sin"].reshape(3, 1, 128))
+    assert np.array_equal(q.reshape(3, 1, -1), g["rope_q"]) and np.array_equal(k.reshape(3, 1, -1), g["rope_k"])
