@@ -12,7 +12,10 @@ reference raises for the same mistakes: layout violations are `ValueError`
 from __future__ import annotations
 
 import ctypes
+import os
 from ctypes import c_float, c_int, c_int64, c_void_p
+
+import torch
 
 from latentserve_b200 import build as _build
 
@@ -60,7 +63,8 @@ def lib() -> ctypes.CDLL:
     """The loaded library, building it first if the sources are newer."""
     global _LIB
     if _LIB is None:
-        path = _build.build()
+        # LATENTSERVE_B200_LIB names a prebuilt library to load instead (tuning builds).
+        path = os.environ.get("LATENTSERVE_B200_LIB") or _build.build()
         handle = ctypes.CDLL(str(path))
         for name, argtypes in _PROTOTYPES.items():
             fn = getattr(handle, name)          # AttributeError = a symbol the header promises is gone
@@ -83,6 +87,10 @@ def ptr(t) -> int:
 
 
 def current_stream(device) -> int:
-    import torch
+    """Raw handle of torch's current stream on `device`."""
+    index = device.index if isinstance(device, torch.device) else torch.device(device).index
+    return raw_stream(torch.cuda.current_device() if index is None else index)
 
-    return torch.cuda.current_stream(device).cuda_stream
+
+def raw_stream(device_index: int) -> int:
+    return torch._C._cuda_getCurrentRawStream(device_index)

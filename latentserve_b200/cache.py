@@ -163,6 +163,7 @@ class _PagedBase:
         self._table_state: list = [None] * mb
         self._block_tables = self._seq_lens_tensor = self._write_slots = None
         self._prefill_slots: Optional[torch.Tensor] = None
+        self._decode_slot_vec: Optional[torch.Tensor] = None      # [b] view of the decode slots
 
     # -- state ---------------------------------------------------------
     @property
@@ -241,12 +242,20 @@ class _PagedBase:
         self._block_tables = self._block_tables_buf[:b]
         self._seq_lens_tensor = self._seq_lens_buf[:b]
 
+    def _slot_vec(self, slots: torch.Tensor, b: int) -> torch.Tensor:
+        """The first b decode slots as a vector (the view made once per advance)."""
+        vec = self._decode_slot_vec
+        if vec is not None and slots is self._write_slots and vec.shape[0] >= b:
+            return vec
+        return slots[:b, 0]
+
     def _ship_decode_slots(self, active, starts) -> None:
         b = len(active)
         self._h_slots[:b] = torch.tensor([self.tables[i].slot(s) for i, s in zip(active, starts)],
                                          dtype=torch.int64)
         self._write_slots_buf[:b, 0].copy_(self._h_slots[:b], non_blocking=False)
         self._write_slots = self._write_slots_buf[:b]
+        self._decode_slot_vec = self._write_slots_buf[:b, 0]
 
 
 class PagedKVCache(_PagedBase):
@@ -287,6 +296,7 @@ class PagedKVCache(_PagedBase):
                 [[self.tables[i].slot(p) for p in range(s, s + n)] for i, s in zip(active, starts)],
                 dtype=torch.int64, device=self.device)
             self._write_slots = self._prefill_slots
+            self._decode_slot_vec = None
         self._ship_tables(active)
 
     def write(self, layer_idx: int, k: torch.Tensor, v: torch.Tensor, start_pos: int = 0) -> None:
@@ -298,7 +308,7 @@ class PagedKVCache(_PagedBase):
         kmin = self.kmin[layer_idx] if self._bounds_on else None
         kmax = self.kmax[layer_idx] if self._bounds_on else None
         if n == 1:
-            kv_write.append_fp16(k, v, slots[:b, 0], self._flat_k[layer_idx],
+            kv_write.append_fp16(k, v, self._slot_vec(slots, b), self._flat_k[layer_idx],
                                  self._flat_v[layer_idx], kmin, kmax, self.block_size)
             return
         # Prefill: the same kernel, one launch per position (bounds stay exact
@@ -319,7 +329,7 @@ class PagedKVCache(_PagedBase):
             raise RuntimeError("call advance(1, batch_size) before rope_write()")
         kmin = self.kmin[layer_idx] if self._bounds_on else None
         kmax = self.kmax[layer_idx] if self._bounds_on else None
-        fe.rope_append_fp16(qkv, cos, sin, positions, slots[:b, 0], q_out, self._flat_k[layer_idx],
+        fe.rope_append_fp16(qkv, cos, sin, positions, self._slot_vec(slots, b), q_out, self._flat_k[layer_idx],
                             self._flat_v[layer_idx], kmin, kmax, q_heads, self.spec.num_kv_heads,
                             self.block_size)
 
@@ -462,6 +472,7 @@ class Int8PagedKVCache(_PagedBase):
                 [[self.tables[i].slot(p) for p in range(s, s + n)] for i, s in zip(active, starts)],
                 dtype=torch.int64, device=self.device)
             self._write_slots = self._prefill_slots
+            self._decode_slot_vec = None
         self._ship_tables(active)
 
     def rope_write(self, layer_idx: int, qkv: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor,
@@ -472,7 +483,7 @@ class Int8PagedKVCache(_PagedBase):
         slots = self._write_slots
         if slots is None or slots.shape[0] < b or slots.shape[1] != 1:
             raise RuntimeError("call advance(1, batch_size) before rope_write()")
-        fe.rope_append_int8(qkv, cos, sin, positions, slots[:b, 0], self._k_res_idx_buf[:b], q_out,
+        fe.rope_append_int8(qkv, cos, sin, positions, self._slot_vec(slots, b), self._k_res_idx_buf[:b], q_out,
                             self._flat_v[layer_idx], self._flat_v_scale[layer_idx],
                             self._flat_v_zero[layer_idx] if self.asymmetric else None,
                             self._k_res_flat[layer_idx], q_heads, self.spec.num_kv_heads,
@@ -488,7 +499,7 @@ class Int8PagedKVCache(_PagedBase):
         consts = dict(asym=self.asymmetric, eps=_EPS, qmax=float(self.v_qmax),
                       levels=float(self.v_levels), offset=float(self.v_offset))
         if n == 1:
-            iw.decode_write(k, v, slots[:b, 0], self._k_res_idx_buf[:b], self._flat_v[layer_idx],
+            iw.decode_write(k, v, self._slot_vec(slots, b), self._k_res_idx_buf[:b], self._flat_v[layer_idx],
                             self._flat_v_scale[layer_idx], zero, self._k_res_flat[layer_idx], **consts)
             return
         # Prefill (set-up path): token by token through the same two kernels,

@@ -159,6 +159,21 @@ def paged_decode_cuda(q, k_pool, v_pool, block_tables, seq_lens, max_seq_len: in
     scratch, valid until the next call with the same shapes. `merge=False`
     stops at the partial states (no output is written) and returns None.
     """
+    fn, args, out, dev_index = plan_decode(q, k_pool, v_pool, block_tables, seq_lens, num_splits,
+                                           softmax_scale, k_scale, v_scale, k_zero, v_zero,
+                                           k_residual, res_rows, impl, merge)
+    _lib.check(fn(*args, _lib.raw_stream(dev_index)), "paged_decode_cuda")
+    return out if merge else None
+
+
+def plan_decode(q, k_pool, v_pool, block_tables, seq_lens, num_splits=None, softmax_scale=None,
+                k_scale=None, v_scale=None, k_zero=None, v_zero=None, k_residual=None, res_rows=None,
+                impl: int = IMPL_MMA, merge: bool = True, out: Optional[torch.Tensor] = None):
+    """Validate one decode call and bind its arguments: returns (entry point,
+    argument tuple without the stream, output tensor, device index). The tuple
+    holds raw addresses, so it is valid for as long as the tensors it was built
+    from are alive and unmoved -- which is how a decode loop calls this path
+    (persistent pools, tables, lengths and projection buffers)."""
     if not q.is_cuda:
         raise RuntimeError("latentserve_b200 has no CPU path: tensors must be on a CUDA device")
     b, h_kv, n_rep, d = q.shape
@@ -173,16 +188,22 @@ def paged_decode_cuda(q, k_pool, v_pool, block_tables, seq_lens, max_seq_len: in
     chunks = choose_chunks(q.device, h_kv, num_splits, b, INT8_CTAS_PER_SM if int8 else CTAS_PER_SM)
     tag = "cuda_i8" if int8 else "cuda"
     acc, m, l, seg = _partials(q, chunks, tag)
-    out = scratch(tag + "_out", (b, h_kv, n_rep, d), q.dtype, q.device)
+    if out is None:
+        out = scratch(tag + "_out", (b, h_kv, n_rep, d), q.dtype, q.device)
+    elif (out.shape != q.shape or out.dtype != q.dtype or out.device != q.device
+          or out.stride(-1) != 1):
+        raise ValueError("out must be an fp16 [B, H_kv, N_REP, 128] tensor on q's device with "
+                         "unit-stride channels")
     out_ptr = out.data_ptr() if merge else 0
     lib = _lib.lib()
-    stream = _lib.current_stream(q.device)
     ptr = _lib.ptr
+    dev_index = q.device.index if q.device.index is not None else torch.cuda.current_device()
     if int8:
         if k_scale is None or v_scale is None:
             raise ValueError("INT8 pools need k_scale and v_scale")
         res_st = k_residual.stride()[:3] if k_residual is not None else (0, 0, 0)
-        rc = lib.ls_paged_decode_int8(
+        fn = lib.ls_paged_decode_int8
+        args = (
             ptr(q), ptr(k_pool), ptr(v_pool), ptr(block_tables), ptr(seq_lens),
             ptr(k_scale), ptr(v_scale), ptr(k_zero), ptr(v_zero), ptr(k_residual), ptr(res_rows),
             ptr(acc), ptr(m), ptr(l), ptr(seg), out_ptr,
@@ -192,17 +213,17 @@ def paged_decode_cuda(q, k_pool, v_pool, block_tables, seq_lens, max_seq_len: in
             k_pool.stride(0), k_pool.stride(1), k_pool.stride(2),
             k_scale.stride(0), k_scale.stride(1),
             v_scale.stride(0), v_scale.stride(1), v_scale.stride(2),
-            *res_st, out.stride(0), out.stride(1), out.stride(2), scale, stream)
+            *res_st, out.stride(0), out.stride(1), out.stride(2), scale)
     else:
         if k_scale is not None or k_residual is not None:
             raise ValueError("fp16 pools take no scales or residual")
-        rc = lib.ls_paged_decode_fp16(
+        fn = lib.ls_paged_decode_fp16
+        args = (
             ptr(q), ptr(k_pool), ptr(v_pool), ptr(block_tables), ptr(seq_lens),
             ptr(acc), ptr(m), ptr(l), ptr(seg), out_ptr,
             b, h_kv, n_rep, d, k_pool.shape[1], block_tables.stride(0), k_pool.shape[0],
             chunks, MIN_CHUNK_PAGES, impl | launch_flags(),
             q.stride(0), q.stride(1), q.stride(2),
             k_pool.stride(0), k_pool.stride(1), k_pool.stride(2),
-            out.stride(0), out.stride(1), out.stride(2), scale, stream)
-    _lib.check(rc, "paged_decode_cuda")
-    return out if merge else None
+            out.stride(0), out.stride(1), out.stride(2), scale)
+    return fn, args, out, dev_index
