@@ -206,6 +206,8 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-pdl", action="store_true",
                     help="ordinary launches instead of programmatic dependent launch")
+    ap.add_argument("--projections", default="cublas", choices=["ls", "cublas"],
+                    help="decode-step workloads: this library's weight-streaming projections, or torch GEMMs")
     ap.add_argument("--quick", action="store_true",
                     help="profiler runs: no e2e / CPU legs, no extension of the load for clock sampling")
     args = ap.parse_args()
@@ -502,7 +504,8 @@ def run_model_step(args):
             cache._fin[i] = (n - 1) // 16
     if ratio is not None:
         cache.enable_page_bounds()
-    model = ds.DecodeModel(shape, dev, max_pos=max(lens) + room + 16, seed=rank)
+    model = ds.DecodeModel(shape, dev, max_pos=max(lens) + room + 16, seed=rank,
+                           projections=args.projections)
     model.set_sparse(ratio)
     hint = max(lens) + room
     runner = ds.GraphedStep(model, cache, batch, hint)
@@ -560,6 +563,7 @@ def run_model_step(args):
                        "kv_cache": kind, "sparse_ratio": ratio, "shared_prefix_tokens": prefix,
                        "sequences_sharing_prefix": len(owners),
                        "layers": shape.num_layers, "programmatic_launch": not args.no_pdl,
+                       "projections": args.projections if batch <= 64 else "cublas",
                        "parallelism": f"replicas x{world} (sequence-sharded, no collective)"},
             "graph_replay_ms": round(graph_ms, 4),
             "tokens_per_s": round(world * batch / (loop_ms * 1e-3), 1),

@@ -270,6 +270,40 @@ int ls_rope_append_int8(const void* qkv, const void* cos, const void* sin, const
                         float eps, float qmax, float inv_qmax, float levels, float inv_levels,
                         float offset, void* stream);
 
+/* Decode-step projection for a batch of m <= 64 token rows, fused with the
+ * element-wise work either side of it:
+ *   out[m, n] = f(x)[m, k] . w[n, k]^T (+ bias[n]),  fp16 in, fp32 accumulate, fp16 out.
+ *   mode & LS_GEMM_NORM:   f(x) = RMSNorm(x (+ res)) * gamma with the fp16 rounding
+ *       sequence of ls_rms_norm; with `res`, res_out <- fp16(x + res) as well
+ *       (res_out must not alias x or res).
+ *   mode & LS_GEMM_SWIGLU: w is [gate; up] stacked ([n, k], n = 2 I) and out is
+ *       [m, I] = fp16(fp16(silu(gate)) * up) of the fp16-rounded products.
+ *   mode & LS_LAUNCH_PROGRAMMATIC: the first weight loads are issued before the
+ *       kernel synchronises on the previous kernel of the stream.
+ *   add_res (no SWIGLU): out = fp16(fp16(product + bias) + add_res[m, n]), the residual
+ *       add that follows o_proj / down_proj; with sumsq_out ([n / 32][64] floats) each
+ *       tile also leaves the per-row sums of out^2 over its 32 columns, which a later
+ *       LS_GEMM_NORM call takes as sumsq_in (+ sumsq_tiles = n / 32 of THAT call, its
+ *       k / 32) instead of reading whole rows for its statistics (res must then be NULL).
+ * k is cut into `splits` slices across CTAs (grid = n / 32 tiles x splits; pick
+ * splits so that the grid is about 2 CTAs per SM); with splits > 1 `part` must
+ * hold (n / 32) * splits * 16 * ceil(m / 16) * 32 floats (n / 32 -> I / 16 tiles
+ * with SWIGLU) and `counters` one int32 per tile, zeroed once before first use
+ * (every launch leaves them at zero). The sum over splits is taken in split order
+ * by whichever CTA finishes last, so results do not depend on timing.
+ * Needs k % 32 == 0, n % 32 == 0, 16-byte aligned rows. Strides in elements.
+ * In LatentServe these are the four `nn.Linear` calls of a Qwen2 decoder layer
+ * (model/latentserve_qwen.py:397-451 runs them through Hugging Face modules)
+ * together with `rms_norm` / `fused_add_rms_norm` / `silu_and_mul`,
+ * kernels/fused_elementwise.py:194-232. */
+#define LS_GEMM_NORM 1
+#define LS_GEMM_SWIGLU 2
+int ls_skinny_gemm(const void* x, const void* res, const void* gamma, void* res_out,
+                   const float* sumsq_in, int sumsq_tiles, const void* w, const void* bias,
+                   const void* add_res, float* sumsq_out, void* out, float* part, int32_t* counters,
+                   int m, int n, int k, int splits, int mode, float eps, int64_t sx, int64_t sres,
+                   int64_t sres_out, int64_t sw, int64_t sadd, int64_t sout, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

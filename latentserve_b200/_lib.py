@@ -51,6 +51,7 @@ _PROTOTYPES = {
     "ls_rms_norm": [P, P, P, P, P, I, I, F, L, L, L, L, P],
     "ls_silu_mul": [P, P, I, I, L, L, P],
     "ls_rope_append_fp16": [P] * 10 + [I] * 5 + [L] * 9 + [P],
+    "ls_skinny_gemm": [P] * 5 + [I] + [P] * 7 + [I] * 5 + [F] + [L] * 6 + [P],
     "ls_rope_append_int8": [P] * 11 + [I] * 4 + [L] * 6 + [I] + [F] * 6 + [P],
 }
 

@@ -22,7 +22,8 @@ HERE = pathlib.Path(__file__).resolve().parent
 CSRC = HERE / "csrc"
 OUT_DIR = HERE / "_C"
 LIB = OUT_DIR / "libls_b200.so"
-SOURCES = ("paged_decode.cu", "kv_write.cu", "page_select.cu", "fused_elementwise.cu")
+SOURCES = ("paged_decode.cu", "kv_write.cu", "page_select.cu", "fused_elementwise.cu",
+           "skinny_gemm.cu")
 ARCH_FLAGS = ("-gencode", "arch=compute_100a,code=sm_100a")
 
 

@@ -34,6 +34,7 @@ rms_norm_kernel(const __half* __restrict__ x, const __half* __restrict__ res,
                 int n, float eps, long long sx, long long sr, long long sy, long long sro) {
     extern __shared__ __align__(16) __half row_s[];          // the (summed) row, n halves
     __shared__ float warp_sum[8];
+    asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");   // let a programmatic successor start its prologue
     const int row = blockIdx.x, tid = threadIdx.x;
     const __half* xr = x + row * sx;
     float acc = 0.f;
@@ -77,6 +78,7 @@ rms_norm_kernel(const __half* __restrict__ x, const __half* __restrict__ res,
 __global__ void __launch_bounds__(256)
 silu_mul_kernel(const __half* __restrict__ gu, __half* __restrict__ out, int inter, long long sgu,
                 long long sout) {
+    asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");   // let a programmatic successor start its prologue
     const int row = blockIdx.y;
     const int i = (blockIdx.x * 256 + threadIdx.x) * 8;
     if (i >= inter) return;
@@ -137,6 +139,7 @@ rope_append_kernel(const __half* __restrict__ qkv, const __half* __restrict__ co
                    long long max_pos, long long num_slots, long long num_res, long long s_qkv,
                    long long s_cos, long long sq_b, long long sp_t, long long sp_h, long long sb_b,
                    long long sb_h, RopeQuant qc) {
+    asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");   // let a programmatic successor start its prologue
     const int heads = hq + 2 * hk;
     const int item = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
     if (item >= batch * heads) return;

@@ -44,6 +44,7 @@ kv_append_fp16_kernel(const __half* __restrict__ k, const __half* __restrict__ v
                       __half* __restrict__ kmax, int batch, int heads, long long num_slots,
                       long long sk_b, long long sk_h, long long sv_b, long long sv_h,
                       long long sp_t, long long sp_h, long long sb_b, long long sb_h) {
+    asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");   // let a programmatic successor start its prologue
     const int row = blockIdx.x * 4 + (threadIdx.x >> 5);
     const int lane = threadIdx.x & 31;
     if (row >= batch * heads) return;
@@ -104,6 +105,7 @@ int8_decode_write_kernel(const __half* __restrict__ k, const __half* __restrict_
                          __half* __restrict__ k_res, int batch, int heads, long long num_slots,
                          long long num_res, long long sk_b, long long sk_h, long long sv_b,
                          long long sv_h, QuantConsts c) {
+    asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");   // let a programmatic successor start its prologue
     const int row = blockIdx.x * 4 + (threadIdx.x >> 5);
     const int lane = threadIdx.x & 31;
     if (row >= batch * heads) return;

@@ -34,6 +34,11 @@
 #define LS_ERR_TOO_LARGE (-5)
 #define LS_ERR_UNSUPPORTED (-6)
 #define LS_ERR_SCRATCH_TOO_SMALL (-7)
+#ifndef LS_LAUNCH_PROGRAMMATIC
+#define LS_LAUNCH_PROGRAMMATIC 0x100
+#endif
+#define LS_GEMM_NORM 1
+#define LS_GEMM_SWIGLU 2
 
 namespace ls {
 

@@ -43,7 +43,6 @@ namespace ls {
 
 #define LS_IMPL_MMA 0
 #define LS_IMPL_SIMT 1
-#define LS_LAUNCH_PROGRAMMATIC 0x100
 
 #ifndef LS_STAGES
 #define LS_STAGES 3                 // cp.async ring depth per warp

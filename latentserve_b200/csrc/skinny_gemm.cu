@@ -1,0 +1,491 @@
+// Decode-step projections: out[M, N] = f(x)[M, K] . W[N, K]^T for a batch of
+// M <= 64 token rows, where W (fp16, row-major, K contiguous) is tens of MB and
+// x is tens of KB. At these shapes the product is a stream of weights through
+// HBM, so the kernel is built around that stream:
+//
+//   * W goes from global memory straight into the registers that feed
+//     mma.sync.m16n8k16 as the B operand: lane (g, t) of a warp reads 16
+//     contiguous bytes of row g at k = 32 c + 8 t, which are the B fragments of
+//     two MMAs once the k index is permuted (the MMA does not care in which
+//     order k is summed as long as A uses the same order; A is read with the
+//     same 16-byte pattern). No shared-memory staging, no ldmatrix.
+//   * A tile is 32 rows of W (4 n-tiles) by a slice of K; the 8 warps of a CTA
+//     take the slice's 32-wide k chunks round-robin, each keeping several chunks
+//     of loads in flight, and add their accumulators through shared memory. The
+//     CTA's slice of the activations is staged in shared memory once; the grid is
+//     sized to what the device holds at once and a CTA walks several tiles, its
+//     warps already loading the next tile's weights while the current one is
+//     reduced.
+//   * K is cut across CTAs (`splits`) where 32-row tiles alone would leave SMs
+//     idle. Partials go to an fp32 scratch and the CTA that arrives last at a
+//     tile's counter adds them in split order (deterministic), exactly as the
+//     decode kernel merges its partials; nobody waits.
+//   * The weight loads of the first chunks are issued BEFORE
+//     griddepcontrol.wait: weights do not depend on the previous kernel, so with
+//     programmatic dependent launch the stream of the next projection starts
+//     while the previous kernel drains.
+//
+// Fused around the product, with the rounding sequence of the unfused model
+// code (and of the reference's kernels/fused_elementwise.py:75-107):
+//   PRO_NORM    x <- RMSNorm(x [+ residual]) * gamma, rounded to fp16 where HF
+//               rounds; the CTA (0, 0) also stores x + residual for the next
+//               residual add. Replaces a norm launch.
+//   EPI_SWIGLU  W = [gate; up] stacked ([2 I, K]); a CTA takes 16 gate rows and
+//               the 16 matching up rows and writes fp16(silu(gate)) * up
+//               ([M, I]). Replaces the SiLU * up launch and the [M, 2 I] round trip.
+//   bias        out += bias (QKV projection).
+//   add_res     out = fp16(fp16(product) + residual): the residual add that follows
+//               o_proj and down_proj. With sumsq_out the same epilogue leaves each
+//               row's sum of squares over the tile's 32 columns, and the next
+//               PRO_NORM projection takes those partials (sumsq_in) instead of
+//               reading whole rows again for its statistics.
+#include "ls_common.cuh"
+
+namespace ls {
+
+constexpr int kGemmThreads = 256;
+constexpr int kGemmWarps = 8;
+constexpr int kTileRows = 32;           // rows of W per CTA
+enum { PRO_NONE = 0, PRO_NORM = 1 };
+enum { EPI_NONE = 0, EPI_SWIGLU = 1 };
+
+struct GemmParams {
+    const __half* x;        // [M, K]
+    const __half* res;      // [M, K] added to x before the norm, or null (PRO_NORM)
+    const __half* gamma;    // [K] (PRO_NORM)
+    __half* res_out;        // [M, K] <- x + res when res is given
+    const float* sumsq_in;  // [sumsq_tiles][64] per-row partial sums of x^2, or null (PRO_NORM)
+    const __half* w;        // [N, K]
+    const __half* bias;     // [N] or null
+    const __half* add_res;  // [M, N] added to the rounded product (EPI_NONE), or null
+    float* sumsq_out;       // [tiles][64] <- per-row sums of out^2 over the tile's 32 columns, or null
+    __half* out;            // [M, N], or [M, N / 2] with EPI_SWIGLU
+    float* part;            // [tiles * splits][M_pad * 32] fp32, splits > 1
+    int* counters;          // [tiles], zero before first use, left at zero
+    int m, n, k, splits, sumsq_tiles;
+    float eps;
+    long long sx, sres, sres_out, sw, sadd, sout;
+};
+
+__device__ __forceinline__ uint4 ldg_stream(const void* p, uint64_t pol) {
+    uint4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.L2::cache_hint.v4.u32 {%0,%1,%2,%3}, [%4], %5;\n"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                 : "l"(p), "l"(pol));
+    return v;
+}
+
+// Activations: L2 hits. A plain load, so the compiler keeps it behind the
+// griddepcontrol.wait barrier and is free to batch independent ones.
+__device__ __forceinline__ uint4 ldg_l2(const __half* p) {
+    return __ldcg(reinterpret_cast<const uint4*>(p));
+}
+
+__device__ __forceinline__ uint4 lds128g(uint32_t addr) {
+    uint4 v;
+    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                 : "r"(addr));
+    return v;
+}
+
+__device__ __forceinline__ void sts128g(uint32_t addr, uint4 v) {
+    asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};\n" ::"r"(addr), "r"(v.x), "r"(v.y), "r"(v.z),
+                 "r"(v.w));
+}
+
+__device__ __forceinline__ float round_h(float f) { return __half2float(__float2half_rn(f)); }
+
+// s = fp16(x + r), eight at a time.
+__device__ __forceinline__ uint4 add8(uint4 a, uint4 b) {
+    uint4 o;
+    const __half2* ah = reinterpret_cast<const __half2*>(&a);
+    const __half2* bh = reinterpret_cast<const __half2*>(&b);
+    uint32_t* oo = reinterpret_cast<uint32_t*>(&o);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const float2 fa = __half22float2(ah[i]), fb = __half22float2(bh[i]);
+        oo[i] = pack_half2(fa.x + fb.x, fa.y + fb.y);
+    }
+    return o;
+}
+
+// y = fp16(gamma * fp16(s * inv)), eight at a time.
+__device__ __forceinline__ uint4 norm8(uint4 s, uint4 gamma, float inv) {
+    uint4 o;
+    const __half2* sh = reinterpret_cast<const __half2*>(&s);
+    const __half2* gh = reinterpret_cast<const __half2*>(&gamma);
+    uint32_t* oo = reinterpret_cast<uint32_t*>(&o);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const float2 fs = __half22float2(sh[i]), fg = __half22float2(gh[i]);
+        oo[i] = pack_half2(fg.x * round_h(fs.x * inv), fg.y * round_h(fs.y * inv));
+    }
+    return o;
+}
+
+__device__ __forceinline__ float sumsq8(uint4 v) {
+    const __half2* h = reinterpret_cast<const __half2*>(&v);
+    float acc = 0.f;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        const float2 f = __half22float2(h[j]);
+        acc += f.x * f.x + f.y * f.y;
+    }
+    return acc;
+}
+
+// Halves between rows of the staged activations: the slice plus a pad that puts
+// consecutive rows 64 bytes apart modulo 128, so the eight rows a quarter-warp
+// reads (16 bytes per lane, four lanes per row) fall on distinct banks.
+__host__ __device__ inline int a_stride_halves(int slice_k) {
+    return slice_k + ((slice_k % 64 == 0) ? 32 : 0);
+}
+
+// MT = 16-row tiles of the batch (M <= 16 MT); U = k chunks a warp keeps in flight.
+// grid (CTAs per split, splits): a CTA walks the tiles blockIdx.x, + gridDim.x, ...
+// of its split with the same staged activations.
+template <int MT, int U, int PRO, int EPI>
+__global__ void __launch_bounds__(kGemmThreads, MT == 1 ? 2 : 1) skinny_gemm_kernel(const GemmParams p) {
+    // [ROWS][astride] fp16 staged activations, then [kGemmWarps][ROWS][32] fp32 for the
+    // reduction over warps.
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    constexpr int ROWS = MT * 16;
+    __shared__ float inv_rms[ROWS];
+    __shared__ float ssq_part[kGemmThreads];
+    __shared__ int is_last;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int g = lane >> 2, t = lane & 3;
+    const int split = blockIdx.y;
+    const int chunks = p.k >> 5;
+    const int per_split = (chunks + p.splits - 1) / p.splits;
+    const int c_begin = split * per_split;
+    const int c_end = min(chunks, c_begin + per_split);
+    const int k0 = c_begin * 32, k1 = c_end * 32;
+    const int astride = a_stride_halves(per_split * 32);
+    const uint32_t abase = smem_u32(smem_raw);
+    float* red = reinterpret_cast<float*>(smem_raw + (size_t)ROWS * astride * sizeof(__half));
+    const int n_tiles = p.n / kTileRows;
+    // Chunks of a tile's slice this warp takes: c_begin + warp + 8 i, i < cpw.
+    const int cpw = max(0, (c_end - c_begin - warp + kGemmWarps - 1) / kGemmWarps);
+
+    asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
+
+    // Rows of W behind this lane's four B fragments, for tile 0 and chunk 0 of the slice.
+    const __half* wrow[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int row = (EPI == EPI_SWIGLU) ? (i < 2 ? 0 : (p.n >> 1)) + (i & 1) * 8 + g : i * 8 + g;
+        wrow[i] = p.w + (long long)row * p.sw + 8 * t + 32 * (c_begin + warp);
+    }
+    const long long tile_step = (long long)((EPI == EPI_SWIGLU) ? 16 : kTileRows) * p.sw;
+    const __half* gptr = (PRO == PRO_NORM) ? p.gamma + 8 * t + 32 * (c_begin + warp) : nullptr;
+    const uint64_t pol = l2_policy_evict_first();
+
+    // A ring of U chunks per warp, slot u holding chunks u, u + U, ... of the current
+    // tile and then chunk u of the CTA's next tile, so the stream does not stop at
+    // tile boundaries.
+    uint4 wbuf[U][4];
+    uint4 gbuf[U];
+    auto load_slot = [&](int u, int tile, int ci) {
+        const long long off = tile * tile_step + 32 * kGemmWarps * ci;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) wbuf[u][i] = ldg_stream(wrow[i] + off, pol);
+        if (PRO == PRO_NORM) gbuf[u] = *reinterpret_cast<const uint4*>(gptr + 32 * kGemmWarps * ci);
+    };
+#pragma unroll
+    for (int u = 0; u < U; ++u)
+        if (u < cpw) load_slot(u, blockIdx.x, u);
+
+    // Everything below reads what the previous kernel wrote.
+    asm volatile("griddepcontrol.wait;\n" ::: "memory");
+
+    if (PRO == PRO_NORM && p.sumsq_in == nullptr) {
+        // One pass over the whole rows: x (+ residual) -> sum of squares, and the
+        // CTA's slice of it into shared memory. 16 threads per row, 16 rows per sweep.
+        const int sub = tid & 15;
+        constexpr int B = 4;                              // vectors in flight per thread
+        for (int r0 = 0; r0 < ROWS; r0 += 16) {
+            const int row = r0 + (tid >> 4);
+            const int rr = min(row, p.m - 1);
+            float acc = 0.f;
+            for (int i0 = sub * 8; i0 < p.k; i0 += 128 * B) {
+                uint4 v[B], r[B];
+#pragma unroll
+                for (int j = 0; j < B; ++j) {
+                    const int i = i0 + 128 * j;
+                    v[j] = make_uint4(0, 0, 0, 0);
+                    r[j] = v[j];
+                    if (i < p.k) {
+                        v[j] = ldg_l2(p.x + rr * p.sx + i);
+                        if (p.res != nullptr) r[j] = ldg_l2(p.res + rr * p.sres + i);
+                    }
+                }
+#pragma unroll
+                for (int j = 0; j < B; ++j) {
+                    const int i = i0 + 128 * j;
+                    if (i >= p.k) continue;
+                    if (p.res != nullptr) {
+                        v[j] = add8(v[j], r[j]);
+                        if (blockIdx.x == 0 && split == 0 && row < p.m)
+                            *reinterpret_cast<uint4*>(p.res_out + rr * p.sres_out + i) = v[j];
+                    }
+                    acc += sumsq8(v[j]);
+                    if (i >= k0 && i < k1) sts128g(abase + 2 * (row * astride + (i - k0)), v[j]);
+                }
+            }
+#pragma unroll
+            for (int off = 8; off > 0; off >>= 1) acc += __shfl_xor_sync(LS_FULL_MASK, acc, off);
+            if (sub == 0) inv_rms[row] = rsqrtf(acc / (float)p.k + p.eps);
+        }
+    } else {
+        // The CTA's slice of x into shared memory, asynchronously ...
+        const int vec_per_row = (k1 - k0) >> 3;
+        for (int v = tid; v < ROWS * vec_per_row; v += kGemmThreads) {
+            const int row = v / vec_per_row, col = (v - row * vec_per_row) * 8;
+            cp_async_16_full(abase + 2 * (row * astride + col), p.x + min(row, p.m - 1) * p.sx + k0 + col);
+        }
+        cp_async_commit();
+        if (PRO == PRO_NORM) {
+            // ... while the row sums of squares left by the kernel that produced x (one
+            // partial per 32 columns) are added up: 256 / ROWS threads per row, each a
+            // strided share of the partials, then those shares in order.
+            constexpr int PARTS = kGemmThreads / ROWS;
+            const int row = tid % ROWS, part = tid / ROWS;
+            float acc = 0.f;
+            for (int i0 = part; i0 < p.sumsq_tiles; i0 += 4 * PARTS) {
+                float v[4];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const int i = i0 + j * PARTS;
+                    v[j] = (i < p.sumsq_tiles) ? __ldcg(p.sumsq_in + i * 64 + row) : 0.f;
+                }
+                acc += (v[0] + v[1]) + (v[2] + v[3]);
+            }
+            ssq_part[part * ROWS + row] = acc;
+            __syncthreads();
+            if (tid < ROWS) {
+                float total = 0.f;
+#pragma unroll
+                for (int q = 0; q < PARTS; ++q) total += ssq_part[q * ROWS + tid];
+                inv_rms[tid] = rsqrtf(total / (float)p.k + p.eps);
+            }
+        }
+        cp_async_wait<0>();
+    }
+    __syncthreads();
+
+    // This lane's A fragments: rows g and g + 8 of each 16-row tile, 16 bytes at 8 t.
+    float inv[MT][2];
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+        for (int hh = 0; hh < 2; ++hh)
+            inv[mt][hh] = (PRO == PRO_NORM) ? inv_rms[mt * 16 + hh * 8 + g] : 1.f;
+    const uint32_t arow = abase + 2 * (g * astride + 8 * t) + 64 * warp;
+
+    for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
+        const bool has_next = tile + (int)gridDim.x < n_tiles;
+        float acc[4][MT][4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+#pragma unroll
+            for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) acc[i][mt][j] = 0.f;
+
+        for (int ci0 = 0; ci0 < cpw; ci0 += U) {
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                const int ci = ci0 + u;
+                if (ci < cpw) {
+                    const uint32_t acol = arow + 64 * kGemmWarps * ci;
+#pragma unroll
+                    for (int mt = 0; mt < MT; ++mt) {
+                        uint4 a0 = lds128g(acol + 2 * (mt * 16) * astride);
+                        uint4 a1 = lds128g(acol + 2 * (mt * 16 + 8) * astride);
+                        if (PRO == PRO_NORM) {
+                            a0 = norm8(a0, gbuf[u], inv[mt][0]);
+                            a1 = norm8(a1, gbuf[u], inv[mt][1]);
+                        }
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) {
+                            mma_16816(acc[i][mt], a0.x, a1.x, a0.y, a1.y, wbuf[u][i].x, wbuf[u][i].y);
+                            mma_16816(acc[i][mt], a0.z, a1.z, a0.w, a1.w, wbuf[u][i].z, wbuf[u][i].w);
+                        }
+                    }
+                    if (ci + U < cpw)
+                        load_slot(u, tile, ci + U);
+                    else if (has_next)
+                        load_slot(u, tile + gridDim.x, u);
+                }
+            }
+        }
+
+        // Warps -> CTA: red[warp][row][col], col = 8 i + 2 t + {0, 1} of the tile's 32 rows of W.
+#pragma unroll
+        for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                float* dst = red + ((warp * ROWS + mt * 16 + g) * 32 + i * 8 + 2 * t);
+                *reinterpret_cast<float2*>(dst) = make_float2(acc[i][mt][0], acc[i][mt][1]);
+                *reinterpret_cast<float2*>(dst + 8 * 32) = make_float2(acc[i][mt][2], acc[i][mt][3]);
+            }
+        __syncthreads();
+
+        auto cta_sum = [&](int e) {
+            float s = 0.f;
+#pragma unroll
+            for (int w = 0; w < kGemmWarps; ++w) s += red[w * ROWS * 32 + e];
+            return s;
+        };
+
+        // The sum for element e goes to red[e] (warp 0's slot): only the thread that owns
+        // e reads or writes that address, so no barrier is needed in between.
+        bool finish = true;
+        if (p.splits > 1) {
+            float* mine = p.part + ((long long)tile * p.splits + split) * (ROWS * 32);
+            for (int e = tid; e < ROWS * 32; e += kGemmThreads) mine[e] = cta_sum(e);
+            __syncthreads();
+            if (tid == 0) {
+                __threadfence();
+                const int seen = atomicAdd(p.counters + tile, 1);
+                is_last = (seen == p.splits - 1);
+                if (is_last) {
+                    p.counters[tile] = 0;               // ready for the next launch
+                    __threadfence();
+                }
+            }
+            __syncthreads();
+            finish = is_last != 0;
+            if (finish) {
+                // Split order, whoever arrives last: the sum does not depend on timing.
+                const float* base = p.part + (long long)tile * p.splits * (ROWS * 32);
+                for (int e = tid; e < ROWS * 32; e += kGemmThreads) {
+                    float s = 0.f;
+                    for (int sp = 0; sp < p.splits; ++sp) s += __ldcg(base + sp * (ROWS * 32) + e);
+                    red[e] = s;
+                }
+            }
+        } else {
+            for (int e = tid; e < ROWS * 32; e += kGemmThreads) red[e] = cta_sum(e);
+        }
+        __syncthreads();
+
+        // Epilogue on red[row][col].
+        if (finish && EPI == EPI_SWIGLU) {
+            for (int e = tid; e < ROWS * 16; e += kGemmThreads) {
+                const int row = e >> 4, j = e & 15;
+                if (row >= p.m) continue;
+                const float gate = round_h(red[row * 32 + j]);
+                const float up = round_h(red[row * 32 + 16 + j]);
+                const float act = round_h(gate / (1.f + expf(-gate)));
+                p.out[row * p.sout + tile * 16 + j] = __float2half_rn(act * up);
+            }
+        } else if (finish) {
+            // A warp covers one row's 32 columns per sweep (256 threads = 8 rows).
+            for (int e = tid; e < ROWS * 32; e += kGemmThreads) {
+                const int row = e >> 5, col = tile * kTileRows + (e & 31);
+                float v = red[e];
+                if (p.bias != nullptr) v += __half2float(p.bias[col]);
+                v = round_h(v);
+                if (p.add_res != nullptr && row < p.m)
+                    v = round_h(v + __half2float(p.add_res[row * p.sadd + col]));
+                if (row < p.m) p.out[row * p.sout + col] = __float2half_rn(v);
+                if (p.sumsq_out != nullptr) {
+                    float sq = (row < p.m) ? v * v : 0.f;
+#pragma unroll
+                    for (int off = 16; off > 0; off >>= 1) sq += __shfl_xor_sync(LS_FULL_MASK, sq, off);
+                    if (lane == 0) p.sumsq_out[tile * 64 + row] = sq;
+                }
+            }
+        }
+        __syncthreads();                                // red is free for the next tile
+    }
+}
+
+template <int MT, int U, int PRO, int EPI>
+static int launch_gemm(const GemmParams& p, int tiles, cudaStream_t stream, bool programmatic) {
+    const int per_split = ((p.k >> 5) + p.splits - 1) / p.splits;
+    const size_t a_bytes = sizeof(__half) * MT * 16 * (size_t)a_stride_halves(per_split * 32);
+    const size_t smem = a_bytes + sizeof(float) * kGemmWarps * MT * 16 * 32;
+    if (smem > 227 * 1024) return LS_ERR_TOO_LARGE;    // cut K into more splits
+    int dev = 0, sms = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    const int resident = (MT == 1 ? 2 : 1) * sms;      // CTAs the device holds at once
+    int per = resident / p.splits;
+    per = per < 1 ? 1 : (per > tiles ? tiles : per);
+    auto kern = skinny_gemm_kernel<MT, U, PRO, EPI>;
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(per, p.splits);
+    cfg.blockDim = dim3(kGemmThreads);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = programmatic ? 1 : 0;
+    e = cudaLaunchKernelEx(&cfg, kern, p);
+    if (e != cudaSuccess) return (int)e;
+    return (int)cudaGetLastError();
+}
+
+template <int PRO, int EPI>
+static int launch_gemm_m(const GemmParams& p, int tiles, cudaStream_t stream, bool programmatic) {
+    if (p.m <= 16) return launch_gemm<1, 3, PRO, EPI>(p, tiles, stream, programmatic);
+    if (p.m <= 32) return launch_gemm<2, 2, PRO, EPI>(p, tiles, stream, programmatic);
+    return launch_gemm<4, 2, PRO, EPI>(p, tiles, stream, programmatic);
+}
+
+}  // namespace ls
+
+extern "C" int ls_skinny_gemm(const void* x, const void* res, const void* gamma, void* res_out,
+                              const float* sumsq_in, int sumsq_tiles, const void* w, const void* bias,
+                              const void* add_res, float* sumsq_out, void* out, float* part,
+                              int32_t* counters, int m, int n, int k, int splits, int mode, float eps,
+                              int64_t sx, int64_t sres, int64_t sres_out, int64_t sw, int64_t sadd,
+                              int64_t sout, void* stream) {
+    using namespace ls;
+    const bool norm = mode & LS_GEMM_NORM, swiglu = mode & LS_GEMM_SWIGLU;
+    if (!x || !w || !out || (norm && !gamma) || (res && !res_out)) return LS_ERR_NULL_POINTER;
+    if ((res && !norm) || (sumsq_in && (!norm || res)) || (swiglu && (bias || add_res || sumsq_out)))
+        return LS_ERR_UNSUPPORTED;
+    if (m <= 0 || n <= 0 || k <= 0 || splits <= 0 || (sumsq_in && sumsq_tiles <= 0))
+        return LS_ERR_BAD_SHAPE;
+    if (m > 64) return LS_ERR_TOO_LARGE;
+    if ((k % 32) || (n % 32) || splits > k / 32) return LS_ERR_UNSUPPORTED;
+    if (splits > 1 && (!part || !counters)) return LS_ERR_NULL_POINTER;
+    auto bad = [](const void* ptr, int64_t stride) {
+        return (reinterpret_cast<uintptr_t>(ptr) & 15) || (stride % 8);
+    };
+    if (bad(x, sx) || bad(w, sw) || (res && (bad(res, sres) || bad(res_out, sres_out))) ||
+        (norm && bad(gamma, 8)))
+        return LS_ERR_MISALIGNED;
+    GemmParams p;
+    p.x = static_cast<const __half*>(x);
+    p.res = static_cast<const __half*>(res);
+    p.gamma = static_cast<const __half*>(gamma);
+    p.res_out = static_cast<__half*>(res_out);
+    p.sumsq_in = sumsq_in;
+    p.sumsq_tiles = sumsq_tiles;
+    p.w = static_cast<const __half*>(w);
+    p.bias = static_cast<const __half*>(bias);
+    p.add_res = static_cast<const __half*>(add_res);
+    p.sumsq_out = sumsq_out;
+    p.out = static_cast<__half*>(out);
+    p.part = part;
+    p.counters = counters;
+    p.m = m; p.n = n; p.k = k; p.splits = splits; p.eps = eps;
+    p.sx = sx; p.sres = sres; p.sres_out = sres_out; p.sw = sw; p.sadd = sadd; p.sout = sout;
+    const int tiles = n / kTileRows;                    // with SWIGLU: 16 gate + 16 up rows each
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const bool pdl = mode & LS_LAUNCH_PROGRAMMATIC;
+    if (norm && swiglu) return launch_gemm_m<PRO_NORM, EPI_SWIGLU>(p, tiles, st, pdl);
+    if (norm) return launch_gemm_m<PRO_NORM, EPI_NONE>(p, tiles, st, pdl);
+    if (swiglu) return launch_gemm_m<PRO_NONE, EPI_SWIGLU>(p, tiles, st, pdl);
+    return launch_gemm_m<PRO_NONE, EPI_NONE>(p, tiles, st, pdl);
+}

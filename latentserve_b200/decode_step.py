@@ -11,12 +11,17 @@ append and attention kernels inside a step of the same shape: dense
 projections and the MLP are plain cuBLAS GEMMs through torch, weights are
 random (N(0, 0.02), fp16).
 
-Per layer, in stream order (`fused=True`, nine launches): [residual add +]
-RMSNorm -> fused QKV GEMM (+bias) -> RoPE(q, k) + KV append (one launch) ->
-paged decode attention (one launch; dense, INT8 or page-sparse) -> o_proj GEMM
--> residual add + RMSNorm -> gate/up GEMM -> SiLU * up -> down GEMM. With
+Per layer, in stream order, with `projections="cublas"` (the default; nine
+launches): [residual add +] RMSNorm -> fused QKV GEMM (+ bias) -> RoPE(q, k) +
+KV append (one launch) -> paged decode attention (one launch; dense, INT8 or
+page-sparse) -> o_proj GEMM -> residual add + RMSNorm -> gate/up GEMM ->
+SiLU * up -> down GEMM, the GEMMs being torch's. With `projections="ls"` the
+projections are this library's weight-streaming kernel (`projections.linear`)
+with the norms, residual adds and SiLU * up folded into them (six launches);
+at batch 16 it is faster than cuBLAS on down_proj only and slower on the
+others, so it is not the default. With
 `fused=False` the norms, RoPE and SwiGLU are plain torch element-wise ops and
-the append is `cache.write` (the form the fused one is tested against).
+the append is `cache.write` (the form the fused ones are tested against).
 `cache.advance(1)` runs on the host before the step and is not part of a
 captured graph, as in the reference (runtime/cuda_graph.py:337).
 """
@@ -32,6 +37,7 @@ import torch
 from latentserve_b200 import fused_elementwise as fe
 from latentserve_b200 import paged_decode as pd
 from latentserve_b200 import paged_sparse as ps
+from latentserve_b200 import projections as pj
 
 
 @dataclass
@@ -74,9 +80,12 @@ class DecodeModel:
     """Random-init weights of the given shape and the decode step over a cache."""
 
     def __init__(self, shape: QwenShape, device, max_pos: int, seed: int = 0,
-                 dtype: torch.dtype = torch.float16, fused: bool = True):
+                 dtype: torch.dtype = torch.float16, fused: bool = True, projections: str = "cublas"):
         self.shape, self.device, self.dtype = shape, torch.device(device), dtype
         self.fused = fused
+        if projections not in ("ls", "cublas"):
+            raise ValueError(f"unknown projections {projections!r}")
+        self.projections = projections
         g = torch.Generator(device=self.device).manual_seed(seed)
         s = shape
 
@@ -129,6 +138,8 @@ class DecodeModel:
         """tokens, positions [B] (device) -> next token ids [B] (greedy), or the
         logits [B, vocab]. The cache must have been advanced by one token for
         these B sequences."""
+        if self.fused and self.projections == "ls" and tokens.shape[0] <= pj.MAX_ROWS:
+            return self._forward_streamed(cache, tokens, positions, context_hint, return_logits)
         if self.fused:
             return self._forward_fused(cache, tokens, positions, context_hint, return_logits)
         s = self.shape
@@ -174,6 +185,33 @@ class DecodeModel:
             x = fe.silu_and_mul(h @ L["wgu"].t()) @ L["wd"].t()
         h, _ = fe.fused_add_rms_norm(x, residual, self.ln_f, s.rms_eps)
         logits = h @ self.embed.t()
+        return logits if return_logits else logits.argmax(dim=-1)
+
+
+    def _forward_streamed(self, cache, tokens, positions, context_hint, return_logits):
+        """Six launches per layer: the norms, residual adds and SiLU * up ride on the projections."""
+        # Rounding differs from `_forward_fused` in one place: the residual stream is
+        # fp16(fp16(o) + r) in both, but here it is formed in o_proj's epilogue.
+        s = self.shape
+        b = tokens.shape[0]
+        stream = self.embed[tokens]                 # the residual stream, fp16 [B, hidden]
+        ss = None                                   # its row sums of squares, once a projection wrote it
+        for i, L in enumerate(self.layers):
+            qkv = pj.linear(stream, L["wqkv"], L["bqkv"], norm_weight=L["ln1"], row_sumsq=ss,
+                            eps=s.rms_eps)
+            q = torch.empty(b, s.q_heads * s.head_dim, dtype=self.dtype, device=self.device)
+            cache.rope_write(i, qkv, self.cos16, self.sin16, positions, q, s.q_heads)
+            a = self.attend(cache, i, q.view(b, s.kv_heads, s.q_heads // s.kv_heads, s.head_dim), b,
+                            context_hint)
+            stream, ss = pj.linear(a.reshape(b, s.q_heads * s.head_dim), L["wo"], add_residual=stream,
+                                   want_sumsq=True)
+            act = pj.linear(stream, L["wgu"], norm_weight=L["ln2"], row_sumsq=ss, eps=s.rms_eps,
+                            swiglu=True)
+            stream, ss = pj.linear(act, L["wd"], add_residual=stream, want_sumsq=True)
+        if s.vocab % 32 == 0:
+            logits = pj.linear(stream, self.embed, norm_weight=self.ln_f, row_sumsq=ss, eps=s.rms_eps)
+        else:
+            logits = fe.rms_norm(stream, self.ln_f, s.rms_eps) @ self.embed.t()
         return logits if return_logits else logits.argmax(dim=-1)
 
 

@@ -86,3 +86,4 @@ def rope_append_int8(qkv, cos, sin, positions, slots, res_idx, q_out, flat_v, fl
         eps, qmax, _reciprocal(qmax), levels, _reciprocal(levels), offset,
         _lib.current_stream(qkv.device))
     _lib.check(rc, "rope_append_int8")
+

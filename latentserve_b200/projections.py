@@ -1,0 +1,135 @@
+"""Decode-step projections on the weight-streaming kernel (`ls_skinny_gemm`).
+
+In the reference the four projections of a decoder layer are Hugging Face
+`nn.Linear` modules (cuBLAS) run by `LatentServeQwen._run_layers`
+(model/latentserve_qwen.py:397-451), with RMSNorm, the residual add and
+SiLU * up as separate (optionally Triton-fused) element-wise launches
+(kernels/fused_elementwise.py:194-232). For a decode batch of tens of rows each
+projection is a stream of weights through HBM, and the element-wise launches
+around it are latency-floor kernels; `linear` folds them into the projection:
+
+    qkv      = linear(s, w_qkv, b_qkv, norm_weight=ln1, row_sumsq=ss)
+    s, ss    = linear(attn, w_o, add_residual=s, want_sumsq=True)    # s = residual stream
+    act      = linear(s, w_gate_up, norm_weight=ln2, row_sumsq=ss, swiglu=True)
+    s, ss    = linear(act, w_down, add_residual=s, want_sumsq=True)
+
+(`row_sumsq` hands the norm its row statistics from the projection that wrote
+the row; without it the kernel reads the whole rows itself, and can add a
+`residual` in front of the norm.)
+
+Rounding follows the unfused model code (fp16 where Hugging Face rounds to
+fp16, fp32 accumulation in the product), so results agree with
+`fused_elementwise` + `torch.matmul` to fp16 rounding of the accumulation
+order; the GPU tests state the tolerance.
+"""
+
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from latentserve_b200 import _lib
+from latentserve_b200 import paged_decode_cuda as pdc
+
+GEMM_NORM, GEMM_SWIGLU = 1, 2
+MAX_ROWS = 64
+TILE_ROWS = 32
+
+
+def _rows_pad(m: int) -> int:
+    return 16 if m <= 16 else 32 if m <= 32 else 64
+
+
+def _stage_budget(rows: int) -> int:
+    """Bytes of staged activations a CTA may hold: what is left of an SM's shared
+    memory after the reduction buffer (1 KB per row), for two resident CTAs at 16
+    rows and one beyond."""
+    return (113 if rows == 16 else 227) * 1024 - rows * 1024
+
+
+def choose_splits(device: torch.device, tiles: int, k: int, m: int = 16) -> int:
+    """Slices of K across CTAs: enough that tiles x splits fills the CTAs the device
+    holds at once (without going past it, which would leave a second, nearly empty
+    wave), every warp still gets a 32-wide chunk, and a CTA's slice of the
+    activations fits its shared memory."""
+    chunks = k // 32
+    rows = _rows_pad(m)
+    resident = (2 if rows == 16 else 1) * pdc.sm_count(device)
+    splits = max(1, min(resident // tiles, chunks // 8 if chunks >= 8 else 1))
+    while splits < chunks and rows * 2 * (32 * -(-chunks // splits) + 32) > _stage_budget(rows):
+        splits += 1
+    return splits
+
+
+def linear(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None, *,
+           norm_weight: Optional[torch.Tensor] = None, residual: Optional[torch.Tensor] = None,
+           row_sumsq: Optional[torch.Tensor] = None, add_residual: Optional[torch.Tensor] = None,
+           want_sumsq: bool = False, eps: float = 1e-6, swiglu: bool = False,
+           out: Optional[torch.Tensor] = None, splits: Optional[int] = None):
+    """x [M, K] fp16 (M <= 64), w [N, K] fp16 -> [M, N] fp16 (or [M, N / 2] with
+    `swiglu`).
+
+    Front: with `norm_weight`, x is RMS-normalised first -- after adding
+    `residual`, when given (the return value is then (out, x + residual)), or
+    with the row statistics in `row_sumsq` (as returned by `want_sumsq`).
+    Back: `add_residual` [M, N] is added to the fp16-rounded product;
+    `want_sumsq` also returns per-row partial sums of squares of the output
+    ([N / 32, 64] fp32), for the next call's `row_sumsq`."""
+    if not x.is_cuda:
+        raise RuntimeError("latentserve_b200 has no CPU path: tensors must be on a CUDA device")
+    if x.dim() != 2 or w.dim() != 2 or x.dtype != torch.float16 or w.dtype != torch.float16:
+        raise ValueError("linear takes fp16 x [M, K] and w [N, K]")
+    m, k = x.shape
+    n = w.shape[0]
+    if w.shape[1] != k or x.stride(1) != 1 or w.stride(1) != 1:
+        raise ValueError("x and w must share K and have unit-stride rows")
+    if m > MAX_ROWS:
+        raise ValueError(f"linear streams weights for at most {MAX_ROWS} rows, got {m}")
+    if (residual is not None or row_sumsq is not None) and norm_weight is None:
+        raise ValueError("residual / row_sumsq belong to the norm: pass norm_weight as well")
+    if residual is not None and row_sumsq is not None:
+        raise ValueError("row_sumsq describes x itself: it cannot be combined with a residual")
+    if residual is not None and (residual.shape != x.shape or residual.dtype != x.dtype
+                                 or residual.stride(1) != 1):
+        raise ValueError("residual must match x")
+    if row_sumsq is not None and (row_sumsq.dtype != torch.float32 or row_sumsq.dim() != 2
+                                  or row_sumsq.shape[1] != 64 or not row_sumsq.is_contiguous()):
+        raise ValueError("row_sumsq must be the contiguous fp32 [tiles, 64] tensor want_sumsq returns")
+    if row_sumsq is not None and row_sumsq.shape[0] * 32 != k:
+        raise ValueError("row_sumsq does not describe rows of this K")
+    if bias is not None and (bias.shape != (n,) or bias.dtype != x.dtype or not bias.is_contiguous()):
+        raise ValueError("bias must be a contiguous fp16 [N] vector")
+    if swiglu and (bias is not None or add_residual is not None or want_sumsq):
+        raise ValueError("the SwiGLU epilogue takes no bias, residual or row statistics")
+    if add_residual is not None and (add_residual.shape != (m, n) or add_residual.dtype != x.dtype
+                                     or add_residual.stride(1) != 1):
+        raise ValueError("add_residual must be fp16 [M, N] with unit-stride rows")
+    mode = (GEMM_NORM if norm_weight is not None else 0) | (GEMM_SWIGLU if swiglu else 0)
+    mode |= pdc.launch_flags()
+    tiles = n // 32
+    n_out = n // 2 if swiglu else n
+    if out is None:
+        out = torch.empty((m, n_out), dtype=x.dtype, device=x.device)
+    elif out.shape != (m, n_out) or out.dtype != x.dtype or out.stride(1) != 1:
+        raise ValueError("out has the wrong shape, dtype or layout")
+    res_out = torch.empty_like(x) if residual is not None else None
+    sumsq = torch.empty((tiles, 64), dtype=torch.float32, device=x.device) if want_sumsq else None
+    if splits is None:
+        splits = choose_splits(x.device, tiles, k, m)
+    part = counters = None
+    if splits > 1:
+        part = pdc.scratch("gemm_part", (tiles * splits * _rows_pad(m) * 32,), torch.float32, x.device)
+        counters = pdc.scratch("gemm_counters", (tiles,), torch.int32, x.device, zero=True)
+    ptr = _lib.ptr
+    rc = _lib.lib().ls_skinny_gemm(
+        x.data_ptr(), ptr(residual), ptr(norm_weight), ptr(res_out), ptr(row_sumsq),
+        row_sumsq.shape[0] if row_sumsq is not None else 0, w.data_ptr(), ptr(bias),
+        ptr(add_residual), ptr(sumsq), out.data_ptr(), ptr(part), ptr(counters), m, n, k, splits, mode,
+        eps, x.stride(0), residual.stride(0) if residual is not None else 0,
+        res_out.stride(0) if res_out is not None else 0, w.stride(0),
+        add_residual.stride(0) if add_residual is not None else 0, out.stride(0),
+        _lib.current_stream(x.device))
+    _lib.check(rc, "linear")
+    extra = tuple(t for t in (res_out, sumsq) if t is not None)
+    return (out, *extra) if extra else out

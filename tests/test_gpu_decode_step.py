@@ -100,18 +100,34 @@ def test_step_with_library_attention_matches_torch_attention(pdl):
     assert same >= 0.9
 
 
+@pytest.mark.parametrize("projections", ["ls", "cublas"])
 @pytest.mark.parametrize("kind", ["fp16", "int8"])
-def test_fused_layer_kernels_match_the_unfused_step(kind):
+def test_fused_layer_kernels_match_the_unfused_step(kind, projections):
     """RMSNorm (+ residual), RoPE + append and SiLU * up as this library's kernels
-    against the same step with torch element-wise ops and cache.write."""
+    (stand-alone with cuBLAS projections, or folded into this library's own
+    projections) against the same step with torch element-wise ops and cache.write."""
     dev = device()
-    fused = _drive(ds.DecodeModel(SHAPE, dev, max_pos=512, seed=5, fused=True), _fresh(kind), _prompts(),
-                   steps=20)
+    fused = _drive(ds.DecodeModel(SHAPE, dev, max_pos=512, seed=5, fused=True, projections=projections),
+                   _fresh(kind), _prompts(), steps=20)
     plain = _drive(ds.DecodeModel(SHAPE, dev, max_pos=512, seed=5, fused=False), _fresh(kind), _prompts(),
                    steps=20)
     for a, b in zip(fused, plain):
         assert torch.isfinite(a).all()
         assert (a - b).abs().max() <= 3e-2 + 2e-2 * b.abs().max()
+
+
+def test_streamed_output_head():
+    """vocab a multiple of 32: the final norm and the output head run on the projection kernel too."""
+    import dataclasses
+
+    dev = device()
+    shape = dataclasses.replace(SHAPE, vocab=1024)
+    a = ds.DecodeModel(shape, dev, max_pos=512, seed=6, fused=True, projections="ls")
+    b = ds.DecodeModel(shape, dev, max_pos=512, seed=6, fused=False)
+    prompts = [[int(t) % 1024 for t in p] for p in _prompts()]
+    for x, y in zip(_drive(a, _fresh("fp16"), prompts, steps=6), _drive(b, _fresh("fp16"), prompts, steps=6)):
+        assert torch.isfinite(x).all()
+        assert (x - y).abs().max() <= 3e-2 + 2e-2 * y.abs().max()
 
 
 def test_graph_replay_produces_the_eager_tokens():
