@@ -45,6 +45,10 @@ extern "C" {
  * kernel. Only set it when the kernel launched just before on the stream does
  * not write seq_lens or block_tables (in LatentServe it is the KV append). */
 #define LS_LAUNCH_PROGRAMMATIC 0x100
+/* ls_paged_decode_int8 only: load pages with per-lane cp.async instead of TMA tile
+ * copies (the form also used, without this flag, for asymmetric pools and for
+ * layouts the tensor maps cannot describe). Same results; kept for comparison. */
+#define LS_LOAD_CP_ASYNC 0x200
 
 /* Partial-state scratch shared by the three decode entry points.
  *

@@ -37,6 +37,7 @@
 #ifndef LS_LAUNCH_PROGRAMMATIC
 #define LS_LAUNCH_PROGRAMMATIC 0x100
 #endif
+#define LS_LOAD_CP_ASYNC 0x200
 #define LS_GEMM_NORM 1
 #define LS_GEMM_SWIGLU 2
 
@@ -91,6 +92,62 @@ __device__ __forceinline__ void cp_async_commit() {
 template <int N>
 __device__ __forceinline__ void cp_async_wait() {
     asm volatile("cp.async.wait_group %0;\n" ::"n"(N) : "memory");
+}
+
+// ---------------------------------------------------------------------------
+// TMA (bulk asynchronous copies into shared memory, completion counted in bytes
+// on an mbarrier). One lane issues a whole tile; nobody computes addresses per
+// 16 bytes. No cluster multicast is used anywhere.
+__device__ __forceinline__ void mbar_init(uint32_t mbar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(mbar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_init_fence() {
+    asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t mbar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(mbar), "r"(bytes)
+                 : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t mbar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(mbar) : "memory");
+}
+// One probe of the phase with the given parity; the instruction itself waits a
+// bounded, implementation-defined time before it answers "not yet".
+__device__ __forceinline__ bool mbar_try_wait(uint32_t mbar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+        "selp.u32 %0, 1, 0, p;\n"
+        "}\n"
+        : "=r"(ok)
+        : "r"(mbar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// Bounded wait: false if the phase did not complete within `limit` probes.
+__device__ __forceinline__ bool mbar_wait_bounded(uint32_t mbar, uint32_t parity, int limit) {
+    for (int i = 0; i < limit; ++i)
+        if (mbar_try_wait(mbar, parity)) return true;
+    return false;
+}
+__device__ __forceinline__ void tma_load_4d(uint32_t dst, const void* tmap, uint32_t mbar, int c0,
+                                            int c1, int c2, int c3, uint64_t policy) {
+    asm volatile(
+        "cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes"
+        ".L2::cache_hint [%0], [%1, {%2, %3, %4, %5}], [%6], %7;\n" ::"r"(dst),
+        "l"(tmap), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(mbar), "l"(policy)
+        : "memory");
+}
+// Untiled bulk copy: both addresses 16-byte aligned, bytes a multiple of 16.
+__device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_t bytes,
+                                          uint32_t mbar) {
+    asm volatile(
+        "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n" ::
+            "r"(dst),
+        "l"(src), "r"(bytes), "r"(mbar)
+        : "memory");
 }
 
 __device__ __forceinline__ void ldmatrix_x4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2,

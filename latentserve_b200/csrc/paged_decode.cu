@@ -35,9 +35,12 @@
 //   * the CTA that delivers a sequence's last outstanding partial (an atomic
 //     arrival count per (sequence, head), no waiting) merges them and writes
 //     the fp16 output, so a layer call is ONE launch.
+#include <cuda.h>
+
 #include "decode_sched.cuh"
 
 #include <mutex>
+#include <type_traits>
 
 namespace ls {
 
@@ -48,7 +51,16 @@ namespace ls {
 #define LS_STAGES 3                 // cp.async ring depth per warp
 #endif
 #ifndef LS_INT8_STAGES
-#define LS_INT8_STAGES 2            // ring depth of the INT8 kernel (smaller stages, more CTAs)
+#define LS_INT8_STAGES 3            // ring depth of the INT8 kernel (4.6 KB stages, 3 CTAs per SM)
+#endif
+#ifndef LS_INT8_TMA_STAGES
+#define LS_INT8_TMA_STAGES 2        // 5 KB stages of the TMA-loading INT8 kernel
+#endif
+#ifndef LS_LAZY_MAX
+#define LS_LAZY_MAX 1                // keep the softmax reference while scores stay within a margin of it
+#endif
+#ifndef LS_INT8_STAGES_ASYM
+#define LS_INT8_STAGES_ASYM 2       // 5.1 KB stages: a third one would cost the third CTA
 #endif
 #ifndef LS_INT8_CTAS
 #define LS_INT8_CTAS 3              // resident CTAs per SM the INT8 kernel is compiled for
@@ -57,6 +69,11 @@ namespace ls {
 #define LS_EVICT_FIRST 1            // L2 evict-first policy on the (read-once) KV page loads
 #endif
 constexpr int kWarps = 4;
+// Tensor maps of the TMA-loading variants (unused and zero for the others).
+struct TmaMaps {
+    CUtensorMap k, v, ks;
+};
+constexpr int kMbarSpinLimit = 1 << 22;   // probes of an mbarrier phase before a warp gives up
 constexpr int kStages = LS_STAGES;
 constexpr int kThreads = kWarps * 32;
 constexpr int kMergeStride = LS_HEAD_DIM + 4;   // floats per merged row (bank-conflict pad)
@@ -157,8 +174,32 @@ struct PageWindow {
 // s[0] = (g, 2t), s[1] = (g, 2t+1), s[2] = (g+8, 2t), s[3] = (g+8, 2t+1).
 // On return s holds the weights 2^(s - m_new); m, l and the output
 // accumulators o[8][4] are rescaled. Scores are in the log2 domain.
+constexpr float kLazyMargin = 8.f;      // log2 units
 __device__ __forceinline__ void softmax_update(float (&s)[4], float (&m)[2], float (&l)[2],
                                                float (&o)[8][4], float& a0, float& a1) {
+#if LS_LAZY_MAX
+    // Usual case after a segment's first pages: no score of the page rises more
+    // than 2^kLazyMargin above the running reference m. Then m is kept as it is
+    // (any shared reference gives the same normalised result; weights stay below
+    // 2^kLazyMargin, well inside fp16) and one vote replaces the six shuffles and
+    // the rescale test. The choice depends on the data only, so results are
+    // reproducible.
+    {
+        const float lim0 = m[0] + kLazyMargin, lim1 = m[1] + kLazyMargin;
+        const bool ok = (m[0] != neg_inf()) & (m[1] != neg_inf()) & (s[0] <= lim0) & (s[2] <= lim0) &
+                        (s[1] <= lim1) & (s[3] <= lim1);
+        if (__all_sync(LS_FULL_MASK, ok)) {
+            a0 = a1 = 1.f;
+            s[0] = ex2(s[0] - m[0]);
+            s[1] = ex2(s[1] - m[1]);
+            s[2] = ex2(s[2] - m[0]);
+            s[3] = ex2(s[3] - m[1]);
+            l[0] += s[0] + s[2];
+            l[1] += s[1] + s[3];
+            return;
+        }
+    }
+#endif
     float mx0 = fmaxf(s[0], s[2]);
     float mx1 = fmaxf(s[1], s[3]);
 #pragma unroll
@@ -238,6 +279,7 @@ __device__ __forceinline__ void load_q_fragments(const DecodeParams& p, int b, i
 // ---------------------------------------------------------------------------
 // fp16 pools: page loads.
 struct PoolFp16 {
+    static constexpr bool kTma = false;
     static constexpr int STAGE_BYTES = 8192;       // K 4096 | V 4096
 
     // 256 16-byte chunks of K and of V per page-head, 8 + 8 per lane: lane l
@@ -499,8 +541,12 @@ struct SimtFp16 {
 //   [7168, 7232)  V scale, 16 fp32      [7232, 7296)  V zero point (asymmetric only)
 template <int ASYM>
 struct PoolInt8 {
-    static constexpr int STAGE_BYTES = 7424;
-    static constexpr int OFF_V = 4096, OFF_KS = 6144, OFF_KZ = 6656, OFF_VS = 7168, OFF_VZ = 7232;
+    static constexpr bool kTma = false;
+    // K 2 KB | V 2 KB | K scales 512 B | V scales 64 B [| K zeros 512 B | V zeros 64 B].
+    // The fp16 K of a sequence's last page does not pass through the ring: the
+    // compute side reads it straight from the residual (once per sequence and head).
+    static constexpr int STAGE_BYTES = ASYM ? 5248 : 4672;
+    static constexpr int OFF_V = 2048, OFF_KS = 4096, OFF_VS = 4608, OFF_KZ = 4672, OFF_VZ = 5184;
 
     // meta = valid tokens | (K came from the residual) << 8
     static __device__ __forceinline__ int issue(const DecodeParams& p, int b, int h,
@@ -510,17 +556,6 @@ struct PoolInt8 {
         if (rr < 0 || rr >= p.num_res_rows) {             // corrupt row index: read nothing, flag it
             if (lane == 0) p.seg_range[2 * p.batch] = 1;
             rr = 0;
-        }
-        if (from_res) {
-            const __half* kr = p.k_res + (long long)rr * p.sr_r + h * p.sr_h;
-#pragma unroll
-            for (int i = 0; i < 8; ++i) {
-                const int ci = i * 32 + lane;
-                const int row = ci >> 4, col = ci & 15;
-                const int nbytes = row < it.valid ? 16 : 0;
-                cp_async_16(stage + row * 256 + ((col ^ (row & 7)) << 4),
-                            kr + (nbytes ? row * p.sr_p + col * 8 : 0), nbytes);
-            }
         }
         // int8 rows: lane l takes chunk (l & 7) of rows 4i + (l >> 3), i = 0..3; a
         // warp-wide copy covers four whole 128-byte rows.
@@ -592,6 +627,46 @@ struct PoolInt8 {
     }
 };
 
+// INT8 pools (symmetric) loaded by TMA: one lane issues the K tile, the V tile
+// (tensor maps with the 128-byte swizzle, which is the chunk ^ (row & 7) layout
+// the compute side reads), the block's K scales (a 4 x 128-byte tile, swizzled
+// the same way) and the page's V scales for all heads (one contiguous piece),
+// against ~220 instructions per page and lane for the cp.async form. Tiles
+// always hold all 16 rows: rows past the sequence's end are stale pool bytes,
+// which for int8 are finite numbers; their scores are masked and their V scales
+// are replaced by zero on the compute side.
+struct PoolInt8Tma {
+    static constexpr bool kTma = true;
+    static constexpr int STAGE_BYTES = 5120;           // stages stay 1024-byte aligned for the swizzle
+    static constexpr int OFF_V = 2048, OFF_KS = 4096, OFF_VS = 4608, OFF_KZ = 0, OFF_VZ = 0;
+
+    static __device__ __forceinline__ int issue(const DecodeParams& p, const TmaMaps& maps, int b,
+                                                int h, const PageItem& it, uint32_t stage,
+                                                uint32_t mbar, int lane) {
+        const bool from_res = p.k_res != nullptr && it.last && it.valid > 0;
+        if (from_res) {
+            const int rr = p.res_rows[b];
+            if ((rr < 0 || rr >= p.num_res_rows) && lane == 0) p.seg_range[2 * p.batch] = 1;
+        }
+        if (lane == 0) {
+            if (it.valid == 0) {
+                mbar_arrive(mbar);                     // nothing to load: the phase completes at once
+            } else {
+                const uint32_t vs_bytes = 16u * p.heads * sizeof(float);
+                mbar_expect_tx(mbar, 2048u + vs_bytes + (from_res ? 0u : 2048u + 512u));
+                const uint64_t pol = l2_policy_evict_first();
+                if (!from_res) {
+                    tma_load_4d(stage, &maps.k, mbar, 0, h, 0, it.blk, pol);
+                    tma_load_4d(stage + OFF_KS, &maps.ks, mbar, 0, 0, h, it.blk, pol);
+                }
+                tma_load_4d(stage + OFF_V, &maps.v, mbar, 0, h, 0, it.blk, pol);
+                bulk_load(stage + OFF_VS, p.v_scale + it.blk * p.vs_b, vs_bytes, mbar);
+            }
+        }
+        return it.valid | (from_res ? 256 : 0);
+    }
+};
+
 __device__ __forceinline__ uint4 lds128(uint32_t addr) {
     uint4 r;
     asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];\n"
@@ -613,9 +688,9 @@ __device__ __forceinline__ float lds32f(uint32_t addr) {
 // the query fragments are built in the same order. For V the m index (output
 // dim) is permuted instead: lane (g, t) takes dims 16g .. 16g+15 of tokens
 // 2t, 2t+1, 2t+8, 2t+9, and tile mt holds dims 16g + 2mt and 16g + 2mt + 1.
-template <int ASYM>
+template <int ASYM, bool TMA = false>
 struct MmaInt8 {
-    using Pool = PoolInt8<ASYM>;
+    using Pool = typename std::conditional<TMA, PoolInt8Tma, PoolInt8<ASYM>>::type;
     static constexpr int kMinCtas = LS_INT8_CTAS;
     float qf[32];              // Q[row g][32t .. 32t+31] in fp32 (row g < n_rep, else 0)
     float o[8][4];             // O^T: tile mt = dims 16g + 2mt (regs 0,1) and +1 (regs 2,3)
@@ -655,11 +730,29 @@ struct MmaInt8 {
         const int g = lane >> 2, t = lane & 3;
         float s[4] = {0.f, 0.f, 0.f, 0.f};
         if (meta & 256) {
-            // Last page: K is exact fp16 in the residual. Its query fragments
-            // are fetched on the spot; this happens once per (sequence, head).
-            uint32_t qb[8][2];
-            load_q_fragments(p, b_, h_, lane, qb);
-            qk_fp16(s, stage, qb, lane);
+            // Last page: K is exact fp16 in the residual, read from global memory in
+            // the same dim order as the int8 path (dims 32t .. 32t+31 of rows g, g+8:
+            // 64 contiguous bytes per row); the query needs no scale. Rows past
+            // `valid` may hold anything: their scores are masked below.
+            int rr = p.res_rows[b_];
+            if (rr < 0 || rr >= p.num_res_rows) rr = 0;           // flagged by the load side
+            const __half* kr = p.k_res + (long long)rr * p.sr_r + h_ * p.sr_h + 32 * t;
+            const uint4* r0 = reinterpret_cast<const uint4*>(kr + g * p.sr_p);
+            const uint4* r1 = reinterpret_cast<const uint4*>(kr + (g + 8) * p.sr_p);
+            uint4 ka[4], kb[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                ka[j] = __ldcg(r0 + j);
+                kb[j] = __ldcg(r1 + j);
+            }
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                mma_16816(s, ka[j].x, kb[j].x, ka[j].y, kb[j].y,
+                          pack_half2(qf[8 * j], qf[8 * j + 1]), pack_half2(qf[8 * j + 2], qf[8 * j + 3]));
+                mma_16816(s, ka[j].z, kb[j].z, ka[j].w, kb[j].w,
+                          pack_half2(qf[8 * j + 4], qf[8 * j + 5]),
+                          pack_half2(qf[8 * j + 6], qf[8 * j + 7]));
+            }
         } else {
             // q' = fp16(q * k_scale), one rounding, in this lane's dim order.
             uint32_t qk[8][2];
@@ -709,8 +802,17 @@ struct MmaInt8 {
         softmax_update(s, m, l, o, a0, a1);
         // V's per-token scale rides on the weight (zero for rows past the end:
         // the scale slots of those rows were zero-filled).
-        const float vs0 = lds32f(stage + Pool::OFF_VS + g * 4);
-        const float vs1 = lds32f(stage + Pool::OFF_VS + (g + 8) * 4);
+        float vs0, vs1;
+        if (TMA) {
+            // The page's scales for all heads, [token][head]; tokens past the end are stale.
+            vs0 = lds32f(stage + Pool::OFF_VS + (g * p.heads + h_) * 4);
+            vs1 = lds32f(stage + Pool::OFF_VS + ((g + 8) * p.heads + h_) * 4);
+            if (g >= valid) vs0 = 0.f;
+            if (g + 8 >= valid) vs1 = 0.f;
+        } else {
+            vs0 = lds32f(stage + Pool::OFF_VS + g * 4);
+            vs1 = lds32f(stage + Pool::OFF_VS + (g + 8) * 4);
+        }
         if (ASYM) {
             const float vz0 = lds32f(stage + Pool::OFF_VZ + g * 4);
             const float vz1 = lds32f(stage + Pool::OFF_VZ + (g + 8) * 4);
@@ -876,14 +978,17 @@ __device__ __forceinline__ void merge_partials(const float* part_acc, const floa
 
 // ---------------------------------------------------------------------------
 template <class State, int MODE, int STAGES>
-__global__ void __launch_bounds__(kThreads, State::kMinCtas) decode_kernel(const DecodeParams p) {
+__global__ void __launch_bounds__(kThreads, State::kMinCtas)
+decode_kernel(const DecodeParams p, const __grid_constant__ TmaMaps maps) {
     extern __shared__ __align__(1024) unsigned char smem[];
     using Pool = typename State::Pool;
     constexpr int STAGE_BYTES = Pool::STAGE_BYTES;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int chunk_id = blockIdx.x, h = blockIdx.y;
 
-    float* merge_o = reinterpret_cast<float*>(smem + kWarps * STAGES * STAGE_BYTES);
+    // After the ring: one mbarrier per (warp, stage) for the TMA-loading variants.
+    const uint32_t mbar0 = smem_u32(smem + kWarps * STAGES * STAGE_BYTES) + warp * STAGES * 8;
+    float* merge_o = reinterpret_cast<float*>(smem + kWarps * STAGES * STAGE_BYTES + kWarps * STAGES * 8);
     float* merge_m = merge_o + kWarps * p.n_rep * kMergeStride;
     float* merge_l = merge_m + kWarps * kRP;
     int* meta = reinterpret_cast<int*>(merge_l + kWarps * kRP);   // [kWarps][STAGES]
@@ -897,6 +1002,14 @@ __global__ void __launch_bounds__(kThreads, State::kMinCtas) decode_kernel(const
     // seq_lens and block_tables while the previous kernel is still finishing.
     // Without the attribute both instructions are no-ops.
     asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
+    if (Pool::kTma) {
+        if (lane == 0) {
+#pragma unroll
+            for (int s = 0; s < STAGES; ++s) mbar_init(mbar0 + 8 * s, 1);
+            mbar_init_fence();
+        }
+        __syncwarp();
+    }
     const int total = build_prefix<MODE, kThreads>(p, cum, scan);
     const int chunk = chunk_size(p, total);
     const int g0 = chunk_id * chunk;
@@ -929,28 +1042,44 @@ __global__ void __launch_bounds__(kThreads, State::kMinCtas) decode_kernel(const
         PageItem item;
         int lb;
         if (win.next(p, cum, h, warp, lane, item, lb)) {
-            const int mt = Pool::issue(p, lb, h, item, ring + stage * STAGE_BYTES, lane);
+            int mt;
+            if constexpr (Pool::kTma)
+                mt = Pool::issue(p, maps, lb, h, item, ring + stage * STAGE_BYTES, mbar0 + 8 * stage, lane);
+            else
+                mt = Pool::issue(p, lb, h, item, ring + stage * STAGE_BYTES, lane);
             if (lane == 0) my_meta[stage] = mt;
         }
-        cp_async_commit();
+        if (!Pool::kTma) cp_async_commit();
     };
 #pragma unroll
     for (int s = 0; s < STAGES - 1; ++s) issue(s);
 
     // Compute side: segment by segment.
     State st;
-    int it = 0;            // pages this warp has consumed
+    int stage = 0;         // ring slot of the page being consumed
+    uint32_t phase = 0;    // parity of that slot's mbarrier phase (TMA variants)
     int b = b0;
     int first_u = g0 - cum[b0];
     for (int guard = 0; guard <= p.batch; ++guard) {
         const int hi = min(g1, cum[b + 1]) - cum[b];
         st.begin(p, b, h, lane);
-        for (int u = first_u + warp; u < hi; u += kWarps, ++it) {
-            cp_async_wait<STAGES - 2>();
+        for (int u = first_u + warp; u < hi; u += kWarps) {
+            if constexpr (Pool::kTma) {
+                // Bounded: a load that never lands is reported (status 2 in the error
+                // slot), not waited for; the result of this launch is then invalid.
+                if (!mbar_wait_bounded(mbar0 + 8 * stage, phase, kMbarSpinLimit)) {
+                    if (lane == 0) p.seg_range[2 * p.batch] = 2;
+                }
+            } else {
+                cp_async_wait<STAGES - 2>();
+            }
             __syncwarp();
-            issue((it + STAGES - 1) % STAGES);
-            const int stage = it % STAGES;
+            issue(stage == 0 ? STAGES - 1 : stage - 1);      // the stage consumed one page ago
             st.compute(p, ring + stage * STAGE_BYTES, my_meta[stage], lane);
+            if (++stage == STAGES) {
+                stage = 0;
+                phase ^= 1u;
+            }
         }
         st.finish(merge_o + warp * p.n_rep * kMergeStride, merge_m + warp * kRP,
                   merge_l + warp * kRP, p.n_rep, lane);
@@ -1048,8 +1177,10 @@ static int validate_common(const DecodeParams& p) {
 }
 
 template <class State, int MODE, int STAGES>
-static int launch_decode(const DecodeParams& p, cudaStream_t stream, bool programmatic = false) {
-    const size_t smem = (size_t)kWarps * STAGES * State::Pool::STAGE_BYTES +
+static int launch_decode(const DecodeParams& p, cudaStream_t stream, bool programmatic = false,
+                         const TmaMaps* maps = nullptr) {
+    static const TmaMaps no_maps = {};
+    const size_t smem = (size_t)kWarps * STAGES * State::Pool::STAGE_BYTES + kWarps * STAGES * 8 +
                         sizeof(float) * ((size_t)kWarps * p.n_rep * kMergeStride + 2 * kWarps * kRP) +
                         sizeof(int) * ((size_t)kWarps * STAGES + kWarps + 1 + p.batch + 1);
     auto kern = decode_kernel<State, MODE, STAGES>;
@@ -1065,12 +1196,67 @@ static int launch_decode(const DecodeParams& p, cudaStream_t stream, bool progra
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = programmatic ? 1 : 0;
-    e = cudaLaunchKernelEx(&cfg, kern, p);
+    e = cudaLaunchKernelEx(&cfg, kern, p, maps ? *maps : no_maps);
     if (e != cudaSuccess) return (int)e;
     return (int)cudaGetLastError();
 }
 
 }  // namespace ls
+
+// ---------------------------------------------------------------------------
+// Tensor maps for the TMA-loading INT8 kernel, encoded per call (a host-side
+// table fill, no device work). The driver entry point is looked up through the
+// runtime, so the library does not link libcuda.
+namespace {
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_tiled_fn() {
+    static EncodeTiledFn fn = [] {
+        void* sym = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q) != cudaSuccess ||
+            q != cudaDriverEntryPointSuccess)
+            sym = nullptr;
+        return reinterpret_cast<EncodeTiledFn>(sym);
+    }();
+    return fn;
+}
+
+// A 4-d map with the 128-byte swizzle: dims innermost first, strides (bytes) of dims 1..3.
+bool encode_4d(CUtensorMap* map, CUtensorMapDataType type, const void* base, const cuuint64_t (&dims)[4],
+               const cuuint64_t (&strides)[3], const cuuint32_t (&box)[4]) {
+    EncodeTiledFn fn = encode_tiled_fn();
+    if (fn == nullptr) return false;
+    const cuuint32_t ones[4] = {1, 1, 1, 1};
+    return fn(map, type, 4, const_cast<void*>(base), dims, strides, box, ones, CU_TENSOR_MAP_INTERLEAVE_NONE,
+              CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+// True if the symmetric INT8 pools have the layout the TMA kernel takes and the maps were built.
+bool build_int8_maps(const ls::DecodeParams& p, ls::TmaMaps* maps) {
+    // pools [blocks][16][H][128] int8 (any strides that are 16-byte multiples, innermost unit);
+    // K scales [blocks][H][128] fp32; V scales [blocks][16][H] fp32 with tokens and heads dense.
+    if (p.heads > 8 || p.vs_h != 1 || p.vs_p != p.heads || (p.vs_b % 4) ||
+        (reinterpret_cast<uintptr_t>(p.v_scale) & 15))
+        return false;
+    const cuuint64_t nb = (cuuint64_t)p.num_blocks, H = (cuuint64_t)p.heads;
+    const cuuint64_t pool_dims[4] = {128, H, 16, nb};
+    const cuuint64_t pool_strides[3] = {(cuuint64_t)p.sk_h, (cuuint64_t)p.sk_p, (cuuint64_t)p.sk_b};
+    const cuuint32_t pool_box[4] = {128, 1, 16, 1};
+    const cuuint64_t ks_dims[4] = {32, 4, H, nb};
+    const cuuint64_t ks_strides[3] = {128, (cuuint64_t)p.ks_h * 4, (cuuint64_t)p.ks_b * 4};
+    const cuuint32_t ks_box[4] = {32, 4, 1, 1};
+    return encode_4d(&maps->k, CU_TENSOR_MAP_DATA_TYPE_UINT8, p.k_pool, pool_dims, pool_strides, pool_box) &&
+           encode_4d(&maps->v, CU_TENSOR_MAP_DATA_TYPE_UINT8, p.v_pool, pool_dims, pool_strides, pool_box) &&
+           encode_4d(&maps->ks, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, p.k_scale, ks_dims, ks_strides, ks_box);
+}
+
+}  // namespace
 
 using ls::DecodeParams;
 
@@ -1247,10 +1433,13 @@ int ls_paged_decode_int8(const void* q, const void* k_pool, const void* v_pool,
     if (k_res && ((reinterpret_cast<uintptr_t>(k_res) & 15) || (sr_r % 8) || (sr_p % 8) || (sr_h % 8)))
         return LS_ERR_MISALIGNED;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    if (flags & ~LS_LAUNCH_PROGRAMMATIC) return LS_ERR_UNSUPPORTED;
+    if (flags & ~(LS_LAUNCH_PROGRAMMATIC | LS_LOAD_CP_ASYNC)) return LS_ERR_UNSUPPORTED;
     const bool pdl = (flags & LS_LAUNCH_PROGRAMMATIC) != 0;
+    ls::TmaMaps maps;
     if (k_zero)
-        rc = ls::launch_decode<ls::MmaInt8<1>, LS_MODE_DENSE, LS_INT8_STAGES>(p, s, pdl);
+        rc = ls::launch_decode<ls::MmaInt8<1>, LS_MODE_DENSE, LS_INT8_STAGES_ASYM>(p, s, pdl);
+    else if (!(flags & LS_LOAD_CP_ASYNC) && build_int8_maps(p, &maps))
+        rc = ls::launch_decode<ls::MmaInt8<0, true>, LS_MODE_DENSE, LS_INT8_TMA_STAGES>(p, s, pdl, &maps);
     else
         rc = ls::launch_decode<ls::MmaInt8<0>, LS_MODE_DENSE, LS_INT8_STAGES>(p, s, pdl);
     return rc;

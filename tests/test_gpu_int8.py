@@ -169,10 +169,19 @@ def _random_int8_case(lens, asym, residual, seed):
     return case
 
 
+@pytest.fixture(params=["tma", "cp_async"])
+def loader(request):
+    """Both page-loading forms of the INT8 kernel (TMA tiles for symmetric pools,
+    per-lane cp.async otherwise or on request)."""
+    pdc.set_int8_loader(request.param)
+    yield request.param
+    pdc.set_int8_loader("tma")
+
+
 @pytest.mark.parametrize("asym", [False, True])
 @pytest.mark.parametrize("residual", [False, True])
 @pytest.mark.parametrize("splits", [None, 1, 3])
-def test_int8_decode_matches_the_oracle(asym, residual, splits):
+def test_int8_decode_matches_the_oracle(asym, residual, splits, loader):
     lens = [1024, 300, 61, 17, 1, 32, 0]
     case = _random_int8_case(lens, asym, residual, seed=21)
     extra = {k: case[k] for k in ("k_scale", "v_scale", "k_zero", "v_zero", "k_residual", "res_rows")
@@ -186,9 +195,29 @@ def test_int8_decode_matches_the_oracle(asym, residual, splits):
         num_splits=splits, k_scale=t["k_scale"], v_scale=t["v_scale"], k_zero=t.get("k_zero"),
         v_zero=t.get("v_zero"), k_residual=t.get("k_residual"), res_rows=t.get("res_rows"))
     close(got, want)
+    assert pdc.error_flag(dev, len(lens), tag="cuda_i8") == 0
 
 
-def test_int8_stale_scales_and_rows_are_never_read():
+def test_int8_loaders_agree_bit_for_bit():
+    """TMA tiles and per-lane cp.async feed the same arithmetic."""
+    lens = [2000, 777, 16, 15, 1]
+    case = _random_int8_case(lens, False, True, seed=23)
+    dev = device()
+    t = {k: torch.from_numpy(np.ascontiguousarray(v)).to(dev) for k, v in case.items()}
+    outs = {}
+    for name in ("tma", "cp_async"):
+        pdc.set_int8_loader(name)
+        try:
+            outs[name] = pdc.paged_decode_cuda(
+                t["q"], t["k_pool"], t["v_pool"], t["block_tables"], t["seq_lens"], max(lens),
+                k_scale=t["k_scale"], v_scale=t["v_scale"], k_residual=t["k_residual"],
+                res_rows=t["res_rows"]).clone()
+        finally:
+            pdc.set_int8_loader("tma")
+    assert torch.equal(outs["tma"], outs["cp_async"])
+
+
+def test_int8_stale_scales_and_rows_are_never_read(loader):
     lens = [100, 37]
     case = _random_int8_case(lens, False, True, seed=22)
     extra = {k: case[k] for k in ("k_scale", "v_scale", "k_residual", "res_rows")}
