@@ -45,10 +45,15 @@ extern "C" {
  * kernel. Only set it when the kernel launched just before on the stream does
  * not write seq_lens or block_tables (in LatentServe it is the KV append). */
 #define LS_LAUNCH_PROGRAMMATIC 0x100
-/* ls_paged_decode_int8 only: load pages with per-lane cp.async instead of TMA tile
- * copies (the form also used, without this flag, for asymmetric pools and for
- * layouts the tensor maps cannot describe). Same results; kept for comparison. */
+/* How the decode entry points bring pages into shared memory. By default the
+ * INT8 kernel (symmetric pools in the standard layout) uses TMA tile copies issued
+ * by one lane per warp -- it is instruction-issue bound and gains 14 % -- and the
+ * fp16 kernels use per-lane cp.async, which measured 3 % faster on those
+ * memory-bound kernels. LS_LOAD_CP_ASYNC / LS_LOAD_TMA force one form (TMA is not
+ * available for asymmetric INT8 pools, the CUDA-core variant, or layouts a tensor
+ * map cannot describe: the cp.async form runs then). Results are identical. */
 #define LS_LOAD_CP_ASYNC 0x200
+#define LS_LOAD_TMA 0x400
 
 /* Partial-state scratch shared by the three decode entry points.
  *

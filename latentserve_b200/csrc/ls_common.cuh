@@ -38,6 +38,7 @@
 #define LS_LAUNCH_PROGRAMMATIC 0x100
 #endif
 #define LS_LOAD_CP_ASYNC 0x200
+#define LS_LOAD_TMA 0x400
 #define LS_GEMM_NORM 1
 #define LS_GEMM_SWIGLU 2
 

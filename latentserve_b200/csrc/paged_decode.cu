@@ -245,21 +245,31 @@ __device__ __forceinline__ void mask_and_scale(float (&s)[4], int valid, float s
 
 // S[16 tokens x 8 rows] += K_page(fp16, swizzled at `kaddr`) . Q^T, with Q^T
 // given as B fragments over natural 16-dim k-steps.
+template <bool TMA = false>
 __device__ __forceinline__ void qk_fp16(float (&s)[4], uint32_t kaddr, const uint32_t (&qb)[8][2],
                                         int lane) {
     const int row = (lane & 7) + ((lane >> 3) & 1) * 8;
-    const uint32_t base = kaddr + row * 256;
     const int sw = row & 7, hi = lane >> 4;
+    if (TMA) {
+        // Two 16 x 128-byte tiles (dims 0..63 | 64..127), each swizzled by row & 7.
+        const uint32_t base = kaddr + row * 128;
 #pragma unroll
-    for (int ks = 0; ks < 8; ++ks) {
-        uint32_t a0, a1, a2, a3;
-        ldmatrix_x4(base + (((2 * ks + hi) ^ sw) << 4), a0, a1, a2, a3);
-        mma_16816(s, a0, a1, a2, a3, qb[ks][0], qb[ks][1]);
+        for (int ks = 0; ks < 8; ++ks) {
+            uint32_t a0, a1, a2, a3;
+            ldmatrix_x4(base + (ks >> 2) * 2048 + (((2 * (ks & 3) + hi) ^ sw) << 4), a0, a1, a2, a3);
+            mma_16816(s, a0, a1, a2, a3, qb[ks][0], qb[ks][1]);
+        }
+    } else {
+        const uint32_t base = kaddr + row * 256;
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks) {
+            uint32_t a0, a1, a2, a3;
+            ldmatrix_x4(base + (((2 * ks + hi) ^ sw) << 4), a0, a1, a2, a3);
+            mma_16816(s, a0, a1, a2, a3, qb[ks][0], qb[ks][1]);
+        }
     }
 }
 
-// B fragments of Q^T over natural k-steps: lane (g, t) holds
-// Q[row g][16 ks + 2t, +1] and [16 ks + 8 + 2t, +1]; rows >= n_rep are zero.
 __device__ __forceinline__ void load_q_fragments(const DecodeParams& p, int b, int h, int lane,
                                                  uint32_t (&qb)[8][2]) {
     const int g = lane >> 2, t = lane & 3;
@@ -324,9 +334,41 @@ struct PoolFp16 {
     }
 };
 
-// Tensor-core state for fp16 pools.
-struct MmaFp16 {
-    using Pool = PoolFp16;
+// fp16 pools loaded by TMA (on request: measured 3 % slower than the cp.async
+// form on this memory-bound kernel, whose 256-byte rows each become two 128-byte
+// tile rows; the INT8 kernel, which is issue-bound, gains 14 % from it). A
+// page-head (16 rows of 256 bytes, strided in the pool) arrives as two 16 x
+// 128-byte tiles per tensor -- dims 0..63 and 64..127, each with the 128-byte
+// swizzle -- issued by one lane. Tiles always hold all 16
+// rows; what lies past the sequence's end is stale pool memory: its scores are
+// masked, and the compute side zeroes those V rows before using the tile.
+struct PoolFp16Tma {
+    static constexpr bool kTma = true;
+    static constexpr int STAGE_BYTES = 8192;       // K lo 2048 | K hi 2048 | V lo 2048 | V hi 2048
+
+    static __device__ __forceinline__ int issue(const DecodeParams&, const TmaMaps& maps, int, int h,
+                                                const PageItem& it, uint32_t stage, uint32_t mbar,
+                                                int lane) {
+        if (lane == 0) {
+            if (it.valid == 0) {
+                mbar_arrive(mbar);
+            } else {
+                mbar_expect_tx(mbar, 8192u);
+                const uint64_t pol = l2_policy_evict_first();
+                tma_load_4d(stage, &maps.k, mbar, 0, h, 0, it.blk, pol);
+                tma_load_4d(stage + 2048, &maps.k, mbar, 64, h, 0, it.blk, pol);
+                tma_load_4d(stage + 4096, &maps.v, mbar, 0, h, 0, it.blk, pol);
+                tma_load_4d(stage + 6144, &maps.v, mbar, 64, h, 0, it.blk, pol);
+            }
+        }
+        return it.valid;
+    }
+};
+
+// Tensor-core state for fp16 pools (TMA = tile layout of PoolFp16Tma).
+template <bool TMA>
+struct MmaFp16T {
+    using Pool = typename std::conditional<TMA, PoolFp16Tma, PoolFp16>::type;
     static constexpr int kMinCtas = 2;
     uint32_t qb[8][2];
     float o[8][4];             // O^T: tile mt = dims 16 mt + g (+8), rows 2t, 2t+1
@@ -345,7 +387,21 @@ struct MmaFp16 {
     __device__ __forceinline__ void compute(const DecodeParams& p, uint32_t stage, int meta,
                                             int lane) {
         float s[4] = {0.f, 0.f, 0.f, 0.f};
-        qk_fp16(s, stage, qb, lane);
+        if (TMA && meta < LS_PAGE) {
+            // A sequence's last page: the tile's V rows past the end are stale pool
+            // memory (possibly NaN patterns) and would meet zero weights: clear them.
+            // The proxy fence orders these stores before the next TMA write to the stage.
+            for (int i = lane; i < (LS_PAGE - meta) * 16; i += 32) {
+                const int row = meta + (i >> 4), c = i & 15;
+                asm volatile("st.shared.v4.u32 [%0], {%1, %1, %1, %1};\n" ::"r"(
+                                 stage + 4096 + (c >> 3) * 2048 + row * 128 + ((c & 7) << 4)),
+                             "r"(0)
+                             : "memory");
+            }
+            asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+            __syncwarp();
+        }
+        qk_fp16<TMA>(s, stage, qb, lane);
         mask_and_scale(s, meta, p.scale_log2, lane);
         float a0, a1;
         softmax_update(s, m, l, o, a0, a1);
@@ -355,13 +411,24 @@ struct MmaFp16 {
         const uint32_t pb1 = movmatrix_trans(pack_half2(s[2], s[3]));
         const int j = lane >> 3;
         const int row = (lane & 7) + (j >> 1) * 8;
-        const uint32_t base = stage + 4096 + row * 256;
         const int sw = row & 7, odd = j & 1;
+        if (TMA) {
+            const uint32_t base = stage + 4096 + row * 128;
 #pragma unroll
-        for (int mt = 0; mt < 8; ++mt) {
-            uint32_t a0r, a1r, a2r, a3r;
-            ldmatrix_x4_trans(base + (((2 * mt + odd) ^ sw) << 4), a0r, a1r, a2r, a3r);
-            mma_16816(o[mt], a0r, a1r, a2r, a3r, pb0, pb1);
+            for (int mt = 0; mt < 8; ++mt) {
+                uint32_t a0r, a1r, a2r, a3r;
+                ldmatrix_x4_trans(base + (mt >> 2) * 2048 + (((2 * (mt & 3) + odd) ^ sw) << 4), a0r, a1r,
+                                  a2r, a3r);
+                mma_16816(o[mt], a0r, a1r, a2r, a3r, pb0, pb1);
+            }
+        } else {
+            const uint32_t base = stage + 4096 + row * 256;
+#pragma unroll
+            for (int mt = 0; mt < 8; ++mt) {
+                uint32_t a0r, a1r, a2r, a3r;
+                ldmatrix_x4_trans(base + (((2 * mt + odd) ^ sw) << 4), a0r, a1r, a2r, a3r);
+                mma_16816(o[mt], a0r, a1r, a2r, a3r, pb0, pb1);
+            }
         }
     }
 
@@ -392,6 +459,9 @@ struct MmaFp16 {
         }
     }
 };
+
+using MmaFp16 = MmaFp16T<false>;
+using MmaFp16Tma = MmaFp16T<true>;
 
 // ---------------------------------------------------------------------------
 // CUDA-core version of the same page step (fp16 pools only). A half-warp owns
@@ -1256,6 +1326,16 @@ bool build_int8_maps(const ls::DecodeParams& p, ls::TmaMaps* maps) {
            encode_4d(&maps->ks, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, p.k_scale, ks_dims, ks_strides, ks_box);
 }
 
+// fp16 pools [blocks][16][H][128] (strides in elements): tiles of 16 tokens x 64 dims.
+bool build_fp16_maps(const ls::DecodeParams& p, ls::TmaMaps* maps) {
+    const cuuint64_t dims[4] = {128, (cuuint64_t)p.heads, 16, (cuuint64_t)p.num_blocks};
+    const cuuint64_t strides[3] = {(cuuint64_t)p.sk_h * 2, (cuuint64_t)p.sk_p * 2, (cuuint64_t)p.sk_b * 2};
+    const cuuint32_t box[4] = {64, 1, 16, 1};
+    if (p.sk_h <= 0 || p.sk_p <= 0 || p.sk_b <= 0) return false;
+    return encode_4d(&maps->k, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, p.k_pool, dims, strides, box) &&
+           encode_4d(&maps->v, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, p.v_pool, dims, strides, box);
+}
+
 }  // namespace
 
 using ls::DecodeParams;
@@ -1309,7 +1389,10 @@ int ls_paged_decode_fp16(const void* q, const void* k_pool, const void* v_pool,
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     const bool pdl = (flags & LS_LAUNCH_PROGRAMMATIC) != 0;
     const int impl = flags & 0xff;
-    if (flags & ~(0xff | LS_LAUNCH_PROGRAMMATIC)) return LS_ERR_UNSUPPORTED;
+    if (flags & ~(0xff | LS_LAUNCH_PROGRAMMATIC | LS_LOAD_CP_ASYNC | LS_LOAD_TMA)) return LS_ERR_UNSUPPORTED;
+    ls::TmaMaps maps;
+    if (impl == LS_IMPL_MMA && (flags & LS_LOAD_TMA) && build_fp16_maps(p, &maps))
+        return ls::launch_decode<ls::MmaFp16Tma, LS_MODE_DENSE, ls::kStages>(p, s, pdl, &maps);
     if (impl == LS_IMPL_SIMT) {
         if (n_rep <= 6)
             rc = ls::launch_decode<ls::SimtFp16<6>, LS_MODE_DENSE, ls::kStages>(p, s, pdl);
@@ -1367,10 +1450,12 @@ int ls_paged_sparse_fp16(const void* q, const void* k_pool, const void* v_pool,
     rc = check_pool_fp16(p);
     if (rc) return rc;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    if (flags & ~LS_LAUNCH_PROGRAMMATIC) return LS_ERR_UNSUPPORTED;
-    rc = ls::launch_decode<ls::MmaFp16, LS_MODE_SPARSE, ls::kStages>(p, s,
-                                                                     (flags & LS_LAUNCH_PROGRAMMATIC) != 0);
-    return rc;
+    if (flags & ~(LS_LAUNCH_PROGRAMMATIC | LS_LOAD_CP_ASYNC | LS_LOAD_TMA)) return LS_ERR_UNSUPPORTED;
+    const bool pdl = (flags & LS_LAUNCH_PROGRAMMATIC) != 0;
+    ls::TmaMaps maps;
+    if ((flags & LS_LOAD_TMA) && build_fp16_maps(p, &maps))
+        return ls::launch_decode<ls::MmaFp16Tma, LS_MODE_SPARSE, ls::kStages>(p, s, pdl, &maps);
+    return ls::launch_decode<ls::MmaFp16, LS_MODE_SPARSE, ls::kStages>(p, s, pdl);
 }
 
 int ls_paged_decode_int8(const void* q, const void* k_pool, const void* v_pool,
@@ -1433,7 +1518,7 @@ int ls_paged_decode_int8(const void* q, const void* k_pool, const void* v_pool,
     if (k_res && ((reinterpret_cast<uintptr_t>(k_res) & 15) || (sr_r % 8) || (sr_p % 8) || (sr_h % 8)))
         return LS_ERR_MISALIGNED;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    if (flags & ~(LS_LAUNCH_PROGRAMMATIC | LS_LOAD_CP_ASYNC)) return LS_ERR_UNSUPPORTED;
+    if (flags & ~(LS_LAUNCH_PROGRAMMATIC | LS_LOAD_CP_ASYNC | LS_LOAD_TMA)) return LS_ERR_UNSUPPORTED;
     const bool pdl = (flags & LS_LAUNCH_PROGRAMMATIC) != 0;
     ls::TmaMaps maps;
     if (k_zero)

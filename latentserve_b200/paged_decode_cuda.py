@@ -31,10 +31,11 @@ LAUNCH_PROGRAMMATIC = 0x100         # see LS_LAUNCH_PROGRAMMATIC in the header
 # does not write those two tensors -- in a LatentServe layer it is the KV
 # append. Off unless asked for (LATENTSERVE_B200_PDL=1 or set_programmatic_launch).
 _PROGRAMMATIC = {"on": os.environ.get("LATENTSERVE_B200_PDL", "0") == "1"}
-LOAD_CP_ASYNC = 0x200               # see LS_LOAD_CP_ASYNC in the header (INT8 pools only)
-# Symmetric INT8 pools are loaded by TMA tile copies; "cp_async" selects the
-# per-lane form instead (same results; for comparison and for the tests).
-_INT8_LOADER = {"name": os.environ.get("LATENTSERVE_B200_INT8_LOADER", "tma")}
+LOAD_CP_ASYNC, LOAD_TMA = 0x200, 0x400   # see LS_LOAD_CP_ASYNC / LS_LOAD_TMA in the header
+# "auto": TMA tile copies for INT8 pools, per-lane cp.async for fp16 pools (the
+# faster form of each); "tma" / "cp_async" force one (same results; for
+# comparison and for the tests).
+_LOADER = {"name": os.environ.get("LATENTSERVE_B200_LOADER", "auto")}
 ROWS_PER_PARTIAL = 8                # query rows a partial holds (GQA ratio <= 8)
 MIN_CHUNK_PAGES = 8                 # never cut the page axis finer than this
 CTAS_PER_SM = 2                     # resident CTAs per SM the kernels are sized for
@@ -54,14 +55,14 @@ def launch_flags() -> int:
     return LAUNCH_PROGRAMMATIC if _PROGRAMMATIC["on"] else 0
 
 
-def set_int8_loader(name: str) -> None:
-    if name not in ("tma", "cp_async"):
-        raise ValueError(f"unknown INT8 loader {name!r}")
-    _INT8_LOADER["name"] = name
+def set_loader(name: str) -> None:
+    if name not in ("auto", "tma", "cp_async"):
+        raise ValueError(f"unknown page loader {name!r}")
+    _LOADER["name"] = name
 
 
-def int8_flags() -> int:
-    return LOAD_CP_ASYNC if _INT8_LOADER["name"] == "cp_async" else 0
+def loader_flags() -> int:
+    return {"auto": 0, "tma": LOAD_TMA, "cp_async": LOAD_CP_ASYNC}[_LOADER["name"]]
 
 
 def scratch(key, shape, dtype, device, zero: bool = False) -> torch.Tensor:
@@ -223,7 +224,7 @@ def plan_decode(q, k_pool, v_pool, block_tables, seq_lens, num_splits=None, soft
             ptr(acc), ptr(m), ptr(l), ptr(seg), out_ptr,
             b, h_kv, n_rep, d, k_pool.shape[1], block_tables.stride(0), k_pool.shape[0],
             0 if k_residual is None else k_residual.shape[0], chunks, MIN_CHUNK_PAGES,
-            launch_flags() | int8_flags(),
+            launch_flags() | loader_flags(),
             q.stride(0), q.stride(1), q.stride(2),
             k_pool.stride(0), k_pool.stride(1), k_pool.stride(2),
             k_scale.stride(0), k_scale.stride(1),
@@ -237,7 +238,7 @@ def plan_decode(q, k_pool, v_pool, block_tables, seq_lens, num_splits=None, soft
             ptr(q), ptr(k_pool), ptr(v_pool), ptr(block_tables), ptr(seq_lens),
             ptr(acc), ptr(m), ptr(l), ptr(seg), out_ptr,
             b, h_kv, n_rep, d, k_pool.shape[1], block_tables.stride(0), k_pool.shape[0],
-            chunks, MIN_CHUNK_PAGES, impl | launch_flags(),
+            chunks, MIN_CHUNK_PAGES, impl | launch_flags() | loader_flags(),
             q.stride(0), q.stride(1), q.stride(2),
             k_pool.stride(0), k_pool.stride(1), k_pool.stride(2),
             out.stride(0), out.stride(1), out.stride(2), scale)

@@ -147,7 +147,7 @@ def sparse_decode(q, k_pool, v_pool, block_tables, seq_lens, sel,
         seq_lens.data_ptr(), sel.data_ptr(), 0.0 if ratio is None else float(ratio), recent,
         acc.data_ptr(), m.data_ptr(), l.data_ptr(), seg.data_ptr(), out.data_ptr(),
         b, h, n_rep, d, k_pool.shape[1], block_tables.stride(0), k_pool.shape[0], num_sel,
-        chunks, pdc.MIN_CHUNK_PAGES, pdc.launch_flags(),
+        chunks, pdc.MIN_CHUNK_PAGES, pdc.launch_flags() | pdc.loader_flags(),
         q.stride(0), q.stride(1), q.stride(2),
         k_pool.stride(0), k_pool.stride(1), k_pool.stride(2),
         sel.stride(0), sel.stride(1), out.stride(0), out.stride(1), out.stride(2),

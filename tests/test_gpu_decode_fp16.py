@@ -13,6 +13,15 @@ from oracle import paged_attention_oracle as orc
 from tests.gpu_util import close, device, on_device
 
 pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(autouse=True, params=["tma", "cp_async"])
+def loader(request):
+    """Every test runs with both page-loading forms of the kernels (TMA tile
+    copies, and per-lane cp.async)."""
+    pdc.set_loader(request.param)
+    yield request.param
+    pdc.set_loader("auto")
 IMPLS = [pdc.IMPL_MMA, pdc.IMPL_SIMT]
 
 

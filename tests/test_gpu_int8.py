@@ -173,9 +173,9 @@ def _random_int8_case(lens, asym, residual, seed):
 def loader(request):
     """Both page-loading forms of the INT8 kernel (TMA tiles for symmetric pools,
     per-lane cp.async otherwise or on request)."""
-    pdc.set_int8_loader(request.param)
+    pdc.set_loader(request.param)
     yield request.param
-    pdc.set_int8_loader("tma")
+    pdc.set_loader("auto")
 
 
 @pytest.mark.parametrize("asym", [False, True])
@@ -206,14 +206,14 @@ def test_int8_loaders_agree_bit_for_bit():
     t = {k: torch.from_numpy(np.ascontiguousarray(v)).to(dev) for k, v in case.items()}
     outs = {}
     for name in ("tma", "cp_async"):
-        pdc.set_int8_loader(name)
+        pdc.set_loader(name)
         try:
             outs[name] = pdc.paged_decode_cuda(
                 t["q"], t["k_pool"], t["v_pool"], t["block_tables"], t["seq_lens"], max(lens),
                 k_scale=t["k_scale"], v_scale=t["v_scale"], k_residual=t["k_residual"],
                 res_rows=t["res_rows"]).clone()
         finally:
-            pdc.set_int8_loader("tma")
+            pdc.set_loader("auto")
     assert torch.equal(outs["tma"], outs["cp_async"])
 
 

@@ -18,6 +18,15 @@ from tests.gpu_util import close, device, on_device
 pytestmark = pytest.mark.gpu
 
 
+@pytest.fixture(autouse=True, params=["tma", "cp_async"])
+def loader(request):
+    """Every test runs with both page-loading forms of the kernels (TMA tile
+    copies, and per-lane cp.async)."""
+    pdc.set_loader(request.param)
+    yield request.param
+    pdc.set_loader("auto")
+
+
 def _with_bounds(case):
     t = on_device(case)
     nb, _, h, d = t["k_pool"].shape
