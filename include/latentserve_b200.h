@@ -54,6 +54,13 @@ extern "C" {
  * map cannot describe: the cp.async form runs then). Results are identical. */
 #define LS_LOAD_CP_ASYNC 0x200
 #define LS_LOAD_TMA 0x400
+/* With LS_LAUNCH_PROGRAMMATIC on the dense entry points (fp16, INT8): also request
+ * the first pages before synchronising on the previous kernel of the stream, except
+ * a sequence's LAST page (the one holding token seq_len - 1), which is requested
+ * after it. Only set it when that previous kernel writes nothing of the pools (pages,
+ * scales, zero points) outside each sequence's last page -- in LatentServe it is the
+ * KV append, which writes the newest token only. */
+#define LS_EARLY_PAGES 0x800
 
 /* Partial-state scratch shared by the three decode entry points.
  *

@@ -59,6 +59,7 @@ struct DecodeParams {
     long long ks_b, ks_h;          // k_scale strides: block, head
     long long vs_b, vs_p, vs_h;    // v_scale strides: block, token, head
     long long sr_r, sr_p, sr_h;    // residual strides: row, token, head
+    int early;                     // LS_EARLY_PAGES: old pages may be read before the dependency wait
     float scale_log2;              // softmax scale * log2(e)
 };
 

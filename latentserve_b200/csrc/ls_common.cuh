@@ -39,6 +39,7 @@
 #endif
 #define LS_LOAD_CP_ASYNC 0x200
 #define LS_LOAD_TMA 0x400
+#define LS_EARLY_PAGES 0x800
 #define LS_GEMM_NORM 1
 #define LS_GEMM_SWIGLU 2
 

@@ -53,6 +53,9 @@ namespace ls {
 #ifndef LS_INT8_STAGES
 #define LS_INT8_STAGES 3            // ring depth of the INT8 kernel (4.6 KB stages, 3 CTAs per SM)
 #endif
+#ifndef LS_FP16_TMA_PROMO
+#define LS_FP16_TMA_PROMO CU_TENSOR_MAP_L2_PROMOTION_L2_256B
+#endif
 #ifndef LS_INT8_TMA_STAGES
 #define LS_INT8_TMA_STAGES 2        // 5 KB stages of the TMA-loading INT8 kernel
 #endif
@@ -1091,10 +1094,38 @@ decode_kernel(const DecodeParams p, const __grid_constant__ TmaMaps maps) {
 
     // Load side. The dense walk needs nothing the previous kernel may have
     // written; the sparse walk reads the selection, which it usually did write.
+    // With LS_EARLY_PAGES the first pages are requested before the dependency
+    // wait as well: a decode step's predecessor (the KV append) writes only the
+    // newest token, which lies in its sequence's last page, so every other page
+    // is immutable; a warp waits before it requests a last page.
     PageWindow<MODE> win;
+    const bool early = MODE == LS_MODE_DENSE && p.early != 0;
     if (MODE == LS_MODE_DENSE && has_work)
         win.begin(p, cursor_begin<kWarps>(cum, p.batch, b0, g0, g1, warp), h, lane);
-    asm volatile("griddepcontrol.wait;\n" ::: "memory");
+    bool waited = false;
+    auto dep_wait = [&]() {
+        if (!waited) asm volatile("griddepcontrol.wait;\n" ::: "memory");
+        waited = true;
+    };
+    auto issue = [&](int stage) {
+        PageItem item;
+        int lb;
+        if (win.next(p, cum, h, warp, lane, item, lb)) {
+            if (item.last) dep_wait();
+            int mt;
+            if constexpr (Pool::kTma)
+                mt = Pool::issue(p, maps, lb, h, item, ring + stage * STAGE_BYTES, mbar0 + 8 * stage, lane);
+            else
+                mt = Pool::issue(p, lb, h, item, ring + stage * STAGE_BYTES, lane);
+            if (lane == 0) my_meta[stage] = mt;
+        }
+        if (!Pool::kTma) cp_async_commit();
+    };
+    if (early && has_work) {
+#pragma unroll
+        for (int s = 0; s < STAGES - 1; ++s) issue(s);
+    }
+    dep_wait();
 
     if (chunk_id == 0 && h == 0) write_seg_ranges<kThreads>(p, cum, chunk);
     if (chunk_id == 0 && p.out != nullptr) {
@@ -1108,21 +1139,10 @@ decode_kernel(const DecodeParams p, const __grid_constant__ TmaMaps maps) {
     if (!has_work) return;
     if (MODE != LS_MODE_DENSE)
         win.begin(p, cursor_begin<kWarps>(cum, p.batch, b0, g0, g1, warp), h, lane);
-    auto issue = [&](int stage) {
-        PageItem item;
-        int lb;
-        if (win.next(p, cum, h, warp, lane, item, lb)) {
-            int mt;
-            if constexpr (Pool::kTma)
-                mt = Pool::issue(p, maps, lb, h, item, ring + stage * STAGE_BYTES, mbar0 + 8 * stage, lane);
-            else
-                mt = Pool::issue(p, lb, h, item, ring + stage * STAGE_BYTES, lane);
-            if (lane == 0) my_meta[stage] = mt;
-        }
-        if (!Pool::kTma) cp_async_commit();
-    };
+    if (!early) {
 #pragma unroll
-    for (int s = 0; s < STAGES - 1; ++s) issue(s);
+        for (int s = 0; s < STAGES - 1; ++s) issue(s);
+    }
 
     // Compute side: segment by segment.
     State st;
@@ -1298,13 +1318,13 @@ EncodeTiledFn encode_tiled_fn() {
 
 // A 4-d map with the 128-byte swizzle: dims innermost first, strides (bytes) of dims 1..3.
 bool encode_4d(CUtensorMap* map, CUtensorMapDataType type, const void* base, const cuuint64_t (&dims)[4],
-               const cuuint64_t (&strides)[3], const cuuint32_t (&box)[4]) {
+               const cuuint64_t (&strides)[3], const cuuint32_t (&box)[4],
+               CUtensorMapL2promotion promo = CU_TENSOR_MAP_L2_PROMOTION_L2_128B) {
     EncodeTiledFn fn = encode_tiled_fn();
     if (fn == nullptr) return false;
     const cuuint32_t ones[4] = {1, 1, 1, 1};
     return fn(map, type, 4, const_cast<void*>(base), dims, strides, box, ones, CU_TENSOR_MAP_INTERLEAVE_NONE,
-              CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
-              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+              CU_TENSOR_MAP_SWIZZLE_128B, promo, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
 // True if the symmetric INT8 pools have the layout the TMA kernel takes and the maps were built.
@@ -1332,8 +1352,11 @@ bool build_fp16_maps(const ls::DecodeParams& p, ls::TmaMaps* maps) {
     const cuuint64_t strides[3] = {(cuuint64_t)p.sk_h * 2, (cuuint64_t)p.sk_p * 2, (cuuint64_t)p.sk_b * 2};
     const cuuint32_t box[4] = {64, 1, 16, 1};
     if (p.sk_h <= 0 || p.sk_p <= 0 || p.sk_b <= 0) return false;
-    return encode_4d(&maps->k, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, p.k_pool, dims, strides, box) &&
-           encode_4d(&maps->v, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, p.v_pool, dims, strides, box);
+    // A row is 256 bytes and arrives as two tile rows: with 256-byte L2 promotion the
+    // first half's request brings the second half into L2 as well.
+    const CUtensorMapL2promotion promo = LS_FP16_TMA_PROMO;
+    return encode_4d(&maps->k, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, p.k_pool, dims, strides, box, promo) &&
+           encode_4d(&maps->v, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, p.v_pool, dims, strides, box, promo);
 }
 
 }  // namespace
@@ -1389,7 +1412,9 @@ int ls_paged_decode_fp16(const void* q, const void* k_pool, const void* v_pool,
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     const bool pdl = (flags & LS_LAUNCH_PROGRAMMATIC) != 0;
     const int impl = flags & 0xff;
-    if (flags & ~(0xff | LS_LAUNCH_PROGRAMMATIC | LS_LOAD_CP_ASYNC | LS_LOAD_TMA)) return LS_ERR_UNSUPPORTED;
+    if (flags & ~(0xff | LS_LAUNCH_PROGRAMMATIC | LS_LOAD_CP_ASYNC | LS_LOAD_TMA | LS_EARLY_PAGES))
+        return LS_ERR_UNSUPPORTED;
+    p.early = (flags & LS_EARLY_PAGES) != 0;
     ls::TmaMaps maps;
     if (impl == LS_IMPL_MMA && (flags & LS_LOAD_TMA) && build_fp16_maps(p, &maps))
         return ls::launch_decode<ls::MmaFp16Tma, LS_MODE_DENSE, ls::kStages>(p, s, pdl, &maps);
@@ -1518,8 +1543,10 @@ int ls_paged_decode_int8(const void* q, const void* k_pool, const void* v_pool,
     if (k_res && ((reinterpret_cast<uintptr_t>(k_res) & 15) || (sr_r % 8) || (sr_p % 8) || (sr_h % 8)))
         return LS_ERR_MISALIGNED;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    if (flags & ~(LS_LAUNCH_PROGRAMMATIC | LS_LOAD_CP_ASYNC | LS_LOAD_TMA)) return LS_ERR_UNSUPPORTED;
+    if (flags & ~(LS_LAUNCH_PROGRAMMATIC | LS_LOAD_CP_ASYNC | LS_LOAD_TMA | LS_EARLY_PAGES))
+        return LS_ERR_UNSUPPORTED;
     const bool pdl = (flags & LS_LAUNCH_PROGRAMMATIC) != 0;
+    p.early = (flags & LS_EARLY_PAGES) != 0;
     ls::TmaMaps maps;
     if (k_zero)
         rc = ls::launch_decode<ls::MmaInt8<1>, LS_MODE_DENSE, LS_INT8_STAGES_ASYM>(p, s, pdl);

@@ -25,6 +25,7 @@ from latentserve_b200 import _lib
 
 IMPL_MMA, IMPL_SIMT = 0, 1          # tensor-core kernel / CUDA-core kernel (fp16 pools)
 LAUNCH_PROGRAMMATIC = 0x100         # see LS_LAUNCH_PROGRAMMATIC in the header
+EARLY_PAGES = 0x800                 # see LS_EARLY_PAGES (dense entry points only)
 # Decode launches use programmatic dependent launch when this is set: the
 # kernel's prologue (which reads only seq_lens and block_tables) overlaps the
 # tail of the previous kernel on the stream. Safe wherever that previous kernel
@@ -47,12 +48,21 @@ _SCRATCH: dict = {}
 _SM_COUNT: dict = {}
 
 
-def set_programmatic_launch(on: bool) -> None:
+def set_programmatic_launch(on: bool, early_pages: bool = True) -> None:
     _PROGRAMMATIC["on"] = bool(on)
+    _PROGRAMMATIC["early"] = bool(early_pages)
 
 
 def launch_flags() -> int:
     return LAUNCH_PROGRAMMATIC if _PROGRAMMATIC["on"] else 0
+
+
+def dense_launch_flags() -> int:
+    """Flags of the dense decode entry points: with programmatic launch on, old
+    pages are requested ahead of the dependency wait as well (the caches of this
+    package and of LatentServe write only the newest token between steps)."""
+    on = _PROGRAMMATIC["on"] and _PROGRAMMATIC.get("early", True)
+    return (LAUNCH_PROGRAMMATIC | EARLY_PAGES) if on else launch_flags()
 
 
 def set_loader(name: str) -> None:
@@ -224,7 +234,7 @@ def plan_decode(q, k_pool, v_pool, block_tables, seq_lens, num_splits=None, soft
             ptr(acc), ptr(m), ptr(l), ptr(seg), out_ptr,
             b, h_kv, n_rep, d, k_pool.shape[1], block_tables.stride(0), k_pool.shape[0],
             0 if k_residual is None else k_residual.shape[0], chunks, MIN_CHUNK_PAGES,
-            launch_flags() | loader_flags(),
+            dense_launch_flags() | loader_flags(),
             q.stride(0), q.stride(1), q.stride(2),
             k_pool.stride(0), k_pool.stride(1), k_pool.stride(2),
             k_scale.stride(0), k_scale.stride(1),
@@ -238,7 +248,7 @@ def plan_decode(q, k_pool, v_pool, block_tables, seq_lens, num_splits=None, soft
             ptr(q), ptr(k_pool), ptr(v_pool), ptr(block_tables), ptr(seq_lens),
             ptr(acc), ptr(m), ptr(l), ptr(seg), out_ptr,
             b, h_kv, n_rep, d, k_pool.shape[1], block_tables.stride(0), k_pool.shape[0],
-            chunks, MIN_CHUNK_PAGES, impl | launch_flags() | loader_flags(),
+            chunks, MIN_CHUNK_PAGES, impl | dense_launch_flags() | loader_flags(),
             q.stride(0), q.stride(1), q.stride(2),
             k_pool.stride(0), k_pool.stride(1), k_pool.stride(2),
             out.stride(0), out.stride(1), out.stride(2), scale)
