@@ -56,6 +56,8 @@ WORKLOADS = {
     "int8_b16_4k": (16, 4096, 8),              # small case for profiler captures
     "sparse50_b8_32k": (8, 32768, 8),
     "sparse50_b8_8k": (8, 8192, 8),            # small case for profiler captures
+    "sparse25_b8_32k": (8, 32768, 8),          # the same batch at a 25 % / 12.5 % page budget
+    "sparse12_b8_32k": (8, 32768, 8),
 }
 # Whole decode steps of a random-init Qwen2.5-1.5B-shaped model (28 layers) over the
 # paged caches: name -> (batch, context, kv cache kind, sparse ratio, shared prefix)
@@ -275,7 +277,8 @@ def main():
         w = synthetic.sparse_pools_on_device(batch, context, layers, dev, seed=rank)
         tables, lens = w["block_tables"], w["seq_lens"]
         pages = -(-context // 16)
-        keep = ps.budget(0.5, pages)
+        sparse_ratio = {"50": 0.5, "25": 0.25, "12": 0.125}[kind[len("sparse"):len("sparse") + 2]]
+        keep = ps.budget(sparse_ratio, pages)
         # indexer reads kmin+kmax of every page-head, writes and re-reads the scores,
         # attention reads the selected pages
         layer_bytes = batch * 2 * (pages * 512 + pages * 8 + keep * 16 * 512)
@@ -284,7 +287,7 @@ def main():
         def layer_call(i, merge=True):
             k, v = w["pools"][i]
             kmin, kmax = w["bounds"][i]
-            return ps.sparse_attention(w["q"][i], k, v, tables, lens, kmin, kmax, ratio=0.5,
+            return ps.sparse_attention(w["q"][i], k, v, tables, lens, kmin, kmax, ratio=sparse_ratio,
                                        max_seq_len=context)
         launches_per_layer, kernel_name = 3, "page_index + topk_pages + decode_kernel<sparse>"
     else:
@@ -372,14 +375,14 @@ def main():
     breakdown = None
     if kind.startswith("sparse"):
         pages_ = -(-context // 16)
-        keep_ = ps.budget(0.5, pages_)
+        keep_ = ps.budget(sparse_ratio, pages_)
         sel_fixed = ps.select(ps.page_scores(w["q"][0], *w["bounds"][0], tables, lens), keep_).clone()
         scores_fixed = ps.page_scores(w["q"][0], *w["bounds"][0], tables, lens).clone()
         breakdown = {
             "page_index_us": round(graph_us(lambda i: ps.page_scores(w["q"][i], *w["bounds"][i], tables, lens), reps), 2),
             "topk_pages_us": round(graph_us(lambda i: ps.select(scores_fixed, keep_), reps), 2),
             "sparse_decode_us": round(graph_us(lambda i: ps.sparse_decode(
-                w["q"][i], w["pools"][i][0], w["pools"][i][1], tables, lens, sel_fixed, ratio=0.5), reps), 2),
+                w["q"][i], w["pools"][i][0], w["pools"][i][1], tables, lens, sel_fixed, ratio=sparse_ratio), reps), 2),
         }
         kernel_ms = breakdown["sparse_decode_us"] * 1e-3
         roof_bytes = batch * 2 * keep_ * 16 * 512
@@ -436,8 +439,10 @@ def main():
                        "early_pages": not (args.no_pdl or args.no_early), "loader": args.loader or "auto",
                        "parallelism": f"replicas x{world} (sequence-sharded, no collective)",
                        "l2": f"no flush: each step reads {step_bytes / 1e9:.2f} GB, L2 is 126 MB",
-                       "step": f"{layers} layer calls (one launch each) replayed from one CUDA graph"},
+                       "step": f"{layers} layer calls ({launches_per_layer} launch(es) each) replayed from one "
+                               "CUDA graph"},
             "pct_of_8TBs": round(100.0 * value / world / 8000.0, 2),
+            "us_per_layer_call": round(1e3 * ms_step / layers, 2),
             "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e,
             "gpu_launches": launches_per_layer * layers * args.steps, "clocks": clocks,
         }

@@ -50,12 +50,43 @@ __device__ __forceinline__ void halve(const float (&in)[N], float (&out)[N / 2],
     }
 }
 
+// Packed fp32 pairs (sm_100 has two-wide fp32 add / mul / fma on 64-bit
+// registers; each half is an ordinary IEEE operation).
+typedef unsigned long long f32x2;
+__device__ __forceinline__ f32x2 pack2(float lo, float hi) {
+    f32x2 r;
+    asm("mov.b64 %0, {%1, %2};\n" : "=l"(r) : "f"(lo), "f"(hi));
+    return r;
+}
+__device__ __forceinline__ void unpack2(f32x2 v, float& lo, float& hi) {
+    asm("mov.b64 {%0, %1}, %2;\n" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ f32x2 mul2(f32x2 a, f32x2 b) {
+    f32x2 r;
+    asm("mul.rn.f32x2 %0, %1, %2;\n" : "=l"(r) : "l"(a), "l"(b));
+    return r;
+}
+__device__ __forceinline__ f32x2 add2(f32x2 a, f32x2 b) {
+    f32x2 r;
+    asm("add.rn.f32x2 %0, %1, %2;\n" : "=l"(r) : "l"(a), "l"(b));
+    return r;
+}
+__device__ __forceinline__ f32x2 fma2(f32x2 a, f32x2 b, f32x2 c) {
+    f32x2 r;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;\n" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+    return r;
+}
+
 // Bounds of 8 (padded) query rows x 4 pages. On return lane l holds the
 // complete bound of page (l >> 3) of the group, query row (l & 7).
-// max(q * lo, q * hi) is evaluated as q * (q >= 0 ? hi : lo): with lo <= hi
-// (they are a page's channel minimum and maximum) that is the same product,
-// bit for bit, for one multiply instead of two and a max.
-__device__ __forceinline__ float bounds_4x8(const float (&q)[8][4], int n_rep,
+// max(q * lo, q * hi) with lo <= hi (a page's channel minimum and maximum) is
+// q * hi for q > 0 and q * lo for q < 0. With q+ = max(q, 0) and q- = min(q, 0)
+// that product is fma(q+, hi, q- * lo), bit for bit: one of the two factors is
+// zero, so one term is a zero and the other is rounded exactly once. No compare,
+// no select -- and rows r, r + 1 go through the two halves of packed fp32
+// instructions, so a term costs 1.5 instructions instead of 4. The per-lane sums
+// run over channels in order, as the reference's do.
+__device__ __forceinline__ float bounds_4x8(const f32x2 (&qp)[4][4], const f32x2 (&qn)[4][4], int n_rep,
                                             const uint2 (&lo_raw)[kGroup],
                                             const uint2 (&hi_raw)[kGroup], int lane) {
     float x[32];
@@ -64,15 +95,20 @@ __device__ __forceinline__ float bounds_4x8(const float (&q)[8][4], int n_rep,
         float lo[4], hi[4];
         unpack4h(lo_raw[pg], lo);
         unpack4h(hi_raw[pg], hi);
+        f32x2 lo2[4], hi2[4];
 #pragma unroll
-        for (int r = 0; r < 8; ++r) {
-            float t = 0.f;
-            if (r < n_rep) {
+        for (int j = 0; j < 4; ++j) {
+            lo2[j] = pack2(lo[j], lo[j]);
+            hi2[j] = pack2(hi[j], hi[j]);
+        }
 #pragma unroll
-                for (int j = 0; j < 4; ++j)
-                    t = __fadd_rn(t, __fmul_rn(q[r][j], q[r][j] >= 0.f ? hi[j] : lo[j]));
+        for (int rp = 0; rp < 4; ++rp) {
+            f32x2 t = pack2(0.f, 0.f);
+            if (2 * rp < n_rep) {
+#pragma unroll
+                for (int j = 0; j < 4; ++j) t = add2(t, fma2(qp[rp][j], hi2[j], mul2(qn[rp][j], lo2[j])));
             }
-            x[pg * 8 + r] = t;
+            unpack2(t, x[pg * 8 + 2 * rp], x[pg * 8 + 2 * rp + 1]);
         }
     }
     float a[16], b[8], c[4], d[2], e[1];
@@ -95,6 +131,7 @@ page_index_kernel(const __half* __restrict__ q, const __half* __restrict__ kmin,
                   int max_pages, int table_stride, int num_blocks, int recent, long long sq_b,
                   long long sq_h, long long sq_m, long long sb_b, long long sb_h, long long ss_b,
                   long long ss_h, long long ss_r) {
+    asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");   // a programmatic successor may start its prologue
     const int b = blockIdx.z, h = blockIdx.y;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int first = (blockIdx.x * kIndexWarps + warp) * kPagesPerWarp;
@@ -113,15 +150,20 @@ page_index_kernel(const __half* __restrict__ q, const __half* __restrict__ kmin,
             if (id >= 0 && id < num_blocks) my_blk = id;
         }
     }
-    float qf[8][4];
+    // q+ and q- of rows (2 rp, 2 rp + 1), channel j, packed; rows past n_rep are zero.
+    f32x2 qp[4][4], qn[4][4];
 #pragma unroll
-    for (int r = 0; r < 8; ++r) {
-        if (r < n_rep) {
-            unpack4h(*reinterpret_cast<const uint2*>(q + b * sq_b + h * sq_h + r * sq_m + lane * 4),
-                     qf[r]);
-        } else {
+    for (int rp = 0; rp < 4; ++rp) {
+        float q0[4] = {0.f, 0.f, 0.f, 0.f}, q1[4] = {0.f, 0.f, 0.f, 0.f};
+        if (2 * rp < n_rep)
+            unpack4h(*reinterpret_cast<const uint2*>(q + b * sq_b + h * sq_h + (2 * rp) * sq_m + lane * 4), q0);
+        if (2 * rp + 1 < n_rep)
+            unpack4h(*reinterpret_cast<const uint2*>(q + b * sq_b + h * sq_h + (2 * rp + 1) * sq_m + lane * 4),
+                     q1);
 #pragma unroll
-            for (int j = 0; j < 4; ++j) qf[r][j] = 0.f;
+        for (int j = 0; j < 4; ++j) {
+            qp[rp][j] = pack2(fmaxf(q0[j], 0.f), fmaxf(q1[j], 0.f));
+            qn[rp][j] = pack2(fminf(q0[j], 0.f), fminf(q1[j], 0.f));
         }
     }
 
@@ -144,7 +186,7 @@ page_index_kernel(const __half* __restrict__ q, const __half* __restrict__ kmin,
     for (int g = 0; g < kGroupsPerWarp; ++g) fetch(g, lo_all[g], hi_all[g]);
 #pragma unroll
     for (int g = 0; g < kGroupsPerWarp; ++g) {
-        float s = bounds_4x8(qf, n_rep, lo_all[g], hi_all[g], lane);
+        float s = bounds_4x8(qp, qn, n_rep, lo_all[g], hi_all[g], lane);
         const int p = first + g * kGroup + (lane >> 3), r = lane & 7;
         const int blk = __shfl_sync(LS_FULL_MASK, my_blk, g * kGroup + (lane >> 3));
         if (PER_HEAD) {
@@ -191,6 +233,7 @@ __global__ void __launch_bounds__(1024)
 topk_pages_kernel(const float* __restrict__ scores, int* __restrict__ sel, int n, int n_pow2, int k,
                   int heads, long long ss_b, long long ss_h, long long sl_b, long long sl_h) {
     extern __shared__ __align__(8) u64 keys[];
+    asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");   // lets the attention kernel's prologue overlap the sort
     const int bh = blockIdx.x, b = bh / heads, h = bh % heads;
     const float* row = scores + b * ss_b + h * ss_h;
     const int base = threadIdx.x * kTopkPerThread;
@@ -266,16 +309,13 @@ static int launch_index(int per_head, const void* q, const void* kmin, const voi
     const int per_cta = ls::kIndexWarps * ls::kPagesPerWarp;
     dim3 grid((max_pages + per_cta - 1) / per_cta, kv_heads, batch);
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    if (per_head)
-        ls::page_index_kernel<1><<<grid, ls::kIndexWarps * 32, 0, s>>>(
-            static_cast<const __half*>(q), static_cast<const __half*>(kmin),
-            static_cast<const __half*>(kmax), block_tables, seq_lens, out, n_rep, max_pages,
-            table_stride, num_blocks, recent, sq_b, sq_h, sq_m, sb_b, sb_h, ss_b, ss_h, ss_r);
-    else
-        ls::page_index_kernel<0><<<grid, ls::kIndexWarps * 32, 0, s>>>(
-            static_cast<const __half*>(q), static_cast<const __half*>(kmin),
-            static_cast<const __half*>(kmax), block_tables, seq_lens, out, n_rep, max_pages,
-            table_stride, num_blocks, recent, sq_b, sq_h, sq_m, sb_b, sb_h, ss_b, ss_h, ss_r);
+    // Plain launches: starting these two kernels ahead of their predecessor's end
+    // (programmatic launch) was measured and made the select + attend sequence slower.
+    auto kern = per_head ? ls::page_index_kernel<1> : ls::page_index_kernel<0>;
+    kern<<<grid, ls::kIndexWarps * 32, 0, s>>>(
+        static_cast<const __half*>(q), static_cast<const __half*>(kmin), static_cast<const __half*>(kmax),
+        block_tables, seq_lens, out, n_rep, max_pages, table_stride, num_blocks, recent, sq_b, sq_h, sq_m,
+        sb_b, sb_h, ss_b, ss_h, ss_r);
     return (int)cudaGetLastError();
 }
 
