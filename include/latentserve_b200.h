@@ -286,7 +286,7 @@ int ls_rope_append_int8(const void* qkv, const void* cos, const void* sin, const
                         float eps, float qmax, float inv_qmax, float levels, float inv_levels,
                         float offset, void* stream);
 
-/* Decode-step projection for a batch of m <= 64 token rows, fused with the
+/* Decode-step projection for a batch of m <= 32 token rows, fused with the
  * element-wise work either side of it:
  *   out[m, n] = f(x)[m, k] . w[n, k]^T (+ bias[n]),  fp16 in, fp32 accumulate, fp16 out.
  *   mode & LS_GEMM_NORM:   f(x) = RMSNorm(x (+ res)) * gamma with the fp16 rounding
@@ -303,7 +303,7 @@ int ls_rope_append_int8(const void* qkv, const void* cos, const void* sin, const
  *       k / 32) instead of reading whole rows for its statistics (res must then be NULL).
  * k is cut into `splits` slices across CTAs (grid = n / 32 tiles x splits; pick
  * splits so that the grid is about 2 CTAs per SM); with splits > 1 `part` must
- * hold (n / 32) * splits * 16 * ceil(m / 16) * 32 floats (n / 32 -> I / 16 tiles
+ * hold (n / 32) * splits * 16 * ceil(m / 16) * 32 floats (k / 32 / splits <= 48 required) (n / 32 -> I / 16 tiles
  * with SWIGLU) and `counters` one int32 per tile, zeroed once before first use
  * (every launch leaves them at zero). The sum over splits is taken in split order
  * by whichever CTA finishes last, so results do not depend on timing.

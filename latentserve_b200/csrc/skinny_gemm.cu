@@ -1,21 +1,24 @@
 // Decode-step projections: out[M, N] = f(x)[M, K] . W[N, K]^T for a batch of
-// M <= 64 token rows, where W (fp16, row-major, K contiguous) is tens of MB and
+// M <= 32 token rows, where W (fp16, row-major, K contiguous) is tens of MB and
 // x is tens of KB. At these shapes the product is a stream of weights through
 // HBM, so the kernel is built around that stream:
 //
-//   * W goes from global memory straight into the registers that feed
-//     mma.sync.m16n8k16 as the B operand: lane (g, t) of a warp reads 16
-//     contiguous bytes of row g at k = 32 c + 8 t, which are the B fragments of
-//     two MMAs once the k index is permuted (the MMA does not care in which
-//     order k is summed as long as A uses the same order; A is read with the
-//     same 16-byte pattern). No shared-memory staging, no ldmatrix.
+//   * Lane (g, t) of a warp takes 16 contiguous bytes of weight row g at
+//     k = 32 c + 8 t: the B fragments of two mma.sync.m16n8k16 once the k index
+//     is permuted (the MMA does not care in which order k is summed as long as
+//     A uses the same order; A is read with the same 16-byte pattern). The
+//     bytes travel by cp.async into a per-warp ring in shared memory -- each
+//     lane's piece at the address that lane reads back, an asynchronous
+//     register spill: no swizzle, no ldmatrix, no barrier -- six 2 KB chunks
+//     deep, 192 KB in flight per SM.
 //   * A tile is 32 rows of W (4 n-tiles) by a slice of K; the 8 warps of a CTA
 //     take the slice's 32-wide k chunks round-robin, each keeping several chunks
-//     of loads in flight, and add their accumulators through shared memory. The
-//     CTA's slice of the activations is staged in shared memory once; the grid is
-//     sized to what the device holds at once and a CTA walks several tiles, its
-//     warps already loading the next tile's weights while the current one is
-//     reduced.
+//     of loads in flight, and add their accumulators through shared memory. A
+//     warp's activation fragments (at most six chunks) are read, normalised and
+//     kept in registers once: they are the same for every tile. The grid is sized
+//     to what the device holds at once and a CTA walks several tiles, its warps'
+//     rings already filling with the next tile's weights while the current one
+//     is reduced.
 //   * K is cut across CTAs (`splits`) where 32-row tiles alone would leave SMs
 //     idle. Partials go to an fp32 scratch and the CTA that arrives last at a
 //     tile's counter adds them in split order (deterministic), exactly as the
@@ -142,17 +145,19 @@ __host__ __device__ inline int a_stride_halves(int slice_k) {
     return slice_k + ((slice_k % 64 == 0) ? 32 : 0);
 }
 
-// MT = 16-row tiles of the batch (M <= 16 MT); U = k chunks a warp keeps in flight.
-// grid (CTAs per split, splits): a CTA walks the tiles blockIdx.x, + gridDim.x, ...
-// of its split with the same staged activations.
-template <int MT, int U, int PRO, int EPI>
+constexpr int kRing = 6;                // chunks of W a warp keeps in flight (2 KB each)
+constexpr int kMaxCpw = 6;              // chunks of a tile a warp may own (its A fragments stay in registers)
+
+// MT = 16-row tiles of the batch (M <= 16 MT). grid (CTAs per split, splits): a
+// CTA walks the tiles blockIdx.x, + gridDim.x, ... of its split.
+template <int MT, int PRO, int EPI>
 __global__ void __launch_bounds__(kGemmThreads, MT == 1 ? 2 : 1) skinny_gemm_kernel(const GemmParams p) {
-    // [ROWS][astride] fp16 staged activations, then [kGemmWarps][ROWS][32] fp32 for the
-    // reduction over warps.
+    // [kGemmWarps][kRing][4][32] x 16 bytes: the warps' rings of W chunks, each lane's
+    // 16 bytes where that lane will read them back (an asynchronous register spill, no
+    // swizzle or warp barrier needed); then [kGemmWarps][ROWS][32] fp32 for the reduction.
     extern __shared__ __align__(16) unsigned char smem_raw[];
     constexpr int ROWS = MT * 16;
     __shared__ float inv_rms[ROWS];
-    __shared__ float ssq_part[kGemmThreads];
     __shared__ int is_last;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int g = lane >> 2, t = lane & 3;
@@ -161,17 +166,18 @@ __global__ void __launch_bounds__(kGemmThreads, MT == 1 ? 2 : 1) skinny_gemm_ker
     const int per_split = (chunks + p.splits - 1) / p.splits;
     const int c_begin = split * per_split;
     const int c_end = min(chunks, c_begin + per_split);
-    const int k0 = c_begin * 32, k1 = c_end * 32;
-    const int astride = a_stride_halves(per_split * 32);
-    const uint32_t abase = smem_u32(smem_raw);
-    float* red = reinterpret_cast<float*>(smem_raw + (size_t)ROWS * astride * sizeof(__half));
+    const uint32_t ring = smem_u32(smem_raw) + warp * (kRing * 2048) + lane * 16;
+    float* red = reinterpret_cast<float*>(smem_raw + kGemmWarps * kRing * 2048);
+    float* ssq_part = red;              // [kGemmThreads], used before the first reduction only
     const int n_tiles = p.n / kTileRows;
-    // Chunks of a tile's slice this warp takes: c_begin + warp + 8 i, i < cpw.
+    // Chunks of a tile's slice this warp takes: c_begin + warp + 8 i, i < cpw <= kMaxCpw.
     const int cpw = max(0, (c_end - c_begin - warp + kGemmWarps - 1) / kGemmWarps);
+    const int my_tiles = (n_tiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x;
+    const int items = my_tiles * cpw;   // (tile, chunk) pairs this warp streams, tile-major
 
     asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
 
-    // Rows of W behind this lane's four B fragments, for tile 0 and chunk 0 of the slice.
+    // Rows of W behind this lane's four B fragments, at the warp's first chunk of tile 0.
     const __half* wrow[4];
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
@@ -179,32 +185,54 @@ __global__ void __launch_bounds__(kGemmThreads, MT == 1 ? 2 : 1) skinny_gemm_ker
         wrow[i] = p.w + (long long)row * p.sw + 8 * t + 32 * (c_begin + warp);
     }
     const long long tile_step = (long long)((EPI == EPI_SWIGLU) ? 16 : kTileRows) * p.sw;
-    const __half* gptr = (PRO == PRO_NORM) ? p.gamma + 8 * t + 32 * (c_begin + warp) : nullptr;
     const uint64_t pol = l2_policy_evict_first();
 
-    // A ring of U chunks per warp, slot u holding chunks u, u + U, ... of the current
-    // tile and then chunk u of the CTA's next tile, so the stream does not stop at
-    // tile boundaries.
-    uint4 wbuf[U][4];
-    uint4 gbuf[U];
-    auto load_slot = [&](int u, int tile, int ci) {
-        const long long off = tile * tile_step + 32 * kGemmWarps * ci;
+    // Load side: item q of the warp's stream goes to ring slot q % kRing.
+    int ld_tile = blockIdx.x, ld_ci = 0, ld_slot = 0, ld_q = 0;
+    auto issue = [&]() {
+        if (ld_q < items) {
+            const long long off = ld_tile * tile_step + 32 * kGemmWarps * ld_ci;
+            const uint32_t dst = ring + ld_slot * 2048;
 #pragma unroll
-        for (int i = 0; i < 4; ++i) wbuf[u][i] = ldg_stream(wrow[i] + off, pol);
-        if (PRO == PRO_NORM) gbuf[u] = *reinterpret_cast<const uint4*>(gptr + 32 * kGemmWarps * ci);
+            for (int i = 0; i < 4; ++i) cp_async_16_stream(dst + i * 512, wrow[i] + off, pol);
+            if (++ld_ci == cpw) {
+                ld_ci = 0;
+                ld_tile += gridDim.x;
+            }
+            ++ld_q;
+        }
+        cp_async_commit();
+        if (++ld_slot == kRing) ld_slot = 0;
     };
 #pragma unroll
-    for (int u = 0; u < U; ++u)
-        if (u < cpw) load_slot(u, blockIdx.x, u);
+    for (int s = 0; s < kRing - 1; ++s) issue();        // weights do not depend on the previous kernel
 
     // Everything below reads what the previous kernel wrote.
     asm volatile("griddepcontrol.wait;\n" ::: "memory");
 
+    // This lane's A fragments for the warp's chunks (rows g, g + 8 of each 16-row tile, 16
+    // bytes at 8 t), requested first so that they travel together with the statistics below.
+    uint4 areg[kMaxCpw][MT][2];
+#pragma unroll
+    for (int ci = 0; ci < kMaxCpw; ++ci) {
+        if (ci < cpw) {
+            const int k = 32 * (c_begin + warp + kGemmWarps * ci) + 8 * t;
+#pragma unroll
+            for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+                for (int hh = 0; hh < 2; ++hh) {
+                    const int rr = min(mt * 16 + hh * 8 + g, p.m - 1);
+                    uint4 a = ldg_l2(p.x + rr * p.sx + k);
+                    if (PRO == PRO_NORM && p.res != nullptr) a = add8(a, ldg_l2(p.res + rr * p.sres + k));
+                    areg[ci][mt][hh] = a;
+                }
+        }
+    }
+
     if (PRO == PRO_NORM && p.sumsq_in == nullptr) {
-        // One pass over the whole rows: x (+ residual) -> sum of squares, and the
-        // CTA's slice of it into shared memory. 16 threads per row, 16 rows per sweep.
+        // Whole rows once: x (+ residual) -> sum of squares. 16 threads per row.
         const int sub = tid & 15;
-        constexpr int B = 4;                              // vectors in flight per thread
+        constexpr int B = 4;
         for (int r0 = 0; r0 < ROWS; r0 += 16) {
             const int row = r0 + (tid >> 4);
             const int rr = min(row, p.m - 1);
@@ -231,61 +259,57 @@ __global__ void __launch_bounds__(kGemmThreads, MT == 1 ? 2 : 1) skinny_gemm_ker
                             *reinterpret_cast<uint4*>(p.res_out + rr * p.sres_out + i) = v[j];
                     }
                     acc += sumsq8(v[j]);
-                    if (i >= k0 && i < k1) sts128g(abase + 2 * (row * astride + (i - k0)), v[j]);
                 }
             }
 #pragma unroll
             for (int off = 8; off > 0; off >>= 1) acc += __shfl_xor_sync(LS_FULL_MASK, acc, off);
             if (sub == 0) inv_rms[row] = rsqrtf(acc / (float)p.k + p.eps);
         }
-    } else {
-        // The CTA's slice of x into shared memory, asynchronously ...
-        const int vec_per_row = (k1 - k0) >> 3;
-        for (int v = tid; v < ROWS * vec_per_row; v += kGemmThreads) {
-            const int row = v / vec_per_row, col = (v - row * vec_per_row) * 8;
-            cp_async_16_full(abase + 2 * (row * astride + col), p.x + min(row, p.m - 1) * p.sx + k0 + col);
-        }
-        cp_async_commit();
-        if (PRO == PRO_NORM) {
-            // ... while the row sums of squares left by the kernel that produced x (one
-            // partial per 32 columns) are added up: 256 / ROWS threads per row, each a
-            // strided share of the partials, then those shares in order.
-            constexpr int PARTS = kGemmThreads / ROWS;
-            const int row = tid % ROWS, part = tid / ROWS;
-            float acc = 0.f;
-            for (int i0 = part; i0 < p.sumsq_tiles; i0 += 4 * PARTS) {
-                float v[4];
+        __syncthreads();
+    } else if (PRO == PRO_NORM) {
+        // Row sums of squares left by the kernel that produced x (one partial per 32
+        // columns): 256 / ROWS threads per row take strided shares, then the shares in order.
+        constexpr int PARTS = kGemmThreads / ROWS;
+        const int row = tid % ROWS, part = tid / ROWS;
+        float acc = 0.f;
+        for (int i0 = part; i0 < p.sumsq_tiles; i0 += 4 * PARTS) {
+            float v[4];
 #pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    const int i = i0 + j * PARTS;
-                    v[j] = (i < p.sumsq_tiles) ? __ldcg(p.sumsq_in + i * 64 + row) : 0.f;
-                }
-                acc += (v[0] + v[1]) + (v[2] + v[3]);
+            for (int j = 0; j < 4; ++j) {
+                const int i = i0 + j * PARTS;
+                v[j] = (i < p.sumsq_tiles) ? __ldcg(p.sumsq_in + i * 64 + row) : 0.f;
             }
-            ssq_part[part * ROWS + row] = acc;
-            __syncthreads();
-            if (tid < ROWS) {
-                float total = 0.f;
-#pragma unroll
-                for (int q = 0; q < PARTS; ++q) total += ssq_part[q * ROWS + tid];
-                inv_rms[tid] = rsqrtf(total / (float)p.k + p.eps);
-            }
+            acc += (v[0] + v[1]) + (v[2] + v[3]);
         }
-        cp_async_wait<0>();
+        ssq_part[part * ROWS + row] = acc;
+        __syncthreads();
+        if (tid < ROWS) {
+            float total = 0.f;
+#pragma unroll
+            for (int q = 0; q < PARTS; ++q) total += ssq_part[q * ROWS + tid];
+            inv_rms[tid] = rsqrtf(total / (float)p.k + p.eps);
+        }
+        __syncthreads();
     }
-    __syncthreads();
 
-    // This lane's A fragments: rows g and g + 8 of each 16-row tile, 16 bytes at 8 t.
-    float inv[MT][2];
+    // Normalise the fragments once the row statistics are there: they are the same for every tile.
+    if (PRO == PRO_NORM) {
 #pragma unroll
-    for (int mt = 0; mt < MT; ++mt)
+        for (int ci = 0; ci < kMaxCpw; ++ci) {
+            if (ci < cpw) {
+                const uint4 gam =
+                    *reinterpret_cast<const uint4*>(p.gamma + 32 * (c_begin + warp + kGemmWarps * ci) + 8 * t);
 #pragma unroll
-        for (int hh = 0; hh < 2; ++hh)
-            inv[mt][hh] = (PRO == PRO_NORM) ? inv_rms[mt * 16 + hh * 8 + g] : 1.f;
-    const uint32_t arow = abase + 2 * (g * astride + 8 * t) + 64 * warp;
+                for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+                    for (int hh = 0; hh < 2; ++hh)
+                        areg[ci][mt][hh] = norm8(areg[ci][mt][hh], gam, inv_rms[mt * 16 + hh * 8 + g]);
+            }
+        }
+    }
 
+    int slot = 0;
     for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
-        const bool has_next = tile + (int)gridDim.x < n_tiles;
         float acc[4][MT][4];
 #pragma unroll
         for (int i = 0; i < 4; ++i)
@@ -293,32 +317,39 @@ __global__ void __launch_bounds__(kGemmThreads, MT == 1 ? 2 : 1) skinny_gemm_ker
             for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
                 for (int j = 0; j < 4; ++j) acc[i][mt][j] = 0.f;
+        // What the epilogue will add to this thread's elements, requested now.
+        constexpr int EPT = ROWS * 32 / kGemmThreads;
+        float pre_bias = 0.f, pre_res[EPT];
+        if (EPI == EPI_NONE) {
+            if (p.bias != nullptr) pre_bias = __half2float(p.bias[tile * kTileRows + lane]);
+#pragma unroll
+            for (int j = 0; j < EPT; ++j) {
+                const int row = (tid >> 5) + j * kGemmWarps;
+                pre_res[j] = (p.add_res != nullptr && row < p.m)
+                                 ? __half2float(p.add_res[row * p.sadd + tile * kTileRows + lane])
+                                 : 0.f;
+            }
+        }
 
-        for (int ci0 = 0; ci0 < cpw; ci0 += U) {
 #pragma unroll
-            for (int u = 0; u < U; ++u) {
-                const int ci = ci0 + u;
-                if (ci < cpw) {
-                    const uint32_t acol = arow + 64 * kGemmWarps * ci;
+        for (int ci = 0; ci < kMaxCpw; ++ci) {
+            if (ci < cpw) {
+                cp_async_wait<kRing - 2>();             // this item's 16-byte pieces have landed
+                issue();                                // refill the slot consumed one item ago
+                const uint32_t src = ring + slot * 2048;
+                if (++slot == kRing) slot = 0;
+                uint4 w[4];
 #pragma unroll
-                    for (int mt = 0; mt < MT; ++mt) {
-                        uint4 a0 = lds128g(acol + 2 * (mt * 16) * astride);
-                        uint4 a1 = lds128g(acol + 2 * (mt * 16 + 8) * astride);
-                        if (PRO == PRO_NORM) {
-                            a0 = norm8(a0, gbuf[u], inv[mt][0]);
-                            a1 = norm8(a1, gbuf[u], inv[mt][1]);
-                        }
+                for (int i = 0; i < 4; ++i) w[i] = lds128g(src + i * 512);
 #pragma unroll
-                        for (int i = 0; i < 4; ++i) {
-                            mma_16816(acc[i][mt], a0.x, a1.x, a0.y, a1.y, wbuf[u][i].x, wbuf[u][i].y);
-                            mma_16816(acc[i][mt], a0.z, a1.z, a0.w, a1.w, wbuf[u][i].z, wbuf[u][i].w);
-                        }
+                for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        mma_16816(acc[i][mt], areg[ci][mt][0].x, areg[ci][mt][1].x, areg[ci][mt][0].y,
+                                  areg[ci][mt][1].y, w[i].x, w[i].y);
+                        mma_16816(acc[i][mt], areg[ci][mt][0].z, areg[ci][mt][1].z, areg[ci][mt][0].w,
+                                  areg[ci][mt][1].w, w[i].z, w[i].w);
                     }
-                    if (ci + U < cpw)
-                        load_slot(u, tile, ci + U);
-                    else if (has_next)
-                        load_slot(u, tile + gridDim.x, u);
-                }
             }
         }
 
@@ -384,13 +415,12 @@ __global__ void __launch_bounds__(kGemmThreads, MT == 1 ? 2 : 1) skinny_gemm_ker
             }
         } else if (finish) {
             // A warp covers one row's 32 columns per sweep (256 threads = 8 rows).
-            for (int e = tid; e < ROWS * 32; e += kGemmThreads) {
+#pragma unroll
+            for (int j = 0; j < EPT; ++j) {
+                const int e = tid + j * kGemmThreads;
                 const int row = e >> 5, col = tile * kTileRows + (e & 31);
-                float v = red[e];
-                if (p.bias != nullptr) v += __half2float(p.bias[col]);
-                v = round_h(v);
-                if (p.add_res != nullptr && row < p.m)
-                    v = round_h(v + __half2float(p.add_res[row * p.sadd + col]));
+                float v = round_h(red[e] + pre_bias);
+                if (p.add_res != nullptr) v = round_h(v + pre_res[j]);
                 if (row < p.m) p.out[row * p.sout + col] = __float2half_rn(v);
                 if (p.sumsq_out != nullptr) {
                     float sq = (row < p.m) ? v * v : 0.f;
@@ -404,19 +434,18 @@ __global__ void __launch_bounds__(kGemmThreads, MT == 1 ? 2 : 1) skinny_gemm_ker
     }
 }
 
-template <int MT, int U, int PRO, int EPI>
+template <int MT, int PRO, int EPI>
 static int launch_gemm(const GemmParams& p, int tiles, cudaStream_t stream, bool programmatic) {
     const int per_split = ((p.k >> 5) + p.splits - 1) / p.splits;
-    const size_t a_bytes = sizeof(__half) * MT * 16 * (size_t)a_stride_halves(per_split * 32);
-    const size_t smem = a_bytes + sizeof(float) * kGemmWarps * MT * 16 * 32;
-    if (smem > 227 * 1024) return LS_ERR_TOO_LARGE;    // cut K into more splits
+    if (per_split > kGemmWarps * kMaxCpw) return LS_ERR_TOO_LARGE;     // cut K into more splits
+    const size_t smem = (size_t)kGemmWarps * kRing * 2048 + sizeof(float) * kGemmWarps * MT * 16 * 32;
     int dev = 0, sms = 0;
     cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     const int resident = (MT == 1 ? 2 : 1) * sms;      // CTAs the device holds at once
     int per = resident / p.splits;
     per = per < 1 ? 1 : (per > tiles ? tiles : per);
-    auto kern = skinny_gemm_kernel<MT, U, PRO, EPI>;
+    auto kern = skinny_gemm_kernel<MT, PRO, EPI>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
     cudaLaunchConfig_t cfg = {};
@@ -436,9 +465,8 @@ static int launch_gemm(const GemmParams& p, int tiles, cudaStream_t stream, bool
 
 template <int PRO, int EPI>
 static int launch_gemm_m(const GemmParams& p, int tiles, cudaStream_t stream, bool programmatic) {
-    if (p.m <= 16) return launch_gemm<1, 3, PRO, EPI>(p, tiles, stream, programmatic);
-    if (p.m <= 32) return launch_gemm<2, 2, PRO, EPI>(p, tiles, stream, programmatic);
-    return launch_gemm<4, 2, PRO, EPI>(p, tiles, stream, programmatic);
+    if (p.m <= 16) return launch_gemm<1, PRO, EPI>(p, tiles, stream, programmatic);
+    return launch_gemm<2, PRO, EPI>(p, tiles, stream, programmatic);
 }
 
 }  // namespace ls
@@ -456,7 +484,7 @@ extern "C" int ls_skinny_gemm(const void* x, const void* res, const void* gamma,
         return LS_ERR_UNSUPPORTED;
     if (m <= 0 || n <= 0 || k <= 0 || splits <= 0 || (sumsq_in && sumsq_tiles <= 0))
         return LS_ERR_BAD_SHAPE;
-    if (m > 64) return LS_ERR_TOO_LARGE;
+    if (m > 32) return LS_ERR_TOO_LARGE;
     if ((k % 32) || (n % 32) || splits > k / 32) return LS_ERR_UNSUPPORTED;
     if (splits > 1 && (!part || !counters)) return LS_ERR_NULL_POINTER;
     auto bad = [](const void* ptr, int64_t stride) {

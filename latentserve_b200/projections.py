@@ -33,33 +33,26 @@ from latentserve_b200 import _lib
 from latentserve_b200 import paged_decode_cuda as pdc
 
 GEMM_NORM, GEMM_SWIGLU = 1, 2
-MAX_ROWS = 64
+MAX_ROWS = 32
 TILE_ROWS = 32
 
 
 def _rows_pad(m: int) -> int:
-    return 16 if m <= 16 else 32 if m <= 32 else 64
+    return 16 if m <= 16 else 32
 
 
-def _stage_budget(rows: int) -> int:
-    """Bytes of staged activations a CTA may hold: what is left of an SM's shared
-    memory after the reduction buffer (1 KB per row), for two resident CTAs at 16
-    rows and one beyond."""
-    return (113 if rows == 16 else 227) * 1024 - rows * 1024
+MAX_CHUNKS_PER_CTA = 48             # 8 warps x 6 chunks whose activations a warp keeps in registers
 
 
 def choose_splits(device: torch.device, tiles: int, k: int, m: int = 16) -> int:
     """Slices of K across CTAs: enough that tiles x splits fills the CTAs the device
     holds at once (without going past it, which would leave a second, nearly empty
-    wave), every warp still gets a 32-wide chunk, and a CTA's slice of the
-    activations fits its shared memory."""
+    wave), every warp still gets a 32-wide chunk, and a CTA's slice is at most 48
+    chunks."""
     chunks = k // 32
-    rows = _rows_pad(m)
-    resident = (2 if rows == 16 else 1) * pdc.sm_count(device)
+    resident = (2 if m <= 16 else 1) * pdc.sm_count(device)
     splits = max(1, min(resident // tiles, chunks // 8 if chunks >= 8 else 1))
-    while splits < chunks and rows * 2 * (32 * -(-chunks // splits) + 32) > _stage_budget(rows):
-        splits += 1
-    return splits
+    return max(splits, -(-chunks // MAX_CHUNKS_PER_CTA))
 
 
 def linear(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None, *,
@@ -67,7 +60,7 @@ def linear(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None
            row_sumsq: Optional[torch.Tensor] = None, add_residual: Optional[torch.Tensor] = None,
            want_sumsq: bool = False, eps: float = 1e-6, swiglu: bool = False,
            out: Optional[torch.Tensor] = None, splits: Optional[int] = None):
-    """x [M, K] fp16 (M <= 64), w [N, K] fp16 -> [M, N] fp16 (or [M, N / 2] with
+    """x [M, K] fp16 (M <= 32), w [N, K] fp16 -> [M, N] fp16 (or [M, N / 2] with
     `swiglu`).
 
     Front: with `norm_weight`, x is RMS-normalised first -- after adding

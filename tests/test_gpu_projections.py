@@ -37,7 +37,7 @@ def _close(got, want):
 SHAPES = [(2048, 1536), (1536, 1536), (1536, 8960), (17920, 1536), (64, 32), (96, 160), (4768, 1536)]
 
 
-@pytest.mark.parametrize("m", [1, 5, 16, 17, 32, 64])
+@pytest.mark.parametrize("m", [1, 5, 16, 17, 32])
 @pytest.mark.parametrize("n,k", SHAPES)
 def test_plain_product(m, n, k):
     dev = device()
@@ -46,7 +46,7 @@ def test_plain_product(m, n, k):
     _close(pj.linear(x, w), want)
 
 
-@pytest.mark.parametrize("m", [3, 16, 48])
+@pytest.mark.parametrize("m", [3, 16, 29])
 def test_bias_and_strided_rows(m):
     dev = device()
     n, k = 2048, 1536
@@ -57,7 +57,7 @@ def test_bias_and_strided_rows(m):
     _close(pj.linear(x, w, b), want)
 
 
-@pytest.mark.parametrize("splits", [1, 2, 3, 6, 48])
+@pytest.mark.parametrize("splits", [1, 2, 3, 6, 48])  # K = 1536: 48 chunks
 def test_split_k_is_deterministic_and_agrees(splits):
     dev = device()
     x, w = _rand((16, 1536), 1.0, 6, dev), _rand((1536, 1536), 0.05, 7, dev)
@@ -67,7 +67,7 @@ def test_split_k_is_deterministic_and_agrees(splits):
     _close(a, x.float() @ w.float().t())
 
 
-@pytest.mark.parametrize("m", [1, 16, 40])
+@pytest.mark.parametrize("m", [1, 16, 31])
 @pytest.mark.parametrize("with_residual", [False, True])
 def test_norm_prologue(m, with_residual):
     dev = device()
@@ -85,7 +85,7 @@ def test_norm_prologue(m, with_residual):
     _close(got, h.float() @ w.float().t() + b.float())
 
 
-@pytest.mark.parametrize("m", [2, 16, 64])
+@pytest.mark.parametrize("m", [2, 16, 32])
 def test_norm_prologue_and_swiglu_epilogue(m):
     dev = device()
     inter, k = 8960, 1536
@@ -106,7 +106,7 @@ def test_norm_prologue_and_swiglu_epilogue(m):
     assert bool((err <= 2e-3 * scale + 3e-3 * wantf.abs()).all()), err.max().item()
 
 
-@pytest.mark.parametrize("m", [1, 16, 33, 64])
+@pytest.mark.parametrize("m", [1, 16, 17, 32])
 def test_residual_epilogue_feeds_the_next_norm(m):
     """o_proj-style call: product + residual with row statistics, then a normed
     projection that takes those statistics instead of reading the rows."""
@@ -146,9 +146,9 @@ def test_argument_errors():
     x, w = _rand((4, 64), 1.0, 19, dev), _rand((40, 64), 1.0, 20, dev)
     with pytest.raises(ValueError):
         pj.linear(x, w)                                          # N not a multiple of 32
-    x, w = _rand((65, 64), 1.0, 21, dev), _rand((64, 64), 1.0, 22, dev)
+    x, w = _rand((33, 64), 1.0, 21, dev), _rand((64, 64), 1.0, 22, dev)
     with pytest.raises(ValueError):
-        pj.linear(x, w)                                          # more than 64 rows
+        pj.linear(x, w)                                          # more than 32 rows
     with pytest.raises(ValueError):
         pj.linear(x[:4], w, residual=x[:4])                      # residual without a norm
     with pytest.raises(RuntimeError):
