@@ -422,6 +422,12 @@ def main():
                "kind": "port",
                "sample": f"one layer call over {seqs} of the {batch} sequences "
                          f"({nbytes / 1e6:.0f} MB of KV), torch CPU fp32 gather-then-softmax, best of 3"}
+    # The reference's own CUDA kernel (its .cu compiled as it is for sm_100a into oracle/_ref,
+    # driven as its host code drives it) on this GPU and this workload, beside ours. Part of
+    # the baseline leg; absent when the cubin was not built.
+    ref_kernel = None
+    if rank == 0 and world == 1 and not args.no_cpu and kind in ("dense", "int8"):
+        ref_kernel = time_reference_kernel(kind, w, tables, lens, seq_lens, layers, step_bytes, graph_us)
     sampler.stop()
 
     if rank == 0:
@@ -443,7 +449,7 @@ def main():
                                "CUDA graph"},
             "pct_of_8TBs": round(100.0 * value / world / 8000.0, 2),
             "us_per_layer_call": round(1e3 * ms_step / layers, 2),
-            "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e,
+            "roofline": roofline, "cpu_baseline": cpu, "reference_kernel": ref_kernel, "e2e": e2e,
             "gpu_launches": launches_per_layer * layers * args.steps, "clocks": clocks,
         }
         print(json.dumps(line))
@@ -588,6 +594,34 @@ def run_model_step(args):
     if dist is not None:
         dist.barrier()
         dist.destroy_process_group()
+
+
+def time_reference_kernel(kind, w, tables, lens, seq_lens, layers, step_bytes, graph_us):
+    """us per layer call and GB/s of the reference's split-KV kernel (fills of its m / l
+    scratch included, as on every call of its host code; its Triton merge not included)."""
+    try:
+        from oracle import ref_kernels
+    except Exception:                                      # the oracle folder did not travel
+        return None
+    name = "paged_decode_int8" if kind == "int8" else "paged_decode_fp16"
+    if not ref_kernels.available(name):
+        return None
+    runs = []
+    for i in range(layers):
+        if kind == "int8":
+            L = w["layers"][i]
+            runs.append(ref_kernels.RefDecode(w["q"][i], L["k_pool"], L["v_pool"], tables, lens,
+                                              max(seq_lens), k_scale=L["k_scale"], v_scale=L["v_scale"],
+                                              k_residual=L["k_residual"], res_rows=w["res_rows"]))
+        else:
+            k, v = w["pools"][i]
+            runs.append(ref_kernels.RefDecode(w["q"][i], k, v, tables, lens, max(seq_lens)))
+    us = graph_us(lambda i: runs[i].launch(), 3)
+    layer_bytes = step_bytes / layers
+    return {"value": round(layer_bytes / (us * 1e-6) / 1e9, 1), "unit": "GB/s", "us_per_layer_call": round(us, 2),
+            "splits": runs[0].splits,
+            "what": f"LatentServe kernels/cuda/{name}.cu compiled for sm_100a, grid (B, splits, H) x 1 warp, "
+                    "m / l fills included, split merge not included"}
 
 
 def run_e2e(args, workload, dev, dist, world):
