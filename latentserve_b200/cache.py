@@ -154,12 +154,28 @@ class _PagedBase:
         self._capacity_pages = max(1, per_seq)
         dev = self.device
         self._block_tables_buf = torch.zeros((mb, self._capacity_pages), dtype=torch.int32, device=dev)
-        self._seq_lens_buf = torch.zeros(mb, dtype=torch.int32, device=dev)
-        self._write_slots_buf = torch.zeros((mb, 1), dtype=torch.int64, device=dev)
-        # Pinned staging: one host copy of each buffer, filled with numpy.
-        self._h_lens = torch.zeros(mb, dtype=torch.int32).pin_memory()
-        self._h_slots = torch.zeros(mb, dtype=torch.int64).pin_memory()
-        self._h_row = torch.zeros(self._capacity_pages, dtype=torch.int32).pin_memory()
+        # Everything a decode step ships besides changed block-table rows lives in ONE
+        # device buffer -- lengths and residual rows (int32), write slots and residual
+        # slots (int64) -- of which the kernels' inputs are typed views, filled by one
+        # asynchronous copy per advance() from one of two pinned host images (the
+        # reference makes several small blocking copies per step,
+        # cache/paged_cache.py:252-273,337-360). An event per image keeps the host from
+        # rewriting an image whose copy has not run yet.
+        off_i64 = -(-(8 * mb) // 16) * 16
+        self._step_bytes = off_i64 + 16 * mb
+        self._step_dev = torch.zeros(self._step_bytes, dtype=torch.uint8, device=dev)
+
+        def views(buf):
+            return (buf[: 4 * mb].view(torch.int32), buf[4 * mb: 8 * mb].view(torch.int32),
+                    buf[off_i64: off_i64 + 8 * mb].view(torch.int64),
+                    buf[off_i64 + 8 * mb: off_i64 + 16 * mb].view(torch.int64))
+
+        self._seq_lens_buf, self._res_rows_buf, slots_dev, self._k_res_idx_buf = views(self._step_dev)
+        self._write_slots_buf = slots_dev.view(mb, 1)
+        self._step_host = [torch.zeros(self._step_bytes, dtype=torch.uint8).pin_memory() for _ in range(2)]
+        self._step_np = [tuple(v.numpy() for v in views(h)) for h in self._step_host]
+        self._step_events: list = [None, None]
+        self._step_next, self._step_open = 0, None
         self._table_state: list = [None] * mb
         self._block_tables = self._seq_lens_tensor = self._write_slots = None
         self._prefill_slots: Optional[torch.Tensor] = None
@@ -237,10 +253,32 @@ class _PagedBase:
                     self._block_tables_buf[row, : len(t.blocks)].copy_(src)
                 self._table_state[row] = state
         b = len(active)
-        self._h_lens[:b] = torch.tensor([self.tables[i].length for i in active], dtype=torch.int32)
-        self._seq_lens_buf[:b].copy_(self._h_lens[:b], non_blocking=False)
+        self._stage()[0][:b] = [self.tables[i].length for i in active]
+        self._flush_stage()
         self._block_tables = self._block_tables_buf[:b]
         self._seq_lens_tensor = self._seq_lens_buf[:b]
+
+    def _stage(self):
+        """Host image being filled for this advance(): numpy views (lens, res_rows,
+        slots, res_idx). Opened on first use; starts as a copy of the last one shipped,
+        so fields an advance() does not touch keep their values."""
+        if self._step_open is None:
+            i = self._step_next
+            if self._step_events[i] is not None:
+                self._step_events[i].synchronize()
+            self._step_host[i].copy_(self._step_host[1 - i])
+            self._step_open = i
+        return self._step_np[self._step_open]
+
+    def _flush_stage(self) -> None:
+        i = self._step_open
+        if i is None:
+            return
+        self._step_dev.copy_(self._step_host[i], non_blocking=True)
+        if self._step_events[i] is None:
+            self._step_events[i] = torch.cuda.Event()
+        self._step_events[i].record()
+        self._step_next, self._step_open = 1 - i, None
 
     def _slot_vec(self, slots: torch.Tensor, b: int) -> torch.Tensor:
         """The first b decode slots as a vector (the view made once per advance)."""
@@ -251,9 +289,7 @@ class _PagedBase:
 
     def _ship_decode_slots(self, active, starts) -> None:
         b = len(active)
-        self._h_slots[:b] = torch.tensor([self.tables[i].slot(s) for i, s in zip(active, starts)],
-                                         dtype=torch.int64)
-        self._write_slots_buf[:b, 0].copy_(self._h_slots[:b], non_blocking=False)
+        self._stage()[2][:b] = [self.tables[i].slot(s) for i, s in zip(active, starts)]
         self._write_slots = self._write_slots_buf[:b]
         self._decode_slot_vec = self._write_slots_buf[:b, 0]
 
@@ -386,8 +422,6 @@ class Int8PagedKVCache(_PagedBase):
         self._k_residual = [torch.zeros(mb, block_size, h, d, dtype=spec.dtype, device=dev)
                             for _ in layers]
         self._k_res_flat = [r.view(mb * block_size, h, d) for r in self._k_residual]
-        self._k_res_idx_buf = torch.zeros(mb, dtype=torch.int64, device=dev)
-        self._res_rows_buf = torch.zeros(mb, dtype=torch.int32, device=dev)
         self._res_rows = None
         self._fin = [0] * mb            # K pages already quantised, per slot (all layers at once)
         self.deferred_finalize = True   # the only mode: pages finalise in the next advance()
@@ -462,9 +496,9 @@ class Int8PagedKVCache(_PagedBase):
         if n == 1:
             b, bs = len(active), self.block_size
             self._ship_decode_slots(active, starts)
-            self._k_res_idx_buf[:b].copy_(torch.tensor(
-                [i * bs + st % bs for i, st in zip(active, starts)], dtype=torch.int64))
-            self._res_rows_buf[:b].copy_(torch.tensor(active, dtype=torch.int32))
+            stage = self._stage()
+            stage[3][:b] = [i * bs + st % bs for i, st in zip(active, starts)]
+            stage[1][:b] = active
             self._res_rows = self._res_rows_buf[:b]
             self._prefill_slots = None
         else:
