@@ -215,6 +215,18 @@ int ls_int8_finalize_blocks(const void* k_res, const int64_t* res_rows, const in
                             float inv_qmax, float levels, float inv_levels, float offset,
                             void* stream);
 
+/* The same for `layers` layers in one launch, when the layers' residuals, pools and
+ * scales are slices of stacked tensors: layer l's tensors start sr_l / sk_l / ss_l
+ * elements after layer l-1's. The same residual rows go to the same blocks in every
+ * layer (a sequence's page completes in all layers at once). */
+int ls_int8_finalize_layers(const void* k_res, const int64_t* res_rows, const int64_t* block_ids,
+                            void* k_pool, float* k_scale, float* k_zero, int count, int layers,
+                            int kv_heads, int head_dim, int page, int64_t num_rows, int64_t num_blocks,
+                            int64_t sr_l, int64_t sr_r, int64_t sr_p, int64_t sr_h, int64_t sk_l,
+                            int64_t sk_b, int64_t sk_p, int64_t sk_h, int64_t ss_l, int64_t ss_b,
+                            int64_t ss_h, int asym, float eps, float qmax, float inv_qmax, float levels,
+                            float inv_levels, float offset, void* stream);
+
 /* Page scores for sparse selection: Quest upper bound from per-page K min/max,
  * maximised over the R query rows; +inf for page 0 and the `recent` last
  * pages, -inf past the sequence's end. fp32 evaluation order as the reference.

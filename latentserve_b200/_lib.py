@@ -45,6 +45,7 @@ _PROTOTYPES = {
     "ls_kv_append_fp16": [P, P, P, P, P, P, P, I, I, I, I] + [L] * 9 + [P],
     "ls_int8_decode_write": [P, P, P, P, P, P, P, P, I, I, I] + [L] * 6 + [I] + [F] * 6 + [P],
     "ls_int8_finalize_blocks": [P, P, P, P, P, P, I, I, I, I] + [L] * 10 + [I] + [F] * 6 + [P],
+    "ls_int8_finalize_layers": [P, P, P, P, P, P, I, I, I, I, I] + [L] * 13 + [I] + [F] * 6 + [P],
     "ls_page_index": [P, P, P, P, P, P] + [I] * 9 + [L] * 7 + [P],
     "ls_page_index_heads": [P, P, P, P, P, P] + [I] * 8 + [L] * 8 + [P],
     "ls_topk_pages": [P, P, I, I, I, I, L, L, L, L, P],

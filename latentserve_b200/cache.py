@@ -155,22 +155,25 @@ class _PagedBase:
         dev = self.device
         self._block_tables_buf = torch.zeros((mb, self._capacity_pages), dtype=torch.int32, device=dev)
         # Everything a decode step ships besides changed block-table rows lives in ONE
-        # device buffer -- lengths and residual rows (int32), write slots and residual
-        # slots (int64) -- of which the kernels' inputs are typed views, filled by one
+        # device buffer -- lengths and residual rows (int32), write slots, residual slots
+        # and the pages to finalise (int64) -- of which the kernels' inputs are typed views, filled by one
         # asynchronous copy per advance() from one of two pinned host images (the
         # reference makes several small blocking copies per step,
         # cache/paged_cache.py:252-273,337-360). An event per image keeps the host from
         # rewriting an image whose copy has not run yet.
         off_i64 = -(-(8 * mb) // 16) * 16
-        self._step_bytes = off_i64 + 16 * mb
+        self._step_bytes = off_i64 + 32 * mb
         self._step_dev = torch.zeros(self._step_bytes, dtype=torch.uint8, device=dev)
 
         def views(buf):
             return (buf[: 4 * mb].view(torch.int32), buf[4 * mb: 8 * mb].view(torch.int32),
                     buf[off_i64: off_i64 + 8 * mb].view(torch.int64),
-                    buf[off_i64 + 8 * mb: off_i64 + 16 * mb].view(torch.int64))
+                    buf[off_i64 + 8 * mb: off_i64 + 16 * mb].view(torch.int64),
+                    buf[off_i64 + 16 * mb: off_i64 + 24 * mb].view(torch.int64),
+                    buf[off_i64 + 24 * mb: off_i64 + 32 * mb].view(torch.int64))
 
-        self._seq_lens_buf, self._res_rows_buf, slots_dev, self._k_res_idx_buf = views(self._step_dev)
+        (self._seq_lens_buf, self._res_rows_buf, slots_dev, self._k_res_idx_buf, self._fin_rows_buf,
+         self._fin_ids_buf) = views(self._step_dev)
         self._write_slots_buf = slots_dev.view(mb, 1)
         self._step_host = [torch.zeros(self._step_bytes, dtype=torch.uint8).pin_memory() for _ in range(2)]
         self._step_np = [tuple(v.numpy() for v in views(h)) for h in self._step_host]
@@ -260,7 +263,7 @@ class _PagedBase:
 
     def _stage(self):
         """Host image being filled for this advance(): numpy views (lens, res_rows,
-        slots, res_idx). Opened on first use; starts as a copy of the last one shipped,
+        slots, res_idx, fin_rows, fin_ids). Opened on first use; starts as a copy of the last one shipped,
         so fields an advance() does not touch keep their values."""
         if self._step_open is None:
             i = self._step_next
@@ -409,18 +412,25 @@ class Int8PagedKVCache(_PagedBase):
         self.k_qmax = self.v_qmax = 127
         self.k_levels = self.v_levels = 255
         self.k_offset = self.v_offset = 128
-        self.k_pool = [torch.zeros(nb, block_size, h, d, dtype=torch.int8, device=dev) for _ in layers]
+        # K side: one tensor per kind with the layers stacked (the per-layer tensors the
+        # kernels take are its slices), so a completed page is finalised in every layer by
+        # one launch.
+        nl = spec.num_layers
+        self._k_pool_all = torch.zeros(nl, nb, block_size, h, d, dtype=torch.int8, device=dev)
+        self._k_scale_all = torch.ones(nl, nb, h, d, dtype=torch.float32, device=dev)
+        self._k_zero_all = torch.zeros(nl, nb, h, d, dtype=torch.float32, device=dev) if asymmetric else None
+        self.k_pool = [self._k_pool_all[i] for i in layers]
         self.v_pool = [torch.zeros(nb, block_size, h, d, dtype=torch.int8, device=dev) for _ in layers]
-        self.k_scale_pool = [torch.ones(nb, h, d, dtype=torch.float32, device=dev) for _ in layers]
+        self.k_scale_pool = [self._k_scale_all[i] for i in layers]
         self.v_scale_pool = [torch.ones(nb, block_size, h, dtype=torch.float32, device=dev)
                              for _ in layers]
-        self.k_zero_pool = [torch.zeros_like(t) for t in self.k_scale_pool] if asymmetric else []
+        self.k_zero_pool = [self._k_zero_all[i] for i in layers] if asymmetric else []
         self.v_zero_pool = [torch.zeros_like(t) for t in self.v_scale_pool] if asymmetric else []
         self._flat_v = [t.view(-1, h, d) for t in self.v_pool]
         self._flat_v_scale = [t.view(-1, h) for t in self.v_scale_pool]
         self._flat_v_zero = [t.view(-1, h) for t in self.v_zero_pool]
-        self._k_residual = [torch.zeros(mb, block_size, h, d, dtype=spec.dtype, device=dev)
-                            for _ in layers]
+        self._k_res_all = torch.zeros(nl, mb, block_size, h, d, dtype=spec.dtype, device=dev)
+        self._k_residual = [self._k_res_all[i] for i in layers]
         self._k_res_flat = [r.view(mb * block_size, h, d) for r in self._k_residual]
         self._res_rows = None
         self._fin = [0] * mb            # K pages already quantised, per slot (all layers at once)
@@ -458,9 +468,11 @@ class Int8PagedKVCache(_PagedBase):
         return dict(eps=_EPS, qmax=float(self.k_qmax), levels=float(self.k_levels),
                     offset=float(self.k_offset))
 
-    def _finalize_pending(self, seqs: Sequence[int]) -> None:
-        """Quantise, in every layer, the page each of `seqs` completed since
-        its last finalisation. At most one per sequence: the residual holds one."""
+    def _collect_pending(self, seqs: Sequence[int]) -> int:
+        """The page each of `seqs` completed since its last finalisation (at most one
+        per sequence: the residual holds one) into the step's staging image; returns
+        how many there are. `_launch_finalize` quantises them, in every layer, once
+        the image is on the device."""
         bs = self.block_size
         rows, ids = [], []
         for s in seqs:
@@ -474,15 +486,16 @@ class Int8PagedKVCache(_PagedBase):
             rows.append(s)
             ids.append(self.tables[s].blocks[done - 1])
             self._fin[s] = done
-        if not rows:
-            return
-        r = torch.tensor(rows, dtype=torch.int64, device=self.device)
-        i = torch.tensor(ids, dtype=torch.int64, device=self.device)
-        for layer in range(self.spec.num_layers):
-            iw.finalize_blocks(self._k_residual[layer], r, i, self.k_pool[layer],
-                               self.k_scale_pool[layer],
-                               self.k_zero_pool[layer] if self.asymmetric else None,
-                               **self._quant_consts())
+        if rows:
+            stage = self._stage()
+            stage[4][: len(rows)] = rows
+            stage[5][: len(rows)] = ids
+        return len(rows)
+
+    def _launch_finalize(self, count: int) -> None:
+        iw.finalize_layers(self._k_res_all, self._fin_rows_buf, self._fin_ids_buf, count,
+                           self._k_pool_all, self._k_scale_all, self._k_zero_all,
+                           **self._quant_consts())
 
     def advance(self, n: int, batch_size: Optional[int] = None,
                 slots: Optional[Sequence[int]] = None) -> None:
@@ -490,7 +503,10 @@ class Int8PagedKVCache(_PagedBase):
             self.set_active(slots)
         elif batch_size is not None:
             self.set_active(range(batch_size))
-        self._finalize_pending(self._active)
+        # Pages completed by the previous step are still whole in the residual: they are
+        # quantised below, after this step's staging copy and before anything writes the
+        # residual again.
+        pending = self._collect_pending(self._active)
         active, starts = self._grow(n, None, None)
         self._starts = starts
         if n == 1:
@@ -508,6 +524,7 @@ class Int8PagedKVCache(_PagedBase):
             self._write_slots = self._prefill_slots
             self._decode_slot_vec = None
         self._ship_tables(active)
+        self._launch_finalize(pending)
 
     def rope_write(self, layer_idx: int, qkv: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor,
                    positions: torch.Tensor, q_out: torch.Tensor, q_heads: int) -> None:

@@ -142,7 +142,8 @@ int8_decode_write_kernel(const __half* __restrict__ k, const __half* __restrict_
         *reinterpret_cast<const uint2*>(k + b * sk_b + h * sk_h + lane * 4);
 }
 
-// grid (N, H), block 128: thread = channel, loop over the page's 16 tokens.
+// grid (N, H, layers), block 128: thread = channel, loop over the page's 16 tokens.
+// Layers are the same tensors `s*_l` elements apart (0 for a single layer).
 __global__ void __launch_bounds__(LS_HEAD_DIM)
 int8_finalize_blocks_kernel(const __half* __restrict__ k_res, const long long* __restrict__ res_rows,
                             const long long* __restrict__ block_ids,
@@ -150,10 +151,15 @@ int8_finalize_blocks_kernel(const __half* __restrict__ k_res, const long long* _
                             float* __restrict__ k_zero, long long num_rows, long long num_blocks,
                             long long sr_r, long long sr_p, long long sr_h, long long sk_b,
                             long long sk_p, long long sk_h, long long ss_b, long long ss_h,
-                            QuantConsts c) {
+                            long long sr_l, long long sk_l, long long ss_l, QuantConsts c) {
     const int n = blockIdx.x, h = blockIdx.y, d = threadIdx.x;
+    const long long layer = blockIdx.z;
     const long long rr = res_rows[n], blk = block_ids[n];
     if (rr < 0 || rr >= num_rows || blk < 0 || blk >= num_blocks) return;
+    k_res += layer * sr_l;
+    k_pool += layer * sk_l;
+    k_scale += layer * ss_l;
+    if (k_zero != nullptr) k_zero += layer * ss_l;
     const __half* src = k_res + rr * sr_r + h * sr_h + d;
     float f[LS_PAGE];
 #pragma unroll
@@ -237,6 +243,28 @@ int ls_int8_decode_write(const void* k, const void* v, const int64_t* slots, con
     return (int)cudaGetLastError();
 }
 
+int ls_int8_finalize_layers(const void* k_res, const int64_t* res_rows, const int64_t* block_ids,
+                            void* k_pool, float* k_scale, float* k_zero, int count, int layers,
+                            int kv_heads, int head_dim, int page, int64_t num_rows, int64_t num_blocks,
+                            int64_t sr_l, int64_t sr_r, int64_t sr_p, int64_t sr_h, int64_t sk_l,
+                            int64_t sk_b, int64_t sk_p, int64_t sk_h, int64_t ss_l, int64_t ss_b,
+                            int64_t ss_h, int asym, float eps, float qmax, float inv_qmax, float levels,
+                            float inv_levels, float offset, void* stream) {
+    if (!k_res || !res_rows || !block_ids || !k_pool || !k_scale) return LS_ERR_NULL_POINTER;
+    if (asym && !k_zero) return LS_ERR_NULL_POINTER;
+    if (head_dim != LS_HEAD_DIM || page != LS_PAGE) return LS_ERR_UNSUPPORTED;
+    if (count < 0 || layers <= 0 || layers > 65535 || kv_heads <= 0 || kv_heads > 65535)
+        return LS_ERR_BAD_SHAPE;
+    if (count == 0) return LS_OK;
+    ls::QuantConsts c = {asym, eps, qmax, inv_qmax, levels, inv_levels, offset};
+    ls::int8_finalize_blocks_kernel<<<dim3(count, kv_heads, layers), LS_HEAD_DIM, 0,
+                                      static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const __half*>(k_res), reinterpret_cast<const long long*>(res_rows),
+        reinterpret_cast<const long long*>(block_ids), static_cast<signed char*>(k_pool), k_scale,
+        k_zero, num_rows, num_blocks, sr_r, sr_p, sr_h, sk_b, sk_p, sk_h, ss_b, ss_h, sr_l, sk_l, ss_l, c);
+    return (int)cudaGetLastError();
+}
+
 int ls_int8_finalize_blocks(const void* k_res, const int64_t* res_rows, const int64_t* block_ids,
                             void* k_pool, float* k_scale, float* k_zero, int count, int kv_heads,
                             int head_dim, int page, int64_t num_rows, int64_t num_blocks,
@@ -244,18 +272,10 @@ int ls_int8_finalize_blocks(const void* k_res, const int64_t* res_rows, const in
                             int64_t sk_h, int64_t ss_b, int64_t ss_h, int asym, float eps, float qmax,
                             float inv_qmax, float levels, float inv_levels, float offset,
                             void* stream) {
-    if (!k_res || !res_rows || !block_ids || !k_pool || !k_scale) return LS_ERR_NULL_POINTER;
-    if (asym && !k_zero) return LS_ERR_NULL_POINTER;
-    if (head_dim != LS_HEAD_DIM || page != LS_PAGE) return LS_ERR_UNSUPPORTED;
-    if (count < 0 || kv_heads <= 0 || kv_heads > 65535) return LS_ERR_BAD_SHAPE;
-    if (count == 0) return LS_OK;
-    ls::QuantConsts c = {asym, eps, qmax, inv_qmax, levels, inv_levels, offset};
-    ls::int8_finalize_blocks_kernel<<<dim3(count, kv_heads), LS_HEAD_DIM, 0,
-                                      static_cast<cudaStream_t>(stream)>>>(
-        static_cast<const __half*>(k_res), reinterpret_cast<const long long*>(res_rows),
-        reinterpret_cast<const long long*>(block_ids), static_cast<signed char*>(k_pool), k_scale,
-        k_zero, num_rows, num_blocks, sr_r, sr_p, sr_h, sk_b, sk_p, sk_h, ss_b, ss_h, c);
-    return (int)cudaGetLastError();
+    return ls_int8_finalize_layers(k_res, res_rows, block_ids, k_pool, k_scale, k_zero, count, 1, kv_heads,
+                                   head_dim, page, num_rows, num_blocks, 0, sr_r, sr_p, sr_h, 0, sk_b, sk_p,
+                                   sk_h, 0, ss_b, ss_h, asym, eps, qmax, inv_qmax, levels, inv_levels,
+                                   offset, stream);
 }
 
 }  // extern "C"

@@ -229,6 +229,9 @@ class GraphedStep:
         self.graph: Optional[torch.cuda.CUDAGraph] = None
 
     def _run(self):
+        # Positions are the cache's lengths minus one: taken on the device, inside the
+        # graph, from the buffer advance() ships, so a step needs no copy of its own.
+        torch.sub(self.cache.seq_lens_tensor(self.batch), 1, out=self.positions)
         self.next_tokens.copy_(self.model.forward(self.cache, self.tokens, self.positions, self.hint))
 
     def capture(self) -> None:
@@ -246,8 +249,6 @@ class GraphedStep:
 
     def step(self, feed_back: bool = True) -> torch.Tensor:
         """advance(1) must have been called; positions are taken from the cache."""
-        lens = self.cache.seq_lens[: self.batch]
-        self.positions.copy_(torch.tensor([n - 1 for n in lens], dtype=torch.long), non_blocking=True)
         if self.graph is None:
             self._run()
         else:

@@ -86,3 +86,35 @@ def finalize_blocks(k_residual: torch.Tensor, res_rows: torch.Tensor, block_ids:
         int(asym), eps, qmax, _reciprocal(qmax), levels, _reciprocal(levels), offset,
         _lib.current_stream(k_pool.device))
     _lib.check(rc, "int8 finalize_blocks")
+
+
+def finalize_layers(k_residual: torch.Tensor, res_rows: torch.Tensor, block_ids: torch.Tensor,
+                    count: int, k_pool: torch.Tensor, k_scale: torch.Tensor,
+                    k_zero: Optional[torch.Tensor] = None, *, eps: float, qmax: float,
+                    levels: float, offset: float) -> None:
+    """`finalize_blocks` for every layer in one launch: `k_residual`
+    [layers, max_batch, 16, H, D], `k_pool` [layers, num_blocks, 16, H, D],
+    `k_scale` / `k_zero` [layers, num_blocks, H, D]; the first `count` entries of
+    `res_rows` / `block_ids` (int64, device) apply to every layer."""
+    if count == 0:
+        return
+    if res_rows.dtype != torch.int64 or block_ids.dtype != torch.int64 or min(
+            res_rows.numel(), block_ids.numel()) < count:
+        raise ValueError("res_rows and block_ids must be int64 vectors of at least `count` entries")
+    if k_residual.dim() != 5 or k_pool.dim() != 5 or k_scale.dim() != 4 or k_pool.shape[0] != k_residual.shape[0]:
+        raise ValueError("finalize_layers takes layer-stacked tensors")
+    if k_residual.stride(-1) != 1 or k_pool.stride(-1) != 1 or k_scale.stride(-1) != 1:
+        raise ValueError("channels must be unit-stride")
+    asym = k_zero is not None
+    if asym and k_zero.stride() != k_scale.stride():
+        raise ValueError("k_zero must share k_scale's layout")
+    rc = _lib.lib().ls_int8_finalize_layers(
+        k_residual.data_ptr(), res_rows.data_ptr(), block_ids.data_ptr(), k_pool.data_ptr(),
+        k_scale.data_ptr(), _lib.ptr(k_zero), count, k_pool.shape[0], k_pool.shape[3], k_pool.shape[4],
+        k_pool.shape[2], k_residual.shape[1], k_pool.shape[1],
+        k_residual.stride(0), k_residual.stride(1), k_residual.stride(2), k_residual.stride(3),
+        k_pool.stride(0), k_pool.stride(1), k_pool.stride(2), k_pool.stride(3),
+        k_scale.stride(0), k_scale.stride(1), k_scale.stride(2),
+        int(asym), eps, qmax, _reciprocal(qmax), levels, _reciprocal(levels), offset,
+        _lib.current_stream(k_pool.device))
+    _lib.check(rc, "int8 finalize_layers")
