@@ -150,6 +150,25 @@ int ls_paged_decode_int8(const void* q, const void* k_pool, const void* v_pool,
                          int64_t sr_r, int64_t sr_p, int64_t sr_h, int64_t so_b, int64_t so_h,
                          int64_t so_m, float softmax_scale, void* stream);
 
+/* INT8 pools, attention over the pages in `sel` only: ls_paged_decode_int8 with the
+ * page-list arguments of ls_paged_sparse_fp16 in front (symmetric pools only). The
+ * reference has no such kernel (its sparse path is fp16 only,
+ * docs/phase16_int8_sparse.md:21-26); here it is one more instance of the same
+ * decode kernel. A selected page that is the sequence's last takes its K from the
+ * fp16 residual, as in the dense INT8 kernel. */
+int ls_paged_sparse_int8(const int32_t* sel, float ratio, int recent, int num_sel, int64_t sl_b,
+                         int64_t sl_h, const void* q, const void* k_pool, const void* v_pool,
+                         const int32_t* block_tables, const int32_t* seq_lens, const float* k_scale,
+                         const float* v_scale, const float* k_zero, const float* v_zero,
+                         const void* k_res, const int32_t* res_rows, float* part_acc, float* part_m,
+                         float* part_l, int32_t* seg_range, void* out, int batch, int kv_heads,
+                         int n_rep, int head_dim, int page, int max_pages, int num_blocks,
+                         int num_res_rows, int num_chunks, int min_chunk, int flags, int64_t sq_b,
+                         int64_t sq_h, int64_t sq_m, int64_t sk_b, int64_t sk_p, int64_t sk_h,
+                         int64_t ks_b, int64_t ks_h, int64_t vs_b, int64_t vs_p, int64_t vs_h,
+                         int64_t sr_r, int64_t sr_p, int64_t sr_h, int64_t so_b, int64_t so_h,
+                         int64_t so_m, float softmax_scale, void* stream);
+
 /* Attention over selected pages only.
  * Replaces kernels/cuda/paged_sparse_fp16.cu:205-364 (kernel `paged_sparse_fp16`)
  * as launched by kernels/cuda/paged_sparse.py:185-219.
@@ -288,15 +307,17 @@ int ls_rope_append_fp16(const void* qkv, const void* cos, const void* sin, const
                         int64_t sp_t, int64_t sp_h, int64_t sb_b, int64_t sb_h, void* stream);
 
 /* The same for the INT8 cache: rotated K into the fp16 residual (row res_idx[b]),
- * V quantised per (token, head) and scattered, bit-exact with ls_int8_decode_write.
+ * V quantised per (token, head) and scattered, bit-exact with ls_int8_decode_write;
+ * with kmin / kmax (fp16 [NB, H, 128], strides sb_b, sb_h) also the page bounds of the
+ * exact fp16 K, for the INT8 + sparse path.
  * Replaces `_rope_kernel` followed by `int8_decode_write`, kernels/cuda/int8_write.cu:45-78. */
 int ls_rope_append_int8(const void* qkv, const void* cos, const void* sin, const int64_t* positions,
                         const int64_t* slots, const int64_t* res_idx, void* q_out, void* flat_v,
-                        float* flat_v_scale, float* flat_v_zero, void* k_res, int batch, int q_heads,
-                        int kv_heads, int head_dim, int64_t max_pos, int64_t num_slots,
-                        int64_t num_res, int64_t s_qkv, int64_t s_cos, int64_t sq_b, int asym,
-                        float eps, float qmax, float inv_qmax, float levels, float inv_levels,
-                        float offset, void* stream);
+                        float* flat_v_scale, float* flat_v_zero, void* k_res, void* kmin, void* kmax,
+                        int batch, int q_heads, int kv_heads, int head_dim, int64_t max_pos,
+                        int64_t num_slots, int64_t num_res, int64_t s_qkv, int64_t s_cos, int64_t sq_b,
+                        int64_t sb_b, int64_t sb_h, int asym, float eps, float qmax, float inv_qmax,
+                        float levels, float inv_levels, float offset, void* stream);
 
 /* Decode-step projection for a batch of m <= 32 token rows, fused with the
  * element-wise work either side of it:

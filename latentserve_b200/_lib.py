@@ -40,6 +40,7 @@ _PROTOTYPES = {
     "ls_paged_decode_fp16": [P, P, P, P, P, P, P, P, P, P] + [I] * 10 + [L] * 9 + [F, P],
     "ls_paged_sparse_fp16": [P, P, P, P, P, P, F, I, P, P, P, P, P] + [I] * 11 + [L] * 11 + [F, P],
     "ls_paged_decode_int8": [P] * 16 + [I] * 11 + [L] * 17 + [F, P],
+    "ls_paged_sparse_int8": [P, F, I, I, L, L] + [P] * 16 + [I] * 11 + [L] * 17 + [F, P],
     "ls_paged_decode_fp16_noalloc": [P, P, P, P, P, P] + [I] * 9 + [L] * 9 + [F, P],
     "ls_combine": [P, P, P, P, P, I, I, I, L, L, L, P],
     "ls_kv_append_fp16": [P, P, P, P, P, P, P, I, I, I, I] + [L] * 9 + [P],
@@ -53,7 +54,7 @@ _PROTOTYPES = {
     "ls_silu_mul": [P, P, I, I, L, L, P],
     "ls_rope_append_fp16": [P] * 10 + [I] * 5 + [L] * 9 + [P],
     "ls_skinny_gemm": [P] * 5 + [I] + [P] * 7 + [I] * 5 + [F] + [L] * 6 + [P],
-    "ls_rope_append_int8": [P] * 11 + [I] * 4 + [L] * 6 + [I] + [F] * 6 + [P],
+    "ls_rope_append_int8": [P] * 13 + [I] * 4 + [L] * 8 + [I] + [F] * 6 + [P],
 }
 
 

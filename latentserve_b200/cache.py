@@ -151,6 +151,8 @@ class _PagedBase:
         mb = spec.max_batch_size
         self.tables = [BlockTable(self.allocator) for _ in range(mb)]
         self._active = list(range(mb))
+        self._active_range: Optional[int] = None       # n when the active set is known to be range(n)
+        self._decode_slots: list = []
         self._capacity_pages = max(1, per_seq)
         dev = self.device
         self._block_tables_buf = torch.zeros((mb, self._capacity_pages), dtype=torch.int32, device=dev)
@@ -198,6 +200,7 @@ class _PagedBase:
 
     def set_active(self, slots: Sequence[int]) -> None:
         slots = list(slots)
+        self._active_range = None
         if len(set(slots)) != len(slots) or any(not 0 <= s < len(self.tables) for s in slots):
             raise ValueError(f"bad active set {slots}")
         self._active = slots
@@ -230,12 +233,37 @@ class _PagedBase:
         return self._seq_lens_tensor if batch_size is None else self._seq_lens_tensor[:batch_size]
 
     # -- per-step staging ------------------------------------------------
-    def _grow(self, n: int, batch_size, slots):
+    def _activate(self, batch_size, slots) -> None:
+        """`set_active` for advance(): skipped when the request is the active set already
+        (every step of a steady decode loop)."""
         if slots is not None:
-            self.set_active(slots)
+            if list(slots) != self._active:
+                self.set_active(slots)
         elif batch_size is not None:
-            self.set_active(range(batch_size))
+            if self._active_range != batch_size:
+                self.set_active(range(batch_size))
+                self._active_range = batch_size
+
+    def _grow(self, n: int, batch_size, slots):
+        self._activate(batch_size, slots)
         active = self._active
+        if n == 1:
+            # One pass: previous length, a new block where the token opens a page, the
+            # token's flat slot.
+            bs, tables, alloc = self.block_size, self.tables, self.allocator
+            starts, slot_list = [], []
+            for i in active:
+                t = tables[i]
+                length, blocks = t.length, t.blocks
+                need = -(-(length + 1) // bs) - len(blocks)
+                if need > 0:
+                    blocks.extend(alloc.allocate(need))
+                    t.version += 1
+                slot_list.append(blocks[length // bs] * bs + length % bs)
+                t.length = length + 1
+                starts.append(length)
+            self._decode_slots = slot_list
+            return active, starts
         starts = [self.tables[i].length for i in active]
         for i in active:
             self.tables[i].append(n)
@@ -292,7 +320,7 @@ class _PagedBase:
 
     def _ship_decode_slots(self, active, starts) -> None:
         b = len(active)
-        self._stage()[2][:b] = [self.tables[i].slot(s) for i, s in zip(active, starts)]
+        self._stage()[2][:b] = self._decode_slots          # computed by _grow
         self._write_slots = self._write_slots_buf[:b]
         self._decode_slot_vec = self._write_slots_buf[:b, 0]
 
@@ -320,6 +348,7 @@ class PagedKVCache(_PagedBase):
                 t.free()
         self._table_state = [None] * len(self.tables)
         self._active = list(range(len(self.tables)))
+        self._active_range = None
 
     def shareable_blocks(self, index: int) -> int:
         return self.tables[index].length // self.block_size
@@ -433,6 +462,9 @@ class Int8PagedKVCache(_PagedBase):
         self._k_residual = [self._k_res_all[i] for i in layers]
         self._k_res_flat = [r.view(mb * block_size, h, d) for r in self._k_residual]
         self._res_rows = None
+        self._bounds_on = False         # page bounds of the exact fp16 K, for INT8 + sparse (an extension)
+        self.kmin: list = []
+        self.kmax: list = []
         self._fin = [0] * mb            # K pages already quantised, per slot (all layers at once)
         self.deferred_finalize = True   # the only mode: pages finalise in the next advance()
 
@@ -442,6 +474,7 @@ class Int8PagedKVCache(_PagedBase):
                 t.free()
         self._table_state = [None] * len(self.tables)
         self._active = list(range(len(self.tables)))
+        self._active_range = None
         self._fin = [0] * len(self.tables)
 
     def free_sequence(self, index: int) -> None:
@@ -458,6 +491,23 @@ class Int8PagedKVCache(_PagedBase):
 
     def residual(self, layer_idx: int) -> torch.Tensor:
         return self._k_residual[layer_idx]
+
+    def enable_page_bounds(self) -> None:
+        """Keep each block's per-channel min / max of the exact fp16 K (as the fp16
+        cache does) so that the sparse indexer can run over an INT8 cache. Must be
+        switched on while the cache is empty: finalised pages no longer hold exact K."""
+        if self._bounds_on:
+            return
+        if any(t.length for t in self.tables):
+            raise RuntimeError("enable_page_bounds() on an INT8 cache must precede the first write")
+        nb, _, h, d = self.k_pool[0].shape
+        self.kmin = [torch.zeros(nb, h, d, dtype=self.spec.dtype, device=self.device)
+                     for _ in range(self.spec.num_layers)]
+        self.kmax = [torch.zeros_like(t) for t in self.kmin]
+        self._bounds_on = True
+
+    def page_bounds(self, layer_idx: int):
+        return (self.kmin[layer_idx], self.kmax[layer_idx]) if self._bounds_on else None
 
     def residual_rows_tensor(self, batch_size: Optional[int] = None) -> torch.Tensor:
         if self._res_rows is None:
@@ -499,10 +549,7 @@ class Int8PagedKVCache(_PagedBase):
 
     def advance(self, n: int, batch_size: Optional[int] = None,
                 slots: Optional[Sequence[int]] = None) -> None:
-        if slots is not None:
-            self.set_active(slots)
-        elif batch_size is not None:
-            self.set_active(range(batch_size))
+        self._activate(batch_size, slots)
         # Pages completed by the previous step are still whole in the residual: they are
         # quantised below, after this step's staging copy and before anything writes the
         # residual again.
@@ -539,13 +586,20 @@ class Int8PagedKVCache(_PagedBase):
                             self._flat_v_zero[layer_idx] if self.asymmetric else None,
                             self._k_res_flat[layer_idx], q_heads, self.spec.num_kv_heads,
                             asym=self.asymmetric, eps=_EPS, qmax=float(self.v_qmax),
-                            levels=float(self.v_levels), offset=float(self.v_offset))
+                            levels=float(self.v_levels), offset=float(self.v_offset),
+                            kmin=self.kmin[layer_idx] if self._bounds_on else None,
+                            kmax=self.kmax[layer_idx] if self._bounds_on else None)
 
     def write(self, layer_idx: int, k: torch.Tensor, v: torch.Tensor, start_pos: int = 0) -> None:
         b, h, n, d = k.shape
         slots = self._write_slots
         if slots is None or slots.shape[0] < b or slots.shape[1] != n:
             raise RuntimeError("call advance(n, batch_size) before write()")
+        if self._bounds_on:                       # bounds of the rows as given (exact fp16 K)
+            for j in range(n):
+                kv_write.update_bounds_only(k[:, :, j], self._slot_vec(slots, b) if n == 1 else
+                                            slots[:b, j].contiguous(), self.kmin[layer_idx],
+                                            self.kmax[layer_idx], self.block_size)
         zero = self._flat_v_zero[layer_idx] if self.asymmetric else None
         consts = dict(asym=self.asymmetric, eps=_EPS, qmax=float(self.v_qmax),
                       levels=float(self.v_levels), offset=float(self.v_offset))

@@ -114,6 +114,30 @@ __device__ __forceinline__ void rope_head(float (&lo)[2], float (&hi)[2], const 
     hi[1] = rh(rh(b1 * c2.y) + rh(a1 * s2.y));
 }
 
+// Page bounds of K for the sparse indexer: the block's per-channel minimum and
+// maximum over its written rows (reset by the first row of a page). One warp,
+// lane l owning dims 2l, 2l+1 and 64+2l, 64+2l+1 of the new row.
+__device__ __forceinline__ void update_page_bounds(__half* kmin, __half* kmax, long long bi, bool first,
+                                                   int lane, const float (&lo)[2], const float (&hi)[2],
+                                                   uint32_t plo, uint32_t phi) {
+    if (first) {
+        *reinterpret_cast<uint32_t*>(kmin + bi + 2 * lane) = plo;
+        *reinterpret_cast<uint32_t*>(kmin + bi + 64 + 2 * lane) = phi;
+        *reinterpret_cast<uint32_t*>(kmax + bi + 2 * lane) = plo;
+        *reinterpret_cast<uint32_t*>(kmax + bi + 64 + 2 * lane) = phi;
+        return;
+    }
+#pragma unroll
+    for (int part = 0; part < 2; ++part) {
+        const int d = part * 64 + 2 * lane;
+        const float2 mn = __half22float2(*reinterpret_cast<__half2*>(kmin + bi + d));
+        const float2 mx = __half22float2(*reinterpret_cast<__half2*>(kmax + bi + d));
+        const float v0 = part ? hi[0] : lo[0], v1 = part ? hi[1] : lo[1];
+        *reinterpret_cast<uint32_t*>(kmin + bi + d) = pack_half2(fminf(mn.x, v0), fminf(mn.y, v1));
+        *reinterpret_cast<uint32_t*>(kmax + bi + d) = pack_half2(fmaxf(mx.x, v0), fmaxf(mx.y, v1));
+    }
+}
+
 struct RopeQuant {
     int asym;
     float eps, qmax, inv_qmax, levels, inv_levels, offset;
@@ -168,25 +192,9 @@ rope_append_kernel(const __half* __restrict__ qkv, const __half* __restrict__ co
         __half* pool = static_cast<__half*>(is_k ? k_dst : v_dst) + slot * sp_t + kvh * sp_h;
         *reinterpret_cast<uint32_t*>(pool + 2 * lane) = plo;
         *reinterpret_cast<uint32_t*>(pool + 64 + 2 * lane) = phi;
-        if (is_k && kmin != nullptr) {
-            const long long bi = (slot / LS_PAGE) * sb_b + kvh * sb_h;
-            if (slot % LS_PAGE == 0) {            // first token of a page: reset
-                *reinterpret_cast<uint32_t*>(kmin + bi + 2 * lane) = plo;
-                *reinterpret_cast<uint32_t*>(kmin + bi + 64 + 2 * lane) = phi;
-                *reinterpret_cast<uint32_t*>(kmax + bi + 2 * lane) = plo;
-                *reinterpret_cast<uint32_t*>(kmax + bi + 64 + 2 * lane) = phi;
-            } else {
-#pragma unroll
-                for (int part = 0; part < 2; ++part) {
-                    const int d = part * 64 + 2 * lane;
-                    const float2 mn = __half22float2(*reinterpret_cast<__half2*>(kmin + bi + d));
-                    const float2 mx = __half22float2(*reinterpret_cast<__half2*>(kmax + bi + d));
-                    const float v0 = part ? hi[0] : lo[0], v1 = part ? hi[1] : lo[1];
-                    *reinterpret_cast<uint32_t*>(kmin + bi + d) = pack_half2(fminf(mn.x, v0), fminf(mn.y, v1));
-                    *reinterpret_cast<uint32_t*>(kmax + bi + d) = pack_half2(fmaxf(mx.x, v0), fmaxf(mx.y, v1));
-                }
-            }
-        }
+        if (is_k && kmin != nullptr)
+            update_page_bounds(kmin, kmax, (slot / LS_PAGE) * sb_b + kvh * sb_h, slot % LS_PAGE == 0, lane, lo,
+                               hi, plo, phi);
         return;
     }
     if (is_k) {                                   // INT8 cache: rotated K stays exact in the residual
@@ -195,6 +203,9 @@ rope_append_kernel(const __half* __restrict__ qkv, const __half* __restrict__ co
         __half* dst = static_cast<__half*>(k_dst) + (ridx * hk + kvh) * LS_HEAD_DIM;
         *reinterpret_cast<uint32_t*>(dst + 2 * lane) = plo;
         *reinterpret_cast<uint32_t*>(dst + 64 + 2 * lane) = phi;
+        if (kmin != nullptr)                      // bounds of the exact fp16 K, as for the fp16 cache
+            update_page_bounds(kmin, kmax, (slot / LS_PAGE) * sb_b + kvh * sb_h, slot % LS_PAGE == 0, lane, lo,
+                               hi, plo, phi);
         return;
     }
     // INT8 V: the reference's quantiser (kernels/cuda/int8_write.cu:45-78), per (token, head).
@@ -292,14 +303,18 @@ int ls_rope_append_fp16(const void* qkv, const void* cos, const void* sin, const
 
 int ls_rope_append_int8(const void* qkv, const void* cos, const void* sin, const int64_t* positions,
                         const int64_t* slots, const int64_t* res_idx, void* q_out, void* flat_v,
-                        float* flat_v_scale, float* flat_v_zero, void* k_res, int batch, int q_heads,
-                        int kv_heads, int head_dim, int64_t max_pos, int64_t num_slots,
-                        int64_t num_res, int64_t s_qkv, int64_t s_cos, int64_t sq_b, int asym,
-                        float eps, float qmax, float inv_qmax, float levels, float inv_levels,
-                        float offset, void* stream) {
+                        float* flat_v_scale, float* flat_v_zero, void* k_res, void* kmin, void* kmax,
+                        int batch, int q_heads, int kv_heads, int head_dim, int64_t max_pos,
+                        int64_t num_slots, int64_t num_res, int64_t s_qkv, int64_t s_cos, int64_t sq_b,
+                        int64_t sb_b, int64_t sb_h, int asym, float eps, float qmax, float inv_qmax,
+                        float levels, float inv_levels, float offset, void* stream) {
     if (!qkv || !cos || !sin || !positions || !slots || !res_idx || !q_out || !flat_v ||
         !flat_v_scale || !k_res)
         return LS_ERR_NULL_POINTER;
+    if ((kmin == nullptr) != (kmax == nullptr)) return LS_ERR_NULL_POINTER;
+    if (kmin && ((reinterpret_cast<uintptr_t>(kmin) & 3) || (reinterpret_cast<uintptr_t>(kmax) & 3) ||
+                 (sb_b % 2) || (sb_h % 2)))
+        return LS_ERR_MISALIGNED;
     if (asym && !flat_v_zero) return LS_ERR_NULL_POINTER;
     if (head_dim != LS_HEAD_DIM) return LS_ERR_UNSUPPORTED;
     if (batch <= 0 || q_heads <= 0 || kv_heads <= 0 || max_pos <= 0 || num_slots <= 0 || num_res <= 0)
@@ -315,8 +330,9 @@ int ls_rope_append_int8(const void* qkv, const void* cos, const void* sin, const
         static_cast<const __half*>(qkv), static_cast<const __half*>(cos),
         static_cast<const __half*>(sin), reinterpret_cast<const long long*>(positions),
         reinterpret_cast<const long long*>(slots), reinterpret_cast<const long long*>(res_idx),
-        static_cast<__half*>(q_out), k_res, flat_v, nullptr, nullptr, flat_v_scale, flat_v_zero, batch,
-        q_heads, kv_heads, max_pos, num_slots, num_res, s_qkv, s_cos, sq_b, 0, 0, 0, 0, qc);
+        static_cast<__half*>(q_out), k_res, flat_v, static_cast<__half*>(kmin), static_cast<__half*>(kmax),
+        flat_v_scale, flat_v_zero, batch, q_heads, kv_heads, max_pos, num_slots, num_res, s_qkv, s_cos, sq_b,
+        0, 0, sb_b, sb_h, qc);
     return (int)cudaGetLastError();
 }
 

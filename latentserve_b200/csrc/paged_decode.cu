@@ -1483,7 +1483,8 @@ int ls_paged_sparse_fp16(const void* q, const void* k_pool, const void* v_pool,
     return ls::launch_decode<ls::MmaFp16, LS_MODE_SPARSE, ls::kStages>(p, s, pdl);
 }
 
-int ls_paged_decode_int8(const void* q, const void* k_pool, const void* v_pool,
+static int int8_decode_impl(const int32_t* sel, float ratio, int recent, int num_sel, int64_t sl_b,
+                            int64_t sl_h, const void* q, const void* k_pool, const void* v_pool,
                          const int32_t* block_tables, const int32_t* seq_lens, const float* k_scale,
                          const float* v_scale, const float* k_zero, const float* v_zero,
                          const void* k_res, const int32_t* res_rows, float* part_acc, float* part_m,
@@ -1500,6 +1501,11 @@ int ls_paged_decode_int8(const void* q, const void* k_pool, const void* v_pool,
     if ((k_zero == nullptr) != (v_zero == nullptr)) return LS_ERR_NULL_POINTER;
     if ((k_res == nullptr) != (res_rows == nullptr)) return LS_ERR_NULL_POINTER;
     DecodeParams p = {};
+    p.sel = sel;
+    p.ratio = ratio;
+    p.recent = recent;
+    p.num_sel = num_sel;
+    p.sl_b = sl_b; p.sl_h = sl_h;
     p.q = static_cast<const __half*>(q);
     p.k_pool = k_pool;
     p.v_pool = v_pool;
@@ -1548,13 +1554,55 @@ int ls_paged_decode_int8(const void* q, const void* k_pool, const void* v_pool,
     const bool pdl = (flags & LS_LAUNCH_PROGRAMMATIC) != 0;
     p.early = (flags & LS_EARLY_PAGES) != 0;
     ls::TmaMaps maps;
+    const bool tma = !k_zero && !(flags & LS_LOAD_CP_ASYNC) && build_int8_maps(p, &maps);
+    if (sel != nullptr) {
+        // Attention over the selected pages only (symmetric pools).
+        if (k_zero) return LS_ERR_UNSUPPORTED;
+        p.early = 0;
+        if (tma)
+            return ls::launch_decode<ls::MmaInt8<0, true>, LS_MODE_SPARSE, LS_INT8_TMA_STAGES>(p, s, pdl, &maps);
+        return ls::launch_decode<ls::MmaInt8<0>, LS_MODE_SPARSE, LS_INT8_STAGES>(p, s, pdl);
+    }
     if (k_zero)
         rc = ls::launch_decode<ls::MmaInt8<1>, LS_MODE_DENSE, LS_INT8_STAGES_ASYM>(p, s, pdl);
-    else if (!(flags & LS_LOAD_CP_ASYNC) && build_int8_maps(p, &maps))
+    else if (tma)
         rc = ls::launch_decode<ls::MmaInt8<0, true>, LS_MODE_DENSE, LS_INT8_TMA_STAGES>(p, s, pdl, &maps);
     else
         rc = ls::launch_decode<ls::MmaInt8<0>, LS_MODE_DENSE, LS_INT8_STAGES>(p, s, pdl);
     return rc;
+}
+
+int ls_paged_decode_int8(const void* q, const void* k_pool, const void* v_pool,
+                         const int32_t* block_tables, const int32_t* seq_lens, const float* k_scale,
+                         const float* v_scale, const float* k_zero, const float* v_zero,
+                         const void* k_res, const int32_t* res_rows, float* part_acc, float* part_m,
+                         float* part_l, int32_t* seg_range, void* out, int batch, int kv_heads,
+                         int n_rep, int head_dim, int page, int max_pages, int num_blocks,
+                         int num_res_rows, int num_chunks, int min_chunk, int flags, int64_t sq_b,
+                         int64_t sq_h, int64_t sq_m, int64_t sk_b, int64_t sk_p, int64_t sk_h, int64_t ks_b,
+                         int64_t ks_h,
+                         int64_t vs_b, int64_t vs_p, int64_t vs_h, int64_t sr_r, int64_t sr_p,
+                         int64_t sr_h, int64_t so_b, int64_t so_h, int64_t so_m, float softmax_scale,
+                         void* stream) {
+    return int8_decode_impl(nullptr, 0.f, 0, 0, 0, 0, q, k_pool, v_pool, block_tables, seq_lens, k_scale, v_scale, k_zero, v_zero, k_res, res_rows, part_acc, part_m, part_l, seg_range, out, batch, kv_heads, n_rep, head_dim, page, max_pages, num_blocks, num_res_rows, num_chunks, min_chunk, flags, sq_b, sq_h, sq_m, sk_b, sk_p, sk_h, ks_b, ks_h, vs_b, vs_p, vs_h, sr_r, sr_p, sr_h, so_b, so_h, so_m, softmax_scale, stream);
+}
+
+int ls_paged_sparse_int8(const int32_t* sel, float ratio, int recent, int num_sel, int64_t sl_b,
+                         int64_t sl_h, const void* q, const void* k_pool, const void* v_pool,
+                         const int32_t* block_tables, const int32_t* seq_lens, const float* k_scale,
+                         const float* v_scale, const float* k_zero, const float* v_zero,
+                         const void* k_res, const int32_t* res_rows, float* part_acc, float* part_m,
+                         float* part_l, int32_t* seg_range, void* out, int batch, int kv_heads,
+                         int n_rep, int head_dim, int page, int max_pages, int num_blocks,
+                         int num_res_rows, int num_chunks, int min_chunk, int flags, int64_t sq_b,
+                         int64_t sq_h, int64_t sq_m, int64_t sk_b, int64_t sk_p, int64_t sk_h, int64_t ks_b,
+                         int64_t ks_h,
+                         int64_t vs_b, int64_t vs_p, int64_t vs_h, int64_t sr_r, int64_t sr_p,
+                         int64_t sr_h, int64_t so_b, int64_t so_h, int64_t so_m, float softmax_scale,
+                         void* stream) {
+    if (!sel) return LS_ERR_NULL_POINTER;
+    if (num_sel <= 0) return LS_ERR_BAD_SHAPE;
+    return int8_decode_impl(sel, ratio, recent, num_sel, sl_b, sl_h, q, k_pool, v_pool, block_tables, seq_lens, k_scale, v_scale, k_zero, v_zero, k_res, res_rows, part_acc, part_m, part_l, seg_range, out, batch, kv_heads, n_rep, head_dim, page, max_pages, num_blocks, num_res_rows, num_chunks, min_chunk, flags, sq_b, sq_h, sq_m, sk_b, sk_p, sk_h, ks_b, ks_h, vs_b, vs_p, vs_h, sr_r, sr_p, sr_h, so_b, so_h, so_m, softmax_scale, stream);
 }
 
 int ls_combine(const float* part_acc, const float* part_m, const float* part_l,

@@ -118,18 +118,18 @@ class DecodeModel:
 
     def attend(self, cache, layer: int, q: torch.Tensor, batch: int, context_hint: int) -> torch.Tensor:
         tables, lens = cache.block_tables_tensor(batch), cache.seq_lens_tensor(batch)
+        extra = {}
+        if hasattr(cache, "k_scale_pool"):
+            extra = dict(k_scale=cache.k_scale_pool[layer], v_scale=cache.v_scale_pool[layer],
+                         k_residual=cache.residual(layer), res_rows=cache.residual_rows_tensor(batch))
         bounds = cache.page_bounds(layer) if (self.sparse_ratio is not None
                                               and hasattr(cache, "page_bounds")) else None
         if bounds is not None:
             return ps.sparse_attention(q, cache.k_pool[layer], cache.v_pool[layer], tables, lens,
                                        bounds[0], bounds[1], ratio=self.sparse_ratio,
-                                       max_seq_len=context_hint)
-        extra = {}
-        if hasattr(cache, "k_scale_pool"):
-            extra = dict(k_scale=cache.k_scale_pool[layer], v_scale=cache.v_scale_pool[layer],
-                         k_residual=cache.residual(layer), res_rows=cache.residual_rows_tensor(batch))
-            if cache.asymmetric:
-                extra.update(k_zero=cache.k_zero_pool[layer], v_zero=cache.v_zero_pool[layer])
+                                       max_seq_len=context_hint, **extra)
+        if extra and cache.asymmetric:
+            extra.update(k_zero=cache.k_zero_pool[layer], v_zero=cache.v_zero_pool[layer])
         return pd.paged_decode_attention(q, cache.k_pool[layer], cache.v_pool[layer], tables, lens,
                                          max_seq_len=context_hint, **extra)
 

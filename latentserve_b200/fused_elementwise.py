@@ -72,7 +72,7 @@ def rope_append_fp16(qkv, cos, sin, positions, slots, q_out, flat_k, flat_v, kmi
 
 def rope_append_int8(qkv, cos, sin, positions, slots, res_idx, q_out, flat_v, flat_v_scale,
                      flat_v_zero, k_res, q_heads: int, kv_heads: int, *, asym: bool, eps: float,
-                     qmax: float, levels: float, offset: float) -> None:
+                     qmax: float, levels: float, offset: float, kmin=None, kmax=None) -> None:
     """As above for the INT8 cache: flat_v int8 [num_slots, kv_heads, 128], its fp32
     scales (and zero points) [num_slots, kv_heads], k_res fp16 [rows, kv_heads, 128]
     with res_idx [B] int64; all contiguous."""
@@ -81,8 +81,10 @@ def rope_append_int8(qkv, cos, sin, positions, slots, res_idx, q_out, flat_v, fl
     rc = _lib.lib().ls_rope_append_int8(
         qkv.data_ptr(), cos.data_ptr(), sin.data_ptr(), positions.data_ptr(), slots.data_ptr(),
         res_idx.data_ptr(), q_out.data_ptr(), flat_v.data_ptr(), flat_v_scale.data_ptr(),
-        _lib.ptr(flat_v_zero), k_res.data_ptr(), qkv.shape[0], q_heads, kv_heads, 128, cos.shape[0],
-        flat_v.shape[0], k_res.shape[0], qkv.stride(0), cos.stride(0), q_out.stride(0), int(asym),
+        _lib.ptr(flat_v_zero), k_res.data_ptr(), _lib.ptr(kmin), _lib.ptr(kmax), qkv.shape[0], q_heads,
+        kv_heads, 128, cos.shape[0], flat_v.shape[0], k_res.shape[0], qkv.stride(0), cos.stride(0),
+        q_out.stride(0), kmin.stride(0) if kmin is not None else 0,
+        kmin.stride(1) if kmin is not None else 0, int(asym),
         eps, qmax, _reciprocal(qmax), levels, _reciprocal(levels), offset,
         _lib.current_stream(qkv.device))
     _lib.check(rc, "rope_append_int8")

@@ -124,10 +124,14 @@ def select(scores: torch.Tensor, k: int, sorted: bool = True) -> torch.Tensor:
 def sparse_decode(q, k_pool, v_pool, block_tables, seq_lens, sel,
                   num_splits: Optional[int] = None,
                   softmax_scale: Optional[float] = None,
-                  ratio: Optional[float] = None, recent: int = 2) -> torch.Tensor:
+                  ratio: Optional[float] = None, recent: int = 2,
+                  k_scale=None, v_scale=None, k_residual=None, res_rows=None) -> torch.Tensor:
     """Attention over the pages in `sel` [B, H, K] only. With `ratio`, each
     sequence attends the first n entries its own length is owed (computed on
-    the device); entries that are not pages of the sequence are skipped."""
+    the device); entries that are not pages of the sequence are skipped.
+    INT8 pools (symmetric; an extension, the reference's sparse path is fp16
+    only) take `k_scale`, `v_scale` and, for the still-filling last page,
+    `k_residual` / `res_rows`, as `paged_decode_attention` does."""
     if not q.is_cuda:
         raise RuntimeError("latentserve_b200 has no CPU path: tensors must be on a CUDA device")
     b, h, n_rep, d = q.shape
@@ -139,19 +143,46 @@ def sparse_decode(q, k_pool, v_pool, block_tables, seq_lens, sel,
         raise ValueError("block tables and sequence lengths must be int32")
     num_sel = sel.shape[-1]
     scale = softmax_scale if softmax_scale is not None else 1.0 / math.sqrt(d)
-    chunks = pdc.choose_chunks(q.device, h, num_splits, b)
-    acc, m, l, seg = pdc._partials(q, chunks, "sparse")
-    out = pdc.scratch("sparse_out", (b, h, n_rep, d), q.dtype, q.device)
-    rc = _lib.lib().ls_paged_sparse_fp16(
-        q.data_ptr(), k_pool.data_ptr(), v_pool.data_ptr(), block_tables.data_ptr(),
-        seq_lens.data_ptr(), sel.data_ptr(), 0.0 if ratio is None else float(ratio), recent,
-        acc.data_ptr(), m.data_ptr(), l.data_ptr(), seg.data_ptr(), out.data_ptr(),
-        b, h, n_rep, d, k_pool.shape[1], block_tables.stride(0), k_pool.shape[0], num_sel,
-        chunks, pdc.MIN_CHUNK_PAGES, pdc.launch_flags() | pdc.loader_flags(),
-        q.stride(0), q.stride(1), q.stride(2),
-        k_pool.stride(0), k_pool.stride(1), k_pool.stride(2),
-        sel.stride(0), sel.stride(1), out.stride(0), out.stride(1), out.stride(2),
-        scale, _lib.current_stream(q.device))
+    int8 = k_pool.dtype == torch.int8
+    chunks = pdc.choose_chunks(q.device, h, num_splits, b,
+                               pdc.INT8_CTAS_PER_SM if int8 else pdc.CTAS_PER_SM)
+    tag = "sparse_i8" if int8 else "sparse"
+    acc, m, l, seg = pdc._partials(q, chunks, tag)
+    out = pdc.scratch(tag + "_out", (b, h, n_rep, d), q.dtype, q.device)
+    flags = pdc.launch_flags() | pdc.loader_flags()
+    ratio_f = 0.0 if ratio is None else float(ratio)
+    ptr = _lib.ptr
+    if int8:
+        if not pdc.eligible(q, k_pool, k_scale, k_residual, v_scale=v_scale, res_rows=res_rows):
+            raise ValueError("INT8 pools need fp32 k_scale / v_scale (and k_residual with res_rows) in the "
+                             "layouts paged_decode_attention takes")
+        res_st = k_residual.stride()[:3] if k_residual is not None else (0, 0, 0)
+        rc = _lib.lib().ls_paged_sparse_int8(
+            sel.data_ptr(), ratio_f, recent, num_sel, sel.stride(0), sel.stride(1),
+            q.data_ptr(), k_pool.data_ptr(), v_pool.data_ptr(), block_tables.data_ptr(),
+            seq_lens.data_ptr(), k_scale.data_ptr(), v_scale.data_ptr(), 0, 0, ptr(k_residual),
+            ptr(res_rows), acc.data_ptr(), m.data_ptr(), l.data_ptr(), seg.data_ptr(), out.data_ptr(),
+            b, h, n_rep, d, k_pool.shape[1], block_tables.stride(0), k_pool.shape[0],
+            0 if k_residual is None else k_residual.shape[0], chunks, pdc.MIN_CHUNK_PAGES, flags,
+            q.stride(0), q.stride(1), q.stride(2),
+            k_pool.stride(0), k_pool.stride(1), k_pool.stride(2),
+            k_scale.stride(0), k_scale.stride(1),
+            v_scale.stride(0), v_scale.stride(1), v_scale.stride(2),
+            *res_st, out.stride(0), out.stride(1), out.stride(2), scale,
+            _lib.current_stream(q.device))
+    else:
+        if k_scale is not None or k_residual is not None:
+            raise ValueError("fp16 pools take no scales or residual")
+        rc = _lib.lib().ls_paged_sparse_fp16(
+            q.data_ptr(), k_pool.data_ptr(), v_pool.data_ptr(), block_tables.data_ptr(),
+            seq_lens.data_ptr(), sel.data_ptr(), ratio_f, recent,
+            acc.data_ptr(), m.data_ptr(), l.data_ptr(), seg.data_ptr(), out.data_ptr(),
+            b, h, n_rep, d, k_pool.shape[1], block_tables.stride(0), k_pool.shape[0], num_sel,
+            chunks, pdc.MIN_CHUNK_PAGES, flags,
+            q.stride(0), q.stride(1), q.stride(2),
+            k_pool.stride(0), k_pool.stride(1), k_pool.stride(2),
+            sel.stride(0), sel.stride(1), out.stride(0), out.stride(1), out.stride(2),
+            scale, _lib.current_stream(q.device))
     _lib.check(rc, "sparse_decode")
     return out
 
@@ -160,9 +191,11 @@ def sparse_attention(q, k_pool, v_pool, block_tables, seq_lens, kmin, kmax,
                      ratio: float = 0.25, recent: int = 2,
                      num_splits: Optional[int] = None, max_seq_len: Optional[int] = None,
                      softmax_scale: Optional[float] = None,
-                     scoring: str = "bounds") -> torch.Tensor:
+                     scoring: str = "bounds", k_scale=None, v_scale=None, k_residual=None,
+                     res_rows=None) -> torch.Tensor:
     """Index, select, attend. ratio >= 1 still runs all three. The budget
-    follows `max_seq_len` (the context) when given, else the table's width."""
+    follows `max_seq_len` (the context) when given, else the table's width.
+    The INT8 arguments are passed through to `sparse_decode`."""
     page = k_pool.shape[1]
     pages = block_tables.shape[1] if max_seq_len is None else min(
         block_tables.shape[1], -(-max_seq_len // page))
@@ -176,4 +209,5 @@ def sparse_attention(q, k_pool, v_pool, block_tables, seq_lens, kmin, kmax,
         raise ValueError(f"unknown scoring {scoring!r}")
     sel = select(scores, k, sorted=True)
     return sparse_decode(q, k_pool, v_pool, block_tables, seq_lens, sel, num_splits,
-                         softmax_scale, ratio=ratio, recent=recent)
+                         softmax_scale, ratio=ratio, recent=recent, k_scale=k_scale, v_scale=v_scale,
+                         k_residual=k_residual, res_rows=res_rows)

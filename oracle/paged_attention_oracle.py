@@ -297,10 +297,13 @@ def select(scores, k):
     return order[..., :k].astype(np.int32)
 
 
-def sparse_decode(q, k_pool, v_pool, tables, lens, sel, ratio=None, recent=2, softmax_scale=None):
+def sparse_decode(q, k_pool, v_pool, tables, lens, sel, ratio=None, recent=2, softmax_scale=None,
+                  k_scale=None, v_scale=None, k_residual=None, res_rows=None):
     """Attention over the first n entries of sel[b, h] that are pages of the
     sequence (n = the sequence's own budget when `ratio` is given, else all).
-    -> fp32 [B, H, R, D]."""
+    -> fp32 [B, H, R, D]. With the INT8 arguments the rows are dequantised as in
+    `paged_decode` (the reference has no INT8 sparse kernel; the definition is
+    the same masked softmax over the same dequantised rows)."""
     b, h_kv, n_rep, d = q.shape
     scale = F32(softmax_scale if softmax_scale is not None else 1.0 / math.sqrt(d))
     out = np.zeros((b, h_kv, n_rep, d), dtype=F32)
@@ -312,7 +315,8 @@ def sparse_decode(q, k_pool, v_pool, tables, lens, sel, ratio=None, recent=2, so
         if num_pages == 0:
             continue
         n = num_sel if counts is None else min(int(counts[i]), num_sel)
-        k, v = gather_sequence(i, k_pool, v_pool, tables, lens)
+        k, v = gather_sequence(i, k_pool, v_pool, tables, lens, k_scale, v_scale, None, None, k_residual,
+                               res_rows)
         for head in range(h_kv):
             keep = np.zeros(length, dtype=bool)
             for p in sel[i, head, :n]:

@@ -63,6 +63,25 @@ def test_final_page_lengths_and_empty_sequences(impl):
     assert (got[7] == 0).all() and (got[9] == 0).all()          # empty sequences give zeros
 
 
+def test_largest_batch_the_kernels_take_and_one_past_it():
+    """1024 sequences (the prefix-sum limit of the scheduler), short and ragged, some empty."""
+    rng = np.random.default_rng(12)
+    lens = rng.integers(0, 40, size=1024).tolist()
+    case = synthetic.dense_case(lens, seed=12)
+    want = orc.paged_decode(case["q"], case["k_pool"], case["v_pool"], case["block_tables"],
+                            case["seq_lens"])
+    close(_run(on_device(case)), want)
+    over = synthetic.dense_case([3] * 1025, seed=13)
+    with pytest.raises(ValueError):
+        _run(on_device(over))
+
+
+def test_every_sequence_empty_gives_zeros():
+    case = synthetic.dense_case([0, 0, 0], seed=14)
+    got = _run(on_device(case))
+    assert got.shape == (3, 2, 6, 128) and (got == 0).all()
+
+
 def test_no_cross_sequence_leak_and_stale_rows_are_never_read():
     """Rows past each sequence's end, and every block no table names, hold NaN."""
     lens = [100, 37, 260]

@@ -217,6 +217,72 @@ def test_int8_loaders_agree_bit_for_bit():
     assert torch.equal(outs["tma"], outs["cp_async"])
 
 
+@pytest.mark.parametrize("ratio", [None, 0.5])
+def test_int8_sparse_decode_matches_the_oracle(ratio, loader):
+    """Attention over a page list on INT8 pools (an extension: the reference's sparse
+    kernel is fp16 only) against masked softmax over the dequantised rows."""
+    from latentserve_b200 import paged_sparse as ps
+
+    lens = [700, 333, 64, 17, 0]
+    case = _random_int8_case(lens, False, True, seed=31)
+    rng = np.random.default_rng(32)
+    pages = -(-max(lens) // 16)
+    sel = np.stack([np.stack([rng.permutation(pages)[:24] for _ in range(2)]) for _ in lens]).astype(np.int32)
+    sel[0, 0, 3] = -1                                            # not a page: skipped
+    if 20 not in sel[1, 1]:
+        sel[1, 1, 0] = 20                                        # the sequence's last page (K from the residual)
+    sel[2, :, 5] = pages + 7                                     # past the table: skipped
+    extra = {k: case[k] for k in ("k_scale", "v_scale", "k_residual", "res_rows")}
+    want = orc.sparse_decode(case["q"], case["k_pool"], case["v_pool"], case["block_tables"],
+                             case["seq_lens"], sel, ratio=ratio, **extra)
+    dev = device()
+    t = {k: torch.from_numpy(np.ascontiguousarray(v)).to(dev) for k, v in case.items()}
+    got = ps.sparse_decode(t["q"], t["k_pool"], t["v_pool"], t["block_tables"], t["seq_lens"],
+                           torch.from_numpy(sel).to(dev), ratio=ratio, k_scale=t["k_scale"],
+                           v_scale=t["v_scale"], k_residual=t["k_residual"], res_rows=t["res_rows"])
+    close(got, want)
+
+
+def test_int8_cache_with_page_bounds_runs_the_sparse_pipeline():
+    """Int8PagedKVCache keeping page bounds of the exact K: index + select + INT8
+    attention at a full budget equals the dense INT8 attention; bounds equal the
+    fp16 cache's for the same tokens."""
+    from latentserve_b200 import cache as lc, paged_decode as pd, paged_sparse as ps
+
+    dev = device()
+    spec = lc.KVCacheSpec(num_layers=1, num_kv_heads=2, head_dim=128, max_seq_len=256,
+                          max_batch_size=2, device="cuda")
+    c8, c16 = lc.Int8PagedKVCache(spec, num_blocks=40), lc.PagedKVCache(spec, num_blocks=40)
+    c8.enable_page_bounds()
+    c16.enable_page_bounds()
+    rng = np.random.default_rng(33)
+    for i, n in enumerate([70, 37]):
+        k = torch.from_numpy(rng.standard_normal((1, 2, n, 128)).astype(np.float16)).to(dev)
+        v = torch.from_numpy(rng.standard_normal((1, 2, n, 128)).astype(np.float16)).to(dev)
+        for c in (c8, c16):
+            c.advance(n, slots=[i])
+            c.write(0, k, v)
+    for _ in range(12):                                          # decode steps across a page boundary
+        k = torch.from_numpy(rng.standard_normal((2, 2, 1, 128)).astype(np.float16)).to(dev)
+        v = torch.from_numpy(rng.standard_normal((2, 2, 1, 128)).astype(np.float16)).to(dev)
+        for c in (c8, c16):
+            c.advance(1, slots=[0, 1])
+            c.write(0, k, v)
+    # Same tokens, same block ids (both allocators hand out blocks in the same order).
+    assert c8.tables[0].blocks == c16.tables[0].blocks and c8.tables[1].blocks == c16.tables[1].blocks
+    used = sorted(set(c8.tables[0].blocks + c8.tables[1].blocks))
+    assert torch.equal(c8.kmin[0][used], c16.kmin[0][used]) and torch.equal(c8.kmax[0][used], c16.kmax[0][used])
+    q = torch.from_numpy(rng.standard_normal((2, 2, 6, 128)).astype(np.float16)).to(dev)
+    tables, lens = c8.block_tables_tensor(2), c8.seq_lens_tensor(2)
+    args = dict(k_scale=c8.k_scale_pool[0], v_scale=c8.v_scale_pool[0], k_residual=c8.residual(0),
+                res_rows=c8.residual_rows_tensor(2))
+    dense = pd.paged_decode_attention(q, c8.k_pool[0], c8.v_pool[0], tables, lens, max_seq_len=c8.max_len,
+                                      **args).clone()
+    full = ps.sparse_attention(q, c8.k_pool[0], c8.v_pool[0], tables, lens, c8.kmin[0], c8.kmax[0],
+                               ratio=1.0, max_seq_len=c8.max_len, **args)
+    assert (full.float() - dense.float()).abs().max() <= 2e-3
+
+
 def test_int8_stale_scales_and_rows_are_never_read(loader):
     lens = [100, 37]
     case = _random_int8_case(lens, False, True, seed=22)

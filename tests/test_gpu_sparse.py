@@ -106,6 +106,17 @@ def test_topk_is_bit_exact_with_ties_to_the_lower_index(n, k):
     assert np.array_equal(got.cpu().numpy(), orc.select(s, k))
 
 
+def test_topk_longest_row_and_one_past_it():
+    """8192 pages (a 128K context) is the longest row the sort takes."""
+    rng = np.random.default_rng(8192)
+    s = rng.standard_normal((2, 2, 8192)).astype(np.float32)
+    s[0, 1, 100:4000] = 0.25                                   # a long run of ties
+    got = ps.select(torch.from_numpy(s).to(device()), 4096)
+    assert np.array_equal(got.cpu().numpy(), orc.select(s, 4096))
+    with pytest.raises(ValueError):
+        ps.select(torch.zeros(1, 2, 8193, device=device()), 16)
+
+
 def test_selection_end_to_end_is_bit_exact_on_the_sparse_workload_shape():
     """Scores from the kernel, selection from the kernel, against the oracle
     chain, at 2048 pages and a 50 % budget."""
