@@ -65,6 +65,7 @@ STEP_WORKLOADS = {
     "qwen_step_b16_16k": (16, 16384, "fp16", None, 0),
     "qwen_step_b16_16k_int8": (16, 16384, "int8", None, 0),
     "qwen_step_b16_16k_sparse50": (16, 16384, "fp16", 0.5, 0),
+    "qwen_step_b16_16k_int8_sparse50": (16, 16384, "int8", 0.5, 0),
     "qwen_step_b64_ragged": (64, "loguniform_1k_32k", "fp16", None, 4096),
     "qwen_step_b64_ragged_int8": (64, "loguniform_1k_32k", "int8", None, 4096),
 }
@@ -497,6 +498,11 @@ def run_model_step(args):
     blocks = int(1.2 * sum(-(-(n + room) // 16) for n in lens)) + 64
     cache = (lc.Int8PagedKVCache if kind == "int8" else lc.PagedKVCache)(spec, num_blocks=blocks)
     g = torch.Generator(device=dev).manual_seed(rank)
+    if kind == "int8" and ratio is not None:       # the INT8 cache keeps bounds from its first write on
+        cache.enable_page_bounds()
+        for layer in range(shape.num_layers):      # synthetic history: plausible bounds everywhere
+            cache.kmin[layer].normal_(generator=g).sub_(1.5)
+            cache.kmax[layer].normal_(generator=g).abs_().add_(cache.kmin[layer])
     for layer in range(shape.num_layers):          # synthetic history: random K/V everywhere
         if kind == "int8":
             cache.k_pool[layer].random_(-127, 128, generator=g)
@@ -522,7 +528,7 @@ def run_model_step(args):
         cache.tables[i].append(n - 1 - have)
         if kind == "int8":
             cache._fin[i] = (n - 1) // 16
-    if ratio is not None:
+    if ratio is not None and kind != "int8":
         cache.enable_page_bounds()
     model = ds.DecodeModel(shape, dev, max_pos=max(lens) + room + 16, seed=rank,
                            projections=args.projections)
