@@ -290,7 +290,7 @@ def main():
             kmin, kmax = w["bounds"][i]
             return ps.sparse_attention(w["q"][i], k, v, tables, lens, kmin, kmax, ratio=sparse_ratio,
                                        max_seq_len=context)
-        launches_per_layer, kernel_name = 3, "page_index + topk_pages + decode_kernel<sparse>"
+        launches_per_layer, kernel_name = 3, "page_index + select_pages + decode_kernel<sparse>"
     else:
         w = synthetic.dense_pools_on_device(batch, seq_lens, layers, dev, seed=rank)
         tables, lens = w["block_tables"], w["seq_lens"]
@@ -381,7 +381,9 @@ def main():
         scores_fixed = ps.page_scores(w["q"][0], *w["bounds"][0], tables, lens).clone()
         breakdown = {
             "page_index_us": round(graph_us(lambda i: ps.page_scores(w["q"][i], *w["bounds"][i], tables, lens), reps), 2),
-            "topk_pages_us": round(graph_us(lambda i: ps.select(scores_fixed, keep_), reps), 2),
+            "select_pages_us": round(graph_us(lambda i: ps.select_for_attention(
+                scores_fixed, lens, keep_, sparse_ratio), reps), 2),
+            "topk_pages_us_not_on_the_path": round(graph_us(lambda i: ps.select(scores_fixed, keep_), reps), 2),
             "sparse_decode_us": round(graph_us(lambda i: ps.sparse_decode(
                 w["q"][i], w["pools"][i][0], w["pools"][i][1], tables, lens, sel_fixed, ratio=sparse_ratio), reps), 2),
         }

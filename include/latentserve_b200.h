@@ -274,6 +274,18 @@ int ls_page_index_heads(const void* q, const void* kmin, const void* kmax,
 int ls_topk_pages(const float* scores, int32_t* sel, int batch, int kv_heads, int num_pages, int k,
                   int64_t ss_b, int64_t ss_h, int64_t sl_b, int64_t sl_h, void* stream);
 
+/* Selection for the fused index -> select -> attend path, without the sort: for each
+ * (sequence, head) the n pages with the highest scores, n = the sequence's own budget
+ * from its own length (the rule ls_paged_sparse_* applies: max(recent + 1,
+ * ceil(ratio x pages)), capped at its pages and at k; ratio <= 0 or >= 1: min(pages, k)),
+ * ties to the lower page -- the same set as the first n entries ls_topk_pages returns --
+ * written in ascending page order and followed by -1 up to k. A radix search for the
+ * n-th largest score and two block scans; about half the time of the sort. No
+ * counterpart in the reference (it sorts with torch.topk, kernels/cuda/paged_sparse.py:164-168,249). */
+int ls_select_pages(const float* scores, const int32_t* seq_lens, int32_t* sel, int batch, int kv_heads,
+                    int num_pages, int k, float ratio, int recent, int64_t ss_b, int64_t ss_h,
+                    int64_t sl_b, int64_t sl_h, void* stream);
+
 /* ---- The per-layer kernels around attention (the callers' side of the path) ---- */
 
 /* RMSNorm over fp16 rows, optionally fused with the residual add:

@@ -287,6 +287,160 @@ topk_pages_kernel(const float* __restrict__ scores, int* __restrict__ sel, int n
         if (base + e < k) dst[base + e] = (int)(0xffffffffu - (uint32_t)(v[e] & 0xffffffffull));
 }
 
+// ---------------------------------------------------------------------------
+// Selection without the sort, for the fused index -> select -> attend path: the
+// attention kernel needs the SET of pages a sequence is owed (its own budget n
+// from its own length), not their order by score. One CTA per (sequence, head):
+// a 4-pass radix search over the 32-bit order keys finds the n-th largest key T,
+// then every key above T is kept, and of the keys equal to T the ones with the
+// lowest page numbers (the same tie rule as the sort), by two block scans. Output:
+// the kept pages in ascending page order, then -1 up to k. The kept set equals
+// the first n entries of the sorted selection, bit for bit.
+constexpr int kSelectThreads = 512;
+
+template <int E>
+__global__ void __launch_bounds__(kSelectThreads)
+select_pages_kernel(const float* __restrict__ scores, const int* __restrict__ seq_lens,
+                    int* __restrict__ sel, int n, int k, int heads, float ratio, int recent,
+                    long long ss_b, long long ss_h, long long sl_b, long long sl_h) {
+    __shared__ int hist[256];
+    __shared__ int warp_tot[kSelectThreads / 32][2];
+    __shared__ unsigned s_prefix;
+    __shared__ int s_remaining;
+    asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
+    const int bh = blockIdx.x, b = bh / heads, h = bh % heads;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const float* row = scores + b * ss_b + h * ss_h;
+    int* out = sel + b * sl_b + h * sl_h;
+
+    // How many pages this sequence attends: the rule of the attention kernel.
+    const int L = max(seq_lens[b], 0);
+    const int np = (L + LS_PAGE - 1) / LS_PAGE;
+    int want = np;
+    if (ratio > 0.f && ratio < 1.f) want = max(recent + 1, (int)ceilf(ratio * (float)np));
+    const int n_keep = min(min(want, np), min(k, n));
+
+    unsigned key[E];
+    if ((n & 3) == 0 && ((reinterpret_cast<uintptr_t>(row) & 15) == 0)) {
+#pragma unroll
+        for (int e = 0; e < E; e += 4) {
+            const int i = tid * E + e;
+            float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (i < n) v = *reinterpret_cast<const float4*>(row + i);
+            key[e] = (i < n) ? order_key(v.x) : 0u;          // padding: below every real key
+            key[e + 1] = (i < n) ? order_key(v.y) : 0u;
+            key[e + 2] = (i < n) ? order_key(v.z) : 0u;
+            key[e + 3] = (i < n) ? order_key(v.w) : 0u;
+        }
+    } else {
+#pragma unroll
+        for (int e = 0; e < E; ++e) {
+            const int i = tid * E + e;
+            key[e] = (i < n) ? order_key(row[i]) : 0u;
+        }
+    }
+    if (n_keep <= 0) {
+        for (int i = tid; i < k; i += kSelectThreads) out[i] = -1;
+        return;
+    }
+
+    // Radix search, 8 bits a pass from the top: prefix = decided high bits of T,
+    // remaining = how many keys are still to be taken among those matching the prefix.
+    // Two barriers a pass: warp 0 clears the histogram it has just read.
+    unsigned prefix = 0, mask = 0;
+    int remaining = n_keep;
+    if (tid < 256) hist[tid] = 0;
+    __syncthreads();
+#pragma unroll 1
+    for (int shift = 24; shift >= 0; shift -= 8) {
+        // Scores cluster in a few top-byte values, so lanes of a warp that hit the same
+        // bin add once between them (match.any) instead of serialising 32 atomics.
+#pragma unroll
+        for (int e = 0; e < E; ++e) {
+            const bool in = (key[e] & mask) == prefix && tid * E + e < n;
+            const unsigned bin = in ? ((key[e] >> shift) & 255u) : 256u;
+            const unsigned peers = __match_any_sync(LS_FULL_MASK, bin);
+            if (in && lane == __ffs(peers) - 1) atomicAdd(&hist[bin], __popc(peers));
+        }
+        __syncthreads();
+        if (warp == 0) {
+            // lane l owns bins 255 - 8 l .. 248 - 8 l (descending); inclusive scan over lanes.
+            int local[8], sum = 0;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                local[j] = hist[255 - (8 * lane + j)];
+                hist[255 - (8 * lane + j)] = 0;             // ready for the next pass
+                sum += local[j];
+            }
+            int incl = sum;
+#pragma unroll
+            for (int off = 1; off < 32; off <<= 1) {
+                const int v = __shfl_up_sync(LS_FULL_MASK, incl, off);
+                if (lane >= off) incl += v;
+            }
+            int before = incl - sum;                        // keys in bins above this lane's
+            if (before < remaining && remaining <= incl) {
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    if (before + local[j] >= remaining) {
+                        s_prefix = prefix | ((unsigned)(255 - (8 * lane + j)) << shift);
+                        s_remaining = remaining - before;
+                        break;
+                    }
+                    before += local[j];
+                }
+            }
+        }
+        __syncthreads();
+        // s_prefix / s_remaining are rewritten only after the next pass's first barrier.
+        prefix = s_prefix;
+        remaining = s_remaining;
+        mask |= 0xffu << shift;
+    }
+    const unsigned T = prefix;                              // the n_keep-th largest key
+    const int take_eq = remaining;                          // keys equal to T to keep, lowest pages first
+
+    // Block scans over (keys equal to T, keys above T), in page order.
+    int eq_local = 0, gt_local = 0;
+#pragma unroll
+    for (int e = 0; e < E; ++e) {
+        const bool real = tid * E + e < n;
+        eq_local += real && key[e] == T;
+        gt_local += real && key[e] > T;
+    }
+    int eq_incl = eq_local, gt_incl = gt_local;
+#pragma unroll
+    for (int off = 1; off < 32; off <<= 1) {
+        const int a = __shfl_up_sync(LS_FULL_MASK, eq_incl, off);
+        const int c = __shfl_up_sync(LS_FULL_MASK, gt_incl, off);
+        if (lane >= off) {
+            eq_incl += a;
+            gt_incl += c;
+        }
+    }
+    if (lane == 31) {
+        warp_tot[warp][0] = eq_incl;
+        warp_tot[warp][1] = gt_incl;
+    }
+    __syncthreads();
+    int eq_before = eq_incl - eq_local, gt_before = gt_incl - gt_local;
+    for (int w = 0; w < warp; ++w) {
+        eq_before += warp_tot[w][0];
+        gt_before += warp_tot[w][1];
+    }
+    // Position of a kept key = kept keys before it = (above T before it) + min(equal before it, take_eq).
+#pragma unroll
+    for (int e = 0; e < E; ++e) {
+        const int i = tid * E + e;
+        if (i >= n) break;
+        const bool gt = key[e] > T, eq = key[e] == T;
+        if (gt || (eq && eq_before < take_eq)) out[gt_before + min(eq_before, take_eq)] = i;
+        gt_before += gt;
+        eq_before += eq;
+    }
+    for (int i = n_keep + tid; i < k; i += kSelectThreads) out[i] = -1;
+}
+
 }  // namespace ls
 
 extern "C" {
@@ -370,6 +524,25 @@ int ls_topk_pages(const float* scores, int32_t* sel, int batch, int kv_heads, in
     else if (per_thread == 4) LS_LAUNCH_TOPK(4);
     else LS_LAUNCH_TOPK(8);
 #undef LS_LAUNCH_TOPK
+    return (int)cudaGetLastError();
+}
+
+int ls_select_pages(const float* scores, const int32_t* seq_lens, int32_t* sel, int batch, int kv_heads,
+                    int num_pages, int k, float ratio, int recent, int64_t ss_b, int64_t ss_h,
+                    int64_t sl_b, int64_t sl_h, void* stream) {
+    if (!scores || !seq_lens || !sel) return LS_ERR_NULL_POINTER;
+    if (batch <= 0 || kv_heads <= 0 || num_pages <= 0 || k <= 0 || k > num_pages || recent < 0)
+        return LS_ERR_BAD_SHAPE;
+    if (num_pages > ls::kTopkMaxRow || (long long)batch * kv_heads > 2147483647LL) return LS_ERR_TOO_LARGE;
+    if (((uintptr_t)scores & 3) || ((uintptr_t)sel & 3)) return LS_ERR_MISALIGNED;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const int grid = batch * kv_heads;
+    if (num_pages <= 4 * ls::kSelectThreads)
+        ls::select_pages_kernel<4><<<grid, ls::kSelectThreads, 0, st>>>(
+            scores, seq_lens, sel, num_pages, k, kv_heads, ratio, recent, ss_b, ss_h, sl_b, sl_h);
+    else
+        ls::select_pages_kernel<16><<<grid, ls::kSelectThreads, 0, st>>>(
+            scores, seq_lens, sel, num_pages, k, kv_heads, ratio, recent, ss_b, ss_h, sl_b, sl_h);
     return (int)cudaGetLastError();
 }
 

@@ -121,6 +121,29 @@ def select(scores: torch.Tensor, k: int, sorted: bool = True) -> torch.Tensor:
     return sel
 
 
+def select_for_attention(scores: torch.Tensor, seq_lens: torch.Tensor, k: int, ratio: Optional[float],
+                         recent: int = 2) -> torch.Tensor:
+    """The pages `sparse_decode(..., ratio=ratio)` would attend out of
+    `select(scores, k)`: per (sequence, head) the n best pages, n = that
+    sequence's own budget, in ascending page order, then -1 up to k. Same set as
+    the first n entries of the sorted selection (ties to the lower page), without
+    sorting the row. -> int32 [B, H, k]."""
+    b, h, n = scores.shape
+    if not 0 < k <= n:
+        raise ValueError(f"k must be in [1, {n}], got {k}")
+    if scores.stride(-1) != 1 or scores.dtype != torch.float32:
+        raise ValueError("scores must be fp32 with a unit-stride page axis")
+    if seq_lens.dtype != torch.int32:
+        raise ValueError("sequence lengths must be int32")
+    sel = pdc.scratch("sparse_sel_set", (b, h, k), torch.int32, scores.device)
+    rc = _lib.lib().ls_select_pages(scores.data_ptr(), seq_lens.data_ptr(), sel.data_ptr(), b, h, n, k,
+                                    0.0 if ratio is None else float(ratio), recent,
+                                    scores.stride(0), scores.stride(1), sel.stride(0), sel.stride(1),
+                                    _lib.current_stream(scores.device))
+    _lib.check(rc, "select_for_attention")
+    return sel
+
+
 def sparse_decode(q, k_pool, v_pool, block_tables, seq_lens, sel,
                   num_splits: Optional[int] = None,
                   softmax_scale: Optional[float] = None,
@@ -207,7 +230,9 @@ def sparse_attention(q, k_pool, v_pool, block_tables, seq_lens, kmin, kmax,
         scores = page_scores(q, kmin, kmax, block_tables, seq_lens, recent)
     else:
         raise ValueError(f"unknown scoring {scoring!r}")
-    sel = select(scores, k, sorted=True)
+    # The reference sorts (`select(scores, k, sorted=True)`) and lets each sequence attend the
+    # first n entries it is owed; the same n pages are picked here without the sort.
+    sel = select_for_attention(scores, seq_lens, k, ratio, recent)
     return sparse_decode(q, k_pool, v_pool, block_tables, seq_lens, sel, num_splits,
                          softmax_scale, ratio=ratio, recent=recent, k_scale=k_scale, v_scale=v_scale,
                          k_residual=k_residual, res_rows=res_rows)

@@ -106,6 +106,37 @@ def test_topk_is_bit_exact_with_ties_to_the_lower_index(n, k):
     assert np.array_equal(got.cpu().numpy(), orc.select(s, k))
 
 
+@pytest.mark.parametrize("n,k,ratio", [(2048, 1024, 0.5), (2048, 2048, 1.0), (700, 44, 0.0625), (33, 3, 0.05),
+                                       (1, 1, 0.5), (257, 256, None), (8192, 4096, 0.5), (5000, 1250, 0.25)])
+def test_selection_without_the_sort_picks_the_same_pages(n, k, ratio):
+    """`select_for_attention` against the sorted selection: per sequence the first n
+    entries of the sort (n = its own budget), as a set and in ascending page order."""
+    rng = np.random.default_rng(n * 7 + k)
+    s = rng.standard_normal((4, 2, n)).astype(np.float32)
+    lens = np.asarray([n * 16, max(1, n * 16 - 5), max(1, (n // 2) * 16 + 3), 0], dtype=np.int32)
+    for b, L in enumerate(lens):                                  # what the indexer would write
+        np_ = -(-int(L) // 16)
+        s[b, :, np_:] = -np.inf
+        if np_:
+            s[b, :, 0] = np.inf
+            s[b, :, max(0, np_ - 2):np_] = np.inf
+    if n > 40:
+        s[0, 0, 10:30] = s[0, 0, 10]                              # runs of exact ties
+        s[1, 1, : n // 2] = np.round(s[1, 1, : n // 2], 1)        # many ties
+        s[2, 0, 5], s[2, 0, 6] = -0.0, 0.0
+    dev = device()
+    got = ps.select_for_attention(torch.from_numpy(s).to(dev), torch.from_numpy(lens).to(dev), k, ratio)
+    got = got.cpu().numpy()
+    order = orc.select(s, k)                                      # stable descending sort, first k
+    counts = orc.budgets(lens, ratio) if ratio is not None and 0 < ratio < 1 else -(-lens // 16)
+    for b in range(4):
+        keep = int(min(counts[b], -(-int(lens[b]) // 16), k))
+        for h in range(2):
+            want = np.sort(order[b, h, :keep])
+            assert np.array_equal(got[b, h, :keep], want), (b, h)
+            assert (got[b, h, keep:] == -1).all()
+
+
 def test_topk_longest_row_and_one_past_it():
     """8192 pages (a 128K context) is the longest row the sort takes."""
     rng = np.random.default_rng(8192)
