@@ -198,6 +198,37 @@ def test_int8_decode_matches_the_oracle(asym, residual, splits, loader):
     assert pdc.error_flag(dev, len(lens), tag="cuda_i8") == 0
 
 
+@pytest.mark.parametrize("strided_scales", [False, True])
+def test_int8_pools_that_are_views_of_larger_tensors(strided_scales, loader):
+    """Pools with head stride 128 inside a 3-head allocation (tensor maps describe them;
+    with strided V scales the TMA loader does not apply and the cp.async form runs)."""
+    lens = [500, 77, 16]
+    case = _random_int8_case(lens, False, True, seed=41)
+    extra = {k: case[k] for k in ("k_scale", "v_scale", "k_residual", "res_rows")}
+    want = orc.paged_decode(case["q"], case["k_pool"], case["v_pool"], case["block_tables"],
+                            case["seq_lens"], **extra)
+    dev = device()
+    t = {k: torch.from_numpy(np.ascontiguousarray(v)).to(dev) for k, v in case.items()}
+    nb = t["k_pool"].shape[0]
+
+    def widen(x, axis):                                          # same values, one spare head alongside
+        shape = list(x.shape)
+        shape[axis] += 1
+        big = torch.full(shape, 3, dtype=x.dtype, device=dev)
+        view = big.narrow(axis, 0, x.shape[axis])
+        view.copy_(x)
+        return view
+
+    k_pool, v_pool = widen(t["k_pool"], 2), widen(t["v_pool"], 2)
+    k_scale = widen(t["k_scale"], 1)
+    v_scale = widen(t["v_scale"], 2) if strided_scales else t["v_scale"]
+    assert not k_pool.is_contiguous() and k_pool.shape == (nb, 16, 2, 128)
+    got = pdc.paged_decode_cuda(t["q"], k_pool, v_pool, t["block_tables"], t["seq_lens"], max(lens),
+                                k_scale=k_scale, v_scale=v_scale, k_residual=t["k_residual"],
+                                res_rows=t["res_rows"])
+    close(got, want)
+
+
 def test_int8_loaders_agree_bit_for_bit():
     """TMA tiles and per-lane cp.async feed the same arithmetic."""
     lens = [2000, 777, 16, 15, 1]
