@@ -985,8 +985,30 @@ __device__ __forceinline__ void merge_partials(const float* part_acc, const floa
     if (!has0) return;
     const long long base0 = ((long long)first * heads + h) * kRP + r0;
     const long long base1 = base0 + kWarps;
-    float mg0 = neg_inf(), mg1 = neg_inf();
-    for (int s = lane; s < count; s += 32) {
+    const float4* src0 = reinterpret_cast<const float4*>(part_acc + base0 * LS_HEAD_DIM) + lane;
+    const float4* src1 = src0 + kWarps * (LS_HEAD_DIM / 4);
+    const long long pstep = step * (LS_HEAD_DIM / 4);
+
+    // One round trip for everything the usual case needs: lane s's (m, l) of partial s,
+    // and the accumulator rows of the first kBatch partials (which do not depend on m).
+    float pm0 = neg_inf(), pm1 = neg_inf(), pl0 = 0.f, pl1 = 0.f;
+    if (lane < count) {
+        pm0 = __ldcg(part_m + base0 + lane * step);
+        pl0 = __ldcg(part_l + base0 + lane * step);
+        if (has1) {
+            pm1 = __ldcg(part_m + base1 + lane * step);
+            pl1 = __ldcg(part_l + base1 + lane * step);
+        }
+    }
+    float4 v0[kBatch], v1[kBatch];
+#pragma unroll
+    for (int j = 0; j < kBatch; ++j) {
+        const bool ok = j < count;
+        v0[j] = ok ? __ldcg(src0 + j * pstep) : make_float4(0.f, 0.f, 0.f, 0.f);
+        v1[j] = (ok && has1) ? __ldcg(src1 + j * pstep) : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    float mg0 = pm0, mg1 = pm1;
+    for (int s = lane + 32; s < count; s += 32) {            // more than 32 partials: rare
         mg0 = fmaxf(mg0, __ldcg(part_m + base0 + s * step));
         if (has1) mg1 = fmaxf(mg1, __ldcg(part_m + base1 + s * step));
     }
@@ -1003,25 +1025,31 @@ __device__ __forceinline__ void merge_partials(const float* part_acc, const floa
         const int s = s0 + lane;
         float w0 = 0.f, w1 = 0.f;
         if (s < count) {
-            w0 = ex2(__ldcg(part_m + base0 + s * step) - ms0);
-            ls0 += w0 * __ldcg(part_l + base0 + s * step);
+            if (s0 > 0) {
+                pm0 = __ldcg(part_m + base0 + s * step);
+                pl0 = __ldcg(part_l + base0 + s * step);
+                if (has1) {
+                    pm1 = __ldcg(part_m + base1 + s * step);
+                    pl1 = __ldcg(part_l + base1 + s * step);
+                }
+            }
+            w0 = ex2(pm0 - ms0);
+            ls0 += w0 * pl0;
             if (has1) {
-                w1 = ex2(__ldcg(part_m + base1 + s * step) - ms1);
-                ls1 += w1 * __ldcg(part_l + base1 + s * step);
+                w1 = ex2(pm1 - ms1);
+                ls1 += w1 * pl1;
             }
         }
         const int n = min(32, count - s0);
-        const float4* src0 =
-            reinterpret_cast<const float4*>(part_acc + (base0 + s0 * step) * LS_HEAD_DIM) + lane;
-        const float4* src1 = src0 + kWarps * (LS_HEAD_DIM / 4);
-        const long long pstep = step * (LS_HEAD_DIM / 4);
         for (int j0 = 0; j0 < n; j0 += kBatch) {
-            float4 v0[kBatch], v1[kBatch];
+            if (s0 + j0 > 0) {                               // the first batch is already here
 #pragma unroll
-            for (int j = 0; j < kBatch; ++j) {
-                const bool ok = j0 + j < n;
-                v0[j] = ok ? __ldcg(src0 + (j0 + j) * pstep) : make_float4(0.f, 0.f, 0.f, 0.f);
-                v1[j] = (ok && has1) ? __ldcg(src1 + (j0 + j) * pstep) : make_float4(0.f, 0.f, 0.f, 0.f);
+                for (int j = 0; j < kBatch; ++j) {
+                    const bool ok = j0 + j < n;
+                    v0[j] = ok ? __ldcg(src0 + (s0 + j0 + j) * pstep) : make_float4(0.f, 0.f, 0.f, 0.f);
+                    v1[j] = (ok && has1) ? __ldcg(src1 + (s0 + j0 + j) * pstep)
+                                         : make_float4(0.f, 0.f, 0.f, 0.f);
+                }
             }
 #pragma unroll
             for (int j = 0; j < kBatch; ++j) {
@@ -1215,15 +1243,17 @@ decode_kernel(const DecodeParams p, const __grid_constant__ TmaMaps maps) {
             if (tid == 0) {
                 int last = 1;
                 if (nseg > 1) {
-                    __threadfence();                          // ... and visible before we count
-                    last = atomicAdd(counter, 1) == nseg - 1;
+                    // Release the CTA's partial (ordered before this by the barrier) and
+                    // acquire the others' in one atomic; the merge reads them from L2.
+                    int seen;
+                    asm volatile("atom.add.acq_rel.gpu.s32 %0, [%1], 1;\n" : "=r"(seen) : "l"(counter) : "memory");
+                    last = seen == nseg - 1;
                     if (last) *counter = 0;                  // ready for the next launch
                 }
                 *flag = last;
             }
             __syncthreads();
             if (*flag) {
-                __threadfence();
                 merge_partials(p.part_acc, p.part_m, p.part_l, c_lo + b, nseg, p.out, p.heads,
                                p.n_rep, b, h, tid, p.so_b, p.so_h, p.so_m);
             }
