@@ -50,33 +50,6 @@ __device__ __forceinline__ void halve(const float (&in)[N], float (&out)[N / 2],
     }
 }
 
-// Packed fp32 pairs (sm_100 has two-wide fp32 add / mul / fma on 64-bit
-// registers; each half is an ordinary IEEE operation).
-typedef unsigned long long f32x2;
-__device__ __forceinline__ f32x2 pack2(float lo, float hi) {
-    f32x2 r;
-    asm("mov.b64 %0, {%1, %2};\n" : "=l"(r) : "f"(lo), "f"(hi));
-    return r;
-}
-__device__ __forceinline__ void unpack2(f32x2 v, float& lo, float& hi) {
-    asm("mov.b64 {%0, %1}, %2;\n" : "=f"(lo), "=f"(hi) : "l"(v));
-}
-__device__ __forceinline__ f32x2 mul2(f32x2 a, f32x2 b) {
-    f32x2 r;
-    asm("mul.rn.f32x2 %0, %1, %2;\n" : "=l"(r) : "l"(a), "l"(b));
-    return r;
-}
-__device__ __forceinline__ f32x2 add2(f32x2 a, f32x2 b) {
-    f32x2 r;
-    asm("add.rn.f32x2 %0, %1, %2;\n" : "=l"(r) : "l"(a), "l"(b));
-    return r;
-}
-__device__ __forceinline__ f32x2 fma2(f32x2 a, f32x2 b, f32x2 c) {
-    f32x2 r;
-    asm("fma.rn.f32x2 %0, %1, %2, %3;\n" : "=l"(r) : "l"(a), "l"(b), "l"(c));
-    return r;
-}
-
 // Bounds of 8 (padded) query rows x 4 pages. On return lane l holds the
 // complete bound of page (l >> 3) of the group, query row (l & 7).
 // max(q * lo, q * hi) with lo <= hi (a page's channel minimum and maximum) is

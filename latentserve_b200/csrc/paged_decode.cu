@@ -834,10 +834,14 @@ struct MmaInt8 {
             for (int i = 0; i < 8; ++i) {
                 const uint32_t slot = (uint32_t)(8 * t + (i ^ t)) << 4;   // see PoolInt8::issue
                 const uint4 sc = lds128(stage + Pool::OFF_KS + slot);
-                qk[i][0] = pack_half2(qf[4 * i] * __uint_as_float(sc.x),
-                                      qf[4 * i + 1] * __uint_as_float(sc.y));
-                qk[i][1] = pack_half2(qf[4 * i + 2] * __uint_as_float(sc.z),
-                                      qf[4 * i + 3] * __uint_as_float(sc.w));
+                // Two products per instruction (packed fp32), each rounded as a single one would be.
+                float p0, p1, p2, p3;
+                unpack2(mul2(pack2(qf[4 * i], qf[4 * i + 1]),
+                             pack2(__uint_as_float(sc.x), __uint_as_float(sc.y))), p0, p1);
+                unpack2(mul2(pack2(qf[4 * i + 2], qf[4 * i + 3]),
+                             pack2(__uint_as_float(sc.z), __uint_as_float(sc.w))), p2, p3);
+                qk[i][0] = pack_half2(p0, p1);
+                qk[i][1] = pack_half2(p2, p3);
                 if (ASYM) {
                     const uint4 z = lds128(stage + Pool::OFF_KZ + slot);
                     zq = fmaf(qf[4 * i], __uint_as_float(z.x), zq);
