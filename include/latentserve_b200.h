@@ -46,12 +46,12 @@ extern "C" {
  * not write seq_lens or block_tables (in LatentServe it is the KV append). */
 #define LS_LAUNCH_PROGRAMMATIC 0x100
 /* How the decode entry points bring pages into shared memory. By default the
- * INT8 kernel (symmetric pools in the standard layout) uses TMA tile copies issued
+ * INT8 kernel (pools in the standard layout) uses TMA tile copies issued
  * by one lane per warp -- it is instruction-issue bound and gains 14 % -- and the
  * fp16 kernels use per-lane cp.async, which measured 3 % faster on those
  * memory-bound kernels. LS_LOAD_CP_ASYNC / LS_LOAD_TMA force one form (TMA is not
- * available for asymmetric INT8 pools, the CUDA-core variant, or layouts a tensor
- * map cannot describe: the cp.async form runs then). Results are identical. */
+ * available for the CUDA-core variant or for layouts a tensor map cannot describe:
+ * the cp.async form runs then). Results are identical. */
 #define LS_LOAD_CP_ASYNC 0x200
 #define LS_LOAD_TMA 0x400
 /* With LS_LAUNCH_PROGRAMMATIC on the dense entry points (fp16, INT8): also request

@@ -74,7 +74,7 @@ namespace ls {
 constexpr int kWarps = 4;
 // Tensor maps of the TMA-loading variants (unused and zero for the others).
 struct TmaMaps {
-    CUtensorMap k, v, ks;
+    CUtensorMap k, v, ks, kz;
 };
 constexpr int kMbarSpinLimit = 1 << 22;   // probes of an mbarrier phase before a warp gives up
 constexpr int kStages = LS_STAGES;
@@ -700,7 +700,7 @@ struct PoolInt8 {
     }
 };
 
-// INT8 pools (symmetric) loaded by TMA: one lane issues the K tile, the V tile
+// INT8 pools loaded by TMA: one lane issues the K tile, the V tile
 // (tensor maps with the 128-byte swizzle, which is the chunk ^ (row & 7) layout
 // the compute side reads), the block's K scales (a 4 x 128-byte tile, swizzled
 // the same way) and the page's V scales for all heads (one contiguous piece),
@@ -708,10 +708,13 @@ struct PoolInt8 {
 // always hold all 16 rows: rows past the sequence's end are stale pool bytes,
 // which for int8 are finite numbers; their scores are masked and their V scales
 // are replaced by zero on the compute side.
+template <int ASYM>
 struct PoolInt8Tma {
     static constexpr bool kTma = true;
-    static constexpr int STAGE_BYTES = 5120;           // stages stay 1024-byte aligned for the swizzle
-    static constexpr int OFF_V = 2048, OFF_KS = 4096, OFF_VS = 4608, OFF_KZ = 0, OFF_VZ = 0;
+    // K 2 KB | V 2 KB | K scales 512 B | V scales (16 x heads) [| K zeros 512 B | V zeros]; stages
+    // and the two swizzled 512-byte tiles stay 1024-byte aligned.
+    static constexpr int STAGE_BYTES = ASYM ? 6144 : 5120;
+    static constexpr int OFF_V = 2048, OFF_KS = 4096, OFF_VS = 4608, OFF_KZ = 5120, OFF_VZ = 5632;
 
     static __device__ __forceinline__ int issue(const DecodeParams& p, const TmaMaps& maps, int b,
                                                 int h, const PageItem& it, uint32_t stage,
@@ -726,14 +729,17 @@ struct PoolInt8Tma {
                 mbar_arrive(mbar);                     // nothing to load: the phase completes at once
             } else {
                 const uint32_t vs_bytes = 16u * p.heads * sizeof(float);
-                mbar_expect_tx(mbar, 2048u + vs_bytes + (from_res ? 0u : 2048u + 512u));
+                mbar_expect_tx(mbar, 2048u + (ASYM ? 2u : 1u) * vs_bytes +
+                                         (from_res ? 0u : 2048u + (ASYM ? 1024u : 512u)));
                 const uint64_t pol = l2_policy_evict_first();
                 if (!from_res) {
                     tma_load_4d(stage, &maps.k, mbar, 0, h, 0, it.blk, pol);
                     tma_load_4d(stage + OFF_KS, &maps.ks, mbar, 0, 0, h, it.blk, pol);
+                    if (ASYM) tma_load_4d(stage + OFF_KZ, &maps.kz, mbar, 0, 0, h, it.blk, pol);
                 }
                 tma_load_4d(stage + OFF_V, &maps.v, mbar, 0, h, 0, it.blk, pol);
                 bulk_load(stage + OFF_VS, p.v_scale + it.blk * p.vs_b, vs_bytes, mbar);
+                if (ASYM) bulk_load(stage + OFF_VZ, p.v_zero + it.blk * p.vs_b, vs_bytes, mbar);
             }
         }
         return it.valid | (from_res ? 256 : 0);
@@ -763,7 +769,7 @@ __device__ __forceinline__ float lds32f(uint32_t addr) {
 // 2t, 2t+1, 2t+8, 2t+9, and tile mt holds dims 16g + 2mt and 16g + 2mt + 1.
 template <int ASYM, bool TMA = false>
 struct MmaInt8 {
-    using Pool = typename std::conditional<TMA, PoolInt8Tma, PoolInt8<ASYM>>::type;
+    using Pool = typename std::conditional<TMA, PoolInt8Tma<ASYM>, PoolInt8<ASYM>>::type;
     static constexpr int kMinCtas = LS_INT8_CTAS;
     float qf[32];              // Q[row g][32t .. 32t+31] in fp32 (row g < n_rep, else 0)
     float o[8][4];             // O^T: tile mt = dims 16g + 2mt (regs 0,1) and +1 (regs 2,3)
@@ -891,8 +897,14 @@ struct MmaInt8 {
             vs1 = lds32f(stage + Pool::OFF_VS + (g + 8) * 4);
         }
         if (ASYM) {
-            const float vz0 = lds32f(stage + Pool::OFF_VZ + g * 4);
-            const float vz1 = lds32f(stage + Pool::OFF_VZ + (g + 8) * 4);
+            float vz0, vz1;
+            if (TMA) {
+                vz0 = (g < valid) ? lds32f(stage + Pool::OFF_VZ + (g * p.heads + h_) * 4) : 0.f;
+                vz1 = (g + 8 < valid) ? lds32f(stage + Pool::OFF_VZ + ((g + 8) * p.heads + h_) * 4) : 0.f;
+            } else {
+                vz0 = lds32f(stage + Pool::OFF_VZ + g * 4);
+                vz1 = lds32f(stage + Pool::OFF_VZ + (g + 8) * 4);
+            }
             zacc[0] = zacc[0] * a0 + (s[0] * vz0 + s[2] * vz1);
             zacc[1] = zacc[1] * a1 + (s[1] * vz0 + s[3] * vz1);
         }
@@ -1375,6 +1387,10 @@ bool build_int8_maps(const ls::DecodeParams& p, ls::TmaMaps* maps) {
     const cuuint64_t ks_dims[4] = {32, 4, H, nb};
     const cuuint64_t ks_strides[3] = {128, (cuuint64_t)p.ks_h * 4, (cuuint64_t)p.ks_b * 4};
     const cuuint32_t ks_box[4] = {32, 4, 1, 1};
+    if (p.k_zero != nullptr &&
+        ((reinterpret_cast<uintptr_t>(p.v_zero) & 15) ||
+         !encode_4d(&maps->kz, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, p.k_zero, ks_dims, ks_strides, ks_box)))
+        return false;                                  // zero points share the scales' layout
     return encode_4d(&maps->k, CU_TENSOR_MAP_DATA_TYPE_UINT8, p.k_pool, pool_dims, pool_strides, pool_box) &&
            encode_4d(&maps->v, CU_TENSOR_MAP_DATA_TYPE_UINT8, p.v_pool, pool_dims, pool_strides, pool_box) &&
            encode_4d(&maps->ks, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, p.k_scale, ks_dims, ks_strides, ks_box);
@@ -1588,7 +1604,7 @@ static int int8_decode_impl(const int32_t* sel, float ratio, int recent, int num
     const bool pdl = (flags & LS_LAUNCH_PROGRAMMATIC) != 0;
     p.early = (flags & LS_EARLY_PAGES) != 0;
     ls::TmaMaps maps;
-    const bool tma = !k_zero && !(flags & LS_LOAD_CP_ASYNC) && build_int8_maps(p, &maps);
+    const bool tma = !(flags & LS_LOAD_CP_ASYNC) && build_int8_maps(p, &maps);
     if (sel != nullptr) {
         // Attention over the selected pages only (symmetric pools).
         if (k_zero) return LS_ERR_UNSUPPORTED;
@@ -1597,7 +1613,9 @@ static int int8_decode_impl(const int32_t* sel, float ratio, int recent, int num
             return ls::launch_decode<ls::MmaInt8<0, true>, LS_MODE_SPARSE, LS_INT8_TMA_STAGES>(p, s, pdl, &maps);
         return ls::launch_decode<ls::MmaInt8<0>, LS_MODE_SPARSE, LS_INT8_STAGES>(p, s, pdl);
     }
-    if (k_zero)
+    if (k_zero && tma)
+        rc = ls::launch_decode<ls::MmaInt8<1, true>, LS_MODE_DENSE, LS_INT8_TMA_STAGES>(p, s, pdl, &maps);
+    else if (k_zero)
         rc = ls::launch_decode<ls::MmaInt8<1>, LS_MODE_DENSE, LS_INT8_STAGES_ASYM>(p, s, pdl);
     else if (tma)
         rc = ls::launch_decode<ls::MmaInt8<0, true>, LS_MODE_DENSE, LS_INT8_TMA_STAGES>(p, s, pdl, &maps);
