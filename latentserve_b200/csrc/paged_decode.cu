@@ -1,5 +1,5 @@
-// Paged GQA decode attention for B200 (sm_100a): dense fp16, INT8 and
-// page-sparse fp16, plus the log-sum-exp merge of the split partials.
+// Paged GQA decode attention for B200 (sm_100a): dense fp16, dense INT8 and
+// page-sparse (fp16 and INT8), plus the log-sum-exp merge of the split partials.
 //
 // Replaces the reference's one-warp-per-program CUDA-core kernels
 //   kernels/cuda/paged_decode_fp16.cu:55-200   (dense fp16)
@@ -11,11 +11,20 @@
 //   * grid = (chunks, KV heads); a CTA of W warps owns one chunk of the
 //     batch's page axis for one KV head, so every CTA streams the same number
 //     of bytes whatever the sequence lengths are.
-//   * each warp is its own cp.async pipeline over its pages (fp16 page-head =
+//   * each warp is its own load pipeline over its pages (fp16 page-head =
 //     16 K rows + 16 V rows of 256 B): STAGES-deep ring in shared memory, rows
 //     stored with a 16-byte-chunk XOR swizzle so that shared-memory reads are
-//     free of bank conflicts. No warp waits on another warp inside the page
-//     loop, and nothing spins: cp.async groups complete on their own.
+//     free of bank conflicts. Two load sides fill the same tiles: per-lane
+//     cp.async (groups complete on their own, nothing spins), and TMA tile
+//     copies issued by one lane (tensor maps with the 128-byte swizzle,
+//     completion counted on an mbarrier per stage, waits bounded). The INT8
+//     kernel is instruction-issue bound and uses TMA by default; the fp16
+//     kernels are memory bound and use cp.async. No warp waits on another warp
+//     inside the page loop.
+//   * with programmatic dependent launch the prologue (prefix sums, block ids)
+//     and, on request, the first page requests run before the kernel
+//     synchronises on its predecessor: everything but a sequence's last page
+//     is immutable between decode steps.
 //   * all query heads of the GQA group share each page load: scores are
 //     S[16 tokens x 8 rows] = K_page . Q^T on the tensor cores (m16n8k16,
 //     fp32 accumulation), the page's weights are transposed in registers
@@ -27,8 +36,9 @@
 //     is folded into the query once per page, V's per-token scale into the
 //     softmax weight, so neither pool is ever dequantised element by element.
 //   * rows past a sequence's end are zero-filled on the way in (cp.async with
-//     a zero source size) and their scores forced to -inf: stale pool bytes,
-//     NaN patterns included, never reach the arithmetic.
+//     a zero source size; the TMA variants clear or neutralise them after
+//     arrival) and their scores forced to -inf: stale pool bytes, NaN patterns
+//     included, never reach the arithmetic.
 //   * at the end of a segment the CTA's warps merge their states through
 //     shared memory and write ONE partial (m, l, acc) per (chunk, sequence,
 //     head); every slot a sequence owns is written, so nothing is pre-filled.
