@@ -80,6 +80,13 @@ __device__ __forceinline__ void cp_async_16_stream(uint32_t dst, const void* src
                  : "memory");
 }
 
+// 8-byte copy with zero-fill: `src_bytes` (0 or 8) are read, the rest of the 8 are zeros.
+__device__ __forceinline__ void cp_async_8(uint32_t dst, const void* src, int src_bytes) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 8, %2;\n" ::"r"(dst), "l"(src),
+                 "r"(src_bytes)
+                 : "memory");
+}
+
 // 4-byte asynchronous copy (scalars such as a per-token V scale).
 __device__ __forceinline__ void cp_async_4(uint32_t dst, const void* src, int src_bytes) {
     asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;\n" ::"r"(dst), "l"(src),

@@ -26,8 +26,15 @@ namespace ls {
 
 constexpr int kIndexWarps = 4;
 constexpr int kGroup = 4;                    // pages reduced together
-constexpr int kGroupsPerWarp = 4;
-constexpr int kPagesPerWarp = kGroup * kGroupsPerWarp;
+constexpr int kItemGroups = 2;               // groups per pipelined item
+constexpr int kItemPages = kGroup * kItemGroups;
+constexpr int kMaxItems = 3;                 // items a warp stages at once (its span / 8)
+constexpr int kItemBytes = kItemPages * 512; // a page's minimum and maximum rows, 256 bytes each
+static_assert(kMaxItems == 3, "page_index_kernel writes out its three waits");
+#ifndef LS_INDEX_CTAS
+#define LS_INDEX_CTAS 4
+#endif
+constexpr int kIndexCtasPerSm = LS_INDEX_CTAS;   // resident CTAs of the index kernel (registers, 48 KB each)
 
 __device__ __forceinline__ void unpack4h(uint2 raw, float (&f)[4]) {
     const __half2* h2 = reinterpret_cast<const __half2*>(&raw);
@@ -93,36 +100,62 @@ __device__ __forceinline__ float bounds_4x8(const f32x2 (&qp)[4][4], const f32x2
     return e[0];
 }
 
-// grid (ceil(max_pages / 64), H, B), block 128: a warp scores 16 pages, four
-// groups of four.
+// grid (ceil(max_pages / (4 * span)), H, B), block 128: a warp scores `span`
+// consecutive pages (8, 16 or 24) of one (sequence, KV head) in items of eight.
+// All of the warp's bounds are requested at once with 8-byte cp.async copies into
+// the warp's own shared memory, one commit group per item, and each item is
+// reduced as soon as its group has landed: one DRAM round trip per warp, and the
+// bounds wait in shared memory instead of 64 registers, which is what lets four
+// CTAs share an SM. Every lane reads back exactly the bytes it copied, so the
+// wait on its own groups is the only synchronisation. The host sizes `span` so
+// that the whole grid is resident at once where the problem allows it.
 // PER_HEAD = 0: scores [B,H,P]; PER_HEAD = 1: heads [B,H,R,P].
 template <int PER_HEAD>
-__global__ void __launch_bounds__(kIndexWarps * 32)
+__global__ void __launch_bounds__(kIndexWarps * 32, kIndexCtasPerSm)
 page_index_kernel(const __half* __restrict__ q, const __half* __restrict__ kmin,
                   const __half* __restrict__ kmax, const int* __restrict__ block_tables,
                   const int* __restrict__ seq_lens, float* __restrict__ out, int n_rep,
-                  int max_pages, int table_stride, int num_blocks, int recent, long long sq_b,
-                  long long sq_h, long long sq_m, long long sb_b, long long sb_h, long long ss_b,
-                  long long ss_h, long long ss_r) {
+                  int max_pages, int span, int table_stride, int num_blocks, int recent,
+                  long long sq_b, long long sq_h, long long sq_m, long long sb_b, long long sb_h,
+                  long long ss_b, long long ss_h, long long ss_r) {
+    __shared__ __align__(16) unsigned char staged[kIndexWarps][kMaxItems][kItemBytes];
     asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");   // a programmatic successor may start its prologue
     const int b = blockIdx.z, h = blockIdx.y;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int first = (blockIdx.x * kIndexWarps + warp) * kPagesPerWarp;
+    const int first = (blockIdx.x * kIndexWarps + warp) * span;
     if (first >= max_pages) return;
+    const int end = min(first + span, max_pages);
+    const int items = (end - first + kItemPages - 1) / kItemPages;
     const int L = max(seq_lens[b], 0);
     const int np = min((L + LS_PAGE - 1) / LS_PAGE, table_stride);
 
-    // Lane j < 16 fetches the block id of page first + j (-1: nothing to score).
-    int my_blk = -1;
+    // Lane j fetches the block id of page first + j (-1: nothing to score).
+    int ids = -1;
     {
         const int p = first + lane;
-        bool need = lane < kPagesPerWarp && p < max_pages && p < np;
+        bool need = p < end && p < np;
         if (!PER_HEAD) need = need && !(p == 0 || p >= np - recent);
         if (need) {
             const int id = block_tables[(long long)b * table_stride + p];
-            if (id >= 0 && id < num_blocks) my_blk = id;
+            if (id >= 0 && id < num_blocks) ids = id;
         }
     }
+    const uint32_t mine = smem_u32(&staged[warp][0][0]) + lane * 8;
+#pragma unroll
+    for (int it = 0; it < kMaxItems; ++it) {
+        if (it < items) {
+#pragma unroll
+            for (int k = 0; k < kItemPages; ++k) {
+                const int blk = __shfl_sync(LS_FULL_MASK, ids, it * kItemPages + k);
+                const long long off = blk >= 0 ? blk * sb_b + h * sb_h + lane * 4 : 0;
+                const uint32_t dst = mine + it * kItemBytes + k * 512;
+                cp_async_8(dst, kmin + off, blk >= 0 ? 8 : 0);          // an unscored page reads as zeros
+                cp_async_8(dst + 256, kmax + off, blk >= 0 ? 8 : 0);
+            }
+        }
+        cp_async_commit();
+    }
+
     // q+ and q- of rows (2 rp, 2 rp + 1), channel j, packed; rows past n_rep are zero.
     f32x2 qp[4][4], qn[4][4];
 #pragma unroll
@@ -140,41 +173,43 @@ page_index_kernel(const __half* __restrict__ q, const __half* __restrict__ kmin,
         }
     }
 
-    auto fetch = [&](int g, uint2 (&lo_raw)[kGroup], uint2 (&hi_raw)[kGroup]) {
+    // Reduces group g of item `it` and writes its scores.
+    auto reduce = [&](int it, int g) {
+        uint2 lo_raw[kGroup], hi_raw[kGroup];
+        const unsigned char* src = &staged[warp][it][g * kGroup * 512 + lane * 8];
 #pragma unroll
         for (int k = 0; k < kGroup; ++k) {
-            const int blk = __shfl_sync(LS_FULL_MASK, my_blk, g * kGroup + k);
-            lo_raw[k] = make_uint2(0, 0);
-            hi_raw[k] = make_uint2(0, 0);
-            if (blk >= 0) {
-                lo_raw[k] = *reinterpret_cast<const uint2*>(kmin + blk * sb_b + h * sb_h + lane * 4);
-                hi_raw[k] = *reinterpret_cast<const uint2*>(kmax + blk * sb_b + h * sb_h + lane * 4);
-            }
+            lo_raw[k] = *reinterpret_cast<const uint2*>(src + k * 512);
+            hi_raw[k] = *reinterpret_cast<const uint2*>(src + k * 512 + 256);
         }
-    };
-    // Every page's bounds are requested before anything is reduced: one DRAM
-    // round trip for the warp's 16 pages.
-    uint2 lo_all[kGroupsPerWarp][kGroup], hi_all[kGroupsPerWarp][kGroup];
-#pragma unroll
-    for (int g = 0; g < kGroupsPerWarp; ++g) fetch(g, lo_all[g], hi_all[g]);
-#pragma unroll
-    for (int g = 0; g < kGroupsPerWarp; ++g) {
-        float s = bounds_4x8(qp, qn, n_rep, lo_all[g], hi_all[g], lane);
-        const int p = first + g * kGroup + (lane >> 3), r = lane & 7;
-        const int blk = __shfl_sync(LS_FULL_MASK, my_blk, g * kGroup + (lane >> 3));
+        float s = bounds_4x8(qp, qn, n_rep, lo_raw, hi_raw, lane);
+        const int slot = it * kItemPages + g * kGroup + (lane >> 3);
+        const int p = first + slot, r = lane & 7;
+        const int blk = __shfl_sync(LS_FULL_MASK, ids, slot);
         if (PER_HEAD) {
             // Pages past the end get a finite 0: their token count of zero
             // removes them downstream, and a stale NaN here would not.
-            if (p < max_pages && r < n_rep) out[b * ss_b + h * ss_h + r * ss_r + p] = blk >= 0 ? s : 0.f;
+            if (p < end && r < n_rep) out[b * ss_b + h * ss_h + r * ss_r + p] = blk >= 0 ? s : 0.f;
         } else {
             if (r >= n_rep || blk < 0) s = neg_inf();
 #pragma unroll
             for (int off = 1; off < 8; off <<= 1) s = fmaxf(s, __shfl_xor_sync(LS_FULL_MASK, s, off));
             if (p >= np) s = neg_inf();                                  // past the end: never chosen
             else if (p == 0 || p >= np - recent) s = pos_inf();          // sink and recent: always kept
-            if (r == 0 && p < max_pages) out[b * ss_b + h * ss_h + p] = s;
+            if (r == 0 && p < end) out[b * ss_b + h * ss_h + p] = s;
         }
-    }
+    };
+    cp_async_wait<kMaxItems - 1>();
+#pragma unroll
+    for (int g = 0; g < kItemGroups; ++g) reduce(0, g);
+    if (items < 2) return;
+    cp_async_wait<kMaxItems - 2>();
+#pragma unroll
+    for (int g = 0; g < kItemGroups; ++g) reduce(1, g);
+    if (items < 3) return;
+    cp_async_wait<0>();
+#pragma unroll
+    for (int g = 0; g < kItemGroups; ++g) reduce(2, g);
 }
 
 // Monotone map from fp32 to uint32: a > b as floats <=> key(a) > key(b).
@@ -433,16 +468,40 @@ static int launch_index(int per_head, const void* q, const void* kmin, const voi
     if (batch > 65535 || kv_heads > 65535) return LS_ERR_TOO_LARGE;
     if ((sq_b % 4) || (sq_h % 4) || (sq_m % 4) || (sb_b % 4) || (sb_h % 4)) return LS_ERR_MISALIGNED;
     if (((uintptr_t)q & 7) || ((uintptr_t)kmin & 7) || ((uintptr_t)kmax & 7)) return LS_ERR_MISALIGNED;
-    const int per_cta = ls::kIndexWarps * ls::kPagesPerWarp;
+    // Pages per warp: the smallest number of items that lets every CTA of the grid
+    // be resident at once (no second wave), capped by what a warp can stage.
+    static int sms_of[64] = {0};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    int sms = dev >= 0 && dev < 64 ? sms_of[dev] : 0;
+    if (sms <= 0) {
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+        if (sms <= 0) sms = 1;
+        if (dev >= 0 && dev < 64) sms_of[dev] = sms;
+    }
+    const long long resident = (long long)ls::kIndexCtasPerSm * sms;
+    int span = ls::kItemPages;
+    for (int items = 1; items <= ls::kMaxItems; ++items) {
+        span = items * ls::kItemPages;
+        const long long per_row = (max_pages + ls::kIndexWarps * span - 1) / (ls::kIndexWarps * span);
+        if (per_row * kv_heads * batch <= resident) break;
+    }
+    const int per_cta = ls::kIndexWarps * span;
     dim3 grid((max_pages + per_cta - 1) / per_cta, kv_heads, batch);
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     // Plain launches: starting these two kernels ahead of their predecessor's end
     // (programmatic launch) was measured and made the select + attend sequence slower.
     auto kern = per_head ? ls::page_index_kernel<1> : ls::page_index_kernel<0>;
+    static bool carveout_set[64][2] = {};
+    const int slot = dev >= 0 && dev < 64 ? dev : 0;
+    if (!carveout_set[slot][per_head ? 1 : 0]) {    // four 48 KB CTAs per SM need the large shared-memory split
+        cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+        carveout_set[slot][per_head ? 1 : 0] = dev >= 0 && dev < 64;
+    }
     kern<<<grid, ls::kIndexWarps * 32, 0, s>>>(
         static_cast<const __half*>(q), static_cast<const __half*>(kmin), static_cast<const __half*>(kmax),
-        block_tables, seq_lens, out, n_rep, max_pages, table_stride, num_blocks, recent, sq_b, sq_h, sq_m,
-        sb_b, sb_h, ss_b, ss_h, ss_r);
+        block_tables, seq_lens, out, n_rep, max_pages, span, table_stride, num_blocks, recent, sq_b, sq_h,
+        sq_m, sb_b, sb_h, ss_b, ss_h, ss_r);
     return (int)cudaGetLastError();
 }
 
