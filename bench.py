@@ -215,8 +215,9 @@ def main():
                          "measured 1.7 %% faster)")
     ap.add_argument("--no-early", action="store_true",
                     help="with programmatic launch: do not request old pages ahead of the dependency wait")
-    ap.add_argument("--projections", default="cublas", choices=["ls", "cublas"],
-                    help="decode-step workloads: this library's weight-streaming projections, or torch GEMMs")
+    ap.add_argument("--projections", default="auto", choices=["auto", "ls", "cublas"],
+                    help="decode-step workloads: this library's weight-streaming projections, torch GEMMs, "
+                         "or (auto) the former up to 16 rows")
     ap.add_argument("--quick", action="store_true",
                     help="profiler runs: no e2e / CPU legs, no extension of the load for clock sampling")
     args = ap.parse_args()
@@ -591,7 +592,7 @@ def run_model_step(args):
                        "kv_cache": kind, "sparse_ratio": ratio, "shared_prefix_tokens": prefix,
                        "sequences_sharing_prefix": len(owners),
                        "layers": shape.num_layers, "programmatic_launch": not args.no_pdl,
-                       "projections": args.projections if batch <= 64 else "cublas",
+                       "projections": "ls" if model.streams_projections(batch) else "cublas",
                        "early_pages": not (args.no_pdl or args.no_early), "loader": args.loader or "tma",
                        "parallelism": f"replicas x{world} (sequence-sharded, no collective)"},
             "graph_replay_ms": round(graph_ms, 4),

@@ -99,7 +99,9 @@ __device__ __forceinline__ void sts128g(uint32_t addr, uint4 v) {
 
 __device__ __forceinline__ float round_h(float f) { return __half2float(__float2half_rn(f)); }
 
-// s = fp16(x + r), eight at a time.
+// s = fp16(fp32(x) + fp32(r)), eight at a time: the fp32 sum is rounded first, as
+// in the separate residual + norm kernel (an fp16 add would round once and could
+// differ on a tie).
 __device__ __forceinline__ uint4 add8(uint4 a, uint4 b) {
     uint4 o;
     const __half2* ah = reinterpret_cast<const __half2*>(&a);
@@ -113,17 +115,34 @@ __device__ __forceinline__ uint4 add8(uint4 a, uint4 b) {
     return o;
 }
 
-// y = fp16(gamma * fp16(s * inv)), eight at a time.
-__device__ __forceinline__ uint4 norm8(uint4 s, uint4 gamma, float inv) {
+// RMSNorm is x * inv_rms(row) * gamma, and the row factor commutes with the
+// product: (x * inv * gamma) W^T = inv * ((x * gamma) W^T). So the A operand is
+// fp16(x * gamma * 2^-8) -- available as soon as x is, without waiting for the
+// row statistics -- and the epilogue multiplies the fp32 sums by inv * 2^8. The
+// fixed 2^-8 keeps x * gamma inside fp16 for un-normalised activations up to
+// 1.6e7 (a residual stream's outlier channels reach thousands); what it pushes
+// into the subnormal range keeps an absolute error of 2^-25 * 2^8, below the
+// rounding error of any element of ordinary size.
+constexpr float kPreScale = 1.f / 256.f, kPostScale = 256.f;
+// gamma * 2^-8, exact in fp16 for |gamma| >= 2^-6 (smaller weights keep an absolute error
+// below 2^-17).
+__device__ __forceinline__ uint4 prescale8(uint4 gamma) {
+    uint4 o;
+    const __half2* gh = reinterpret_cast<const __half2*>(&gamma);
+    __half2* oh = reinterpret_cast<__half2*>(&o);
+    const __half2 c = __floats2half2_rn(kPreScale, kPreScale);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) oh[i] = __hmul2(gh[i], c);
+    return o;
+}
+// fp16(x * gamma'), eight at a time: one rounding of the exact product.
+__device__ __forceinline__ uint4 scale8(uint4 s, uint4 gamma_scaled) {
     uint4 o;
     const __half2* sh = reinterpret_cast<const __half2*>(&s);
-    const __half2* gh = reinterpret_cast<const __half2*>(&gamma);
-    uint32_t* oo = reinterpret_cast<uint32_t*>(&o);
+    const __half2* gh = reinterpret_cast<const __half2*>(&gamma_scaled);
+    __half2* oh = reinterpret_cast<__half2*>(&o);
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        const float2 fs = __half22float2(sh[i]), fg = __half22float2(gh[i]);
-        oo[i] = pack_half2(fg.x * round_h(fs.x * inv), fg.y * round_h(fs.y * inv));
-    }
+    for (int i = 0; i < 4; ++i) oh[i] = __hmul2(sh[i], gh[i]);
     return o;
 }
 
@@ -168,7 +187,6 @@ __global__ void __launch_bounds__(kGemmThreads, MT == 1 ? 2 : 1) skinny_gemm_ker
     const int c_end = min(chunks, c_begin + per_split);
     const uint32_t ring = smem_u32(smem_raw) + warp * (kRing * 2048) + lane * 16;
     float* red = reinterpret_cast<float*>(smem_raw + kGemmWarps * kRing * 2048);
-    float* ssq_part = red;              // [kGemmThreads], used before the first reduction only
     const int n_tiles = p.n / kTileRows;
     // Chunks of a tile's slice this warp takes: c_begin + warp + 8 i, i < cpw <= kMaxCpw.
     const int cpw = max(0, (c_end - c_begin - warp + kGemmWarps - 1) / kGemmWarps);
@@ -210,9 +228,24 @@ __global__ void __launch_bounds__(kGemmThreads, MT == 1 ? 2 : 1) skinny_gemm_ker
     // Everything below reads what the previous kernel wrote.
     asm volatile("griddepcontrol.wait;\n" ::: "memory");
 
+    // Row sums of squares left by the kernel that produced x (one partial per 32
+    // columns): a warp takes ROWS / 8 rows, 256 / ROWS lanes per row take strided
+    // shares. Requested here so that they travel together with the activations.
+    constexpr int LPR = kGemmThreads / ROWS;                 // lanes per row: 16 or 8
+    const int st_row = warp * (ROWS / kGemmWarps) + lane / LPR, st_part = lane % LPR;
+    float st[4] = {0.f, 0.f, 0.f, 0.f};
+    if (PRO == PRO_NORM && p.sumsq_in != nullptr) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int i = st_part + j * LPR;
+            if (i < p.sumsq_tiles) st[j] = __ldcg(p.sumsq_in + i * 64 + st_row);
+        }
+    }
+
     // This lane's A fragments for the warp's chunks (rows g, g + 8 of each 16-row tile, 16
-    // bytes at 8 t), requested first so that they travel together with the statistics below.
+    // bytes at 8 t).
     uint4 areg[kMaxCpw][MT][2];
+    uint4 gam[PRO == PRO_NORM ? kMaxCpw : 1];
 #pragma unroll
     for (int ci = 0; ci < kMaxCpw; ++ci) {
         if (ci < cpw) {
@@ -226,6 +259,21 @@ __global__ void __launch_bounds__(kGemmThreads, MT == 1 ? 2 : 1) skinny_gemm_ker
                     if (PRO == PRO_NORM && p.res != nullptr) a = add8(a, ldg_l2(p.res + rr * p.sres + k));
                     areg[ci][mt][hh] = a;
                 }
+            if (PRO == PRO_NORM) gam[ci] = *reinterpret_cast<const uint4*>(p.gamma + k);
+        }
+    }
+    // Applied in a second pass so that every request above is in flight before the
+    // first one is waited for.
+    if (PRO == PRO_NORM) {
+#pragma unroll
+        for (int ci = 0; ci < kMaxCpw; ++ci) {
+            if (ci < cpw) {
+                const uint4 gs = prescale8(gam[ci]);
+#pragma unroll
+                for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+                    for (int hh = 0; hh < 2; ++hh) areg[ci][mt][hh] = scale8(areg[ci][mt][hh], gs);
+            }
         }
     }
 
@@ -267,45 +315,15 @@ __global__ void __launch_bounds__(kGemmThreads, MT == 1 ? 2 : 1) skinny_gemm_ker
         }
         __syncthreads();
     } else if (PRO == PRO_NORM) {
-        // Row sums of squares left by the kernel that produced x (one partial per 32
-        // columns): 256 / ROWS threads per row take strided shares, then the shares in order.
-        constexpr int PARTS = kGemmThreads / ROWS;
-        const int row = tid % ROWS, part = tid / ROWS;
-        float acc = 0.f;
-        for (int i0 = part; i0 < p.sumsq_tiles; i0 += 4 * PARTS) {
-            float v[4];
+        // The shares requested above, the rest of a long row, and a shuffle tree. Nobody
+        // waits for the result here: the epilogue reads inv_rms after the tile loop's
+        // first barrier.
+        float acc = (st[0] + st[1]) + (st[2] + st[3]);
+        for (int i = st_part + 4 * LPR; i < p.sumsq_tiles; i += LPR)
+            acc += __ldcg(p.sumsq_in + i * 64 + st_row);
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                const int i = i0 + j * PARTS;
-                v[j] = (i < p.sumsq_tiles) ? __ldcg(p.sumsq_in + i * 64 + row) : 0.f;
-            }
-            acc += (v[0] + v[1]) + (v[2] + v[3]);
-        }
-        ssq_part[part * ROWS + row] = acc;
-        __syncthreads();
-        if (tid < ROWS) {
-            float total = 0.f;
-#pragma unroll
-            for (int q = 0; q < PARTS; ++q) total += ssq_part[q * ROWS + tid];
-            inv_rms[tid] = rsqrtf(total / (float)p.k + p.eps);
-        }
-        __syncthreads();
-    }
-
-    // Normalise the fragments once the row statistics are there: they are the same for every tile.
-    if (PRO == PRO_NORM) {
-#pragma unroll
-        for (int ci = 0; ci < kMaxCpw; ++ci) {
-            if (ci < cpw) {
-                const uint4 gam =
-                    *reinterpret_cast<const uint4*>(p.gamma + 32 * (c_begin + warp + kGemmWarps * ci) + 8 * t);
-#pragma unroll
-                for (int mt = 0; mt < MT; ++mt)
-#pragma unroll
-                    for (int hh = 0; hh < 2; ++hh)
-                        areg[ci][mt][hh] = norm8(areg[ci][mt][hh], gam, inv_rms[mt * 16 + hh * 8 + g]);
-            }
-        }
+        for (int off = LPR / 2; off > 0; off >>= 1) acc += __shfl_xor_sync(LS_FULL_MASK, acc, off);
+        if (st_part == 0) inv_rms[st_row] = rsqrtf(acc / (float)p.k + p.eps);
     }
 
     int slot = 0;
@@ -408,8 +426,9 @@ __global__ void __launch_bounds__(kGemmThreads, MT == 1 ? 2 : 1) skinny_gemm_ker
             for (int e = tid; e < ROWS * 16; e += kGemmThreads) {
                 const int row = e >> 4, j = e & 15;
                 if (row >= p.m) continue;
-                const float gate = round_h(red[row * 32 + j]);
-                const float up = round_h(red[row * 32 + 16 + j]);
+                const float f = (PRO == PRO_NORM) ? inv_rms[row] * kPostScale : 1.f;
+                const float gate = round_h(red[row * 32 + j] * f);
+                const float up = round_h(red[row * 32 + 16 + j] * f);
                 const float act = round_h(gate / (1.f + expf(-gate)));
                 p.out[row * p.sout + tile * 16 + j] = __float2half_rn(act * up);
             }
@@ -419,7 +438,8 @@ __global__ void __launch_bounds__(kGemmThreads, MT == 1 ? 2 : 1) skinny_gemm_ker
             for (int j = 0; j < EPT; ++j) {
                 const int e = tid + j * kGemmThreads;
                 const int row = e >> 5, col = tile * kTileRows + (e & 31);
-                float v = round_h(red[e] + pre_bias);
+                const float f = (PRO == PRO_NORM) ? inv_rms[row] * kPostScale : 1.f;
+                float v = round_h(red[e] * f + pre_bias);
                 if (p.add_res != nullptr) v = round_h(v + pre_res[j]);
                 if (row < p.m) p.out[row * p.sout + col] = __float2half_rn(v);
                 if (p.sumsq_out != nullptr) {

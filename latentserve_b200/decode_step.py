@@ -11,15 +11,16 @@ append and attention kernels inside a step of the same shape: dense
 projections and the MLP are plain cuBLAS GEMMs through torch, weights are
 random (N(0, 0.02), fp16).
 
-Per layer, in stream order, with `projections="cublas"` (the default; nine
-launches): [residual add +] RMSNorm -> fused QKV GEMM (+ bias) -> RoPE(q, k) +
-KV append (one launch) -> paged decode attention (one launch; dense, INT8 or
+Per layer, in stream order, with `projections="cublas"` (nine launches):
+[residual add +] RMSNorm -> fused QKV GEMM (+ bias) -> RoPE(q, k) + KV append
+(one launch) -> paged decode attention (one launch; dense, INT8 or
 page-sparse) -> o_proj GEMM -> residual add + RMSNorm -> gate/up GEMM ->
 SiLU * up -> down GEMM, the GEMMs being torch's. With `projections="ls"` the
 projections are this library's weight-streaming kernel (`projections.linear`)
-with the norms, residual adds and SiLU * up folded into them (six launches);
-at batch 16 it is faster than cuBLAS on down_proj only and slower on the
-others, so it is not the default. With
+with the norms, residual adds and SiLU * up folded into them (six launches):
+about 3 % faster per step than the cuBLAS route at batch 16, slower between 17
+and 32 rows, not available beyond. `projections="auto"` (the default) takes the
+streaming kernel up to 16 rows and cuBLAS above. With
 `fused=False` the norms, RoPE and SwiGLU are plain torch element-wise ops and
 the append is `cache.write` (the form the fused ones are tested against).
 `cache.advance(1)` runs on the host before the step and is not part of a
@@ -80,10 +81,10 @@ class DecodeModel:
     """Random-init weights of the given shape and the decode step over a cache."""
 
     def __init__(self, shape: QwenShape, device, max_pos: int, seed: int = 0,
-                 dtype: torch.dtype = torch.float16, fused: bool = True, projections: str = "cublas"):
+                 dtype: torch.dtype = torch.float16, fused: bool = True, projections: str = "auto"):
         self.shape, self.device, self.dtype = shape, torch.device(device), dtype
         self.fused = fused
-        if projections not in ("ls", "cublas"):
+        if projections not in ("auto", "ls", "cublas"):
             raise ValueError(f"unknown projections {projections!r}")
         self.projections = projections
         g = torch.Generator(device=self.device).manual_seed(seed)
@@ -133,12 +134,18 @@ class DecodeModel:
         return pd.paged_decode_attention(q, cache.k_pool[layer], cache.v_pool[layer], tables, lens,
                                          max_seq_len=context_hint, **extra)
 
+    def streams_projections(self, rows: int) -> bool:
+        """Whether a step of `rows` sequences uses `projections.linear` (else torch GEMMs)."""
+        if self.projections == "ls":
+            return rows <= pj.MAX_ROWS
+        return self.projections == "auto" and rows <= 16
+
     def forward(self, cache, tokens: torch.Tensor, positions: torch.Tensor,
                 context_hint: int, return_logits: bool = False) -> torch.Tensor:
         """tokens, positions [B] (device) -> next token ids [B] (greedy), or the
         logits [B, vocab]. The cache must have been advanced by one token for
         these B sequences."""
-        if self.fused and self.projections == "ls" and tokens.shape[0] <= pj.MAX_ROWS:
+        if self.fused and self.streams_projections(tokens.shape[0]):
             return self._forward_streamed(cache, tokens, positions, context_hint, return_logits)
         if self.fused:
             return self._forward_fused(cache, tokens, positions, context_hint, return_logits)
