@@ -119,7 +119,6 @@ page_index_kernel(const __half* __restrict__ q, const __half* __restrict__ kmin,
                   long long sq_b, long long sq_h, long long sq_m, long long sb_b, long long sb_h,
                   long long ss_b, long long ss_h, long long ss_r) {
     __shared__ __align__(16) unsigned char staged[kIndexWarps][kMaxItems][kItemBytes];
-    asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");   // a programmatic successor may start its prologue
     const int b = blockIdx.z, h = blockIdx.y;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int first = (blockIdx.x * kIndexWarps + warp) * span;
@@ -210,6 +209,9 @@ page_index_kernel(const __half* __restrict__ q, const __half* __restrict__ kmin,
     cp_async_wait<0>();
 #pragma unroll
     for (int g = 0; g < kItemGroups; ++g) reduce(2, g);
+    // No early trigger for a programmatic successor: a CTA that has returned counts as
+    // having triggered, so the selection kernel's CTAs arrive while the last warps here
+    // finish and never hold SM slots this kernel's single wave needs.
 }
 
 // Monotone map from fp32 to uint32: a > b as floats <=> key(a) > key(b).
@@ -328,6 +330,9 @@ select_pages_kernel(const float* __restrict__ scores, const int* __restrict__ se
     if (ratio > 0.f && ratio < 1.f) want = max(recent + 1, (int)ceilf(ratio * (float)np));
     const int n_keep = min(min(want, np), min(k, n));
 
+    // Launched programmatically: everything above overlapped the end of the kernel
+    // that writes the scores.
+    asm volatile("griddepcontrol.wait;\n" ::: "memory");
     unsigned key[E];
     if ((n & 3) == 0 && ((reinterpret_cast<uintptr_t>(row) & 15) == 0)) {
 #pragma unroll
@@ -489,8 +494,8 @@ static int launch_index(int per_head, const void* q, const void* kmin, const voi
     const int per_cta = ls::kIndexWarps * span;
     dim3 grid((max_pages + per_cta - 1) / per_cta, kv_heads, batch);
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    // Plain launches: starting these two kernels ahead of their predecessor's end
-    // (programmatic launch) was measured and made the select + attend sequence slower.
+    // A plain launch: starting this kernel ahead of its predecessor's end (programmatic
+    // launch) was measured and left the index -> select -> attend sequence unchanged.
     auto kern = per_head ? ls::page_index_kernel<1> : ls::page_index_kernel<0>;
     static bool carveout_set[64][2] = {};
     const int slot = dev >= 0 && dev < 64 ? dev : 0;
@@ -569,13 +574,27 @@ int ls_select_pages(const float* scores, const int32_t* seq_lens, int32_t* sel, 
     if (((uintptr_t)scores & 3) || ((uintptr_t)sel & 3)) return LS_ERR_MISALIGNED;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const int grid = batch * kv_heads;
+    // A programmatic launch: the CTAs may become resident while the kernel that writes
+    // the scores drains (they wait for it before reading); after a kernel that never
+    // triggers early this is an ordinary launch.
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(grid);
+    cfg.blockDim = dim3(ls::kSelectThreads);
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    const long long a_ss_b = ss_b, a_ss_h = ss_h, a_sl_b = sl_b, a_sl_h = sl_h;
+    cudaError_t e;
     if (num_pages <= 4 * ls::kSelectThreads)
-        ls::select_pages_kernel<4><<<grid, ls::kSelectThreads, 0, st>>>(
-            scores, seq_lens, sel, num_pages, k, kv_heads, ratio, recent, ss_b, ss_h, sl_b, sl_h);
+        e = cudaLaunchKernelEx(&cfg, ls::select_pages_kernel<4>, scores, seq_lens, sel, num_pages, k,
+                               kv_heads, ratio, recent, a_ss_b, a_ss_h, a_sl_b, a_sl_h);
     else
-        ls::select_pages_kernel<16><<<grid, ls::kSelectThreads, 0, st>>>(
-            scores, seq_lens, sel, num_pages, k, kv_heads, ratio, recent, ss_b, ss_h, sl_b, sl_h);
-    return (int)cudaGetLastError();
+        e = cudaLaunchKernelEx(&cfg, ls::select_pages_kernel<16>, scores, seq_lens, sel, num_pages, k,
+                               kv_heads, ratio, recent, a_ss_b, a_ss_h, a_sl_b, a_sl_h);
+    return e != cudaSuccess ? (int)e : (int)cudaGetLastError();
 }
 
 }  // extern "C"
