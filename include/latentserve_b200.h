@@ -342,8 +342,9 @@ int ls_rope_append_int8(const void* qkv, const void* cos, const void* sin, const
  *   mode & LS_LAUNCH_PROGRAMMATIC: the first weight loads are issued before the
  *       kernel synchronises on the previous kernel of the stream.
  *   add_res (no SWIGLU): out = fp16(fp16(product + bias) + add_res[m, n]), the residual
- *       add that follows o_proj / down_proj; with sumsq_out ([n / 32][64] floats) each
- *       tile also leaves the per-row sums of out^2 over its 32 columns, which a later
+ *       add that follows o_proj / down_proj; with sumsq_out ([64][n / 32] floats, a
+ *       row's partials contiguous) each tile also leaves the per-row sums of out^2
+ *       over its 32 columns, which a later
  *       LS_GEMM_NORM call takes as sumsq_in (+ sumsq_tiles = n / 32 of THAT call, its
  *       k / 32) instead of reading whole rows for its statistics (res must then be NULL).
  * k is cut into `splits` slices across CTAs (grid = n / 32 tiles x splits; pick

@@ -57,11 +57,11 @@ struct GemmParams {
     const __half* res;      // [M, K] added to x before the norm, or null (PRO_NORM)
     const __half* gamma;    // [K] (PRO_NORM)
     __half* res_out;        // [M, K] <- x + res when res is given
-    const float* sumsq_in;  // [sumsq_tiles][64] per-row partial sums of x^2, or null (PRO_NORM)
+    const float* sumsq_in;  // [64][sumsq_tiles] per-row partial sums of x^2, or null (PRO_NORM)
     const __half* w;        // [N, K]
     const __half* bias;     // [N] or null
     const __half* add_res;  // [M, N] added to the rounded product (EPI_NONE), or null
-    float* sumsq_out;       // [tiles][64] <- per-row sums of out^2 over the tile's 32 columns, or null
+    float* sumsq_out;       // [64][tiles] <- per-row sums of out^2 over the tile's 32 columns, or null
     __half* out;            // [M, N], or [M, N / 2] with EPI_SWIGLU
     float* part;            // [tiles * splits][M_pad * 32] fp32, splits > 1
     int* counters;          // [tiles], zero before first use, left at zero
@@ -164,6 +164,9 @@ __host__ __device__ inline int a_stride_halves(int slice_k) {
     return slice_k + ((slice_k % 64 == 0) ? 32 : 0);
 }
 
+#ifndef LS_GEMM_CONTIG
+#define LS_GEMM_CONTIG 1
+#endif
 constexpr int kRing = 6;                // chunks of W a warp keeps in flight (2 KB each)
 constexpr int kMaxCpw = 6;              // chunks of a tile a warp may own (its A fragments stay in registers)
 
@@ -188,8 +191,19 @@ __global__ void __launch_bounds__(kGemmThreads, MT == 1 ? 2 : 1) skinny_gemm_ker
     const uint32_t ring = smem_u32(smem_raw) + warp * (kRing * 2048) + lane * 16;
     float* red = reinterpret_cast<float*>(smem_raw + kGemmWarps * kRing * 2048);
     const int n_tiles = p.n / kTileRows;
+#if LS_GEMM_CONTIG
+    // Chunks of a tile's slice this warp takes: cpw <= kMaxCpw consecutive ones from
+    // w_first, so the warp's back-to-back requests walk along each row of W.
+    const int c_share = (c_end - c_begin + kGemmWarps - 1) / kGemmWarps;
+    const int w_first = c_begin + warp * c_share;
+    const int cpw = max(0, min(c_share, c_end - w_first));
+    constexpr int kChunkStep = 1;
+#else
     // Chunks of a tile's slice this warp takes: c_begin + warp + 8 i, i < cpw <= kMaxCpw.
+    const int w_first = c_begin + warp;
     const int cpw = max(0, (c_end - c_begin - warp + kGemmWarps - 1) / kGemmWarps);
+    constexpr int kChunkStep = kGemmWarps;
+#endif
     const int my_tiles = (n_tiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x;
     const int items = my_tiles * cpw;   // (tile, chunk) pairs this warp streams, tile-major
 
@@ -200,7 +214,7 @@ __global__ void __launch_bounds__(kGemmThreads, MT == 1 ? 2 : 1) skinny_gemm_ker
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
         const int row = (EPI == EPI_SWIGLU) ? (i < 2 ? 0 : (p.n >> 1)) + (i & 1) * 8 + g : i * 8 + g;
-        wrow[i] = p.w + (long long)row * p.sw + 8 * t + 32 * (c_begin + warp);
+        wrow[i] = p.w + (long long)row * p.sw + 8 * t + 32 * w_first;
     }
     const long long tile_step = (long long)((EPI == EPI_SWIGLU) ? 16 : kTileRows) * p.sw;
     const uint64_t pol = l2_policy_evict_first();
@@ -209,7 +223,7 @@ __global__ void __launch_bounds__(kGemmThreads, MT == 1 ? 2 : 1) skinny_gemm_ker
     int ld_tile = blockIdx.x, ld_ci = 0, ld_slot = 0, ld_q = 0;
     auto issue = [&]() {
         if (ld_q < items) {
-            const long long off = ld_tile * tile_step + 32 * kGemmWarps * ld_ci;
+            const long long off = ld_tile * tile_step + 32 * kChunkStep * ld_ci;
             const uint32_t dst = ring + ld_slot * 2048;
 #pragma unroll
             for (int i = 0; i < 4; ++i) cp_async_16_stream(dst + i * 512, wrow[i] + off, pol);
@@ -229,8 +243,9 @@ __global__ void __launch_bounds__(kGemmThreads, MT == 1 ? 2 : 1) skinny_gemm_ker
     asm volatile("griddepcontrol.wait;\n" ::: "memory");
 
     // Row sums of squares left by the kernel that produced x (one partial per 32
-    // columns): a warp takes ROWS / 8 rows, 256 / ROWS lanes per row take strided
-    // shares. Requested here so that they travel together with the activations.
+    // columns, a row's partials contiguous): a warp takes ROWS / 8 rows, 256 / ROWS
+    // lanes per row take interleaved shares, so a row's request is one or two
+    // 64-byte segments. Requested here so that they travel with the activations.
     constexpr int LPR = kGemmThreads / ROWS;                 // lanes per row: 16 or 8
     const int st_row = warp * (ROWS / kGemmWarps) + lane / LPR, st_part = lane % LPR;
     float st[4] = {0.f, 0.f, 0.f, 0.f};
@@ -238,7 +253,7 @@ __global__ void __launch_bounds__(kGemmThreads, MT == 1 ? 2 : 1) skinny_gemm_ker
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
             const int i = st_part + j * LPR;
-            if (i < p.sumsq_tiles) st[j] = __ldcg(p.sumsq_in + i * 64 + st_row);
+            if (i < p.sumsq_tiles) st[j] = __ldcg(p.sumsq_in + st_row * p.sumsq_tiles + i);
         }
     }
 
@@ -249,7 +264,7 @@ __global__ void __launch_bounds__(kGemmThreads, MT == 1 ? 2 : 1) skinny_gemm_ker
 #pragma unroll
     for (int ci = 0; ci < kMaxCpw; ++ci) {
         if (ci < cpw) {
-            const int k = 32 * (c_begin + warp + kGemmWarps * ci) + 8 * t;
+            const int k = 32 * (w_first + kChunkStep * ci) + 8 * t;
 #pragma unroll
             for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
@@ -314,17 +329,10 @@ __global__ void __launch_bounds__(kGemmThreads, MT == 1 ? 2 : 1) skinny_gemm_ker
             if (sub == 0) inv_rms[row] = rsqrtf(acc / (float)p.k + p.eps);
         }
         __syncthreads();
-    } else if (PRO == PRO_NORM) {
-        // The shares requested above, the rest of a long row, and a shuffle tree. Nobody
-        // waits for the result here: the epilogue reads inv_rms after the tile loop's
-        // first barrier.
-        float acc = (st[0] + st[1]) + (st[2] + st[3]);
-        for (int i = st_part + 4 * LPR; i < p.sumsq_tiles; i += LPR)
-            acc += __ldcg(p.sumsq_in + i * 64 + st_row);
-#pragma unroll
-        for (int off = LPR / 2; off > 0; off >>= 1) acc += __shfl_xor_sync(LS_FULL_MASK, acc, off);
-        if (st_part == 0) inv_rms[st_row] = rsqrtf(acc / (float)p.k + p.eps);
     }
+    // With statistics from the previous kernel, the shares requested above are added up
+    // after the first tile's products (below): no warp waits for them here.
+    bool stats_pending = PRO == PRO_NORM && p.sumsq_in != nullptr;
 
     int slot = 0;
     for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
@@ -371,6 +379,17 @@ __global__ void __launch_bounds__(kGemmThreads, MT == 1 ? 2 : 1) skinny_gemm_ker
             }
         }
 
+        if (PRO == PRO_NORM && stats_pending) {
+            // Row statistics: this lane's shares, the rest of a long row, a shuffle tree.
+            // The epilogue reads inv_rms after the barrier below.
+            float acc = (st[0] + st[1]) + (st[2] + st[3]);
+            for (int i = st_part + 4 * LPR; i < p.sumsq_tiles; i += LPR)
+                acc += __ldcg(p.sumsq_in + st_row * p.sumsq_tiles + i);
+#pragma unroll
+            for (int off = LPR / 2; off > 0; off >>= 1) acc += __shfl_xor_sync(LS_FULL_MASK, acc, off);
+            if (st_part == 0) inv_rms[st_row] = rsqrtf(acc / (float)p.k + p.eps);
+            stats_pending = false;
+        }
         // Warps -> CTA: red[warp][row][col], col = 8 i + 2 t + {0, 1} of the tile's 32 rows of W.
 #pragma unroll
         for (int mt = 0; mt < MT; ++mt)
@@ -446,7 +465,7 @@ __global__ void __launch_bounds__(kGemmThreads, MT == 1 ? 2 : 1) skinny_gemm_ker
                     float sq = (row < p.m) ? v * v : 0.f;
 #pragma unroll
                     for (int off = 16; off > 0; off >>= 1) sq += __shfl_xor_sync(LS_FULL_MASK, sq, off);
-                    if (lane == 0) p.sumsq_out[tile * 64 + row] = sq;
+                    if (lane == 0) p.sumsq_out[row * n_tiles + tile] = sq;
                 }
             }
         }

@@ -73,7 +73,8 @@ def linear(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None
     with the row statistics in `row_sumsq` (as returned by `want_sumsq`).
     Back: `add_residual` [M, N] is added to the fp16-rounded product;
     `want_sumsq` also returns per-row partial sums of squares of the output
-    ([N / 32, 64] fp32), for the next call's `row_sumsq`."""
+    ([64, N / 32] fp32: row r's partials are contiguous), for the next call's
+    `row_sumsq`."""
     if not x.is_cuda:
         raise RuntimeError("latentserve_b200 has no CPU path: tensors must be on a CUDA device")
     if x.dim() != 2 or w.dim() != 2 or x.dtype != torch.float16 or w.dtype != torch.float16:
@@ -92,9 +93,9 @@ def linear(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None
                                  or residual.stride(1) != 1):
         raise ValueError("residual must match x")
     if row_sumsq is not None and (row_sumsq.dtype != torch.float32 or row_sumsq.dim() != 2
-                                  or row_sumsq.shape[1] != 64 or not row_sumsq.is_contiguous()):
-        raise ValueError("row_sumsq must be the contiguous fp32 [tiles, 64] tensor want_sumsq returns")
-    if row_sumsq is not None and row_sumsq.shape[0] * 32 != k:
+                                  or row_sumsq.shape[0] != 64 or not row_sumsq.is_contiguous()):
+        raise ValueError("row_sumsq must be the contiguous fp32 [64, tiles] tensor want_sumsq returns")
+    if row_sumsq is not None and row_sumsq.shape[1] * 32 != k:
         raise ValueError("row_sumsq does not describe rows of this K")
     if bias is not None and (bias.shape != (n,) or bias.dtype != x.dtype or not bias.is_contiguous()):
         raise ValueError("bias must be a contiguous fp16 [N] vector")
@@ -112,7 +113,7 @@ def linear(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None
     elif out.shape != (m, n_out) or out.dtype != x.dtype or out.stride(1) != 1:
         raise ValueError("out has the wrong shape, dtype or layout")
     res_out = torch.empty_like(x) if residual is not None else None
-    sumsq = torch.empty((tiles, 64), dtype=torch.float32, device=x.device) if want_sumsq else None
+    sumsq = torch.empty((64, tiles), dtype=torch.float32, device=x.device) if want_sumsq else None
     if splits is None:
         splits = choose_splits(x.device, tiles, k, m)
     part = counters = None
@@ -122,7 +123,7 @@ def linear(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None
     ptr = _lib.ptr
     rc = _lib.lib().ls_skinny_gemm(
         x.data_ptr(), ptr(residual), ptr(norm_weight), ptr(res_out), ptr(row_sumsq),
-        row_sumsq.shape[0] if row_sumsq is not None else 0, w.data_ptr(), ptr(bias),
+        row_sumsq.shape[1] if row_sumsq is not None else 0, w.data_ptr(), ptr(bias),
         ptr(add_residual), ptr(sumsq), out.data_ptr(), ptr(part), ptr(counters), m, n, k, splits, mode,
         eps, x.stride(0), residual.stride(0) if residual is not None else 0,
         res_out.stride(0) if res_out is not None else 0, w.stride(0),

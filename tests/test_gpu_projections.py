@@ -141,8 +141,8 @@ def test_residual_epilogue_feeds_the_next_norm(m):
     s, ss = pj.linear(x, w1, add_residual=r, want_sumsq=True)
     want_s = ((x.float() @ w1.float().t()).half().float() + r.float())
     _close(s, want_s)
-    assert ss.shape == (48, 64)
-    got_sq = ss.sum(0)[:m]
+    assert ss.shape == (64, 48)
+    got_sq = ss.sum(1)[:m]
     want_sq = (s.float() ** 2).sum(1)                             # of the values actually stored
     assert torch.allclose(got_sq, want_sq, rtol=1e-5, atol=0)
     y = pj.linear(s, w2, norm_weight=gamma, row_sumsq=ss, eps=1e-6)
