@@ -366,6 +366,27 @@ int ls_skinny_gemm(const void* x, const void* res, const void* gamma, void* res_
                    int m, int n, int k, int splits, int mode, float eps, int64_t sx, int64_t sres,
                    int64_t sres_out, int64_t sw, int64_t sadd, int64_t sout, void* stream);
 
+/* The fused QKV projection of a decode step with RoPE and the fp16 cache append in
+ * its epilogue: ls_skinny_gemm (mode: LS_GEMM_NORM and the launch flags; gamma,
+ * sumsq_in, part / counters, splits as there) over w [(q_heads + 2 kv_heads) * 128, k]
+ * with bias, followed -- on the fp16-rounded projection output, with the roundings of
+ * ls_rope_append_fp16 -- by the rotation of the q and k heads (cos, sin
+ * [max_pos, 128], positions [m]) and the stores of ls_rope_append_fp16: q_out
+ * [m, q_heads * 128], the rotated K row and the V row at flat slot slots[m] of the
+ * pools, the page's K bounds when kmin / kmax are given. Bit-identical to
+ * ls_skinny_gemm + ls_rope_append_fp16; one launch instead of two. m <= 32.
+ * Replaces, in GQAAttention.forward (model/attention/gqa.py:236-267), the QKV
+ * projections, `rope_qk` (kernels/fused_elementwise.py:154-182) and
+ * PagedKVCache.write (cache/paged_cache.py:398-417). */
+int ls_qkv_rope_append_fp16(const void* x, const void* gamma, const float* sumsq_in, int sumsq_tiles,
+                            const void* w, const void* bias, const void* cos, const void* sin,
+                            const int64_t* positions, const int64_t* slots, void* q_out, void* k_pool,
+                            void* v_pool, void* kmin, void* kmax, float* part, int32_t* counters, int m,
+                            int q_heads, int kv_heads, int head_dim, int page, int k, int splits,
+                            int mode, float eps, int64_t max_pos, int64_t num_slots, int64_t sx,
+                            int64_t sw, int64_t s_cos, int64_t sq_b, int64_t sp_t, int64_t sp_h,
+                            int64_t sb_b, int64_t sb_h, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

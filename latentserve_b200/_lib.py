@@ -56,6 +56,7 @@ _PROTOTYPES = {
     "ls_rope_append_fp16": [P] * 10 + [I] * 5 + [L] * 9 + [P],
     "ls_skinny_gemm": [P] * 5 + [I] + [P] * 7 + [I] * 5 + [F] + [L] * 6 + [P],
     "ls_rope_append_int8": [P] * 13 + [I] * 4 + [L] * 8 + [I] + [F] * 6 + [P],
+    "ls_qkv_rope_append_fp16": [P] * 3 + [I] + [P] * 13 + [I] * 8 + [F] + [L] * 10 + [P],
 }
 
 

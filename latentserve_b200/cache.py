@@ -401,6 +401,25 @@ class PagedKVCache(_PagedBase):
                             self._flat_v[layer_idx], kmin, kmax, q_heads, self.spec.num_kv_heads,
                             self.block_size)
 
+    def qkv_rope_write(self, layer_idx: int, x: torch.Tensor, w: torch.Tensor, bias, cos: torch.Tensor,
+                       sin: torch.Tensor, positions: torch.Tensor, q_out: torch.Tensor, q_heads: int, *,
+                       norm_weight=None, row_sumsq=None, eps: float = 1e-6) -> None:
+        """`rope_write` with the fused QKV projection in front of it, in one launch
+        (decode batches of up to 32 rows): x [B, hidden] is (normalised and)
+        multiplied by w [(q_heads + 2 kv_heads) * 128, hidden] + bias, then rotated
+        and appended exactly as `rope_write` does with the projection's output."""
+        from latentserve_b200 import projections as pj
+
+        b = x.shape[0]
+        slots = self._write_slots
+        if slots is None or slots.shape[0] < b or slots.shape[1] != 1:
+            raise RuntimeError("call advance(1, batch_size) before qkv_rope_write()")
+        kmin = self.kmin[layer_idx] if self._bounds_on else None
+        kmax = self.kmax[layer_idx] if self._bounds_on else None
+        pj.qkv_rope_append(x, w, bias, cos, sin, positions, self._slot_vec(slots, b), q_out,
+                           self._flat_k[layer_idx], self._flat_v[layer_idx], kmin, kmax, q_heads,
+                           self.spec.num_kv_heads, norm_weight=norm_weight, row_sumsq=row_sumsq, eps=eps)
+
     def enable_page_bounds(self) -> None:
         """Keep each block's per-channel min / max of K for the sparse indexer.
         Bounds of blocks already written are rebuilt over their written rows."""

@@ -37,6 +37,12 @@
 //               the 16 matching up rows and writes fp16(silu(gate)) * up
 //               ([M, I]). Replaces the SiLU * up launch and the [M, 2 I] round trip.
 //   bias        out += bias (QKV projection).
+//   EPI_ROPE    the fused QKV projection of a decode step: a CTA takes 16 dims of a
+//               head and the 16 dims 64 further on (the rotation partners), adds the
+//               bias, rotates q and k heads by the position's cos / sin row, and
+//               stores q to the query buffer and k, v to the fp16 cache pools at the
+//               sequence's slot (+ the page's K bounds). Replaces the RoPE + append
+//               launch and the [M, N] round trip, with the same roundings.
 //   add_res     out = fp16(fp16(product) + residual): the residual add that follows
 //               o_proj and down_proj. With sumsq_out the same epilogue leaves each
 //               row's sum of squares over the tile's 32 columns, and the next
@@ -50,7 +56,7 @@ constexpr int kGemmThreads = 256;
 constexpr int kGemmWarps = 8;
 constexpr int kTileRows = 32;           // rows of W per CTA
 enum { PRO_NONE = 0, PRO_NORM = 1 };
-enum { EPI_NONE = 0, EPI_SWIGLU = 1 };
+enum { EPI_NONE = 0, EPI_SWIGLU = 1, EPI_ROPE = 2 };
 
 struct GemmParams {
     const __half* x;        // [M, K]
@@ -68,6 +74,18 @@ struct GemmParams {
     int m, n, k, splits, sumsq_tiles;
     float eps;
     long long sx, sres, sres_out, sw, sadd, sout;
+    // EPI_ROPE: heads of 128 in q, k, v order; cos / sin [max_pos][128] (halves duplicated).
+    const __half* cos_t;
+    const __half* sin_t;
+    const long long* positions;   // [M]
+    const long long* slots;       // [M] flat token slots of the pools
+    __half* q_out;                // [M][hq * 128]
+    __half* k_pool;               // [num_slots][hk][128]
+    __half* v_pool;
+    __half* kmin;                 // [num_blocks][hk][128] or null
+    __half* kmax;
+    int hq, hk;
+    long long max_pos, num_slots, s_cos, sq_b, sp_t, sp_h, sb_b, sb_h;
 };
 
 __device__ __forceinline__ uint4 ldg_stream(const void* p, uint64_t pol) {
@@ -213,17 +231,24 @@ __global__ void __launch_bounds__(kGemmThreads, MT == 1 ? 2 : 1) skinny_gemm_ker
     const __half* wrow[4];
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
-        const int row = (EPI == EPI_SWIGLU) ? (i < 2 ? 0 : (p.n >> 1)) + (i & 1) * 8 + g : i * 8 + g;
+        const int row = (EPI == EPI_SWIGLU)
+                            ? (i < 2 ? 0 : (p.n >> 1)) + (i & 1) * 8 + g
+                            : (EPI == EPI_ROPE) ? (i < 2 ? 0 : 64) + (i & 1) * 8 + g : i * 8 + g;
         wrow[i] = p.w + (long long)row * p.sw + 8 * t + 32 * w_first;
     }
-    const long long tile_step = (long long)((EPI == EPI_SWIGLU) ? 16 : kTileRows) * p.sw;
+    // First row of W behind tile t (EPI_ROPE: four tiles per head of 128).
+    auto tile_off = [&](int t) -> long long {
+        const int row = (EPI == EPI_SWIGLU) ? 16 * t : (EPI == EPI_ROPE) ? (t >> 2) * 128 + (t & 3) * 16
+                                                                         : kTileRows * t;
+        return (long long)row * p.sw;
+    };
     const uint64_t pol = l2_policy_evict_first();
 
     // Load side: item q of the warp's stream goes to ring slot q % kRing.
     int ld_tile = blockIdx.x, ld_ci = 0, ld_slot = 0, ld_q = 0;
     auto issue = [&]() {
         if (ld_q < items) {
-            const long long off = ld_tile * tile_step + 32 * kChunkStep * ld_ci;
+            const long long off = tile_off(ld_tile) + 32 * kChunkStep * ld_ci;
             const uint32_t dst = ring + ld_slot * 2048;
 #pragma unroll
             for (int i = 0; i < 4; ++i) cp_async_16_stream(dst + i * 512, wrow[i] + off, pol);
@@ -356,6 +381,35 @@ __global__ void __launch_bounds__(kGemmThreads, MT == 1 ? 2 : 1) skinny_gemm_ker
                                  : 0.f;
             }
         }
+        // EPI_ROPE: this thread's pair of dims (r_d, r_d + 64) of head r_head, for rows
+        // (tid >> 4) + 16 j: bias, position and the position's cos / sin, requested now.
+        constexpr int EPR = ROWS * 16 / kGemmThreads;
+        const int r_head = tile >> 2, r_d = (tile & 3) * 16 + (tid & 15);
+        float rb_lo = 0.f, rb_hi = 0.f, rc1[EPR], rs1[EPR], rc2[EPR], rs2[EPR];
+        bool r_ok[EPR];
+        if (EPI == EPI_ROPE) {
+            if (p.bias != nullptr) {
+                rb_lo = __half2float(p.bias[r_head * 128 + r_d]);
+                rb_hi = __half2float(p.bias[r_head * 128 + r_d + 64]);
+            }
+#pragma unroll
+            for (int j = 0; j < EPR; ++j) {
+                const int row = (tid >> 4) + 16 * j;
+                rc1[j] = rc2[j] = 1.f;
+                rs1[j] = rs2[j] = 0.f;
+                r_ok[j] = row < p.m;
+                if (r_ok[j] && r_head < p.hq + p.hk) {          // q and k heads are rotated
+                    const long long pos = p.positions[row];
+                    r_ok[j] = pos >= 0 && pos < p.max_pos;
+                    if (r_ok[j]) {
+                        rc1[j] = __half2float(p.cos_t[pos * p.s_cos + r_d]);
+                        rc2[j] = __half2float(p.cos_t[pos * p.s_cos + r_d + 64]);
+                        rs1[j] = __half2float(p.sin_t[pos * p.s_cos + r_d]);
+                        rs2[j] = __half2float(p.sin_t[pos * p.s_cos + r_d + 64]);
+                    }
+                }
+            }
+        }
 
 #pragma unroll
         for (int ci = 0; ci < kMaxCpw; ++ci) {
@@ -451,6 +505,48 @@ __global__ void __launch_bounds__(kGemmThreads, MT == 1 ? 2 : 1) skinny_gemm_ker
                 const float act = round_h(gate / (1.f + expf(-gate)));
                 p.out[row * p.sout + tile * 16 + j] = __float2half_rn(act * up);
             }
+        } else if (finish && EPI == EPI_ROPE) {
+            // red[row][c] is dim r_d of the head, red[row][16 + c] its partner r_d + 64.
+#pragma unroll
+            for (int j = 0; j < EPR; ++j) {
+                const int row = (tid >> 4) + 16 * j, c = tid & 15;
+                if (!r_ok[j]) continue;
+                const float f = (PRO == PRO_NORM) ? inv_rms[row] * kPostScale : 1.f;
+                const float a = round_h(__fmaf_rn(red[row * 32 + c], f, rb_lo));        // the projection's fp16 output
+                const float b = round_h(__fmaf_rn(red[row * 32 + 16 + c], f, rb_hi));
+                float y_lo = a, y_hi = b;
+                if (r_head < p.hq + p.hk) {                     // the rounding sequence of rope_append_kernel
+                    y_lo = round_h(round_h(a * rc1[j]) + round_h(-(b * rs1[j])));
+                    y_hi = round_h(round_h(b * rc2[j]) + round_h(a * rs2[j]));
+                }
+                if (r_head < p.hq) {
+                    __half* dst = p.q_out + row * p.sq_b + r_head * 128 + r_d;
+                    dst[0] = __float2half_rn(y_lo);
+                    dst[64] = __float2half_rn(y_hi);
+                    continue;
+                }
+                const long long slot = p.slots[row];
+                if (slot < 0 || slot >= p.num_slots) continue;
+                const bool is_k = r_head < p.hq + p.hk;
+                const int kvh = is_k ? r_head - p.hq : r_head - p.hq - p.hk;
+                __half* dst = (is_k ? p.k_pool : p.v_pool) + slot * p.sp_t + kvh * p.sp_h + r_d;
+                dst[0] = __float2half_rn(y_lo);
+                dst[64] = __float2half_rn(y_hi);
+                if (is_k && p.kmin != nullptr) {
+                    // Page bounds of K: reset by the page's first row, else widened. One
+                    // thread owns a (page, head, dim), and no two sequences write one page.
+                    const long long bi = (slot / LS_PAGE) * p.sb_b + kvh * p.sb_h + r_d;
+                    const bool first = slot % LS_PAGE == 0;
+#pragma unroll
+                    for (int part = 0; part < 2; ++part) {
+                        const float v = part ? y_hi : y_lo;
+                        __half* mn = p.kmin + bi + 64 * part;
+                        __half* mx = p.kmax + bi + 64 * part;
+                        *mn = __float2half_rn(first ? v : fminf(__half2float(*mn), v));
+                        *mx = __float2half_rn(first ? v : fmaxf(__half2float(*mx), v));
+                    }
+                }
+            }
         } else if (finish) {
             // A warp covers one row's 32 columns per sweep (256 threads = 8 rows).
 #pragma unroll
@@ -458,7 +554,7 @@ __global__ void __launch_bounds__(kGemmThreads, MT == 1 ? 2 : 1) skinny_gemm_ker
                 const int e = tid + j * kGemmThreads;
                 const int row = e >> 5, col = tile * kTileRows + (e & 31);
                 const float f = (PRO == PRO_NORM) ? inv_rms[row] * kPostScale : 1.f;
-                float v = round_h(red[e] * f + pre_bias);
+                float v = round_h(__fmaf_rn(red[e], f, pre_bias));
                 if (p.add_res != nullptr) v = round_h(v + pre_res[j]);
                 if (row < p.m) p.out[row * p.sout + col] = __float2half_rn(v);
                 if (p.sumsq_out != nullptr) {
@@ -532,7 +628,7 @@ extern "C" int ls_skinny_gemm(const void* x, const void* res, const void* gamma,
     if (bad(x, sx) || bad(w, sw) || (res && (bad(res, sres) || bad(res_out, sres_out))) ||
         (norm && bad(gamma, 8)))
         return LS_ERR_MISALIGNED;
-    GemmParams p;
+    GemmParams p = {};
     p.x = static_cast<const __half*>(x);
     p.res = static_cast<const __half*>(res);
     p.gamma = static_cast<const __half*>(gamma);
@@ -555,4 +651,64 @@ extern "C" int ls_skinny_gemm(const void* x, const void* res, const void* gamma,
     if (norm) return launch_gemm_m<PRO_NORM, EPI_NONE>(p, tiles, st, pdl);
     if (swiglu) return launch_gemm_m<PRO_NONE, EPI_SWIGLU>(p, tiles, st, pdl);
     return launch_gemm_m<PRO_NONE, EPI_NONE>(p, tiles, st, pdl);
+}
+
+extern "C" int ls_qkv_rope_append_fp16(const void* x, const void* gamma, const float* sumsq_in,
+                                       int sumsq_tiles, const void* w, const void* bias, const void* cos,
+                                       const void* sin, const int64_t* positions, const int64_t* slots,
+                                       void* q_out, void* k_pool, void* v_pool, void* kmin, void* kmax,
+                                       float* part, int32_t* counters, int m, int q_heads, int kv_heads,
+                                       int head_dim, int page, int k, int splits, int mode, float eps,
+                                       int64_t max_pos, int64_t num_slots, int64_t sx, int64_t sw,
+                                       int64_t s_cos, int64_t sq_b, int64_t sp_t, int64_t sp_h,
+                                       int64_t sb_b, int64_t sb_h, void* stream) {
+    using namespace ls;
+    const bool norm = mode & LS_GEMM_NORM;
+    if (!x || !w || !cos || !sin || !positions || !slots || !q_out || !k_pool || !v_pool ||
+        (norm && !gamma))
+        return LS_ERR_NULL_POINTER;
+    if ((kmin == nullptr) != (kmax == nullptr)) return LS_ERR_NULL_POINTER;
+    if (head_dim != LS_HEAD_DIM || page != LS_PAGE || (mode & LS_GEMM_SWIGLU) || (sumsq_in && !norm))
+        return LS_ERR_UNSUPPORTED;
+    if (m <= 0 || q_heads <= 0 || kv_heads <= 0 || k <= 0 || splits <= 0 || max_pos <= 0 ||
+        num_slots <= 0 || (sumsq_in && sumsq_tiles <= 0))
+        return LS_ERR_BAD_SHAPE;
+    if (m > 32) return LS_ERR_TOO_LARGE;
+    if ((k % 32) || splits > k / 32) return LS_ERR_UNSUPPORTED;
+    if (splits > 1 && (!part || !counters)) return LS_ERR_NULL_POINTER;
+    auto bad = [](const void* ptr, int64_t stride) {
+        return (reinterpret_cast<uintptr_t>(ptr) & 15) || (stride % 8);
+    };
+    if (bad(x, sx) || bad(w, sw) || (norm && bad(gamma, 8))) return LS_ERR_MISALIGNED;
+    const void* halves[] = {bias, cos, sin, q_out, k_pool, v_pool, kmin, kmax};
+    for (const void* ptr : halves)
+        if (reinterpret_cast<uintptr_t>(ptr) & 1) return LS_ERR_MISALIGNED;
+    GemmParams p = {};
+    p.x = static_cast<const __half*>(x);
+    p.gamma = static_cast<const __half*>(gamma);
+    p.sumsq_in = sumsq_in;
+    p.sumsq_tiles = sumsq_tiles;
+    p.w = static_cast<const __half*>(w);
+    p.bias = static_cast<const __half*>(bias);
+    p.part = part;
+    p.counters = counters;
+    p.m = m; p.n = (q_heads + 2 * kv_heads) * LS_HEAD_DIM; p.k = k; p.splits = splits; p.eps = eps;
+    p.sx = sx; p.sw = sw;
+    p.cos_t = static_cast<const __half*>(cos);
+    p.sin_t = static_cast<const __half*>(sin);
+    p.positions = reinterpret_cast<const long long*>(positions);
+    p.slots = reinterpret_cast<const long long*>(slots);
+    p.q_out = static_cast<__half*>(q_out);
+    p.k_pool = static_cast<__half*>(k_pool);
+    p.v_pool = static_cast<__half*>(v_pool);
+    p.kmin = static_cast<__half*>(kmin);
+    p.kmax = static_cast<__half*>(kmax);
+    p.hq = q_heads; p.hk = kv_heads;
+    p.max_pos = max_pos; p.num_slots = num_slots; p.s_cos = s_cos; p.sq_b = sq_b;
+    p.sp_t = sp_t; p.sp_h = sp_h; p.sb_b = sb_b; p.sb_h = sb_h;
+    const int tiles = p.n / kTileRows;                  // four per head: 16 dims and their partners
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const bool pdl = mode & LS_LAUNCH_PROGRAMMATIC;
+    if (norm) return launch_gemm_m<PRO_NORM, EPI_ROPE>(p, tiles, st, pdl);
+    return launch_gemm_m<PRO_NONE, EPI_ROPE>(p, tiles, st, pdl);
 }

@@ -196,7 +196,8 @@ class DecodeModel:
 
 
     def _forward_streamed(self, cache, tokens, positions, context_hint, return_logits):
-        """Six launches per layer: the norms, residual adds and SiLU * up ride on the projections."""
+        """Five launches per layer (six with an INT8 cache): the norms, residual adds, SiLU * up and --
+        for the fp16 cache -- RoPE with the KV append ride on the projections."""
         # Rounding differs from `_forward_fused` in one place: the residual stream is
         # fp16(fp16(o) + r) in both, but here it is formed in o_proj's epilogue.
         s = self.shape
@@ -204,10 +205,14 @@ class DecodeModel:
         stream = self.embed[tokens]                 # the residual stream, fp16 [B, hidden]
         ss = None                                   # its row sums of squares, once a projection wrote it
         for i, L in enumerate(self.layers):
-            qkv = pj.linear(stream, L["wqkv"], L["bqkv"], norm_weight=L["ln1"], row_sumsq=ss,
-                            eps=s.rms_eps)
             q = torch.empty(b, s.q_heads * s.head_dim, dtype=self.dtype, device=self.device)
-            cache.rope_write(i, qkv, self.cos16, self.sin16, positions, q, s.q_heads)
+            if hasattr(cache, "qkv_rope_write"):    # fp16 cache: RoPE and the append ride on the projection
+                cache.qkv_rope_write(i, stream, L["wqkv"], L["bqkv"], self.cos16, self.sin16, positions, q,
+                                     s.q_heads, norm_weight=L["ln1"], row_sumsq=ss, eps=s.rms_eps)
+            else:
+                qkv = pj.linear(stream, L["wqkv"], L["bqkv"], norm_weight=L["ln1"], row_sumsq=ss,
+                                eps=s.rms_eps)
+                cache.rope_write(i, qkv, self.cos16, self.sin16, positions, q, s.q_heads)
             a = self.attend(cache, i, q.view(b, s.kv_heads, s.q_heads // s.kv_heads, s.head_dim), b,
                             context_hint)
             stream, ss = pj.linear(a.reshape(b, s.q_heads * s.head_dim), L["wo"], add_residual=stream,

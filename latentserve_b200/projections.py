@@ -132,3 +132,64 @@ def linear(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None
     _lib.check(rc, "linear")
     extra = tuple(t for t in (res_out, sumsq) if t is not None)
     return (out, *extra) if extra else out
+
+
+def qkv_rope_append(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], cos: torch.Tensor,
+                    sin: torch.Tensor, positions: torch.Tensor, slots: torch.Tensor, q_out: torch.Tensor,
+                    flat_k: torch.Tensor, flat_v: torch.Tensor, kmin: Optional[torch.Tensor],
+                    kmax: Optional[torch.Tensor], q_heads: int, kv_heads: int, *,
+                    norm_weight: Optional[torch.Tensor] = None, row_sumsq: Optional[torch.Tensor] = None,
+                    eps: float = 1e-6, splits: Optional[int] = None) -> None:
+    """The fused QKV projection of a decode step with RoPE and the fp16 cache append
+    in its epilogue: what `linear(x, w, bias, norm_weight=..., row_sumsq=...)`
+    followed by `fused_elementwise.rope_append_fp16` writes (rotated q into `q_out`
+    [M, q_heads * 128], rotated k and v at `slots` [M] int64 of the flat pools
+    [num_slots, kv_heads, 128], the page bounds when given), bit for bit, in one
+    launch. w [(q_heads + 2 kv_heads) * 128, K] in q, k, v head order; cos, sin
+    [max_pos, 128] fp16; positions [M] int64."""
+    if not x.is_cuda:
+        raise RuntimeError("latentserve_b200 has no CPU path: tensors must be on a CUDA device")
+    if x.dim() != 2 or w.dim() != 2 or x.dtype != torch.float16 or w.dtype != torch.float16:
+        raise ValueError("qkv_rope_append takes fp16 x [M, K] and w [N, K]")
+    m, k = x.shape
+    n = (q_heads + 2 * kv_heads) * 128
+    if w.shape != (n, k) or x.stride(1) != 1 or w.stride(1) != 1:
+        raise ValueError("w must be [(q_heads + 2 kv_heads) * 128, K] with unit-stride rows, as x")
+    if m > MAX_ROWS:
+        raise ValueError(f"the streaming projection takes at most {MAX_ROWS} rows, got {m}")
+    if row_sumsq is not None and norm_weight is None:
+        raise ValueError("row_sumsq belongs to the norm: pass norm_weight as well")
+    if row_sumsq is not None and (row_sumsq.dtype != torch.float32 or row_sumsq.dim() != 2
+                                  or row_sumsq.shape[0] != 64 or not row_sumsq.is_contiguous()
+                                  or row_sumsq.shape[1] * 32 != k):
+        raise ValueError("row_sumsq must be the contiguous fp32 [64, K / 32] tensor want_sumsq returns")
+    if bias is not None and (bias.shape != (n,) or bias.dtype != x.dtype or not bias.is_contiguous()):
+        raise ValueError("bias must be a contiguous fp16 [N] vector")
+    if flat_k.dtype != torch.float16 or flat_v.dtype != torch.float16 or flat_k.shape != flat_v.shape \
+            or flat_k.stride() != flat_v.stride() or flat_k.stride(2) != 1:
+        raise ValueError("flat_k / flat_v must be fp16 [num_slots, kv_heads, 128] views of one layout")
+    if (kmin is None) != (kmax is None):
+        raise ValueError("kmin and kmax come together")
+    if q_out.shape != (m, q_heads * 128) or q_out.dtype != x.dtype or q_out.stride(1) != 1:
+        raise ValueError("q_out must be fp16 [M, q_heads * 128] with unit-stride rows")
+    if positions.dtype != torch.int64 or slots.dtype != torch.int64 or positions.numel() < m \
+            or slots.numel() < m:
+        raise ValueError("positions and slots must be int64 [M]")
+    tiles = n // 32
+    if splits is None:
+        splits = choose_splits(x.device, tiles, k, m)
+    part = counters = None
+    if splits > 1:
+        part = pdc.scratch("gemm_part", (tiles * splits * _rows_pad(m) * 32,), torch.float32, x.device)
+        counters = pdc.scratch("gemm_counters", (tiles,), torch.int32, x.device, zero=True)
+    mode = (GEMM_NORM if norm_weight is not None else 0) | pdc.launch_flags()
+    ptr = _lib.ptr
+    sb = (kmin.stride(0), kmin.stride(1)) if kmin is not None else (0, 0)
+    rc = _lib.lib().ls_qkv_rope_append_fp16(
+        x.data_ptr(), ptr(norm_weight), ptr(row_sumsq), row_sumsq.shape[1] if row_sumsq is not None else 0,
+        w.data_ptr(), ptr(bias), cos.data_ptr(), sin.data_ptr(), positions.data_ptr(), slots.data_ptr(),
+        q_out.data_ptr(), flat_k.data_ptr(), flat_v.data_ptr(), ptr(kmin), ptr(kmax), ptr(part),
+        ptr(counters), m, q_heads, kv_heads, 128, 16, k, splits, mode, eps, cos.shape[0], flat_k.shape[0],
+        x.stride(0), w.stride(0), cos.stride(0), q_out.stride(0), flat_k.stride(0), flat_k.stride(1),
+        sb[0], sb[1], _lib.current_stream(x.device))
+    _lib.check(rc, "qkv_rope_append")

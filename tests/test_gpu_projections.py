@@ -178,3 +178,56 @@ def test_argument_errors():
         pj.linear(x[:4], w, residual=x[:4])                      # residual without a norm
     with pytest.raises(RuntimeError):
         pj.linear(x[:4].cpu(), w.cpu())
+
+
+@pytest.mark.parametrize("m", [1, 16, 17, 32])
+@pytest.mark.parametrize("norm", ["none", "rows", "stats"])
+def test_qkv_projection_with_rope_and_append_equals_the_two_launches(m, norm):
+    """`qkv_rope_append` against `linear` followed by `rope_append_fp16`: every byte it
+    writes (rotated q, K and V pool rows, page bounds) is the same, rows with an
+    out-of-range position or slot are left alone in the same way."""
+    dev = device()
+    hq, hk, k, max_pos, blocks = 12, 2, 1536, 640, 40
+    n = (hq + 2 * hk) * 128
+    x = _rand((m, k), 1.0, 50, dev)
+    w, bias = _rand((n, k), 0.05, 51, dev), _rand((n,), 0.3, 52, dev)
+    gamma = _gamma(k, 53, dev)
+    g = torch.Generator(device="cpu").manual_seed(54)
+    ang = torch.rand(max_pos, 64, generator=g) * 6.28
+    cos = torch.cat([ang.cos(), ang.cos()], dim=1).half().to(dev)
+    sin = torch.cat([ang.sin(), ang.sin()], dim=1).half().to(dev)
+    positions = torch.randint(0, max_pos, (m,), generator=g).to(dev)
+    perm = torch.randperm(blocks, generator=g)[:m]
+    slots = (perm * 16 + torch.randint(0, 16, (m,), generator=g)).to(dev)
+    if m >= 16:
+        slots[3] = slots[3] // 16 * 16                 # first row of a page: bounds are reset
+        slots[5] = -1                                  # nothing appended for this row
+        positions[7] = max_pos                         # out of range: q and k of this row untouched
+    kwargs = {}
+    if norm != "none":
+        kwargs["norm_weight"] = gamma
+    if norm == "stats":
+        # statistics as an o_proj-style call leaves them: x is that call's output
+        x0, w0 = _rand((m, k), 1.0, 55, dev), _rand((k, k), 0.05, 56, dev)
+        x, ss = pj.linear(x0, w0, add_residual=_rand((m, k), 1.0, 57, dev), want_sumsq=True)
+        kwargs["row_sumsq"] = ss
+
+    def fresh():
+        gen = torch.Generator(device="cpu").manual_seed(58)
+        pool = lambda: torch.randn(blocks * 16, hk, 128, generator=gen).half().to(dev)
+        return pool(), pool(), pool() - 1.0, pool() + 1.0, torch.full((m, hq * 128), 7.0, device=dev).half()
+
+    k1, v1, mn1, mx1, q1 = fresh()
+    qkv = pj.linear(x, w, bias, **kwargs)
+    fe.rope_append_fp16(qkv, cos, sin, positions, slots, q1, k1, v1, mn1.view(blocks, 16, hk, 128)[:, 0],
+                        mx1.view(blocks, 16, hk, 128)[:, 0], hq, hk)
+    k2, v2, mn2, mx2, q2 = fresh()
+    pj.qkv_rope_append(x, w, bias, cos, sin, positions, slots, q2, k2, v2,
+                       mn2.view(blocks, 16, hk, 128)[:, 0], mx2.view(blocks, 16, hk, 128)[:, 0], hq, hk, **kwargs)
+    assert torch.equal(q2, q1)
+    assert torch.equal(k2, k1) and torch.equal(v2, v1)
+    assert torch.equal(mn2, mn1) and torch.equal(mx2, mx1)
+    # ... and without bounds
+    k3, v3, _, _, q3 = fresh()
+    pj.qkv_rope_append(x, w, bias, cos, sin, positions, slots, q3, k3, v3, None, None, hq, hk, **kwargs)
+    assert torch.equal(q3, q1) and torch.equal(k3, k1) and torch.equal(v3, v1)
