@@ -17,9 +17,10 @@ Per layer, in stream order, with `projections="cublas"` (nine launches):
 page-sparse) -> o_proj GEMM -> residual add + RMSNorm -> gate/up GEMM ->
 SiLU * up -> down GEMM, the GEMMs being torch's. With `projections="ls"` the
 projections are this library's weight-streaming kernel (`projections.linear`)
-with the norms, residual adds and SiLU * up folded into them (six launches):
-about 3 % faster per step than the cuBLAS route at batch 16, slower between 17
-and 32 rows, not available beyond. `projections="auto"` (the default) takes the
+with the norms, residual adds and SiLU * up folded into them, and for the fp16
+cache RoPE and the KV append folded into the QKV projection (five launches; six
+with an INT8 cache): about 10 % faster per step than the cuBLAS route at batch
+16, slower between 17 and 32 rows, not available beyond. `projections="auto"` (the default) takes the
 streaming kernel up to 16 rows and cuBLAS above. With
 `fused=False` the norms, RoPE and SwiGLU are plain torch element-wise ops and
 the append is `cache.write` (the form the fused ones are tested against).
