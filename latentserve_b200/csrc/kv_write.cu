@@ -45,6 +45,10 @@ kv_append_fp16_kernel(const __half* __restrict__ k, const __half* __restrict__ v
                       long long sk_b, long long sk_h, long long sv_b, long long sv_h,
                       long long sp_t, long long sp_h, long long sb_b, long long sb_h) {
     asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");   // let a programmatic successor start its prologue
+    // Launched programmatically itself: the launch overlaps the end of the previous
+    // kernel (in a layer loop, the previous layer's attention), and nothing is read or
+    // written before that kernel has completed.
+    asm volatile("griddepcontrol.wait;\n" ::: "memory");
     const int row = blockIdx.x * 4 + (threadIdx.x >> 5);
     const int lane = threadIdx.x & 31;
     if (row >= batch * heads) return;
@@ -211,12 +215,25 @@ int ls_kv_append_fp16(const void* k, const void* v, const int64_t* slots, void* 
     for (uintptr_t a : ptrs)
         if (a & 7) return LS_ERR_MISALIGNED;
     const int rows = batch * kv_heads;
-    ls::kv_append_fp16_kernel<<<(rows + 3) / 4, 128, 0, static_cast<cudaStream_t>(stream)>>>(
-        static_cast<const __half*>(k), static_cast<const __half*>(v),
+    // A programmatic launch (the kernel waits for its predecessor before it touches
+    // memory); after a kernel that never triggers early this is an ordinary launch.
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((rows + 3) / 4);
+    cfg.blockDim = dim3(128);
+    cfg.stream = static_cast<cudaStream_t>(stream);
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    const long long a_ns = num_slots, a_sk_b = sk_b, a_sk_h = sk_h, a_sv_b = sv_b, a_sv_h = sv_h,
+                    a_sp_t = sp_t, a_sp_h = sp_h, a_sb_b = sb_b, a_sb_h = sb_h;
+    cudaError_t e = cudaLaunchKernelEx(
+        &cfg, ls::kv_append_fp16_kernel, static_cast<const __half*>(k), static_cast<const __half*>(v),
         reinterpret_cast<const long long*>(slots), static_cast<__half*>(k_pool),
         static_cast<__half*>(v_pool), static_cast<__half*>(kmin), static_cast<__half*>(kmax), batch,
-        kv_heads, num_slots, sk_b, sk_h, sv_b, sv_h, sp_t, sp_h, sb_b, sb_h);
-    return (int)cudaGetLastError();
+        kv_heads, a_ns, a_sk_b, a_sk_h, a_sv_b, a_sv_h, a_sp_t, a_sp_h, a_sb_b, a_sb_h);
+    return e != cudaSuccess ? (int)e : (int)cudaGetLastError();
 }
 
 int ls_int8_decode_write(const void* k, const void* v, const int64_t* slots, const int64_t* res_idx,
