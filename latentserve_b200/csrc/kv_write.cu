@@ -110,6 +110,7 @@ int8_decode_write_kernel(const __half* __restrict__ k, const __half* __restrict_
                          long long num_res, long long sk_b, long long sk_h, long long sv_b,
                          long long sv_h, QuantConsts c) {
     asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");   // let a programmatic successor start its prologue
+    asm volatile("griddepcontrol.wait;\n" ::: "memory");                // launched programmatically, as the fp16 append
     const int row = blockIdx.x * 4 + (threadIdx.x >> 5);
     const int lane = threadIdx.x & 31;
     if (row >= batch * heads) return;
@@ -252,12 +253,23 @@ int ls_int8_decode_write(const void* k, const void* v, const int64_t* slots, con
         return LS_ERR_MISALIGNED;
     ls::QuantConsts c = {asym, eps, qmax, inv_qmax, levels, inv_levels, offset};
     const int rows = batch * kv_heads;
-    ls::int8_decode_write_kernel<<<(rows + 3) / 4, 128, 0, static_cast<cudaStream_t>(stream)>>>(
-        static_cast<const __half*>(k), static_cast<const __half*>(v),
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((rows + 3) / 4);
+    cfg.blockDim = dim3(128);
+    cfg.stream = static_cast<cudaStream_t>(stream);
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    const long long a_ns = num_slots, a_nr = num_res, a_sk_b = sk_b, a_sk_h = sk_h, a_sv_b = sv_b,
+                    a_sv_h = sv_h;
+    cudaError_t e = cudaLaunchKernelEx(
+        &cfg, ls::int8_decode_write_kernel, static_cast<const __half*>(k), static_cast<const __half*>(v),
         reinterpret_cast<const long long*>(slots), reinterpret_cast<const long long*>(res_idx),
         static_cast<signed char*>(flat_v), flat_v_scale, flat_v_zero, static_cast<__half*>(k_res),
-        batch, kv_heads, num_slots, num_res, sk_b, sk_h, sv_b, sv_h, c);
-    return (int)cudaGetLastError();
+        batch, kv_heads, a_ns, a_nr, a_sk_b, a_sk_h, a_sv_b, a_sv_h, c);
+    return e != cudaSuccess ? (int)e : (int)cudaGetLastError();
 }
 
 int ls_int8_finalize_layers(const void* k_res, const int64_t* res_rows, const int64_t* block_ids,
