@@ -151,8 +151,19 @@ def cpu_oracle_layer(q, k_pool, v_pool, tables, lens, repeats=1):
 
 
 def host_threads() -> int:
+    """Threads of the CPU legs: every CPU this process may run on. Set explicitly,
+    because torchrun exports OMP_NUM_THREADS=1 to its workers and only rank 0 runs
+    the CPU leg (LS_CPU_THREADS overrides)."""
     import torch
 
+    want = int(os.environ.get("LS_CPU_THREADS", "0"))
+    if want <= 0:
+        try:
+            want = len(os.sched_getaffinity(0))
+        except AttributeError:
+            want = os.cpu_count() or 1
+    if torch.get_num_threads() != want:
+        torch.set_num_threads(want)
     return torch.get_num_threads()
 
 
@@ -169,6 +180,7 @@ def run_reference(args, workload):
     if rank != 0:
         return
     sample_seqs = 4
+    cores = host_threads()
     case = synthetic.dense_case([context] * sample_seqs, seed=0, spare=0)
     nbytes = synthetic.kv_bytes_fp16([context] * sample_seqs)
     for _ in range(max(1, min(args.warmup, 2))):
@@ -178,7 +190,6 @@ def run_reference(args, workload):
         cpu_oracle_layer(case["q"], case["k_pool"], case["v_pool"], case["block_tables"], case["seq_lens"])
     dt = (time.perf_counter() - t0) / args.steps
     value = nbytes / dt / 1e9
-    cores = host_threads()
     sample = (f"one layer call over {sample_seqs} of the workload's {batch} sequences at context "
               f"{context} ({nbytes / 1e6:.0f} MB of KV) per step, torch CPU fp32 gather-then-softmax")
     print(json.dumps({
@@ -420,10 +431,11 @@ def main():
         kb = k[blocks[:seqs].reshape(-1)].cpu().numpy()
         vb = v[blocks[:seqs].reshape(-1)].cpu().numpy()
         tb = np.arange(kb.shape[0], dtype=np.int32).reshape(seqs, -1)
+        cpu_cores = host_threads()
         secs = cpu_oracle_layer(w["q"][0][:seqs].cpu().numpy(), kb, vb, tb,
                                 lens[:seqs].cpu().numpy(), repeats=3)
         nbytes = synthetic.kv_bytes_fp16([context] * seqs)
-        cpu = {"value": round(nbytes / secs / 1e9, 3), "unit": "GB/s", "cores": host_threads(),
+        cpu = {"value": round(nbytes / secs / 1e9, 3), "unit": "GB/s", "cores": cpu_cores,
                "kind": "port",
                "sample": f"one layer call over {seqs} of the {batch} sequences "
                          f"({nbytes / 1e6:.0f} MB of KV), torch CPU fp32 gather-then-softmax, best of 3"}
