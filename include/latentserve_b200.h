@@ -57,9 +57,11 @@ extern "C" {
 /* With LS_LAUNCH_PROGRAMMATIC on the dense entry points (fp16, INT8): also request
  * the first pages before synchronising on the previous kernel of the stream, except
  * a sequence's LAST page (the one holding token seq_len - 1), which is requested
- * after it. Only set it when that previous kernel writes nothing of the pools (pages,
- * scales, zero points) outside each sequence's last page -- in LatentServe it is the
- * KV append, which writes the newest token only. */
+ * after it; with INT8 pools the page before the last is held back as well, because
+ * an INT8 cache quantises a K page in the step after the one that filled it. Only set
+ * it when nothing that runs between the previous step's attention and this launch
+ * writes the pools (pages, scales, zero points) outside those pages -- in LatentServe
+ * that is the KV append (the newest token) and, for INT8, the page finalisation. */
 #define LS_EARLY_PAGES 0x800
 
 /* Partial-state scratch shared by the three decode entry points.
@@ -245,6 +247,25 @@ int ls_int8_finalize_layers(const void* k_res, const int64_t* res_rows, const in
                             int64_t sk_b, int64_t sk_p, int64_t sk_h, int64_t ss_l, int64_t ss_b,
                             int64_t ss_h, int asym, float eps, float qmax, float inv_qmax, float levels,
                             float inv_levels, float offset, void* stream);
+
+/* The same with the LENGTH of the page list on the device, so that the launch can be
+ * a fixed node of a captured decode step and the host's per-step work for the INT8
+ * cache is one staged copy and no launch. Replaces the eager torch ops that
+ * Int8PagedKVCache.advance runs through _finalize_pending, outside the graph, on the
+ * step's critical path (cache/int8_paged_cache.py:443-446, 524-552).
+ *   state int32 [2] (device): state[0] = entries of res_rows / block_ids to finalise
+ *   (written by the host's staged copy before the step), state[1] = 0. The grid is
+ *   fixed by max_count (capacity of the lists). The list is consumed once: the kernel
+ *   sets state[0] back to 0 when it is done, so replaying the step without a new list
+ *   finalises nothing. Launch it before the step's first residual write. */
+int ls_int8_finalize_pending(const void* k_res, const int64_t* res_rows, const int64_t* block_ids,
+                             int32_t* state, void* k_pool, float* k_scale, float* k_zero,
+                             int max_count, int layers, int kv_heads, int head_dim, int page,
+                             int64_t num_rows, int64_t num_blocks, int64_t sr_l, int64_t sr_r,
+                             int64_t sr_p, int64_t sr_h, int64_t sk_l, int64_t sk_b, int64_t sk_p,
+                             int64_t sk_h, int64_t ss_l, int64_t ss_b, int64_t ss_h, int asym, float eps,
+                             float qmax, float inv_qmax, float levels, float inv_levels, float offset,
+                             void* stream);
 
 /* Page scores for sparse selection: Quest upper bound from per-page K min/max,
  * maximised over the R query rows; +inf for page 0 and the `recent` last

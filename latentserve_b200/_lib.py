@@ -47,6 +47,7 @@ _PROTOTYPES = {
     "ls_int8_decode_write": [P, P, P, P, P, P, P, P, I, I, I] + [L] * 6 + [I] + [F] * 6 + [P],
     "ls_int8_finalize_blocks": [P, P, P, P, P, P, I, I, I, I] + [L] * 10 + [I] + [F] * 6 + [P],
     "ls_int8_finalize_layers": [P, P, P, P, P, P, I, I, I, I, I] + [L] * 13 + [I] + [F] * 6 + [P],
+    "ls_int8_finalize_pending": [P, P, P, P, P, P, P, I, I, I, I, I] + [L] * 13 + [I] + [F] * 6 + [P],
     "ls_page_index": [P, P, P, P, P, P] + [I] * 9 + [L] * 7 + [P],
     "ls_page_index_heads": [P, P, P, P, P, P] + [I] * 8 + [L] * 8 + [P],
     "ls_select_pages": [P, P, P, I, I, I, I, F, I, L, L, L, L, P],
@@ -98,4 +99,12 @@ def current_stream(device) -> int:
 
 
 def raw_stream(device_index: int) -> int:
+    """Raw handle of torch's current stream on device `device_index`, which must be
+    the current device: the library launches on whatever device is current, so a
+    stream of another device would fail at launch with an opaque CUDA error (and the
+    allocation-free entry point would take the wrong device's built-in array)."""
+    current = torch.cuda.current_device()
+    if device_index != current:
+        raise RuntimeError(f"tensors live on cuda:{device_index} but the current device is cuda:{current}; "
+                           f"call inside `with torch.cuda.device({device_index}):`")
     return torch._C._cuda_getCurrentRawStream(device_index)

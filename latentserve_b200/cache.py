@@ -164,7 +164,8 @@ class _PagedBase:
         # cache/paged_cache.py:252-273,337-360). An event per image keeps the host from
         # rewriting an image whose copy has not run yet.
         off_i64 = -(-(8 * mb) // 16) * 16
-        self._step_bytes = off_i64 + 32 * mb
+        off_state = off_i64 + 32 * mb               # int32 [4]: pages to finalise, arrivals, padding
+        self._step_bytes = off_state + 16
         self._step_dev = torch.zeros(self._step_bytes, dtype=torch.uint8, device=dev)
 
         def views(buf):
@@ -172,10 +173,11 @@ class _PagedBase:
                     buf[off_i64: off_i64 + 8 * mb].view(torch.int64),
                     buf[off_i64 + 8 * mb: off_i64 + 16 * mb].view(torch.int64),
                     buf[off_i64 + 16 * mb: off_i64 + 24 * mb].view(torch.int64),
-                    buf[off_i64 + 24 * mb: off_i64 + 32 * mb].view(torch.int64))
+                    buf[off_i64 + 24 * mb: off_i64 + 32 * mb].view(torch.int64),
+                    buf[off_state: off_state + 16].view(torch.int32))
 
         (self._seq_lens_buf, self._res_rows_buf, slots_dev, self._k_res_idx_buf, self._fin_rows_buf,
-         self._fin_ids_buf) = views(self._step_dev)
+         self._fin_ids_buf, self._fin_state_buf) = views(self._step_dev)
         self._write_slots_buf = slots_dev.view(mb, 1)
         self._step_host = [torch.zeros(self._step_bytes, dtype=torch.uint8).pin_memory() for _ in range(2)]
         self._step_np = [tuple(v.numpy() for v in views(h)) for h in self._step_host]
@@ -291,7 +293,7 @@ class _PagedBase:
 
     def _stage(self):
         """Host image being filled for this advance(): numpy views (lens, res_rows,
-        slots, res_idx, fin_rows, fin_ids). Opened on first use; starts as a copy of the last one shipped,
+        slots, res_idx, fin_rows, fin_ids, fin_state). Opened on first use; starts as a copy of the last one shipped,
         so fields an advance() does not touch keep their values."""
         if self._step_open is None:
             i = self._step_next
@@ -485,7 +487,8 @@ class Int8PagedKVCache(_PagedBase):
         self.kmin: list = []
         self.kmax: list = []
         self._fin = [0] * mb            # K pages already quantised, per slot (all layers at once)
-        self.deferred_finalize = True   # the only mode: pages finalise in the next advance()
+        self.deferred_finalize = True   # the only mode: a page is finalised in the step after it filled up
+        self.finalize_in_step = False   # see enable_finalize_in_step()
 
     def reset(self) -> None:
         for t in self.tables:
@@ -566,6 +569,26 @@ class Int8PagedKVCache(_PagedBase):
                            self._k_pool_all, self._k_scale_all, self._k_zero_all,
                            **self._quant_consts())
 
+    def enable_finalize_in_step(self) -> None:
+        """Move page finalisation out of `advance()` and into the step itself: the
+        first write of a step (`write` / `rope_write` for layer 0) starts with one
+        launch of a fixed grid that finalises, in every layer, the pages `advance()`
+        listed in the staged image -- their number is read on the device -- before
+        anything overwrites the residual. `advance()` then launches nothing: its
+        device work is the one staged copy. Meant for a captured decode step (the
+        launch becomes the graph's first INT8 node); the reference runs these ops
+        eagerly in `advance()`, between replays (cache/int8_paged_cache.py:443-446).
+        Contract of this mode: every `advance()` is followed by a step that writes
+        layer 0 before the next `advance()` -- what a decode loop does. The kernel
+        consumes the list once, so replaying a step without a new `advance()` is
+        harmless."""
+        self.finalize_in_step = True
+
+    def _finalize_in_step(self) -> None:
+        iw.finalize_pending(self._k_res_all, self._fin_rows_buf, self._fin_ids_buf, self._fin_state_buf,
+                            self._k_pool_all, self._k_scale_all, self._k_zero_all,
+                            **self._quant_consts())
+
     def advance(self, n: int, batch_size: Optional[int] = None,
                 slots: Optional[Sequence[int]] = None) -> None:
         self._activate(batch_size, slots)
@@ -589,8 +612,12 @@ class Int8PagedKVCache(_PagedBase):
                 dtype=torch.int64, device=self.device)
             self._write_slots = self._prefill_slots
             self._decode_slot_vec = None
+        if self.finalize_in_step:
+            state = self._stage()[6]
+            state[0], state[1] = pending, 0
         self._ship_tables(active)
-        self._launch_finalize(pending)
+        if not self.finalize_in_step:
+            self._launch_finalize(pending)
 
     def rope_write(self, layer_idx: int, qkv: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor,
                    positions: torch.Tensor, q_out: torch.Tensor, q_heads: int) -> None:
@@ -600,6 +627,8 @@ class Int8PagedKVCache(_PagedBase):
         slots = self._write_slots
         if slots is None or slots.shape[0] < b or slots.shape[1] != 1:
             raise RuntimeError("call advance(1, batch_size) before rope_write()")
+        if self.finalize_in_step and layer_idx == 0:
+            self._finalize_in_step()
         fe.rope_append_int8(qkv, cos, sin, positions, self._slot_vec(slots, b), self._k_res_idx_buf[:b], q_out,
                             self._flat_v[layer_idx], self._flat_v_scale[layer_idx],
                             self._flat_v_zero[layer_idx] if self.asymmetric else None,
@@ -614,6 +643,8 @@ class Int8PagedKVCache(_PagedBase):
         slots = self._write_slots
         if slots is None or slots.shape[0] < b or slots.shape[1] != n:
             raise RuntimeError("call advance(n, batch_size) before write()")
+        if self.finalize_in_step and layer_idx == 0:
+            self._finalize_in_step()
         if self._bounds_on:                       # bounds of the rows as given (exact fp16 K)
             for j in range(n):
                 kv_write.update_bounds_only(k[:, :, j], self._slot_vec(slots, b) if n == 1 else

@@ -147,24 +147,15 @@ int8_decode_write_kernel(const __half* __restrict__ k, const __half* __restrict_
         *reinterpret_cast<const uint2*>(k + b * sk_b + h * sk_h + lane * 4);
 }
 
-// grid (N, H, layers), block 128: thread = channel, loop over the page's 16 tokens.
-// Layers are the same tensors `s*_l` elements apart (0 for a single layer).
-__global__ void __launch_bounds__(LS_HEAD_DIM)
-int8_finalize_blocks_kernel(const __half* __restrict__ k_res, const long long* __restrict__ res_rows,
-                            const long long* __restrict__ block_ids,
-                            signed char* __restrict__ k_pool, float* __restrict__ k_scale,
-                            float* __restrict__ k_zero, long long num_rows, long long num_blocks,
-                            long long sr_r, long long sr_p, long long sr_h, long long sk_b,
-                            long long sk_p, long long sk_h, long long ss_b, long long ss_h,
-                            long long sr_l, long long sk_l, long long ss_l, QuantConsts c) {
-    const int n = blockIdx.x, h = blockIdx.y, d = threadIdx.x;
-    const long long layer = blockIdx.z;
-    const long long rr = res_rows[n], blk = block_ids[n];
-    if (rr < 0 || rr >= num_rows || blk < 0 || blk >= num_blocks) return;
-    k_res += layer * sr_l;
-    k_pool += layer * sk_l;
-    k_scale += layer * ss_l;
-    if (k_zero != nullptr) k_zero += layer * ss_l;
+// One residual row (a sequence's completed K page, exact fp16) quantised into one
+// pool block, per (head, channel): thread = channel, loop over the page's 16 tokens.
+__device__ __forceinline__ void finalize_page(const __half* __restrict__ k_res,
+                                              signed char* __restrict__ k_pool,
+                                              float* __restrict__ k_scale, float* __restrict__ k_zero,
+                                              long long rr, long long blk, int h, int d, long long sr_r,
+                                              long long sr_p, long long sr_h, long long sk_b,
+                                              long long sk_p, long long sk_h, long long ss_b,
+                                              long long ss_h, const QuantConsts& c) {
     const __half* src = k_res + rr * sr_r + h * sr_h + d;
     float f[LS_PAGE];
 #pragma unroll
@@ -191,6 +182,68 @@ int8_finalize_blocks_kernel(const __half* __restrict__ k_res, const long long* _
             dst[t * sk_p] = (signed char)quant_asym(f[t], lo, step, c.levels, c.offset);
         k_scale[blk * ss_b + h * ss_h + d] = step;
         k_zero[blk * ss_b + h * ss_h + d] = __fadd_rn(lo, __fmul_rn(c.offset, step));
+    }
+}
+
+// grid (N, H, layers), block 128. Layers are the same tensors `s*_l` elements apart
+// (0 for a single layer).
+__global__ void __launch_bounds__(LS_HEAD_DIM)
+int8_finalize_blocks_kernel(const __half* __restrict__ k_res, const long long* __restrict__ res_rows,
+                            const long long* __restrict__ block_ids,
+                            signed char* __restrict__ k_pool, float* __restrict__ k_scale,
+                            float* __restrict__ k_zero, long long num_rows, long long num_blocks,
+                            long long sr_r, long long sr_p, long long sr_h, long long sk_b,
+                            long long sk_p, long long sk_h, long long ss_b, long long ss_h,
+                            long long sr_l, long long sk_l, long long ss_l, QuantConsts c) {
+    const int n = blockIdx.x, h = blockIdx.y, d = threadIdx.x;
+    const long long layer = blockIdx.z;
+    const long long rr = res_rows[n], blk = block_ids[n];
+    if (rr < 0 || rr >= num_rows || blk < 0 || blk >= num_blocks) return;
+    finalize_page(k_res + layer * sr_l, k_pool + layer * sk_l, k_scale + layer * ss_l,
+                  k_zero != nullptr ? k_zero + layer * ss_l : nullptr, rr, blk, h, d, sr_r, sr_p, sr_h,
+                  sk_b, sk_p, sk_h, ss_b, ss_h, c);
+}
+
+// The same work with the page list's LENGTH on the device, so that the launch can be
+// a fixed node of a captured decode step: grid (gx, H, layers) is set at capture, the
+// CTAs stride over the first state[0] entries of res_rows / block_ids, and a step
+// with nothing to finalise costs one read per CTA. The list is consumed once: the
+// last CTA to arrive (state[1] counts arrivals; nobody waits) sets state[0] back to
+// zero, so replaying the step again without a new list -- capture warm-ups, timing
+// loops -- does not quantise a residual row that the append has since started to
+// overwrite.
+__global__ void __launch_bounds__(LS_HEAD_DIM)
+int8_finalize_pending_kernel(const __half* __restrict__ k_res, const long long* __restrict__ res_rows,
+                             const long long* __restrict__ block_ids, int* __restrict__ state,
+                             signed char* __restrict__ k_pool, float* __restrict__ k_scale,
+                             float* __restrict__ k_zero, int max_count, long long num_rows,
+                             long long num_blocks, long long sr_r, long long sr_p, long long sr_h,
+                             long long sk_b, long long sk_p, long long sk_h, long long ss_b,
+                             long long ss_h, long long sr_l, long long sk_l, long long ss_l,
+                             QuantConsts c) {
+    __shared__ int s_count;
+    if (threadIdx.x == 0) s_count = *reinterpret_cast<volatile int*>(state);
+    __syncthreads();
+    const int count = min(s_count, max_count);
+    if (count <= 0) return;                              // the usual step: nothing completed
+    const int h = blockIdx.y, d = threadIdx.x;
+    const long long layer = blockIdx.z;
+    for (int n = blockIdx.x; n < count; n += gridDim.x) {
+        const long long rr = res_rows[n], blk = block_ids[n];
+        if (rr < 0 || rr >= num_rows || blk < 0 || blk >= num_blocks) continue;
+        finalize_page(k_res + layer * sr_l, k_pool + layer * sk_l, k_scale + layer * ss_l,
+                      k_zero != nullptr ? k_zero + layer * ss_l : nullptr, rr, blk, h, d, sr_r, sr_p,
+                      sr_h, sk_b, sk_p, sk_h, ss_b, ss_h, c);
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        // Every CTA has read the count before it arrives here, so the last arrival may clear it.
+        __threadfence();
+        const int total = (int)(gridDim.x * gridDim.y * gridDim.z);
+        if (atomicAdd(state + 1, 1) == total - 1) {
+            state[1] = 0;
+            state[0] = 0;
+        }
     }
 }
 
@@ -291,6 +344,31 @@ int ls_int8_finalize_layers(const void* k_res, const int64_t* res_rows, const in
         static_cast<const __half*>(k_res), reinterpret_cast<const long long*>(res_rows),
         reinterpret_cast<const long long*>(block_ids), static_cast<signed char*>(k_pool), k_scale,
         k_zero, num_rows, num_blocks, sr_r, sr_p, sr_h, sk_b, sk_p, sk_h, ss_b, ss_h, sr_l, sk_l, ss_l, c);
+    return (int)cudaGetLastError();
+}
+
+int ls_int8_finalize_pending(const void* k_res, const int64_t* res_rows, const int64_t* block_ids,
+                             int32_t* state, void* k_pool, float* k_scale, float* k_zero,
+                             int max_count, int layers, int kv_heads, int head_dim, int page,
+                             int64_t num_rows, int64_t num_blocks, int64_t sr_l, int64_t sr_r,
+                             int64_t sr_p, int64_t sr_h, int64_t sk_l, int64_t sk_b, int64_t sk_p,
+                             int64_t sk_h, int64_t ss_l, int64_t ss_b, int64_t ss_h, int asym, float eps,
+                             float qmax, float inv_qmax, float levels, float inv_levels, float offset,
+                             void* stream) {
+    if (!k_res || !res_rows || !block_ids || !state || !k_pool || !k_scale) return LS_ERR_NULL_POINTER;
+    if (asym && !k_zero) return LS_ERR_NULL_POINTER;
+    if (head_dim != LS_HEAD_DIM || page != LS_PAGE) return LS_ERR_UNSUPPORTED;
+    if (max_count <= 0 || layers <= 0 || layers > 65535 || kv_heads <= 0 || kv_heads > 65535)
+        return LS_ERR_BAD_SHAPE;
+    if ((uintptr_t)state & 3) return LS_ERR_MISALIGNED;
+    ls::QuantConsts c = {asym, eps, qmax, inv_qmax, levels, inv_levels, offset};
+    const int gx = max_count < 16 ? max_count : 16;
+    ls::int8_finalize_pending_kernel<<<dim3(gx, kv_heads, layers), LS_HEAD_DIM, 0,
+                                       static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const __half*>(k_res), reinterpret_cast<const long long*>(res_rows),
+        reinterpret_cast<const long long*>(block_ids), state, static_cast<signed char*>(k_pool), k_scale,
+        k_zero, max_count, num_rows, num_blocks, sr_r, sr_p, sr_h, sk_b, sk_p, sk_h, ss_b, ss_h, sr_l, sk_l,
+        ss_l, c);
     return (int)cudaGetLastError();
 }
 

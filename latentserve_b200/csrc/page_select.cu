@@ -20,8 +20,6 @@
 // sums with 31 shuffles for all 32.
 #include "ls_common.cuh"
 
-#include <cstdlib>
-
 namespace ls {
 
 constexpr int kIndexWarps = 4;
@@ -542,11 +540,7 @@ int ls_topk_pages(const float* scores, int32_t* sel, int batch, int kv_heads, in
     if (((uintptr_t)scores & 3) || ((uintptr_t)sel & 3)) return LS_ERR_MISALIGNED;
     const size_t smem = sizeof(unsigned long long) * (size_t)n_pow2;
     // Keys per thread: 4 measured best at 2048 keys (512 threads); 8 beyond 4096.
-    int per_thread = n_pow2 <= 4096 ? 4 : 8;
-    if (const char* env = getenv("LS_TOPK_E")) {
-        const int e = atoi(env);
-        if ((e == 2 || e == 4 || e == 8) && n_pow2 / e <= 1024 && n_pow2 / e >= 32) per_thread = e;
-    }
+    const int per_thread = n_pow2 <= 4096 ? 4 : 8;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const int grid = batch * kv_heads;
 #define LS_LAUNCH_TOPK(E)                                                                          \
@@ -557,8 +551,7 @@ int ls_topk_pages(const float* scores, int32_t* sel, int batch, int kv_heads, in
         ls::topk_pages_kernel<E><<<grid, n_pow2 / E, smem, st>>>(scores, sel, num_pages, n_pow2, k, \
                                                                  kv_heads, ss_b, ss_h, sl_b, sl_h); \
     } while (0)
-    if (per_thread == 2) LS_LAUNCH_TOPK(2);
-    else if (per_thread == 4) LS_LAUNCH_TOPK(4);
+    if (per_thread == 4) LS_LAUNCH_TOPK(4);
     else LS_LAUNCH_TOPK(8);
 #undef LS_LAUNCH_TOPK
     return (int)cudaGetLastError();

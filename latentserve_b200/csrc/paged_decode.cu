@@ -101,7 +101,8 @@ constexpr int kRP = 8;                          // query rows held per partial
 struct PageItem {
     int blk;
     int valid;      // tokens of the page that exist (0 = skip)
-    int last;       // 1 if this is the sequence's last page
+    int last;       // bit 0: the sequence's last page; bit 1: a page the step before this
+                    // launch may still be writing (never requested ahead of the dependency wait)
 };
 
 // Lookahead over a warp's page sequence. Lane j of the warp holds the block id
@@ -139,7 +140,10 @@ struct PageWindow {
             if (id >= 0 && id < p.num_blocks) {
                 b_ = id;
                 v_ = min(LS_PAGE, cached_len - page * LS_PAGE);
-                l_ = page == np - 1;
+                // INT8 pools: the page before the last is rewritten (K bytes and K scales,
+                // by the page-finalize kernel) in the step whose new token opened the last
+                // page, so it counts as mutable too; every earlier page is final.
+                l_ = (page == np - 1 ? 1 : 0) | ((p.k_scale != nullptr && page >= np - 2) ? 2 : 0);
             } else {
                 p.seg_range[2 * p.batch] = 1;      // corrupt table: read nothing, flag it
             }
@@ -639,7 +643,7 @@ struct PoolInt8 {
     // meta = valid tokens | (K came from the residual) << 8
     static __device__ __forceinline__ int issue(const DecodeParams& p, int b, int h,
                                                 const PageItem& it, uint32_t stage, int lane) {
-        bool from_res = p.k_res != nullptr && it.last && it.valid > 0;
+        bool from_res = p.k_res != nullptr && (it.last & 1) && it.valid > 0;
         int rr = from_res ? p.res_rows[b] : 0;
         if (rr < 0 || rr >= p.num_res_rows) {             // corrupt row index: read nothing, flag it
             if (lane == 0) p.seg_range[2 * p.batch] = 1;
@@ -734,7 +738,7 @@ struct PoolInt8Tma {
     static __device__ __forceinline__ int issue(const DecodeParams& p, const TmaMaps& maps, int b,
                                                 int h, const PageItem& it, uint32_t stage,
                                                 uint32_t mbar, int lane) {
-        const bool from_res = p.k_res != nullptr && it.last && it.valid > 0;
+        const bool from_res = p.k_res != nullptr && (it.last & 1) && it.valid > 0;
         if (from_res) {
             const int rr = p.res_rows[b];
             if ((rr < 0 || rr >= p.num_res_rows) && lane == 0) p.seg_range[2 * p.batch] = 1;
@@ -1156,7 +1160,10 @@ decode_kernel(const DecodeParams p, const __grid_constant__ TmaMaps maps) {
     // With LS_EARLY_PAGES the first pages are requested before the dependency
     // wait as well: a decode step's predecessor (the KV append) writes only the
     // newest token, which lies in its sequence's last page, so every other page
-    // is immutable; a warp waits before it requests a last page.
+    // is immutable; a warp waits before it requests a last page. An INT8 cache also
+    // rewrites the page before the last one (its K page is quantised, by a kernel that
+    // precedes the append, in the step after it filled up), so there the wait comes
+    // before either of a sequence's two last pages.
     PageWindow<MODE> win;
     const bool early = MODE == LS_MODE_DENSE && p.early != 0;
     if (MODE == LS_MODE_DENSE && has_work)

@@ -240,6 +240,10 @@ class GraphedStep:
         self.positions = torch.zeros(batch, dtype=torch.long, device=dev)
         self.next_tokens = torch.zeros(batch, dtype=torch.long, device=dev)
         self.graph: Optional[torch.cuda.CUDAGraph] = None
+        # INT8 cache: completed K pages are quantised by the step's first launch, not by
+        # advance() between replays.
+        if hasattr(cache, "enable_finalize_in_step"):
+            cache.enable_finalize_in_step()
 
     def _run(self):
         # Positions are the cache's lengths minus one: taken on the device, inside the

@@ -118,3 +118,36 @@ def finalize_layers(k_residual: torch.Tensor, res_rows: torch.Tensor, block_ids:
         int(asym), eps, qmax, _reciprocal(qmax), levels, _reciprocal(levels), offset,
         _lib.current_stream(k_pool.device))
     _lib.check(rc, "int8 finalize_layers")
+
+
+def finalize_pending(k_residual: torch.Tensor, res_rows: torch.Tensor, block_ids: torch.Tensor,
+                     state: torch.Tensor, k_pool: torch.Tensor, k_scale: torch.Tensor,
+                     k_zero: Optional[torch.Tensor] = None, *, eps: float, qmax: float,
+                     levels: float, offset: float) -> None:
+    """`finalize_layers` with the number of pages on the device: `state` int32 [2]
+    holds (pages to finalise, 0); the kernel finalises the first state[0] entries of
+    `res_rows` / `block_ids` in every layer and sets state[0] back to zero. Always one
+    launch of a fixed grid (sized by the lists' capacity), so it can be a node of a
+    captured decode step; a step with nothing to finalise costs one read per CTA."""
+    if res_rows.dtype != torch.int64 or block_ids.dtype != torch.int64:
+        raise ValueError("res_rows and block_ids must be int64 vectors")
+    if state.dtype != torch.int32 or state.numel() < 2 or not state.is_contiguous():
+        raise ValueError("state must be a contiguous int32 tensor of two entries")
+    if k_residual.dim() != 5 or k_pool.dim() != 5 or k_scale.dim() != 4 or k_pool.shape[0] != k_residual.shape[0]:
+        raise ValueError("finalize_pending takes layer-stacked tensors")
+    if k_residual.stride(-1) != 1 or k_pool.stride(-1) != 1 or k_scale.stride(-1) != 1:
+        raise ValueError("channels must be unit-stride")
+    asym = k_zero is not None
+    if asym and k_zero.stride() != k_scale.stride():
+        raise ValueError("k_zero must share k_scale's layout")
+    rc = _lib.lib().ls_int8_finalize_pending(
+        k_residual.data_ptr(), res_rows.data_ptr(), block_ids.data_ptr(), state.data_ptr(),
+        k_pool.data_ptr(), k_scale.data_ptr(), _lib.ptr(k_zero),
+        min(res_rows.numel(), block_ids.numel()), k_pool.shape[0], k_pool.shape[3], k_pool.shape[4],
+        k_pool.shape[2], k_residual.shape[1], k_pool.shape[1],
+        k_residual.stride(0), k_residual.stride(1), k_residual.stride(2), k_residual.stride(3),
+        k_pool.stride(0), k_pool.stride(1), k_pool.stride(2), k_pool.stride(3),
+        k_scale.stride(0), k_scale.stride(1), k_scale.stride(2),
+        int(asym), eps, qmax, _reciprocal(qmax), levels, _reciprocal(levels), offset,
+        _lib.current_stream(k_pool.device))
+    _lib.check(rc, "int8 finalize_pending")

@@ -151,20 +151,31 @@ def seg_len(batch: int, kv_heads: int) -> int:
     return 2 * batch + 2 + batch * kv_heads
 
 
+def seg_scratch(tag: str, batch: int, kv_heads: int, device) -> torch.Tensor:
+    """The bookkeeping scratch of one (batch, KV heads) shape. Its layout depends
+    on the batch size (slot ranges in [0, 2B), the error flag at [2B], arrival
+    counters from [2B + 2)), and the arrival counters must read zero when a launch
+    starts, so the buffer is keyed by the shape, never by its flat length: (5, 2)
+    and (2, 8) are both 22 ints long, and one's slot ranges would be the other's
+    counters."""
+    return scratch(f"{tag}_seg_b{batch}_h{kv_heads}", (seg_len(batch, kv_heads),), torch.int32,
+                   device, zero=True)
+
+
 def _partials(q: torch.Tensor, chunks: int, tag: str):
     b, h = q.shape[0], q.shape[1]
     slots = b + chunks
     acc = scratch(tag + "_acc", (slots, h, ROWS_PER_PARTIAL, 128), torch.float32, q.device)
     m = scratch(tag + "_m", (slots, h, ROWS_PER_PARTIAL), torch.float32, q.device)
     l = scratch(tag + "_l", (slots, h, ROWS_PER_PARTIAL), torch.float32, q.device)
-    seg = scratch(tag + "_seg", (seg_len(b, h),), torch.int32, q.device, zero=True)
+    seg = seg_scratch(tag, b, h, q.device)
     return acc, m, l, seg
 
 
 def error_flag(device, batch: int, kv_heads: int = 2, tag: str = "cuda") -> int:
     """1 if a launch at this batch size met a block id (or residual row)
     outside its pool and skipped it. Reading it synchronises; for tests."""
-    seg = _SCRATCH.get((tag + "_seg", (seg_len(batch, kv_heads),), torch.int32,
+    seg = _SCRATCH.get((f"{tag}_seg_b{batch}_h{kv_heads}", (seg_len(batch, kv_heads),), torch.int32,
                         str(torch.device(device))))
     return 0 if seg is None else int(seg[2 * batch].item())
 

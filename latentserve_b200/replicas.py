@@ -32,15 +32,18 @@ def partition_by_tokens(lens: Sequence[int], world: int) -> list[list[int]]:
     return shards
 
 
-def max_over_ranks(value: float, dist=None, device=None) -> float:
-    """The slowest rank's time: what a multi-replica number must be quoted on."""
-    if dist is None or not dist.is_initialized() or dist.get_world_size() == 1:
-        return float(value)
-    import torch
+def max_over_ranks(value, dist=None, device=None):
+    """The slowest rank's time: what a multi-replica number must be quoted on.
+    A float, or a list of times reduced element by element."""
+    many = isinstance(value, (list, tuple))
+    values = [float(v) for v in value] if many else [float(value)]
+    if dist is not None and dist.is_initialized() and dist.get_world_size() > 1:
+        import torch
 
-    t = torch.tensor([float(value)], dtype=torch.float64, device=device or "cpu")
-    dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    return float(t.item())
+        t = torch.tensor(values, dtype=torch.float64, device=device or "cpu")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        values = [float(x) for x in t.tolist()]
+    return values if many else values[0]
 
 
 def aggregate_throughput(units_per_rank: float, seconds: float, world: int) -> float:

@@ -13,10 +13,12 @@ HAS_RES, MIN_BLOCKS).
 
 from __future__ import annotations
 
+import os
 import pathlib
 import shutil
 import subprocess
 import sys
+from typing import Optional
 
 HERE = pathlib.Path(__file__).resolve().parent
 OUT = HERE / "_ref"
@@ -24,15 +26,31 @@ OUT = HERE / "_ref"
 TARGETS = (
     ("paged_decode_fp16.cubin", "paged_decode_fp16.cu", ()),
     ("paged_decode_int8.cubin", "paged_decode_int8.cu", ("-DASYM=0", "-DHAS_RES=1", "-DMIN_BLOCKS=12")),
+    # page_bounds_update, page_index, page_index_heads and paged_sparse_fp16 in one module
+    # (kernels/cuda/paged_sparse.py:43-57 passes PAGES_PER_WARP = 16)
+    ("paged_sparse_fp16.cubin", "paged_sparse_fp16.cu", ("-DPAGES_PER_WARP=16",)),
 )
 COMMON = ("-DHEAD_DIM=128", "-DNREP=6", "-DPAGE=16", "-DTOKG=4")
 
 
-def build(reference_root: str = "/root/reference") -> list[pathlib.Path]:
-    src_dir = pathlib.Path(reference_root) / "kernels" / "cuda"
+def reference_checkout() -> Optional[pathlib.Path]:
+    """A LatentServe source checkout, if one is at hand: the directory
+    `LATENTSERVE_REFERENCE` names, else a `reference` directory beside this
+    repository. None when neither holds the kernel sources."""
+    for cand in (os.environ.get("LATENTSERVE_REFERENCE"), HERE.parent.parent / "reference"):
+        if cand and (pathlib.Path(cand) / "kernels" / "cuda" / "paged_decode_fp16.cu").is_file():
+            return pathlib.Path(cand)
+    return None
+
+
+def build(reference_root=None) -> list[pathlib.Path]:
+    root = pathlib.Path(reference_root) if reference_root else reference_checkout()
+    if root is None:
+        raise FileNotFoundError("no LatentServe checkout: set LATENTSERVE_REFERENCE")
+    src_dir = root / "kernels" / "cuda"
     nvcc = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
     if not src_dir.is_dir():
-        raise FileNotFoundError(f"no LatentServe checkout at {reference_root}")
+        raise FileNotFoundError(f"no LatentServe checkout at {root}")
     OUT.mkdir(exist_ok=True)
     built = []
     for name, src, extra in TARGETS:

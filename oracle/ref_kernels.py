@@ -35,17 +35,18 @@ def _check(res):
     return res[1] if len(res) == 2 else res[1:]
 
 
-def _function(name: str):
+def _function(name: str, module: Optional[str] = None):
+    """Kernel `name` of `oracle/_ref/<module>.cubin` (module = name by default)."""
     from cuda.bindings import driver
 
     dev = torch.cuda.current_device()
-    key = (name, dev)
+    key = (name, module or name, dev)
     if key not in _FUNCS:
         torch.cuda.init()
         torch.zeros(1, device="cuda")                      # make sure the primary context is current
-        data = (REF_DIR / f"{name}.cubin").read_bytes()
-        module = _check(driver.cuModuleLoadData(data))
-        _FUNCS[key] = (module, _check(driver.cuModuleGetFunction(module, name.encode())))
+        data = (REF_DIR / f"{module or name}.cubin").read_bytes()
+        mod = _check(driver.cuModuleLoadData(data))
+        _FUNCS[key] = (mod, _check(driver.cuModuleGetFunction(mod, name.encode())))
     return _FUNCS[key][1]
 
 
@@ -110,3 +111,59 @@ class RefDecode:
         w = torch.where(torch.isinf(mg) & (mg < 0), torch.zeros_like(m), torch.exp(m - mg))
         den = (l * w).sum(dim=2).clamp_min(1e-20)
         return ((acc * w.unsqueeze(-1)).sum(dim=2) / den.unsqueeze(-1)).to(torch.float16)
+
+
+class RefSparse:
+    """The reference's sparse trio for one layer call, as its host code runs it
+    (kernels/cuda/paged_sparse.py:104-123, 164-168, 185-251): `page_index` (grid
+    (B, H, ceil(max_pages / 64)), 128 threads), `torch.topk(sorted=True)` with the
+    cast to int32, then `paged_sparse_fp16` (grid (B, splits, H), one warp) after
+    the fills of its m / l scratch. `launch()` enqueues all of it on torch's current
+    stream; `combine()` is the torch form of the merge (the reference's is Triton)."""
+
+    def __init__(self, q, k_pool, v_pool, block_tables, seq_lens, kmin, kmax, ratio: float,
+                 max_seq_len: int, recent: int = 2, softmax_scale: Optional[float] = None):
+        b, h, r, d = q.shape
+        self.shape = (b, h, r, d)
+        self.index_fn = _function("page_index", "paged_sparse_fp16")
+        self.attend_fn = _function("paged_sparse_fp16")
+        self.max_pages = block_tables.shape[1]
+        pages = min(self.max_pages, -(-max_seq_len // k_pool.shape[1]))
+        self.k = pages if ratio >= 1.0 else min(pages, max(recent + 1, math.ceil(ratio * pages)))
+        self.splits = max(1, min(choose_splits(b, h, self.k), self.k))
+        dev = q.device
+        self.scores = torch.empty((b, h, self.max_pages), dtype=torch.float32, device=dev)
+        self.acc = torch.empty((b, h, self.splits, 16, d), dtype=torch.float32, device=dev)
+        self.m = torch.empty((b, h, self.splits, 16), dtype=torch.float32, device=dev)
+        self.l = torch.empty((b, h, self.splits, 16), dtype=torch.float32, device=dev)
+        self.sel = torch.zeros((b, h, self.k), dtype=torch.int32, device=dev)
+        scale = softmax_scale if softmax_scale is not None else 1.0 / math.sqrt(d)
+        P, I, L, F = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong, ctypes.c_float
+        self.index_params = (
+            (q.data_ptr(), kmin.data_ptr(), kmax.data_ptr(), block_tables.data_ptr(), seq_lens.data_ptr(),
+             self.scores.data_ptr(), self.max_pages, recent, *q.stride()[:3], *kmin.stride()[:2],
+             *self.scores.stride()[:2]),
+            (P,) * 6 + (I, I) + (L,) * 7)
+        self.attend_params = (
+            (q.data_ptr(), k_pool.data_ptr(), v_pool.data_ptr(), block_tables.data_ptr(),
+             seq_lens.data_ptr(), self.sel.data_ptr(), float(ratio), recent, self.acc.data_ptr(),
+             self.m.data_ptr(), self.l.data_ptr(), self.max_pages, self.k, self.splits, *q.stride()[:3],
+             *k_pool.stride()[:3], *self.sel.stride()[:2], *self.acc.stride()[:4], *self.m.stride()[:3],
+             scale),
+            (P,) * 6 + (F, I) + (P,) * 3 + (I,) * 3 + (L,) * 15 + (F,))
+        self.keep = (q, k_pool, v_pool, block_tables, seq_lens, kmin, kmax)
+
+    def launch(self) -> None:
+        from cuda.bindings import driver
+
+        b, h, _, _ = self.shape
+        stream = torch.cuda.current_stream().cuda_stream
+        grid_z = -(-self.max_pages // 64)
+        _check(driver.cuLaunchKernel(self.index_fn, b, h, grid_z, 128, 1, 1, 0, stream, self.index_params, 0))
+        self.sel.copy_(torch.topk(self.scores, self.k, dim=-1, sorted=True).indices)    # topk + cast to int32
+        self.m.fill_(float("-inf"))
+        self.l.zero_()
+        _check(driver.cuLaunchKernel(self.attend_fn, b, self.splits, h, 32, 1, 1, 0, stream,
+                                     self.attend_params, 0))
+
+    combine = RefDecode.combine

@@ -3,12 +3,16 @@ no such tree is on the path (the library itself never needs one)."""
 
 import importlib
 import os
+import pathlib
 import sys
 
 import pytest
 import torch
 
-REF = os.environ.get("LATENTSERVE_REFERENCE", "/root/reference")
+from oracle.build_ref import reference_checkout
+
+# A source checkout if one is at hand, else the copy installed under baseline/_ref.
+REF = str(reference_checkout() or pathlib.Path(__file__).resolve().parents[1] / "baseline" / "_ref")
 have_reference = os.path.isdir(os.path.join(REF, "kernels", "cuda"))
 pytestmark = pytest.mark.skipif(not have_reference, reason="no LatentServe tree to install into")
 

@@ -231,6 +231,23 @@ def test_corrupt_block_ids_are_skipped_and_flagged_not_read():
     assert pdc.error_flag(device(), 2, 2) == 1
 
 
+def test_batch_shapes_with_equally_long_bookkeeping_do_not_share_it():
+    """(5 sequences, 2 KV heads) and (2 sequences, 8 KV heads) both need 22 ints of
+    bookkeeping, laid out differently: slot ranges of the first would be arrival
+    counters of the second. Each shape has its own buffer, so both calls, in either
+    order and repeated, match the oracle."""
+    a = synthetic.dense_case([3000, 1500, 900, 2200, 4000], h=2, seed=60)      # several segments each
+    b = synthetic.dense_case([3500, 2600], h=8, seed=61)
+    assert pdc.seg_len(5, 2) == pdc.seg_len(2, 8)
+    ta, tb = on_device(a), on_device(b)
+    want_a = orc.paged_decode(a["q"], a["k_pool"], a["v_pool"], a["block_tables"], a["seq_lens"])
+    want_b = orc.paged_decode(b["q"], b["k_pool"], b["v_pool"], b["block_tables"], b["seq_lens"])
+    for _ in range(2):
+        close(_run(ta), want_a)
+        close(_run(tb), want_b)
+    assert pdc.seg_scratch("cuda", 5, 2, device()).data_ptr() != pdc.seg_scratch("cuda", 2, 8, device()).data_ptr()
+
+
 def test_partials_then_stand_alone_combine_equal_the_fused_launch():
     from latentserve_b200 import _lib
 

@@ -397,3 +397,128 @@ def test_cache_decode_steps_reproduce_the_reference_cache_bytes(asym, golden_dir
                             **{k: v.cpu().numpy() for k, v in extra.items()})
     close(got, want)
     close(got, g["out"], atol=2e-2)
+
+
+def test_finalize_pending_reads_its_count_on_the_device_and_consumes_it_once():
+    """The in-step form of page finalisation: same bytes as the host-counted launch,
+    the count comes from device memory, and a second launch without a new list
+    changes nothing even though the residual has moved on."""
+    dev = device()
+    rng = np.random.default_rng(19)
+    layers, rows, h, d, nb = 3, 6, 2, 128, 24
+    res = torch.from_numpy((rng.standard_normal((layers, rows, 16, h, d)) * 2).astype(np.float16)).to(dev)
+    pick = torch.tensor([4, 1, 5, 0, 0, 0], device=dev)              # capacity 6, three in use
+    ids = torch.tensor([7, 23, 2, 0, 0, 0], device=dev)
+    consts = CONSTS
+    want_pool = torch.zeros(layers, nb, 16, h, d, dtype=torch.int8, device=dev)
+    want_scale = torch.ones(layers, nb, h, d, device=dev)
+    iw.finalize_layers(res, pick, ids, 3, want_pool, want_scale, None, **consts)
+    pool, scale = torch.zeros_like(want_pool), torch.ones_like(want_scale)
+    state = torch.tensor([3, 0, 0, 0], dtype=torch.int32, device=dev)
+    iw.finalize_pending(res, pick, ids, state, pool, scale, None, **consts)
+    torch.cuda.synchronize()
+    assert torch.equal(pool, want_pool) and torch.equal(scale, want_scale)
+    assert state.tolist()[:2] == [0, 0]                              # consumed, arrivals reset
+    res.mul_(0.5)                                                    # the residual moves on
+    iw.finalize_pending(res, pick, ids, state, pool, scale, None, **consts)
+    torch.cuda.synchronize()
+    assert torch.equal(pool, want_pool) and torch.equal(scale, want_scale)
+    # A count past the lists' capacity is clamped; out-of-range entries are skipped.
+    state.copy_(torch.tensor([99, 0, 0, 0], dtype=torch.int32))
+    ids[3:] = torch.tensor([nb + 5, -1, 10_000_000], device=dev)
+    iw.finalize_pending(res, pick, ids, state, pool, scale, None, **consts)
+    torch.cuda.synchronize()
+    untouched = torch.ones(nb, dtype=torch.bool, device=dev)
+    untouched[ids[:3]] = False
+    assert (pool[:, untouched] == 0).all() and state.tolist()[:2] == [0, 0]
+
+
+def _int8_decode_loop(programmatic: bool, graphed: bool, in_step: bool, steps: int = 44):
+    """Prefill four sequences, then `steps` decode steps of two layers (write +
+    attention per layer) over an Int8PagedKVCache; returns every step's outputs and
+    the cache in its final state, and the last step's queries."""
+    from latentserve_b200 import paged_decode as pd
+
+    dev = device()
+    layers, batch = 2, 4
+    spec = lc.KVCacheSpec(num_layers=layers, num_kv_heads=2, head_dim=128, max_seq_len=1024,
+                          max_batch_size=batch, device="cuda")
+    cache = lc.Int8PagedKVCache(spec, num_blocks=4 * 64 + 8)
+    if in_step:
+        cache.enable_finalize_in_step()
+    g = torch.Generator(device=dev).manual_seed(77)
+    for i, n in enumerate([700, 333, 130, 47]):                      # 47: completes a page at once
+        cache.advance(n, slots=[i])
+        for layer in range(layers):
+            k = torch.randn(1, 2, n, 128, dtype=torch.float16, device=dev, generator=g)
+            v = torch.randn(1, 2, n, 128, dtype=torch.float16, device=dev, generator=g)
+            cache.write(layer, k, v)
+    feed_k = torch.randn(steps, layers, batch, 2, 1, 128, dtype=torch.float16, device=dev, generator=g)
+    feed_v = torch.randn(steps, layers, batch, 2, 1, 128, dtype=torch.float16, device=dev, generator=g)
+    feed_q = torch.randn(steps, layers, batch, 2, 6, 128, dtype=torch.float16, device=dev, generator=g)
+    k_in, v_in, q_in = feed_k[0].clone(), feed_v[0].clone(), feed_q[0].clone()
+    out = torch.zeros(layers, batch, 2, 6, 128, dtype=torch.float16, device=dev)
+
+    def body():
+        for layer in range(layers):
+            cache.write(layer, k_in[layer], v_in[layer])
+            pd.paged_decode_attention(
+                q_in[layer], cache.k_pool[layer], cache.v_pool[layer], cache.block_tables_tensor(batch),
+                cache.seq_lens_tensor(batch), k_scale=cache.k_scale_pool[layer],
+                v_scale=cache.v_scale_pool[layer], max_seq_len=1024, k_residual=cache.residual(layer),
+                res_rows=cache.residual_rows_tensor(batch), out=out[layer])
+
+    pdc.set_programmatic_launch(programmatic, early_pages=True)
+    pd.set_decode_backend("cuda")
+    outs, graph = [], None
+    try:
+        for s in range(steps):
+            cache.advance(1, batch_size=batch)
+            k_in.copy_(feed_k[s]); v_in.copy_(feed_v[s]); q_in.copy_(feed_q[s])
+            if graphed and graph is None:
+                side = torch.cuda.Stream()
+                side.wait_stream(torch.cuda.current_stream())
+                with torch.cuda.stream(side):
+                    body()                                           # warm-up run of this very step
+                torch.cuda.current_stream().wait_stream(side)
+                torch.cuda.synchronize()
+                graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graph):
+                    body()
+            if graph is not None:
+                graph.replay()
+            else:
+                body()
+            outs.append(out.clone())
+        torch.cuda.synchronize()
+    finally:
+        pdc.set_programmatic_launch(False)
+    assert pdc.error_flag(dev, batch, tag="cuda_i8") == 0
+    return outs, cache, feed_q[-1]
+
+
+def test_int8_programmatic_launch_with_early_pages_across_page_finalisation(loader):
+    """44 steps take every sequence across two or three page boundaries, so pages are
+    quantised (rewritten) between steps while the next attention launch is already
+    requesting old pages ahead of its dependency wait. Outputs and cache bytes must
+    equal the plain-launch run bit for bit: eager, replayed from a graph, and with
+    the finalisation inside the captured step."""
+    base, c0, last_q = _int8_decode_loop(programmatic=False, graphed=False, in_step=False)
+    for programmatic, graphed, in_step in [(True, False, False), (True, True, False),
+                                           (True, True, True), (False, True, True),
+                                           (True, False, True)]:
+        got, c1, _ = _int8_decode_loop(programmatic, graphed, in_step)
+        for s, (a, b) in enumerate(zip(base, got)):
+            assert torch.equal(a, b), f"step {s} differs (programmatic={programmatic}, " \
+                                      f"graphed={graphed}, in_step={in_step})"
+        assert torch.equal(c0._k_pool_all, c1._k_pool_all) and torch.equal(c0._k_scale_all, c1._k_scale_all)
+        assert all(torch.equal(a, b) for a, b in zip(c0.v_pool, c1.v_pool))
+    # The reference run itself against the oracle on the cache's final state.
+    layer = 1
+    want = orc.paged_decode(
+        last_q[layer].cpu().numpy(),
+        c0.k_pool[layer].cpu().numpy(), c0.v_pool[layer].cpu().numpy(),
+        c0.block_tables_tensor(4).cpu().numpy(), c0.seq_lens_tensor(4).cpu().numpy(),
+        k_scale=c0.k_scale_pool[layer].cpu().numpy(), v_scale=c0.v_scale_pool[layer].cpu().numpy(),
+        k_residual=c0.residual(layer).cpu().numpy(), res_rows=c0.residual_rows_tensor(4).cpu().numpy())
+    close(base[-1][layer], want)

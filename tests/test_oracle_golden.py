@@ -183,3 +183,35 @@ def test_elementwise_restatements_match_the_reference_forms(golden_dir):
     q = orc.rope(g["q"].reshape(3, 12, 128), g["cos"].reshape(3, 1, 128), g["sin"].reshape(3, 1, 128))
     k = orc.rope(g["k"].reshape(3, 2, 128), g["cos"].reshape(3, 1, 128), g["sin"].reshape(3, 1, 128))
     assert np.array_equal(q.reshape(3, 1, -1), g["rope_q"]) and np.array_equal(k.reshape(3, 1, -1), g["rope_k"])
+
+
+@pytest.mark.parametrize("name", sorted(DENSE))
+def test_the_timed_cpu_baseline_is_the_same_function(name, golden_dir):
+    """`paged_decode_torch_cpu` is what bench.py times as the CPU baseline and as the
+    reference arm: pinned to the reference's own output and to the numpy oracle, on
+    ragged batches (padding and masking included)."""
+    import torch
+
+    g = np.load(golden_dir / f"{name}.npz")
+    c = DENSE[name]()
+    got = orc.paged_decode_torch_cpu(*(torch.from_numpy(c[k]) for k in
+                                       ("q", "k_pool", "v_pool", "block_tables", "seq_lens"))).numpy()
+    np.testing.assert_allclose(got, g["out_splits1"], atol=5e-6, rtol=1e-5)
+    want = orc.paged_decode(c["q"], c["k_pool"], c["v_pool"], c["block_tables"], c["seq_lens"])
+    np.testing.assert_allclose(got, want, atol=5e-6, rtol=1e-5)
+
+
+def test_the_timed_cpu_baseline_honours_the_softmax_scale_and_a_compact_pool():
+    """The bench hands it a pool renumbered to the sample's own blocks."""
+    import torch
+
+    c = synthetic.dense_case([200, 77, 16], seed=5)
+    blocks = c["block_tables"].reshape(-1)
+    compact = dict(c, k_pool=c["k_pool"][blocks], v_pool=c["v_pool"][blocks],
+                   block_tables=np.arange(blocks.size, dtype=np.int32).reshape(c["block_tables"].shape))
+    got = orc.paged_decode_torch_cpu(*(torch.from_numpy(compact[k]) for k in
+                                       ("q", "k_pool", "v_pool", "block_tables", "seq_lens")),
+                                     softmax_scale=0.05).numpy()
+    want = orc.paged_decode(c["q"], c["k_pool"], c["v_pool"], c["block_tables"], c["seq_lens"],
+                            softmax_scale=0.05)
+    np.testing.assert_allclose(got, want, atol=5e-6, rtol=1e-5)

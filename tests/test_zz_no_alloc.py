@@ -67,3 +67,24 @@ def test_shapes_past_the_fixed_scratch_are_refused():
     big = on_device(synthetic.dense_case([16] * 65, seed=44))
     rc, _ = _noalloc(big, 8)                       # 65 sequences > 64
     assert rc == -8
+
+
+def test_a_block_id_outside_the_pool_is_skipped_not_read():
+    """The kernel checks every block id against the pool size on the device and
+    skips a page whose id is out of range, so a corrupt table cannot make this
+    entry point read outside the pool. The flag that records the skip lives in the
+    built-in array, which this entry point gives no way to read: the call still
+    returns 0 and the output is finite, computed without that page."""
+    case = synthetic.dense_case([64, 64], seed=45)
+    t = on_device(case)
+    t["block_tables"][1, 2] = 10_000_000
+    rc, got = _noalloc(t, pdc.choose_chunks(device(), 2, None, 2))
+    torch.cuda.synchronize()
+    assert rc == 0 and torch.isfinite(got).all()
+    # Sequence 0 is untouched by the bad entry; sequence 1 equals attention without page 2.
+    want = orc.paged_decode(case["q"], case["k_pool"], case["v_pool"], case["block_tables"], case["seq_lens"])
+    close(got[0:1], want[0:1])
+    sel = np.array([[[0, 1, 3], [0, 1, 3]]] * 2, dtype=np.int32)
+    without = orc.sparse_decode(case["q"], case["k_pool"], case["v_pool"], case["block_tables"],
+                                case["seq_lens"], sel)
+    close(got[1:2], without[1:2])
