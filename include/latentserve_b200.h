@@ -83,7 +83,7 @@ extern "C" {
  *                                        before first use.
  * None of it needs filling between calls. `num_chunks` x H is the grid: the
  * fp16 kernels are sized for 2 resident CTAs per SM and the INT8 kernels for
- * 3, so num_chunks = 2*SMs / H (3*SMs / H for INT8) is the natural choice; `min_chunk` (>= 1) is the fewest pages a chunk may hold.
+ * 4, so num_chunks = 2*SMs / H (4*SMs / H for INT8) is the natural choice; `min_chunk` (>= 1) is the fewest pages a chunk may hold.
  * If `out` is non-NULL the same launch also merges the partials — the CTA that
  * delivers a sequence's last partial does it, nobody waits — and `out`
  * receives fp16 [B, H, R, 128] with the given strides; sequences of length 0
@@ -122,9 +122,16 @@ int ls_paged_decode_fp16(const void* q, const void* k_pool, const void* v_pool,
  *   LS_ERR_NOALLOC_LIMIT and nothing is launched. `out` is required.
  *   The first call on a device resolves the array's device address
  *   (cudaGetSymbolAddress, with that device current): make it before any
- *   stream capture starts. Calls share the array: its bookkeeping part is
- *   cleared on `stream` at the start of every call, and calls whose kernels
- *   overlap on one GPU race — keep them ordered. Allocates nothing. */
+ *   stream capture starts. The address is remembered per device ordinal for the
+ *   life of the process and does not survive a cudaDeviceReset; `stream` must
+ *   belong to the device that is current at the call. Calls share the array: its
+ *   bookkeeping part is cleared on `stream` at the start of every call, and calls
+ *   whose kernels overlap on one GPU race — keep them ordered. Allocates nothing.
+ *   Block ids are checked against num_blocks on the device and a page with an id
+ *   outside the pool is skipped, never read; the word that records such a skip
+ *   lives in the built-in array and this entry point offers no way to read it, so
+ *   a caller with an untrusted block table validates it on the host (the ordinary
+ *   entry point reports it in seg_range[2B]). */
 int ls_paged_decode_fp16_noalloc(const void* q, const void* k_pool, const void* v_pool,
                                  const int32_t* block_tables, const int32_t* seq_lens, void* out,
                                  int batch, int kv_heads, int n_rep, int head_dim, int page,
@@ -279,6 +286,26 @@ int ls_page_index(const void* q, const void* kmin, const void* kmax, const int32
                   int head_dim, int page, int max_pages, int table_stride, int num_blocks,
                   int recent, int64_t sq_b, int64_t sq_h, int64_t sq_m, int64_t sb_b, int64_t sb_h,
                   int64_t ss_b, int64_t ss_h, void* stream);
+
+/* ls_page_index followed by ls_select_pages (below) behind one call, with the launch
+ * flags the other entry points take. Same scores, same selection.
+ * Replaces `page_scores` + `select` as `sparse_attention` runs them back to back,
+ * kernels/cuda/paged_sparse.py:222-251.
+ *   scores float [B,H,max_pages] (written); sel int32 [B,H,k] (written).
+ *   flags: LS_LAUNCH_PROGRAMMATIC, and with it LS_EARLY_PAGES: block ids and page bounds are
+ *   requested before the index kernel synchronises on the previous kernel of the stream. Only
+ *   set that when nothing between the previous step and this launch writes block_tables,
+ *   seq_lens or the bounds of any page but a sequence's last (the bounds it reads are never a
+ *   last page's, given recent >= 1; with recent == 0 the flag is ignored). (Folding the
+ *   selection into the index kernel's last-arriving CTA per row was built and measured: a
+ *   128-thread CTA selects slower than the 512-thread kernel does, 51 against 46 us per
+ *   layer call at 8 x 32 768, so the two stay separate launches.) */
+int ls_page_index_select(const void* q, const void* kmin, const void* kmax, const int32_t* block_tables,
+                         const int32_t* seq_lens, float* scores, int32_t* sel, int batch, int kv_heads,
+                         int n_rep, int head_dim, int page, int max_pages, int table_stride,
+                         int num_blocks, int recent, int k, float ratio, int flags, int64_t sq_b,
+                         int64_t sq_h, int64_t sq_m, int64_t sb_b, int64_t sb_h, int64_t ss_b, int64_t ss_h,
+                         int64_t sl_b, int64_t sl_h, void* stream);
 
 /* Per-query-row bounds float [B,H,R,max_pages] (sh_b, sh_h, sh_r), 0 past the end.
  * Replaces `page_index_heads`, kernels/cuda/paged_sparse_fp16.cu:141-190. */

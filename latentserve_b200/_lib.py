@@ -50,6 +50,7 @@ _PROTOTYPES = {
     "ls_int8_finalize_pending": [P, P, P, P, P, P, P, I, I, I, I, I] + [L] * 13 + [I] + [F] * 6 + [P],
     "ls_page_index": [P, P, P, P, P, P] + [I] * 9 + [L] * 7 + [P],
     "ls_page_index_heads": [P, P, P, P, P, P] + [I] * 8 + [L] * 8 + [P],
+    "ls_page_index_select": [P] * 7 + [I] * 10 + [F, I] + [L] * 9 + [P],
     "ls_select_pages": [P, P, P, I, I, I, I, F, I, L, L, L, L, P],
     "ls_topk_pages": [P, P, I, I, I, I, L, L, L, L, P],
     "ls_rms_norm": [P, P, P, P, P, I, I, F, L, L, L, L, P],

@@ -281,7 +281,8 @@ class _PagedBase:
                     raise RuntimeError(f"sequence in slot {i} needs {len(t.blocks)} pages, past the "
                                        f"cache's capacity of {self._capacity_pages}")
                 if t.blocks:
-                    # A fresh pinned row each time: the copy below is asynchronous.
+                    # A fresh (pageable) host row each time, so the copy completes on the
+                    # host before the row can change: only rows whose block list changed.
                     src = torch.tensor(t.blocks, dtype=torch.int32)
                     self._block_tables_buf[row, : len(t.blocks)].copy_(src)
                 self._table_state[row] = state
@@ -421,6 +422,28 @@ class PagedKVCache(_PagedBase):
         pj.qkv_rope_append(x, w, bias, cos, sin, positions, self._slot_vec(slots, b), q_out,
                            self._flat_k[layer_idx], self._flat_v[layer_idx], kmin, kmax, q_heads,
                            self.spec.num_kv_heads, norm_weight=norm_weight, row_sumsq=row_sumsq, eps=eps)
+
+    def rewind(self, length: int, slots: Optional[Sequence[int]] = None) -> None:
+        """Shorten the active sequences (or `slots`) back to `length` tokens, keeping
+        their blocks: growing again reuses the same blocks and slots and overwrites the
+        tokens past `length` (cache/paged_cache.py:275-303 in the reference). The page the
+        rewind lands in gets its bounds recomputed over the rows that remain. Host-side
+        set-up, not the hot path: the next `advance()` ships the new lengths."""
+        bs = self.block_size
+        for i in (self._active if slots is None else slots):
+            table = self.tables[i]
+            if not 0 <= length <= table.length:
+                raise ValueError(f"cannot rewind slot {i} from {table.length} to {length}")
+            table.length = length
+            if self._bounds_on and length % bs:
+                blk, rows = table.blocks[length // bs], length % bs
+                for layer in range(len(self.k_pool)):
+                    self.kmin[layer][blk] = self.k_pool[layer][blk, :rows].amin(dim=0)
+                    self.kmax[layer][blk] = self.k_pool[layer][blk, :rows].amax(dim=0)
+        if self._block_tables is not None:                  # lengths as the kernels see them
+            active = self._active
+            self._stage()[0][:len(active)] = [self.tables[i].length for i in active]
+            self._flush_stage()
 
     def enable_page_bounds(self) -> None:
         """Keep each block's per-channel min / max of K for the sparse indexer.

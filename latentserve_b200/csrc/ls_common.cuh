@@ -162,11 +162,16 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t mbar, uint32_t parity) {
         : "memory");
     return ok != 0;
 }
-// Bounded wait: false if the phase did not complete within `limit` probes.
-__device__ __forceinline__ bool mbar_wait_bounded(uint32_t mbar, uint32_t parity, int limit) {
-    for (int i = 0; i < limit; ++i)
+// Bounded wait: false if the phase did not complete within `limit` probes. The first
+// probe, which usually finds the data there, is inline; the loop is kept out of line.
+static __device__ __noinline__ bool mbar_wait_slow(uint32_t mbar, uint32_t parity, int limit) {
+    for (int i = 1; i < limit; ++i)
         if (mbar_try_wait(mbar, parity)) return true;
     return false;
+}
+__device__ __forceinline__ bool mbar_wait_bounded(uint32_t mbar, uint32_t parity, int limit) {
+    if (mbar_try_wait(mbar, parity)) return true;
+    return mbar_wait_slow(mbar, parity, limit);
 }
 __device__ __forceinline__ void tma_load_4d(uint32_t dst, const void* tmap, uint32_t mbar, int c0,
                                             int c1, int c2, int c3, uint64_t policy) {

@@ -98,120 +98,6 @@ __device__ __forceinline__ float bounds_4x8(const f32x2 (&qp)[4][4], const f32x2
     return e[0];
 }
 
-// grid (ceil(max_pages / (4 * span)), H, B), block 128: a warp scores `span`
-// consecutive pages (8, 16 or 24) of one (sequence, KV head) in items of eight.
-// All of the warp's bounds are requested at once with 8-byte cp.async copies into
-// the warp's own shared memory, one commit group per item, and each item is
-// reduced as soon as its group has landed: one DRAM round trip per warp, and the
-// bounds wait in shared memory instead of 64 registers, which is what lets four
-// CTAs share an SM. Every lane reads back exactly the bytes it copied, so the
-// wait on its own groups is the only synchronisation. The host sizes `span` so
-// that the whole grid is resident at once where the problem allows it.
-// PER_HEAD = 0: scores [B,H,P]; PER_HEAD = 1: heads [B,H,R,P].
-template <int PER_HEAD>
-__global__ void __launch_bounds__(kIndexWarps * 32, kIndexCtasPerSm)
-page_index_kernel(const __half* __restrict__ q, const __half* __restrict__ kmin,
-                  const __half* __restrict__ kmax, const int* __restrict__ block_tables,
-                  const int* __restrict__ seq_lens, float* __restrict__ out, int n_rep,
-                  int max_pages, int span, int table_stride, int num_blocks, int recent,
-                  long long sq_b, long long sq_h, long long sq_m, long long sb_b, long long sb_h,
-                  long long ss_b, long long ss_h, long long ss_r) {
-    __shared__ __align__(16) unsigned char staged[kIndexWarps][kMaxItems][kItemBytes];
-    const int b = blockIdx.z, h = blockIdx.y;
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int first = (blockIdx.x * kIndexWarps + warp) * span;
-    if (first >= max_pages) return;
-    const int end = min(first + span, max_pages);
-    const int items = (end - first + kItemPages - 1) / kItemPages;
-    const int L = max(seq_lens[b], 0);
-    const int np = min((L + LS_PAGE - 1) / LS_PAGE, table_stride);
-
-    // Lane j fetches the block id of page first + j (-1: nothing to score).
-    int ids = -1;
-    {
-        const int p = first + lane;
-        bool need = p < end && p < np;
-        if (!PER_HEAD) need = need && !(p == 0 || p >= np - recent);
-        if (need) {
-            const int id = block_tables[(long long)b * table_stride + p];
-            if (id >= 0 && id < num_blocks) ids = id;
-        }
-    }
-    const uint32_t mine = smem_u32(&staged[warp][0][0]) + lane * 8;
-#pragma unroll
-    for (int it = 0; it < kMaxItems; ++it) {
-        if (it < items) {
-#pragma unroll
-            for (int k = 0; k < kItemPages; ++k) {
-                const int blk = __shfl_sync(LS_FULL_MASK, ids, it * kItemPages + k);
-                const long long off = blk >= 0 ? blk * sb_b + h * sb_h + lane * 4 : 0;
-                const uint32_t dst = mine + it * kItemBytes + k * 512;
-                cp_async_8(dst, kmin + off, blk >= 0 ? 8 : 0);          // an unscored page reads as zeros
-                cp_async_8(dst + 256, kmax + off, blk >= 0 ? 8 : 0);
-            }
-        }
-        cp_async_commit();
-    }
-
-    // q+ and q- of rows (2 rp, 2 rp + 1), channel j, packed; rows past n_rep are zero.
-    f32x2 qp[4][4], qn[4][4];
-#pragma unroll
-    for (int rp = 0; rp < 4; ++rp) {
-        float q0[4] = {0.f, 0.f, 0.f, 0.f}, q1[4] = {0.f, 0.f, 0.f, 0.f};
-        if (2 * rp < n_rep)
-            unpack4h(*reinterpret_cast<const uint2*>(q + b * sq_b + h * sq_h + (2 * rp) * sq_m + lane * 4), q0);
-        if (2 * rp + 1 < n_rep)
-            unpack4h(*reinterpret_cast<const uint2*>(q + b * sq_b + h * sq_h + (2 * rp + 1) * sq_m + lane * 4),
-                     q1);
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            qp[rp][j] = pack2(fmaxf(q0[j], 0.f), fmaxf(q1[j], 0.f));
-            qn[rp][j] = pack2(fminf(q0[j], 0.f), fminf(q1[j], 0.f));
-        }
-    }
-
-    // Reduces group g of item `it` and writes its scores.
-    auto reduce = [&](int it, int g) {
-        uint2 lo_raw[kGroup], hi_raw[kGroup];
-        const unsigned char* src = &staged[warp][it][g * kGroup * 512 + lane * 8];
-#pragma unroll
-        for (int k = 0; k < kGroup; ++k) {
-            lo_raw[k] = *reinterpret_cast<const uint2*>(src + k * 512);
-            hi_raw[k] = *reinterpret_cast<const uint2*>(src + k * 512 + 256);
-        }
-        float s = bounds_4x8(qp, qn, n_rep, lo_raw, hi_raw, lane);
-        const int slot = it * kItemPages + g * kGroup + (lane >> 3);
-        const int p = first + slot, r = lane & 7;
-        const int blk = __shfl_sync(LS_FULL_MASK, ids, slot);
-        if (PER_HEAD) {
-            // Pages past the end get a finite 0: their token count of zero
-            // removes them downstream, and a stale NaN here would not.
-            if (p < end && r < n_rep) out[b * ss_b + h * ss_h + r * ss_r + p] = blk >= 0 ? s : 0.f;
-        } else {
-            if (r >= n_rep || blk < 0) s = neg_inf();
-#pragma unroll
-            for (int off = 1; off < 8; off <<= 1) s = fmaxf(s, __shfl_xor_sync(LS_FULL_MASK, s, off));
-            if (p >= np) s = neg_inf();                                  // past the end: never chosen
-            else if (p == 0 || p >= np - recent) s = pos_inf();          // sink and recent: always kept
-            if (r == 0 && p < end) out[b * ss_b + h * ss_h + p] = s;
-        }
-    };
-    cp_async_wait<kMaxItems - 1>();
-#pragma unroll
-    for (int g = 0; g < kItemGroups; ++g) reduce(0, g);
-    if (items < 2) return;
-    cp_async_wait<kMaxItems - 2>();
-#pragma unroll
-    for (int g = 0; g < kItemGroups; ++g) reduce(1, g);
-    if (items < 3) return;
-    cp_async_wait<0>();
-#pragma unroll
-    for (int g = 0; g < kItemGroups; ++g) reduce(2, g);
-    // No early trigger for a programmatic successor: a CTA that has returned counts as
-    // having triggered, so the selection kernel's CTAs arrive while the last warps here
-    // finish and never hold SM slots this kernel's single wave needs.
-}
-
 // Monotone map from fp32 to uint32: a > b as floats <=> key(a) > key(b).
 // -0 is folded onto +0 first so the two compare equal, as they do as floats.
 __device__ __forceinline__ uint32_t order_key(float x) {
@@ -306,38 +192,50 @@ topk_pages_kernel(const float* __restrict__ scores, int* __restrict__ sel, int n
 // the first n entries of the sorted selection, bit for bit.
 constexpr int kSelectThreads = 512;
 
-template <int E>
-__global__ void __launch_bounds__(kSelectThreads)
-select_pages_kernel(const float* __restrict__ scores, const int* __restrict__ seq_lens,
-                    int* __restrict__ sel, int n, int k, int heads, float ratio, int recent,
-                    long long ss_b, long long ss_h, long long sl_b, long long sl_h) {
-    __shared__ int hist[256];
-    __shared__ int warp_tot[kSelectThreads / 32][2];
-    __shared__ unsigned s_prefix;
-    __shared__ int s_remaining;
-    asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
-    const int bh = blockIdx.x, b = bh / heads, h = bh % heads;
-    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const float* row = scores + b * ss_b + h * ss_h;
-    int* out = sel + b * sl_b + h * sl_h;
+// Shared scratch of select_row.
+constexpr int kDigitBits = 11;                 // radix digit: 2048 bins
+constexpr int kBins = 1 << kDigitBits;
+struct SelectScratch {
+    int hist[kBins];
+    int warp_tot[32][2];
+    unsigned lo, hi;                           // smallest / largest finite key of the row
+    int n_inf, n_fin;                          // keys that are +inf / finite
+    unsigned prefix;
+    int remaining;
+};
 
-    // How many pages this sequence attends: the rule of the attention kernel.
-    const int L = max(seq_lens[b], 0);
+// How many pages a sequence attends: the rule of the attention kernel
+// (kernels/cuda/paged_sparse_fp16.cu:242-247 in the reference).
+__device__ __forceinline__ int pages_owed(int len, float ratio, int recent, int k, int n) {
+    const int L = max(len, 0);
     const int np = (L + LS_PAGE - 1) / LS_PAGE;
     int want = np;
     if (ratio > 0.f && ratio < 1.f) want = max(recent + 1, (int)ceilf(ratio * (float)np));
-    const int n_keep = min(min(want, np), min(k, n));
+    return min(min(want, np), min(k, n));
+}
 
-    // Launched programmatically: everything above overlapped the end of the kernel
-    // that writes the scores.
-    asm volatile("griddepcontrol.wait;\n" ::: "memory");
+// One row of scores -> the n_keep best pages in ascending page order, then -1 up to k.
+// Called by all THREADS threads of a CTA; thread i holds keys [i * E, (i + 1) * E).
+//
+// The n_keep-th largest key T is found by a radix search from the top, 11 bits a
+// pass, that starts below the bits every key of the row has in common (scores of one
+// row lie within a few binades, so the upper 8-10 bits of their order keys agree: two
+// passes instead of the four a byte-wise search over all 32 bits takes). Then every
+// key above T is kept, and of the keys equal to T the ones with the lowest page
+// numbers, by two block scans.
+template <int THREADS, int E>
+__device__ __forceinline__ void select_row(const float* __restrict__ row, int* __restrict__ out, int n,
+                                           int k, int n_keep, SelectScratch& sc) {
+    static_assert(kBins % THREADS == 0, "every thread scans the same number of bins");
+    constexpr int BPT = kBins / THREADS;                    // bins per thread
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     unsigned key[E];
     if ((n & 3) == 0 && ((reinterpret_cast<uintptr_t>(row) & 15) == 0)) {
 #pragma unroll
         for (int e = 0; e < E; e += 4) {
             const int i = tid * E + e;
             float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-            if (i < n) v = *reinterpret_cast<const float4*>(row + i);
+            if (i < n) v = __ldcg(reinterpret_cast<const float4*>(row + i));
             key[e] = (i < n) ? order_key(v.x) : 0u;          // padding: below every real key
             key[e + 1] = (i < n) ? order_key(v.y) : 0u;
             key[e + 2] = (i < n) ? order_key(v.z) : 0u;
@@ -347,66 +245,118 @@ select_pages_kernel(const float* __restrict__ scores, const int* __restrict__ se
 #pragma unroll
         for (int e = 0; e < E; ++e) {
             const int i = tid * E + e;
-            key[e] = (i < n) ? order_key(row[i]) : 0u;
+            key[e] = (i < n) ? order_key(__ldcg(row + i)) : 0u;
         }
     }
     if (n_keep <= 0) {
-        for (int i = tid; i < k; i += kSelectThreads) out[i] = -1;
+        for (int i = tid; i < k; i += THREADS) out[i] = -1;
         return;
     }
 
-    // Radix search, 8 bits a pass from the top: prefix = decided high bits of T,
-    // remaining = how many keys are still to be taken among those matching the prefix.
-    // Two barriers a pass: warp 0 clears the histogram it has just read.
-    unsigned prefix = 0, mask = 0;
-    int remaining = n_keep;
-    if (tid < 256) hist[tid] = 0;
+    // Forced pages score +inf and pages past the end -inf: both are set aside (the former
+    // are always kept, the latter never needed), so that what is searched is the range of
+    // the finite scores. The bits above the highest bit in which the smallest and the
+    // largest of those differ are common to all of them and need no pass.
+    constexpr unsigned kPosInf = 0xff800000u, kNegInf = 0x007fffffu;      // order keys of +inf, -inf
+    unsigned lo = 0xffffffffu, hi = 0u;
+    int n_inf = 0, n_fin = 0;
+#pragma unroll
+    for (int e = 0; e < E; ++e) {
+        if (tid * E + e < n) {
+            if (key[e] == kPosInf) {
+                ++n_inf;
+            } else if (key[e] != kNegInf) {
+                ++n_fin;
+                lo = min(lo, key[e]);
+                hi = max(hi, key[e]);
+            }
+        }
+    }
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) {
+        lo = min(lo, __shfl_xor_sync(LS_FULL_MASK, lo, off));
+        hi = max(hi, __shfl_xor_sync(LS_FULL_MASK, hi, off));
+        n_inf += __shfl_xor_sync(LS_FULL_MASK, n_inf, off);
+        n_fin += __shfl_xor_sync(LS_FULL_MASK, n_fin, off);
+    }
+    if (tid == 0) {
+        sc.lo = 0xffffffffu;
+        sc.hi = 0u;
+        sc.n_inf = 0;
+        sc.n_fin = 0;
+    }
+    for (int i = tid; i < kBins; i += THREADS) sc.hist[i] = 0;
     __syncthreads();
+    if (lane == 0) {
+        atomicMin(&sc.lo, lo);
+        atomicMax(&sc.hi, hi);
+        atomicAdd(&sc.n_inf, n_inf);
+        atomicAdd(&sc.n_fin, n_fin);
+    }
+    __syncthreads();
+    lo = sc.lo;
+    hi = sc.hi;
+    n_inf = sc.n_inf;
+    n_fin = sc.n_fin;
+    int top = 0, remaining = n_keep;
+    unsigned mask = 0xffffffffu, prefix;
+    if (n_keep <= n_inf) {
+        prefix = kPosInf;                                   // the forced pages alone fill the budget
+    } else if (n_keep > n_inf + n_fin) {
+        prefix = kNegInf;                                   // more owed than scored: never on a sound table
+        remaining = n_keep - n_inf - n_fin;
+    } else {
+        remaining = n_keep - n_inf;
+        top = 32 - __clz(lo ^ hi);                          // undecided low bits (0: all finite keys equal)
+        mask = top >= 32 ? 0u : ~((1u << top) - 1u);        // decided (common) high bits
+        prefix = hi & mask;
+    }
 #pragma unroll 1
-    for (int shift = 24; shift >= 0; shift -= 8) {
-        // Scores cluster in a few top-byte values, so lanes of a warp that hit the same
-        // bin add once between them (match.any) instead of serialising 32 atomics.
+    while (top > 0) {
+        const int w = min(kDigitBits, top), shift = top - w;
+        const unsigned dmask = (1u << w) - 1u;
 #pragma unroll
         for (int e = 0; e < E; ++e) {
-            const bool in = (key[e] & mask) == prefix && tid * E + e < n;
-            const unsigned bin = in ? ((key[e] >> shift) & 255u) : 256u;
-            const unsigned peers = __match_any_sync(LS_FULL_MASK, bin);
-            if (in && lane == __ffs(peers) - 1) atomicAdd(&hist[bin], __popc(peers));
+            if ((key[e] & mask) == prefix && key[e] != kPosInf && key[e] != kNegInf && tid * E + e < n)
+                atomicAdd(&sc.hist[(key[e] >> shift) & dmask], 1);
         }
         __syncthreads();
-        if (warp == 0) {
-            // lane l owns bins 255 - 8 l .. 248 - 8 l (descending); inclusive scan over lanes.
-            int local[8], sum = 0;
+        // Thread i owns bins kBins-1 - BPT i .. (descending); inclusive scan over threads.
+        int local[BPT], sum = 0;
 #pragma unroll
-            for (int j = 0; j < 8; ++j) {
-                local[j] = hist[255 - (8 * lane + j)];
-                hist[255 - (8 * lane + j)] = 0;             // ready for the next pass
-                sum += local[j];
-            }
-            int incl = sum;
+        for (int j = 0; j < BPT; ++j) {
+            const int bin = kBins - 1 - (BPT * tid + j);
+            local[j] = sc.hist[bin];
+            sc.hist[bin] = 0;                               // ready for the next pass
+            sum += local[j];
+        }
+        int incl = sum;
 #pragma unroll
-            for (int off = 1; off < 32; off <<= 1) {
-                const int v = __shfl_up_sync(LS_FULL_MASK, incl, off);
-                if (lane >= off) incl += v;
-            }
-            int before = incl - sum;                        // keys in bins above this lane's
-            if (before < remaining && remaining <= incl) {
+        for (int off = 1; off < 32; off <<= 1) {
+            const int v = __shfl_up_sync(LS_FULL_MASK, incl, off);
+            if (lane >= off) incl += v;
+        }
+        if (lane == 31) sc.warp_tot[warp][0] = incl;
+        __syncthreads();
+        int before = incl - sum;                            // keys in bins above this thread's
+        for (int wq = 0; wq < warp; ++wq) before += sc.warp_tot[wq][0];
+        if (before < remaining && remaining <= before + sum) {
 #pragma unroll
-                for (int j = 0; j < 8; ++j) {
-                    if (before + local[j] >= remaining) {
-                        s_prefix = prefix | ((unsigned)(255 - (8 * lane + j)) << shift);
-                        s_remaining = remaining - before;
-                        break;
-                    }
-                    before += local[j];
+            for (int j = 0; j < BPT; ++j) {
+                if (before + local[j] >= remaining) {
+                    sc.prefix = prefix | ((unsigned)(kBins - 1 - (BPT * tid + j)) << shift);
+                    sc.remaining = remaining - before;
+                    break;
                 }
+                before += local[j];
             }
         }
         __syncthreads();
-        // s_prefix / s_remaining are rewritten only after the next pass's first barrier.
-        prefix = s_prefix;
-        remaining = s_remaining;
-        mask |= 0xffu << shift;
+        // sc.prefix / sc.remaining / warp_tot are rewritten only after the next pass's first barrier.
+        prefix = sc.prefix;
+        remaining = sc.remaining;
+        mask |= dmask << shift;
+        top = shift;
     }
     const unsigned T = prefix;                              // the n_keep-th largest key
     const int take_eq = remaining;                          // keys equal to T to keep, lowest pages first
@@ -429,15 +379,16 @@ select_pages_kernel(const float* __restrict__ scores, const int* __restrict__ se
             gt_incl += c;
         }
     }
+    __syncthreads();                                        // warp_tot of the last pass has been read
     if (lane == 31) {
-        warp_tot[warp][0] = eq_incl;
-        warp_tot[warp][1] = gt_incl;
+        sc.warp_tot[warp][0] = eq_incl;
+        sc.warp_tot[warp][1] = gt_incl;
     }
     __syncthreads();
     int eq_before = eq_incl - eq_local, gt_before = gt_incl - gt_local;
     for (int w = 0; w < warp; ++w) {
-        eq_before += warp_tot[w][0];
-        gt_before += warp_tot[w][1];
+        eq_before += sc.warp_tot[w][0];
+        gt_before += sc.warp_tot[w][1];
     }
     // Position of a kept key = kept keys before it = (above T before it) + min(equal before it, take_eq).
 #pragma unroll
@@ -449,7 +400,148 @@ select_pages_kernel(const float* __restrict__ scores, const int* __restrict__ se
         gt_before += gt;
         eq_before += eq;
     }
-    for (int i = n_keep + tid; i < k; i += kSelectThreads) out[i] = -1;
+    for (int i = n_keep + tid; i < k; i += THREADS) out[i] = -1;
+}
+
+// grid (ceil(max_pages / (4 * span)), H, B), block 128: a warp scores `span`
+// consecutive pages (8, 16 or 24) of one (sequence, KV head) in items of eight.
+// All of the warp's bounds are requested at once with 8-byte cp.async copies into
+// the warp's own shared memory, one commit group per item, and each item is
+// reduced as soon as its group has landed: one DRAM round trip per warp, and the
+// bounds wait in shared memory instead of 64 registers, which is what lets four
+// CTAs share an SM. Every lane reads back exactly the bytes it copied, so the
+// wait on its own groups is the only synchronisation. The host sizes `span` so
+// that the whole grid is resident at once where the problem allows it.
+//
+// Launched programmatically with `early` set, the block ids and the bounds are
+// requested BEFORE the kernel synchronises on its predecessor: the pages whose bounds
+// it reads are never a sequence's last page (page 0 and the `recent` last pages are
+// not scored at all), and only a last page's bounds change between decode steps. The
+// queries, which the predecessor usually wrote, are read after the wait.
+//
+// PER_HEAD = 0: scores [B,H,P]; PER_HEAD = 1: heads [B,H,R,P].
+template <int PER_HEAD>
+__global__ void __launch_bounds__(kIndexWarps * 32, kIndexCtasPerSm)
+page_index_kernel(const __half* __restrict__ q, const __half* __restrict__ kmin,
+                  const __half* __restrict__ kmax, const int* __restrict__ block_tables,
+                  const int* __restrict__ seq_lens, float* __restrict__ out, int n_rep,
+                  int max_pages, int span, int table_stride, int num_blocks, int recent, int early,
+                  long long sq_b, long long sq_h, long long sq_m, long long sb_b, long long sb_h,
+                  long long ss_b, long long ss_h, long long ss_r) {
+    __shared__ __align__(16) unsigned char staged[kIndexWarps][kMaxItems][kItemBytes];
+    const int b = blockIdx.z, h = blockIdx.y;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int first = (blockIdx.x * kIndexWarps + warp) * span;
+    const int end = min(first + span, max_pages);
+    const int items = first < max_pages ? (end - first + kItemPages - 1) / kItemPages : 0;
+    if (!early) asm volatile("griddepcontrol.wait;\n" ::: "memory");
+    const int L = max(seq_lens[b], 0);
+    const int np = min((L + LS_PAGE - 1) / LS_PAGE, table_stride);
+
+    // Lane j fetches the block id of page first + j (-1: nothing to score).
+    int ids = -1;
+    {
+        const int p = first + lane;
+        bool need = p < end && p < np;
+        if (!PER_HEAD) need = need && !(p == 0 || p >= np - recent);
+        if (need) {
+            const int id = block_tables[(long long)b * table_stride + p];
+            if (id >= 0 && id < num_blocks) ids = id;
+        }
+    }
+    const uint32_t mine = smem_u32(&staged[warp][0][0]) + lane * 8;
+#pragma unroll
+    for (int it = 0; it < kMaxItems; ++it) {
+        if (it < items) {
+#pragma unroll
+            for (int k = 0; k < kItemPages; ++k) {
+                const int blk = __shfl_sync(LS_FULL_MASK, ids, it * kItemPages + k);
+                const long long off = blk >= 0 ? blk * sb_b + h * sb_h + lane * 4 : 0;
+                const uint32_t dst = mine + it * kItemBytes + k * 512;
+                cp_async_8(dst, kmin + off, blk >= 0 ? 8 : 0);          // an unscored page reads as zeros
+                cp_async_8(dst + 256, kmax + off, blk >= 0 ? 8 : 0);
+            }
+        }
+        cp_async_commit();
+    }
+    if (early) asm volatile("griddepcontrol.wait;\n" ::: "memory");
+
+    // q+ and q- of rows (2 rp, 2 rp + 1), channel j, packed; rows past n_rep are zero.
+    f32x2 qp[4][4], qn[4][4];
+#pragma unroll
+    for (int rp = 0; rp < 4; ++rp) {
+        float q0[4] = {0.f, 0.f, 0.f, 0.f}, q1[4] = {0.f, 0.f, 0.f, 0.f};
+        if (2 * rp < n_rep)
+            unpack4h(*reinterpret_cast<const uint2*>(q + b * sq_b + h * sq_h + (2 * rp) * sq_m + lane * 4), q0);
+        if (2 * rp + 1 < n_rep)
+            unpack4h(*reinterpret_cast<const uint2*>(q + b * sq_b + h * sq_h + (2 * rp + 1) * sq_m + lane * 4),
+                     q1);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            qp[rp][j] = pack2(fmaxf(q0[j], 0.f), fmaxf(q1[j], 0.f));
+            qn[rp][j] = pack2(fminf(q0[j], 0.f), fminf(q1[j], 0.f));
+        }
+    }
+
+    // Reduces group g of item `it` and writes its scores.
+    auto reduce = [&](int it, int g) {
+        uint2 lo_raw[kGroup], hi_raw[kGroup];
+        const unsigned char* src = &staged[warp][it][g * kGroup * 512 + lane * 8];
+#pragma unroll
+        for (int k = 0; k < kGroup; ++k) {
+            lo_raw[k] = *reinterpret_cast<const uint2*>(src + k * 512);
+            hi_raw[k] = *reinterpret_cast<const uint2*>(src + k * 512 + 256);
+        }
+        float s = bounds_4x8(qp, qn, n_rep, lo_raw, hi_raw, lane);
+        const int slot = it * kItemPages + g * kGroup + (lane >> 3);
+        const int p = first + slot, r = lane & 7;
+        const int blk = __shfl_sync(LS_FULL_MASK, ids, slot);
+        if (PER_HEAD) {
+            // Pages past the end get a finite 0: their token count of zero
+            // removes them downstream, and a stale NaN here would not.
+            if (p < end && r < n_rep) out[b * ss_b + h * ss_h + r * ss_r + p] = blk >= 0 ? s : 0.f;
+        } else {
+            if (r >= n_rep || blk < 0) s = neg_inf();
+#pragma unroll
+            for (int off = 1; off < 8; off <<= 1) s = fmaxf(s, __shfl_xor_sync(LS_FULL_MASK, s, off));
+            if (p >= np) s = neg_inf();                                  // past the end: never chosen
+            else if (p == 0 || p >= np - recent) s = pos_inf();          // sink and recent: always kept
+            if (r == 0 && p < end) out[b * ss_b + h * ss_h + p] = s;
+        }
+    };
+    if (items > 0) {
+        cp_async_wait<kMaxItems - 1>();
+#pragma unroll
+        for (int g = 0; g < kItemGroups; ++g) reduce(0, g);
+    }
+    if (items > 1) {
+        cp_async_wait<kMaxItems - 2>();
+#pragma unroll
+        for (int g = 0; g < kItemGroups; ++g) reduce(1, g);
+    }
+    if (items > 2) {
+        cp_async_wait<0>();
+#pragma unroll
+        for (int g = 0; g < kItemGroups; ++g) reduce(2, g);
+    }
+    // No early trigger for a programmatic successor: a CTA that has returned counts as
+    // having triggered, so the next kernel's CTAs arrive while the last warps here
+    // finish and never hold SM slots this kernel's single wave needs.
+}
+
+template <int E>
+__global__ void __launch_bounds__(kSelectThreads)
+select_pages_kernel(const float* __restrict__ scores, const int* __restrict__ seq_lens,
+                    int* __restrict__ sel, int n, int k, int heads, float ratio, int recent,
+                    long long ss_b, long long ss_h, long long sl_b, long long sl_h) {
+    __shared__ SelectScratch sc;
+    asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
+    const int bh = blockIdx.x, b = bh / heads, h = bh % heads;
+    const int n_keep = pages_owed(seq_lens[b], ratio, recent, k, n);
+    // Launched programmatically: everything above overlapped the end of the kernel
+    // that writes the scores.
+    asm volatile("griddepcontrol.wait;\n" ::: "memory");
+    select_row<kSelectThreads, E>(scores + b * ss_b + h * ss_h, sel + b * sl_b + h * sl_h, n, k, n_keep, sc);
 }
 
 }  // namespace ls
@@ -461,7 +553,7 @@ static int launch_index(int per_head, const void* q, const void* kmin, const voi
                         int kv_heads, int n_rep, int head_dim, int page, int max_pages,
                         int table_stride, int num_blocks, int recent, int64_t sq_b, int64_t sq_h,
                         int64_t sq_m, int64_t sb_b, int64_t sb_h, int64_t ss_b, int64_t ss_h,
-                        int64_t ss_r, void* stream) {
+                        int64_t ss_r, void* stream, int flags = 0) {
     if (!q || !kmin || !kmax || !block_tables || !seq_lens || !out) return LS_ERR_NULL_POINTER;
     if (head_dim != LS_HEAD_DIM || page != LS_PAGE) return LS_ERR_UNSUPPORTED;
     if (batch <= 0 || kv_heads <= 0 || n_rep <= 0 || max_pages <= 0 || table_stride < max_pages ||
@@ -490,22 +582,37 @@ static int launch_index(int per_head, const void* q, const void* kmin, const voi
         if (per_row * kv_heads * batch <= resident) break;
     }
     const int per_cta = ls::kIndexWarps * span;
-    dim3 grid((max_pages + per_cta - 1) / per_cta, kv_heads, batch);
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    // A plain launch: starting this kernel ahead of its predecessor's end (programmatic
-    // launch) was measured and left the index -> select -> attend sequence unchanged.
     auto kern = per_head ? ls::page_index_kernel<1> : ls::page_index_kernel<0>;
     static bool carveout_set[64][2] = {};
     const int slot = dev >= 0 && dev < 64 ? dev : 0;
-    if (!carveout_set[slot][per_head ? 1 : 0]) {    // four 48 KB CTAs per SM need the large shared-memory split
+    const int variant = per_head ? 1 : 0;
+    if (!carveout_set[slot][variant]) {    // four 48 KB CTAs per SM need the large shared-memory split
         cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
-        carveout_set[slot][per_head ? 1 : 0] = dev >= 0 && dev < 64;
+        carveout_set[slot][variant] = dev >= 0 && dev < 64;
     }
-    kern<<<grid, ls::kIndexWarps * 32, 0, s>>>(
-        static_cast<const __half*>(q), static_cast<const __half*>(kmin), static_cast<const __half*>(kmax),
-        block_tables, seq_lens, out, n_rep, max_pages, span, table_stride, num_blocks, recent, sq_b, sq_h,
-        sq_m, sb_b, sb_h, ss_b, ss_h, ss_r);
-    return (int)cudaGetLastError();
+    // With LS_LAUNCH_PROGRAMMATIC the launch may begin while the previous kernel of the stream
+    // drains; with LS_EARLY_PAGES on top of it the bounds are requested before the kernel
+    // synchronises on that predecessor (see the kernel). Per-head bounds score a sequence's
+    // last page too, and so does recent == 0: no early requests then.
+    const bool programmatic = (flags & LS_LAUNCH_PROGRAMMATIC) != 0;
+    const int early = programmatic && (flags & LS_EARLY_PAGES) && !per_head && recent >= 1;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((max_pages + per_cta - 1) / per_cta, kv_heads, batch);
+    cfg.blockDim = dim3(ls::kIndexWarps * 32);
+    cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = programmatic ? 1 : 0;
+    const long long a_sq_b = sq_b, a_sq_h = sq_h, a_sq_m = sq_m, a_sb_b = sb_b, a_sb_h = sb_h, a_ss_b = ss_b,
+                    a_ss_h = ss_h, a_ss_r = ss_r;
+    cudaError_t e = cudaLaunchKernelEx(
+        &cfg, kern, static_cast<const __half*>(q), static_cast<const __half*>(kmin),
+        static_cast<const __half*>(kmax), block_tables, seq_lens, out, n_rep, max_pages, span, table_stride,
+        num_blocks, recent, early, a_sq_b, a_sq_h, a_sq_m, a_sb_b, a_sb_h, a_ss_b, a_ss_h, a_ss_r);
+    return e != cudaSuccess ? (int)e : (int)cudaGetLastError();
 }
 
 int ls_page_index(const void* q, const void* kmin, const void* kmax, const int32_t* block_tables,
@@ -588,6 +695,22 @@ int ls_select_pages(const float* scores, const int32_t* seq_lens, int32_t* sel, 
         e = cudaLaunchKernelEx(&cfg, ls::select_pages_kernel<16>, scores, seq_lens, sel, num_pages, k,
                                kv_heads, ratio, recent, a_ss_b, a_ss_h, a_sl_b, a_sl_h);
     return e != cudaSuccess ? (int)e : (int)cudaGetLastError();
+}
+
+int ls_page_index_select(const void* q, const void* kmin, const void* kmax, const int32_t* block_tables,
+                         const int32_t* seq_lens, float* scores, int32_t* sel, int batch, int kv_heads,
+                         int n_rep, int head_dim, int page, int max_pages, int table_stride,
+                         int num_blocks, int recent, int k, float ratio, int flags, int64_t sq_b,
+                         int64_t sq_h, int64_t sq_m, int64_t sb_b, int64_t sb_h, int64_t ss_b, int64_t ss_h,
+                         int64_t sl_b, int64_t sl_h, void* stream) {
+    if (!sel) return LS_ERR_NULL_POINTER;
+    if (flags & ~(LS_LAUNCH_PROGRAMMATIC | LS_EARLY_PAGES)) return LS_ERR_UNSUPPORTED;
+    int rc = launch_index(0, q, kmin, kmax, block_tables, seq_lens, scores, batch, kv_heads, n_rep, head_dim,
+                          page, max_pages, table_stride, num_blocks, recent, sq_b, sq_h, sq_m, sb_b, sb_h,
+                          ss_b, ss_h, 0, stream, flags);
+    if (rc) return rc;
+    return ls_select_pages(scores, seq_lens, sel, batch, kv_heads, max_pages, k, ratio, recent, ss_b, ss_h,
+                           sl_b, sl_h, stream);
 }
 
 }  // extern "C"

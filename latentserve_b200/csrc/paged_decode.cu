@@ -35,6 +35,9 @@
 //     their way into the MMA fragments; K's per-(block, head, channel) scale
 //     is folded into the query once per page, V's per-token scale into the
 //     softmax weight, so neither pool is ever dequantised element by element.
+//     V comes in through ldmatrix.trans on byte pairs and enters its MMA as
+//     1152 + v (the byte permute's raw result); one more MMA per page sums the
+//     weights, and 1152 x that sum comes off every output dim at the end.
 //   * rows past a sequence's end are zero-filled on the way in (cp.async with
 //     a zero source size; the TMA variants clear or neutralise them after
 //     arrival) and their scores forced to -inf: stale pool bytes, NaN patterns
@@ -63,28 +66,12 @@ namespace ls {
 #ifndef LS_INT8_STAGES
 #define LS_INT8_STAGES 3            // ring depth of the INT8 kernel (4.6 KB stages, 3 CTAs per SM)
 #endif
-#ifndef LS_FP16_TMA_PROMO
-#define LS_FP16_TMA_PROMO CU_TENSOR_MAP_L2_PROMOTION_L2_256B
-#endif
 #ifndef LS_INT8_TMA_STAGES
 #define LS_INT8_TMA_STAGES 2        // 5 KB stages of the TMA-loading INT8 kernel
 #endif
-#ifndef LS_ISSUE_AFTER
-#define LS_ISSUE_AFTER 0              // 1: refill a ring stage right after it is consumed (whole ring in
-                                    // flight); measured 0.5-2 % slower than refilling the stage consumed one
-                                    // page ago, before the compute
-#endif
-#ifndef LS_LAZY_MAX
-#define LS_LAZY_MAX 1                // keep the softmax reference while scores stay within a margin of it
-#endif
-#ifndef LS_INT8_STAGES_ASYM
 #define LS_INT8_STAGES_ASYM 2       // 5.1 KB stages: a third one would cost the third CTA
-#endif
 #ifndef LS_INT8_CTAS
-#define LS_INT8_CTAS 3              // resident CTAs per SM the INT8 kernel is compiled for
-#endif
-#ifndef LS_EVICT_FIRST
-#define LS_EVICT_FIRST 1            // L2 evict-first policy on the (read-once) KV page loads
+#define LS_INT8_CTAS 4              // resident CTAs per SM the INT8 kernel is compiled for (128 registers)
 #endif
 constexpr int kWarps = 4;
 // Tensor maps of the TMA-loading variants (unused and zero for the others).
@@ -96,6 +83,7 @@ constexpr int kStages = LS_STAGES;
 constexpr int kThreads = kWarps * 32;
 constexpr int kMergeStride = LS_HEAD_DIM + 4;   // floats per merged row (bank-conflict pad)
 constexpr int kRP = 8;                          // query rows held per partial
+
 
 // What the load side knows about the page it is about to fetch.
 struct PageItem {
@@ -115,15 +103,15 @@ template <int MODE>
 struct PageWindow {
     Cursor c;                       // first page of the current window
     int n, i;                       // pages in the window, next one to hand out
-    int blk, valid, last;           // lane j: page j
+    int blk, vl;                    // lane j: page j's block id, and valid tokens | last-page bits << 8
     Cursor nc;                      // the window after this one
-    int nn, nblk, nvalid, nlast;
+    int nn, nblk, nvl;
     bool have_next;
     int cached_b, cached_len;
 
     __device__ __forceinline__ void fill(const DecodeParams& p, const Cursor& cur, int h, int lane,
-                                         int& cnt, int& b_, int& v_, int& l_) {
-        cnt = 0; b_ = 0; v_ = 0; l_ = 0;
+                                         int& cnt, int& b_, int& vl_) {
+        cnt = 0; b_ = 0; vl_ = 0;
         if (cur.done) return;
         if (cur.b != cached_b) {
             cached_b = cur.b;
@@ -139,11 +127,11 @@ struct PageWindow {
             const int id = p.block_tables[(long long)cur.b * p.max_pages + page];
             if (id >= 0 && id < p.num_blocks) {
                 b_ = id;
-                v_ = min(LS_PAGE, cached_len - page * LS_PAGE);
                 // INT8 pools: the page before the last is rewritten (K bytes and K scales,
                 // by the page-finalize kernel) in the step whose new token opened the last
                 // page, so it counts as mutable too; every earlier page is final.
-                l_ = (page == np - 1 ? 1 : 0) | ((p.k_scale != nullptr && page >= np - 2) ? 2 : 0);
+                const int last = (page == np - 1 ? 1 : 0) | ((p.k_scale != nullptr && page >= np - 2) ? 2 : 0);
+                vl_ = min(LS_PAGE, cached_len - page * LS_PAGE) | (last << 8);
             } else {
                 p.seg_range[2 * p.batch] = 1;      // corrupt table: read nothing, flag it
             }
@@ -155,7 +143,7 @@ struct PageWindow {
         cached_b = -1;
         cached_len = 0;
         c = first;
-        fill(p, c, h, lane, n, blk, valid, last);
+        fill(p, c, h, lane, n, blk, vl);
         i = 0;
         have_next = false;
     }
@@ -165,7 +153,7 @@ struct PageWindow {
         nc = c;
         nc.u += kWarps * n;
         cursor_normalize<kWarps>(nc, cum, p.batch, warp);
-        fill(p, nc, h, lane, nn, nblk, nvalid, nlast);
+        fill(p, nc, h, lane, nn, nblk, nvl);
         have_next = true;
     }
 
@@ -175,14 +163,15 @@ struct PageWindow {
         if (i == n) {
             if (n == 0) return false;
             if (!have_next) prefetch(p, cum, h, warp, lane);
-            c = nc; n = nn; blk = nblk; valid = nvalid; last = nlast;
+            c = nc; n = nn; blk = nblk; vl = nvl;
             have_next = false;
             i = 0;
             if (n == 0) return false;
         }
         it.blk = __shfl_sync(LS_FULL_MASK, blk, i);
-        it.valid = __shfl_sync(LS_FULL_MASK, valid, i);
-        it.last = __shfl_sync(LS_FULL_MASK, last, i);
+        const int v = __shfl_sync(LS_FULL_MASK, vl, i);
+        it.valid = v & 255;
+        it.last = v >> 8;
         b = c.b;
         ++i;
         if (!have_next && i + 2 >= n) prefetch(p, cum, h, warp, lane);
@@ -197,9 +186,9 @@ struct PageWindow {
 // On return s holds the weights 2^(s - m_new); m, l and the output
 // accumulators o[8][4] are rescaled. Scores are in the log2 domain.
 constexpr float kLazyMargin = 8.f;      // log2 units
+template <int TILES>
 __device__ __forceinline__ void softmax_update(float (&s)[4], float (&m)[2], float (&l)[2],
-                                               float (&o)[8][4], float& a0, float& a1) {
-#if LS_LAZY_MAX
+                                               float (&o)[TILES][4], float& a0, float& a1) {
     // Usual case after a segment's first pages: no score of the page rises more
     // than 2^kLazyMargin above the running reference m. Then m is kept as it is
     // (any shared reference gives the same normalised result; weights stay below
@@ -221,7 +210,6 @@ __device__ __forceinline__ void softmax_update(float (&s)[4], float (&m)[2], flo
             return;
         }
     }
-#endif
     float mx0 = fmaxf(s[0], s[2]);
     float mx1 = fmaxf(s[1], s[3]);
 #pragma unroll
@@ -248,7 +236,7 @@ __device__ __forceinline__ void softmax_update(float (&s)[4], float (&m)[2], flo
     // few pages) the factors are exactly 1 and the rescale is skipped.
     if (a0 != 1.f || a1 != 1.f) {
 #pragma unroll
-        for (int mt = 0; mt < 8; ++mt) {
+        for (int mt = 0; mt < TILES; ++mt) {
             o[mt][0] *= a0;
             o[mt][1] *= a1;
             o[mt][2] *= a0;
@@ -319,7 +307,8 @@ struct PoolFp16 {
     // covers two whole 256-byte rows. Row r lands at r * 256 with its chunks
     // XOR-swizzled by r & 7.
     static __device__ __forceinline__ int issue(const DecodeParams& p, int, int h,
-                                                const PageItem& it, uint32_t stage, int lane) {
+                                                const PageItem& it, uint32_t stage, int lane,
+                                                uint64_t pol) {
         const int hi = lane >> 4, col = lane & 15;
         const long long lane_off = hi * p.sk_p + col * 8;
         const long long row2 = 2 * p.sk_p;
@@ -328,19 +317,11 @@ struct PoolFp16 {
         const uint32_t dst0 = stage + hi * 256;
         const uint32_t c0 = (uint32_t)(col ^ hi) << 4;      // ((2i + hi) & 7) = (2i & 7) | hi
         if (it.valid == LS_PAGE) {
-#if LS_EVICT_FIRST
-            const uint64_t pol = l2_policy_evict_first();
-#endif
 #pragma unroll
             for (int i = 0; i < 8; ++i) {
                 const uint32_t dst = dst0 + i * 512 + (c0 ^ (((2 * i) & 7) << 4));
-#if LS_EVICT_FIRST
                 cp_async_16_stream(dst, kb + i * row2, pol);
                 cp_async_16_stream(dst + 4096, vb + i * row2, pol);
-#else
-                cp_async_16_full(dst, kb + i * row2);
-                cp_async_16_full(dst + 4096, vb + i * row2);
-#endif
             }
         } else {
 #pragma unroll
@@ -370,13 +351,12 @@ struct PoolFp16Tma {
 
     static __device__ __forceinline__ int issue(const DecodeParams&, const TmaMaps& maps, int, int h,
                                                 const PageItem& it, uint32_t stage, uint32_t mbar,
-                                                int lane) {
+                                                int lane, uint64_t pol) {
         if (lane == 0) {
             if (it.valid == 0) {
                 mbar_arrive(mbar);
             } else {
                 mbar_expect_tx(mbar, 8192u);
-                const uint64_t pol = l2_policy_evict_first();
                 tma_load_4d(stage, &maps.k, mbar, 0, h, 0, it.blk, pol);
                 tma_load_4d(stage + 2048, &maps.k, mbar, 64, h, 0, it.blk, pol);
                 tma_load_4d(stage + 4096, &maps.v, mbar, 0, h, 0, it.blk, pol);
@@ -642,7 +622,8 @@ struct PoolInt8 {
 
     // meta = valid tokens | (K came from the residual) << 8
     static __device__ __forceinline__ int issue(const DecodeParams& p, int b, int h,
-                                                const PageItem& it, uint32_t stage, int lane) {
+                                                const PageItem& it, uint32_t stage, int lane,
+                                                uint64_t pol) {
         bool from_res = p.k_res != nullptr && (it.last & 1) && it.valid > 0;
         int rr = from_res ? p.res_rows[b] : 0;
         if (rr < 0 || rr >= p.num_res_rows) {             // corrupt row index: read nothing, flag it
@@ -661,19 +642,12 @@ struct PoolInt8 {
         const signed char* vb =
             static_cast<const signed char*>(p.v_pool) + it.blk * p.sk_b + h * p.sk_h + lane_off;
         const bool full = it.valid == LS_PAGE;
-#if LS_EVICT_FIRST
-        const uint64_t pol = l2_policy_evict_first();
-#endif
         if (!from_res) {
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
                 const uint32_t dst = dst0 + i * 512 + (c0 ^ (((4 * i) & 7) << 4));
                 if (full) {
-#if LS_EVICT_FIRST
                     cp_async_16_stream(dst, kb + i * row4, pol);
-#else
-                    cp_async_16_full(dst, kb + i * row4);
-#endif
                 } else {
                     const int nbytes = 4 * i + r0 < it.valid ? 16 : 0;
                     cp_async_16(dst, nbytes ? kb + i * row4 : static_cast<const signed char*>(p.k_pool),
@@ -695,11 +669,7 @@ struct PoolInt8 {
         for (int i = 0; i < 4; ++i) {
             const uint32_t dst = dst0 + OFF_V + i * 512 + (c0 ^ (((4 * i) & 7) << 4));
             if (full) {
-#if LS_EVICT_FIRST
                 cp_async_16_stream(dst, vb + i * row4, pol);
-#else
-                cp_async_16_full(dst, vb + i * row4);
-#endif
             } else {
                 const int nbytes = 4 * i + r0 < it.valid ? 16 : 0;
                 cp_async_16(dst, nbytes ? vb + i * row4 : static_cast<const signed char*>(p.v_pool),
@@ -737,7 +707,7 @@ struct PoolInt8Tma {
 
     static __device__ __forceinline__ int issue(const DecodeParams& p, const TmaMaps& maps, int b,
                                                 int h, const PageItem& it, uint32_t stage,
-                                                uint32_t mbar, int lane) {
+                                                uint32_t mbar, int lane, uint64_t pol) {
         const bool from_res = p.k_res != nullptr && (it.last & 1) && it.valid > 0;
         if (from_res) {
             const int rr = p.res_rows[b];
@@ -750,7 +720,6 @@ struct PoolInt8Tma {
                 const uint32_t vs_bytes = 16u * p.heads * sizeof(float);
                 mbar_expect_tx(mbar, 2048u + (ASYM ? 2u : 1u) * vs_bytes +
                                          (from_res ? 0u : 2048u + (ASYM ? 1024u : 512u)));
-                const uint64_t pol = l2_policy_evict_first();
                 if (!from_res) {
                     tma_load_4d(stage, &maps.k, mbar, 0, h, 0, it.blk, pol);
                     tma_load_4d(stage + OFF_KS, &maps.ks, mbar, 0, 0, h, it.blk, pol);
@@ -765,6 +734,10 @@ struct PoolInt8Tma {
     }
 };
 
+__device__ __forceinline__ uint32_t hmul2_u32(uint32_t a, uint32_t b) {
+    const __half2 r = __hmul2(*reinterpret_cast<const __half2*>(&a), *reinterpret_cast<const __half2*>(&b));
+    return *reinterpret_cast<const uint32_t*>(&r);
+}
 __device__ __forceinline__ uint4 lds128(uint32_t addr) {
     uint4 r;
     asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];\n"
@@ -784,17 +757,23 @@ __device__ __forceinline__ float lds32f(uint32_t addr) {
 // for the int8 K page lane (g, t) takes dims 32t .. 32t+31 of rows g and g+8
 // (two 16-byte shared loads per row) and k-step ks uses dims 32t + 4ks .. +3;
 // the query fragments are built in the same order. For V the m index (output
-// dim) is permuted instead: lane (g, t) takes dims 16g .. 16g+15 of tokens
-// 2t, 2t+1, 2t+8, 2t+9, and tile mt holds dims 16g + 2mt and 16g + 2mt + 1.
+// dim) is permuted instead: the tile's 16-byte chunk mt comes in through
+// ldmatrix.trans on byte pairs, and output tile mt holds dims 16mt + 2g (rows g)
+// and 16mt + 2g + 1 (rows g + 8).
 template <int ASYM, bool TMA = false>
 struct MmaInt8 {
     using Pool = typename std::conditional<TMA, PoolInt8Tma<ASYM>, PoolInt8<ASYM>>::type;
     static constexpr int kMinCtas = LS_INT8_CTAS;
-    float qf[32];              // Q[row g][32t .. 32t+31] in fp32 (row g < n_rep, else 0)
-    float o[8][4];             // O^T: tile mt = dims 16g + 2mt (regs 0,1) and +1 (regs 2,3)
+    uint32_t qh[16];           // Q[row g][32t .. 32t+31] as half2 pairs (row g < n_rep, else 0)
+    float o[9][4];             // O^T: tile mt < 8 = dims 16mt + 2g (regs 0,1) and +1 (regs 2,3), with V
+                               // still carrying its conversion bias; tile 8 = sum of the weights per row
+                               // (what the bias has to be taken off with at the end)
     float m[2], l[2];
     float zacc[2];             // asymmetric V: sum_t w * zero_t, added to every dim
     int b_, h_;
+    uint32_t vs_off;           // byte offset of this lane's first V scale inside a stage (TMA layout)
+    uint32_t oneq[4];          // half2(1, 1) four times over: the constant A operand of the MMA that sums
+                               // the weights, held in registers (not re-made per page)
 
     __device__ __forceinline__ void begin(const DecodeParams& p, int b, int h, int lane) {
         b_ = b;
@@ -802,8 +781,13 @@ struct MmaInt8 {
         m[0] = m[1] = neg_inf();
         l[0] = l[1] = 0.f;
         zacc[0] = zacc[1] = 0.f;
+        vs_off = (uint32_t)(((lane >> 2) * p.heads + h) * 4);
 #pragma unroll
-        for (int mt = 0; mt < 8; ++mt)
+        for (int i = 0; i < 4; ++i) {
+            asm volatile("mov.b32 %0, 0x3C003C00;\n" : "=r"(oneq[i]));
+        }
+#pragma unroll
+        for (int mt = 0; mt < 9; ++mt)
 #pragma unroll
             for (int i = 0; i < 4; ++i) o[mt][i] = 0.f;
         const int g = lane >> 2, t = lane & 3;
@@ -812,22 +796,29 @@ struct MmaInt8 {
         for (int i = 0; i < 4; ++i) {
             uint4 raw = make_uint4(0, 0, 0, 0);
             if (g < p.n_rep) raw = *reinterpret_cast<const uint4*>(src + 8 * i);
-            const __half2* h2 = reinterpret_cast<const __half2*>(&raw);
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                const float2 f = __half22float2(h2[j]);
-                qf[8 * i + 2 * j] = f.x;
-                qf[8 * i + 2 * j + 1] = f.y;
-            }
+            qh[4 * i] = raw.x;
+            qh[4 * i + 1] = raw.y;
+            qh[4 * i + 2] = raw.z;
+            qh[4 * i + 3] = raw.w;
         }
     }
 
+    // A full page of a sequence's interior (all 16 tokens, K in the pool) takes the
+    // straight-line form: no masks, no residual branch. Anything else -- a last page, a
+    // page to skip -- takes the general one.
     __device__ __forceinline__ void compute(const DecodeParams& p, uint32_t stage, int meta,
                                             int lane) {
-        const int valid = meta & 255;
+        if (meta == LS_PAGE) compute_page<true>(p, stage, meta, lane);
+        else compute_page<false>(p, stage, meta, lane);
+    }
+
+    template <bool FULL>
+    __device__ __forceinline__ void compute_page(const DecodeParams& p, uint32_t stage, int meta,
+                                                 int lane) {
+        const int valid = FULL ? LS_PAGE : (meta & 255);
         const int g = lane >> 2, t = lane & 3;
         float s[4] = {0.f, 0.f, 0.f, 0.f};
-        if (meta & 256) {
+        if (!FULL && (meta & 256)) {
             // Last page: K is exact fp16 in the residual, read from global memory in
             // the same dim order as the int8 path (dims 32t .. 32t+31 of rows g, g+8:
             // 64 contiguous bytes per row); the query needs no scale. Rows past
@@ -845,34 +836,28 @@ struct MmaInt8 {
             }
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
-                mma_16816(s, ka[j].x, kb[j].x, ka[j].y, kb[j].y,
-                          pack_half2(qf[8 * j], qf[8 * j + 1]), pack_half2(qf[8 * j + 2], qf[8 * j + 3]));
-                mma_16816(s, ka[j].z, kb[j].z, ka[j].w, kb[j].w,
-                          pack_half2(qf[8 * j + 4], qf[8 * j + 5]),
-                          pack_half2(qf[8 * j + 6], qf[8 * j + 7]));
+                mma_16816(s, ka[j].x, kb[j].x, ka[j].y, kb[j].y, qh[4 * j], qh[4 * j + 1]);
+                mma_16816(s, ka[j].z, kb[j].z, ka[j].w, kb[j].w, qh[4 * j + 2], qh[4 * j + 3]);
             }
         } else {
-            // q' = fp16(q * k_scale), one rounding, in this lane's dim order.
+            // q' = q * fp16(k_scale) in half precision (the query stays in half2 registers:
+            // sixteen fewer than its fp32 form), in this lane's dim order.
             uint32_t qk[8][2];
             float zq = 0.f;
 #pragma unroll
             for (int i = 0; i < 8; ++i) {
                 const uint32_t slot = (uint32_t)(8 * t + (i ^ t)) << 4;   // see PoolInt8::issue
                 const uint4 sc = lds128(stage + Pool::OFF_KS + slot);
-                // Two products per instruction (packed fp32), each rounded as a single one would be.
-                float p0, p1, p2, p3;
-                unpack2(mul2(pack2(qf[4 * i], qf[4 * i + 1]),
-                             pack2(__uint_as_float(sc.x), __uint_as_float(sc.y))), p0, p1);
-                unpack2(mul2(pack2(qf[4 * i + 2], qf[4 * i + 3]),
-                             pack2(__uint_as_float(sc.z), __uint_as_float(sc.w))), p2, p3);
-                qk[i][0] = pack_half2(p0, p1);
-                qk[i][1] = pack_half2(p2, p3);
+                qk[i][0] = hmul2_u32(qh[2 * i], pack_half2(__uint_as_float(sc.x), __uint_as_float(sc.y)));
+                qk[i][1] = hmul2_u32(qh[2 * i + 1], pack_half2(__uint_as_float(sc.z), __uint_as_float(sc.w)));
                 if (ASYM) {
                     const uint4 z = lds128(stage + Pool::OFF_KZ + slot);
-                    zq = fmaf(qf[4 * i], __uint_as_float(z.x), zq);
-                    zq = fmaf(qf[4 * i + 1], __uint_as_float(z.y), zq);
-                    zq = fmaf(qf[4 * i + 2], __uint_as_float(z.z), zq);
-                    zq = fmaf(qf[4 * i + 3], __uint_as_float(z.w), zq);
+                    const float2 qa = __half22float2(*reinterpret_cast<const __half2*>(&qh[2 * i]));
+                    const float2 qb = __half22float2(*reinterpret_cast<const __half2*>(&qh[2 * i + 1]));
+                    zq = fmaf(qa.x, __uint_as_float(z.x), zq);
+                    zq = fmaf(qa.y, __uint_as_float(z.y), zq);
+                    zq = fmaf(qb.x, __uint_as_float(z.z), zq);
+                    zq = fmaf(qb.y, __uint_as_float(z.w), zq);
                 }
             }
             const uint32_t r0 = stage + g * 128, r1 = stage + (g + 8) * 128;
@@ -883,11 +868,16 @@ struct MmaInt8 {
             w1[1] = lds128(r1 + (((2 * t + 1) ^ g) << 4));
             const uint32_t* k0 = reinterpret_cast<const uint32_t*>(w0);
             const uint32_t* k1 = reinterpret_cast<const uint32_t*>(w1);
+            // int8 x -> fp16 exactly: 0x6400 | (x ^ 0x80) is 1024 + (x + 128), minus 1152.
+            // (Leaving the bias in and taking it off with a second MMA against a constant was
+            // measured too: eight more tensor-core instructions per page cost more, under the
+            // power cap, than the thirty-two half2 subtractions they replace.)
 #pragma unroll
             for (int ks = 0; ks < 8; ++ks) {
+                const uint32_t x0 = k0[ks] ^ 0x80808080u, x1 = k1[ks] ^ 0x80808080u;
                 uint32_t a0, a1, a2, a3;
-                bytes4_to_half2x2(k0[ks] ^ 0x80808080u, a0, a2);
-                bytes4_to_half2x2(k1[ks] ^ 0x80808080u, a1, a3);
+                bytes4_to_half2x2(x0, a0, a2);
+                bytes4_to_half2x2(x1, a1, a3);
                 mma_16816(s, a0, a1, a2, a3, qk[ks][0], qk[ks][1]);
             }
             if (ASYM) {
@@ -899,7 +889,12 @@ struct MmaInt8 {
                 s[0] += z0; s[1] += z1; s[2] += z0; s[3] += z1;
             }
         }
-        mask_and_scale(s, valid, p.scale_log2, lane);
+        if (FULL) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) s[i] *= p.scale_log2;
+        } else {
+            mask_and_scale(s, valid, p.scale_log2, lane);
+        }
         float a0, a1;
         softmax_update(s, m, l, o, a0, a1);
         // V's per-token scale rides on the weight (zero for rows past the end:
@@ -907,10 +902,10 @@ struct MmaInt8 {
         float vs0, vs1;
         if (TMA) {
             // The page's scales for all heads, [token][head]; tokens past the end are stale.
-            vs0 = lds32f(stage + Pool::OFF_VS + (g * p.heads + h_) * 4);
-            vs1 = lds32f(stage + Pool::OFF_VS + ((g + 8) * p.heads + h_) * 4);
-            if (g >= valid) vs0 = 0.f;
-            if (g + 8 >= valid) vs1 = 0.f;
+            vs0 = lds32f(stage + Pool::OFF_VS + vs_off);
+            vs1 = lds32f(stage + Pool::OFF_VS + vs_off + 32 * p.heads);
+            if (!FULL && g >= valid) vs0 = 0.f;
+            if (!FULL && g + 8 >= valid) vs1 = 0.f;
         } else {
             vs0 = lds32f(stage + Pool::OFF_VS + g * 4);
             vs1 = lds32f(stage + Pool::OFF_VS + (g + 8) * 4);
@@ -918,8 +913,8 @@ struct MmaInt8 {
         if (ASYM) {
             float vz0, vz1;
             if (TMA) {
-                vz0 = (g < valid) ? lds32f(stage + Pool::OFF_VZ + (g * p.heads + h_) * 4) : 0.f;
-                vz1 = (g + 8 < valid) ? lds32f(stage + Pool::OFF_VZ + ((g + 8) * p.heads + h_) * 4) : 0.f;
+                vz0 = (g < valid) ? lds32f(stage + Pool::OFF_VZ + vs_off) : 0.f;
+                vz1 = (g + 8 < valid) ? lds32f(stage + Pool::OFF_VZ + vs_off + 32 * p.heads) : 0.f;
             } else {
                 vz0 = lds32f(stage + Pool::OFF_VZ + g * 4);
                 vz1 = lds32f(stage + Pool::OFF_VZ + (g + 8) * 4);
@@ -930,37 +925,29 @@ struct MmaInt8 {
         const uint32_t pb0 = movmatrix_trans(pack_half2(s[0] * vs0, s[1] * vs0));
         const uint32_t pb1 = movmatrix_trans(pack_half2(s[2] * vs1, s[3] * vs1));
 
-        // V fragments: tokens 2t, 2t+1, 2t+8, 2t+9, dims 16g .. 16g+15.
-        const uint32_t vbase = stage + Pool::OFF_V;
-        uint4 v[4];
-        v[0] = lds128(vbase + (2 * t) * 128 + ((g ^ ((2 * t) & 7)) << 4));
-        v[1] = lds128(vbase + (2 * t + 1) * 128 + ((g ^ ((2 * t + 1) & 7)) << 4));
-        v[2] = lds128(vbase + (2 * t + 8) * 128 + ((g ^ ((2 * t) & 7)) << 4));
-        v[3] = lds128(vbase + (2 * t + 9) * 128 + ((g ^ ((2 * t + 1) & 7)) << 4));
-        const uint32_t* vw0 = reinterpret_cast<const uint32_t*>(&v[0]);
-        const uint32_t* vw1 = reinterpret_cast<const uint32_t*>(&v[1]);
-        const uint32_t* vw2 = reinterpret_cast<const uint32_t*>(&v[2]);
-        const uint32_t* vw3 = reinterpret_cast<const uint32_t*>(&v[3]);
+        // V^T fragments straight out of the int8 tile: ldmatrix.trans on 16-bit units
+        // (a unit = two neighbouring dims of one token) hands lane (g, t) the unit g of
+        // tokens 2t and 2t+1 in one register -- bytes [T.dA, T.dB, T+1.dA, T+1.dB] -- which
+        // two byte permutes turn into the half2 pairs (tokens 2t, 2t+1) of dims A and B.
+        // Matrices of one ldmatrix.x4: tokens 0-7 / 8-15 of 16-byte chunk 2q, then of 2q+1;
+        // output tile mt = chunk mt holds dims 16mt + 2g (rows g) and 16mt + 2g + 1 (rows g+8).
+        // As for K, the values enter as 1152 + v; tile 8 accumulates the weights alone
+        // (A = all ones) and finish() takes 1152 x that off every dim.
         const uint32_t magic = 0x64646464u;
-        const __half2 off = __floats2half2_rn(1152.f, 1152.f);
+        mma_16816(o[8], oneq[0], oneq[1], oneq[2], oneq[3], pb0, pb1);
+        const int mi = lane >> 3;                                   // the matrix this lane addresses
+        const int vrow = (lane & 7) + (mi & 1) * 8;
+        const uint32_t vaddr = stage + Pool::OFF_V + vrow * 128;
+        const int sw = vrow & 7, hi = mi >> 1;
 #pragma unroll
-        for (int mt = 0; mt < 8; ++mt) {
-            const int j = mt >> 1;
-            const uint32_t sel = (mt & 1) ? 0x7632u : 0x5410u;
-            // [T0.dA, T0.dB, T1.dA, T1.dB] and the same for tokens T2, T3
-            const uint32_t x01 = prmt(vw0[j], vw1[j], sel) ^ 0x80808080u;
-            const uint32_t x23 = prmt(vw2[j], vw3[j], sel) ^ 0x80808080u;
-            uint32_t f[4];
-            f[0] = prmt(x01, magic, 0x4240u);   // dim A, tokens T0 T1
-            f[1] = prmt(x01, magic, 0x4341u);   // dim B, tokens T0 T1
-            f[2] = prmt(x23, magic, 0x4240u);   // dim A, tokens T2 T3
-            f[3] = prmt(x23, magic, 0x4341u);   // dim B, tokens T2 T3
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                const __half2 hv = __hsub2(*reinterpret_cast<__half2*>(&f[i]), off);
-                f[i] = *reinterpret_cast<const uint32_t*>(&hv);
-            }
-            mma_16816(o[mt], f[0], f[1], f[2], f[3], pb0, pb1);
+        for (int q = 0; q < 4; ++q) {
+            uint32_t m0, m1, m2, m3;
+            ldmatrix_x4_trans(vaddr + (((2 * q + hi) ^ sw) << 4), m0, m1, m2, m3);
+            m0 ^= 0x80808080u; m1 ^= 0x80808080u; m2 ^= 0x80808080u; m3 ^= 0x80808080u;
+            mma_16816(o[2 * q], prmt(m0, magic, 0x4240u), prmt(m0, magic, 0x4341u), prmt(m1, magic, 0x4240u),
+                      prmt(m1, magic, 0x4341u), pb0, pb1);
+            mma_16816(o[2 * q + 1], prmt(m2, magic, 0x4240u), prmt(m2, magic, 0x4341u),
+                      prmt(m3, magic, 0x4240u), prmt(m3, magic, 0x4341u), pb0, pb1);
         }
     }
 
@@ -976,10 +963,12 @@ struct MmaInt8 {
         }
         const int g = lane >> 2, t = lane & 3;
         const int r0 = 2 * t, r1 = r0 + 1;
-        const float z0 = ASYM ? zacc[0] : 0.f, z1 = ASYM ? zacc[1] : 0.f;
+        // minus the conversion bias of V (tile 8 = the weights' sum), plus the zero points' share
+        const float z0 = (ASYM ? zacc[0] : 0.f) - 1152.f * o[8][0];
+        const float z1 = (ASYM ? zacc[1] : 0.f) - 1152.f * o[8][1];
 #pragma unroll
         for (int mt = 0; mt < 8; ++mt) {
-            const int d = 16 * g + 2 * mt;
+            const int d = 16 * mt + 2 * g;
             if (r0 < n_rep) {
                 mo[r0 * kMergeStride + d] = o[mt][0] + z0;
                 mo[r0 * kMergeStride + d + 1] = o[mt][2] + z0;
@@ -1127,8 +1116,7 @@ decode_kernel(const DecodeParams p, const __grid_constant__ TmaMaps maps) {
     float* merge_o = reinterpret_cast<float*>(smem + kWarps * STAGES * STAGE_BYTES + kWarps * STAGES * 8);
     float* merge_m = merge_o + kWarps * p.n_rep * kMergeStride;
     float* merge_l = merge_m + kWarps * kRP;
-    int* meta = reinterpret_cast<int*>(merge_l + kWarps * kRP);   // [kWarps][STAGES]
-    int* scan = meta + kWarps * STAGES;                           // [kWarps]
+    int* scan = reinterpret_cast<int*>(merge_l + kWarps * kRP);   // [kWarps]
     int* flag = scan + kWarps;                                    // [1]
     int* cum = flag + 1;                                          // [batch + 1]
 
@@ -1153,7 +1141,6 @@ decode_kernel(const DecodeParams p, const __grid_constant__ TmaMaps maps) {
     const bool has_work = g0 < total;
     const int b0 = has_work ? find_seq(cum, p.batch, g0) : 0;
     const uint32_t ring = smem_u32(smem + warp * (STAGES * STAGE_BYTES));
-    int* my_meta = meta + warp * STAGES;
 
     // Load side. The dense walk needs nothing the previous kernel may have
     // written; the sparse walk reads the selection, which it usually did write.
@@ -1173,24 +1160,34 @@ decode_kernel(const DecodeParams p, const __grid_constant__ TmaMaps maps) {
         if (!waited) asm volatile("griddepcontrol.wait;\n" ::: "memory");
         waited = true;
     };
-    auto issue = [&](int stage) {
+    // KV pages are read once per step: evict-first keeps tables, lengths, queries and
+    // partials in L2.
+    const uint64_t pol = l2_policy_evict_first();
+    // What the load side knows about the page in each ring slot (valid tokens, flags):
+    // warp-uniform, indexed by compile-time slot numbers only, so it lives in registers.
+    int slot_meta[STAGES];
+#pragma unroll
+    for (int s = 0; s < STAGES; ++s) slot_meta[s] = 0;
+    auto issue = [&](int slot) {
         PageItem item;
         int lb;
         if (win.next(p, cum, h, warp, lane, item, lb)) {
             if (item.last) dep_wait();
             int mt;
             if constexpr (Pool::kTma)
-                mt = Pool::issue(p, maps, lb, h, item, ring + stage * STAGE_BYTES, mbar0 + 8 * stage, lane);
+                mt = Pool::issue(p, maps, lb, h, item, ring + slot * STAGE_BYTES, mbar0 + 8 * slot, lane, pol);
             else
-                mt = Pool::issue(p, lb, h, item, ring + stage * STAGE_BYTES, lane);
-            if (lane == 0) my_meta[stage] = mt;
+                mt = Pool::issue(p, lb, h, item, ring + slot * STAGE_BYTES, lane, pol);
+#pragma unroll
+            for (int q = 0; q < STAGES; ++q) slot_meta[q] = slot == q ? mt : slot_meta[q];
         }
         if (!Pool::kTma) cp_async_commit();
     };
-    if (early && has_work) {
+    auto issue_first = [&]() {                               // STAGES - 1 pages ahead
 #pragma unroll
-        for (int s = 0; s < STAGES - 1 + LS_ISSUE_AFTER; ++s) issue(s);
-    }
+        for (int s = 0; s < STAGES - 1; ++s) issue(s);
+    };
+    if (early && has_work) issue_first();
     dep_wait();
 
     if (chunk_id == 0 && h == 0) write_seg_ranges<kThreads>(p, cum, chunk);
@@ -1205,12 +1202,11 @@ decode_kernel(const DecodeParams p, const __grid_constant__ TmaMaps maps) {
     if (!has_work) return;
     if (MODE != LS_MODE_DENSE)
         win.begin(p, cursor_begin<kWarps>(cum, p.batch, b0, g0, g1, warp), h, lane);
-    if (!early) {
-#pragma unroll
-        for (int s = 0; s < STAGES - 1 + LS_ISSUE_AFTER; ++s) issue(s);
-    }
+    if (!early) issue_first();
 
-    // Compute side: segment by segment.
+    // Compute side: segment by segment. One page step: wait for the slot, refill the slot
+    // consumed one page ago, compute. (A copy of the step per ring slot, with the slot a
+    // compile-time constant, was measured: the larger code cost more than the immediates saved.)
     State st;
     int stage = 0;         // ring slot of the page being consumed
     uint32_t phase = 0;    // parity of that slot's mbarrier phase (TMA variants)
@@ -1220,27 +1216,26 @@ decode_kernel(const DecodeParams p, const __grid_constant__ TmaMaps maps) {
         const int hi = min(g1, cum[b + 1]) - cum[b];
         st.begin(p, b, h, lane);
         for (int u = first_u + warp; u < hi; u += kWarps) {
-            if constexpr (Pool::kTma) {
-                // Bounded: a load that never lands is reported (status 2 in the error
-                // slot), not waited for; the result of this launch is then invalid.
-                if (!mbar_wait_bounded(mbar0 + 8 * stage, phase, kMbarSpinLimit)) {
-                    if (lane == 0) p.seg_range[2 * p.batch] = 2;
+            {
+                const uint32_t bar = mbar0 + 8 * stage;
+                if constexpr (Pool::kTma) {
+                    if (!mbar_wait_bounded(bar, phase, kMbarSpinLimit)) {
+                        if (lane == 0) p.seg_range[2 * p.batch] = 2;
+                    }
+                } else {
+                    cp_async_wait<STAGES - 2>();
                 }
-            } else {
-                cp_async_wait<STAGES - 2 + LS_ISSUE_AFTER>();
-            }
-            __syncwarp();
-#if LS_ISSUE_AFTER
-            // The whole ring is kept in flight: a stage is refilled as soon as it has
-            // been consumed (STAGES pages requested ahead of the one being computed).
-            const int meta_now = my_meta[stage];
-            st.compute(p, ring + stage * STAGE_BYTES, meta_now, lane);
-            __syncwarp();                                    // every lane is done with the stage
-            issue(stage);
+                __syncwarp();
+                int meta_now = slot_meta[0];
+#pragma unroll
+                for (int q = 1; q < STAGES; ++q) meta_now = stage == q ? slot_meta[q] : meta_now;
+                issue(stage == 0 ? STAGES - 1 : stage - 1);          // the slot consumed one page ago
+#ifndef LS_LOADS_ONLY
+                st.compute(p, ring + stage * STAGE_BYTES, meta_now, lane);
 #else
-            issue(stage == 0 ? STAGES - 1 : stage - 1);      // the stage consumed one page ago
-            st.compute(p, ring + stage * STAGE_BYTES, my_meta[stage], lane);
+                (void)meta_now;                          // build flag: pages land, nothing is computed
 #endif
+            }
             if (++stage == STAGES) {
                 stage = 0;
                 phase ^= 1u;
@@ -1349,7 +1344,7 @@ static int launch_decode(const DecodeParams& p, cudaStream_t stream, bool progra
     static const TmaMaps no_maps = {};
     const size_t smem = (size_t)kWarps * STAGES * State::Pool::STAGE_BYTES + kWarps * STAGES * 8 +
                         sizeof(float) * ((size_t)kWarps * p.n_rep * kMergeStride + 2 * kWarps * kRP) +
-                        sizeof(int) * ((size_t)kWarps * STAGES + kWarps + 1 + p.batch + 1);
+                        sizeof(int) * ((size_t)kWarps + 1 + p.batch + 1);
     auto kern = decode_kernel<State, MODE, STAGES>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
@@ -1435,7 +1430,7 @@ bool build_fp16_maps(const ls::DecodeParams& p, ls::TmaMaps* maps) {
     if (p.sk_h <= 0 || p.sk_p <= 0 || p.sk_b <= 0) return false;
     // A row is 256 bytes and arrives as two tile rows: with 256-byte L2 promotion the
     // first half's request brings the second half into L2 as well.
-    const CUtensorMapL2promotion promo = LS_FP16_TMA_PROMO;
+    const CUtensorMapL2promotion promo = CU_TENSOR_MAP_L2_PROMOTION_L2_256B;
     return encode_4d(&maps->k, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, p.k_pool, dims, strides, box, promo) &&
            encode_4d(&maps->v, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, p.v_pool, dims, strides, box, promo);
 }

@@ -144,6 +144,31 @@ def select_for_attention(scores: torch.Tensor, seq_lens: torch.Tensor, k: int, r
     return sel
 
 
+def index_and_select(q, kmin, kmax, block_tables, seq_lens, k: int, ratio: Optional[float],
+                     recent: int = 2):
+    """`page_scores` then `select_for_attention` behind one library call. Same
+    scores, same pages. -> (scores fp32 [B, H, max_pages], sel int32 [B, H, k]). With
+    programmatic launch on (`paged_decode_cuda.set_programmatic_launch`) the page
+    bounds are requested while the previous kernel of the stream drains; they are
+    never a sequence's last page's, the only bounds a decode step's append changes."""
+    b, h, n_rep, d = q.shape
+    max_pages = block_tables.shape[1]
+    if not 0 < k <= max_pages:
+        raise ValueError(f"k must be in [1, {max_pages}], got {k}")
+    if seq_lens.dtype != torch.int32 or block_tables.dtype != torch.int32:
+        raise ValueError("block tables and sequence lengths must be int32")
+    scores = pdc.scratch("sparse_scores", (b, h, max_pages), torch.float32, q.device)
+    sel = pdc.scratch("sparse_sel_set", (b, h, k), torch.int32, q.device)
+    rc = _lib.lib().ls_page_index_select(
+        q.data_ptr(), kmin.data_ptr(), kmax.data_ptr(), block_tables.data_ptr(), seq_lens.data_ptr(),
+        scores.data_ptr(), sel.data_ptr(), b, h, n_rep, d, 16, max_pages,
+        block_tables.stride(0), kmin.shape[0], recent, k, 0.0 if ratio is None else float(ratio),
+        pdc.dense_launch_flags(), q.stride(0), q.stride(1), q.stride(2), kmin.stride(0), kmin.stride(1),
+        scores.stride(0), scores.stride(1), sel.stride(0), sel.stride(1), _lib.current_stream(q.device))
+    _lib.check(rc, "index_and_select")
+    return scores, sel
+
+
 def sparse_decode(q, k_pool, v_pool, block_tables, seq_lens, sel,
                   num_splits: Optional[int] = None,
                   softmax_scale: Optional[float] = None,
@@ -223,16 +248,17 @@ def sparse_attention(q, k_pool, v_pool, block_tables, seq_lens, kmin, kmax,
     pages = block_tables.shape[1] if max_seq_len is None else min(
         block_tables.shape[1], -(-max_seq_len // page))
     k = budget(ratio, pages, recent)
+    # The reference sorts (`select(scores, k, sorted=True)`) and lets each sequence attend the
+    # first n entries it is owed; the same n pages are picked here without the sort, and for
+    # the bounds scoring by the index kernel itself.
     if scoring == "mass":
         scores = page_scores_mass(q, kmin, kmax, block_tables, seq_lens, recent, softmax_scale,
                                   page=page)
+        sel = select_for_attention(scores, seq_lens, k, ratio, recent)
     elif scoring == "bounds":
-        scores = page_scores(q, kmin, kmax, block_tables, seq_lens, recent)
+        _, sel = index_and_select(q, kmin, kmax, block_tables, seq_lens, k, ratio, recent)
     else:
         raise ValueError(f"unknown scoring {scoring!r}")
-    # The reference sorts (`select(scores, k, sorted=True)`) and lets each sequence attend the
-    # first n entries it is owed; the same n pages are picked here without the sort.
-    sel = select_for_attention(scores, seq_lens, k, ratio, recent)
     return sparse_decode(q, k_pool, v_pool, block_tables, seq_lens, sel, num_splits,
                          softmax_scale, ratio=ratio, recent=recent, k_scale=k_scale, v_scale=v_scale,
                          k_residual=k_residual, res_rows=res_rows)

@@ -306,3 +306,73 @@ def test_fp16_cache_decode_steps_with_bounds_and_prefix_sharing():
         close(got, want)
     cache.free_sequence(0)
     assert cache.allocator.ref_count(shared[0]) == 1           # still held by sequence 1
+
+
+@pytest.mark.parametrize("lens,ratio", [([700, 333, 64, 17, 0], 0.25), ([32768, 9000], 0.5),
+                                        ([65536, 40000, 100], 0.5), ([70000, 5000], 0.25)])
+@pytest.mark.parametrize("programmatic", [False, True])
+def test_index_and_select_behind_one_call_equals_the_two_calls(lens, ratio, programmatic):
+    """Scores and picked pages of `index_and_select` against `page_scores` followed by
+    `select_for_attention`, bit for bit: ragged rows, rows of 2048, 4096 and more
+    pages, with and without requesting the bounds ahead of the dependency wait, three
+    times in a row."""
+    dev = device()
+    pages = max(1, -(-max(lens) // 16))
+    g = torch.Generator(device=dev).manual_seed(len(lens) * 1000 + pages)
+    nb = sum(-(-x // 16) for x in lens) + 5
+    kmin = torch.randn(nb, 2, 128, dtype=torch.float16, device=dev, generator=g) - 1.0
+    kmax = kmin + torch.rand(nb, 2, 128, dtype=torch.float16, device=dev, generator=g) * 3
+    q = torch.randn(len(lens), 2, 6, 128, dtype=torch.float16, device=dev, generator=g)
+    perm = torch.randperm(nb, device=dev, generator=g).to(torch.int32)
+    tables = torch.zeros(len(lens), pages, dtype=torch.int32, device=dev)
+    at = 0
+    for i, x in enumerate(lens):
+        n = -(-x // 16)
+        tables[i, :n] = perm[at:at + n]
+        at += n
+    seq = torch.tensor(lens, dtype=torch.int32, device=dev)
+    k = ps.budget(ratio, pages)
+    want_scores = ps.page_scores(q, kmin, kmax, tables, seq).clone()
+    want_sel = ps.select_for_attention(want_scores, seq, k, ratio).clone()
+    pdc.set_programmatic_launch(programmatic, early_pages=True)
+    try:
+        for _ in range(3):
+            scores, sel = ps.index_and_select(q, kmin, kmax, tables, seq, k, ratio)
+            assert torch.equal(scores, want_scores)
+            assert torch.equal(sel, want_sel)
+            sel.fill_(-7)
+        torch.cuda.synchronize()
+    finally:
+        pdc.set_programmatic_launch(False)
+
+
+def test_rewind_reuses_blocks_and_recomputes_the_landing_pages_bounds():
+    """Decode from one prefilled state, rewind, decode again with other tokens
+    (the reference's oracle-study use, cache/paged_cache.py:275-303): same blocks, same
+    slots, bounds of the page the rewind lands in taken over its remaining rows."""
+    dev = device()
+    spec = lc.KVCacheSpec(num_layers=1, num_kv_heads=2, head_dim=128, max_seq_len=128, max_batch_size=1,
+                          device="cuda")
+    cache = lc.PagedKVCache(spec, num_blocks=12)
+    cache.enable_page_bounds()
+    g = torch.Generator(device=dev).manual_seed(3)
+    k = torch.randn(1, 2, 40, 128, dtype=torch.float16, device=dev, generator=g)
+    cache.advance(40, slots=[0])
+    cache.write(0, k, k)
+    blocks = list(cache.tables[0].blocks)
+    for _ in range(10):                                   # to 50 tokens: page 3 opened
+        cache.advance(1, slots=[0])
+        cache.write(0, torch.randn(1, 2, 1, 128, dtype=torch.float16, device=dev, generator=g) * 5,
+                    torch.zeros(1, 2, 1, 128, dtype=torch.float16, device=dev))
+    cache.rewind(40)
+    assert cache.seq_lens == [40] and int(cache.seq_lens_tensor(1)[0]) == 40
+    blk = blocks[2]
+    assert torch.equal(cache.kmin[0][blk], k[0, :, 32:40].amin(dim=1))
+    assert torch.equal(cache.kmax[0][blk], k[0, :, 32:40].amax(dim=1))
+    new = torch.randn(1, 2, 1, 128, dtype=torch.float16, device=dev, generator=g)
+    cache.advance(1, slots=[0])
+    cache.write(0, new, new)
+    assert cache.tables[0].blocks[:3] == blocks[:3] and int(cache.seq_lens_tensor(1)[0]) == 41
+    assert torch.equal(cache.k_pool[0][blk, 8], new[0, :, 0])
+    with pytest.raises(ValueError):
+        cache.rewind(99)
