@@ -21,8 +21,9 @@ One JSON line comes out:
              a burst figure, the later ones run under the power cap).
   e2e        the same metric through the public Python API with HOST buffers:
              each step copies the queries and the new K/V rows of all layers
-             from pinned host memory, runs cache.write() and
-             paged_decode_attention() per layer, eagerly, reads the outputs
+             from pinned host memory (one copy), runs cache.write() and
+             paged_decode_attention() per layer, eagerly (one launch per layer:
+             the append rides on the attention kernel), reads the outputs
              back to the host, and runs cache.advance() for the next step
              (block tables, lengths and slots shipped to the device) while the
              GPU is still working on this one.
@@ -743,15 +744,20 @@ def run_e2e(args, workload, ranks: Ranks):
     random.Random(0).shuffle(cache.allocator._free)      # shuffled block tables, as in `value`
     for i in range(batch):
         cache.tables[i].append(context - 1)
-    host_q = torch.randn(layers, batch, h, r, d).half().pin_memory()
-    host_k = torch.randn(layers, batch, h, 1, d).half().pin_memory()
-    host_v = torch.randn(layers, batch, h, 1, d).half().pin_memory()
+    # One pinned host image per step: for every layer and (sequence, KV head) the six query
+    # rows, then the new K row, then the new V row; one copy to the device, of which the
+    # layers' q / k / v are strided views.
+    host_in = torch.randn(layers, batch, h, r + 2, d).half().pin_memory()
     host_out = torch.empty(layers, batch, h, r, d, dtype=torch.float16).pin_memory()
-    dq, dk, dv = (torch.empty_like(x, device=dev) for x in (host_q, host_k, host_v))
+    dev_in = torch.empty_like(host_in, device=dev)
     dout = torch.empty(layers, batch, h, r, d, dtype=torch.float16, device=dev)
+    cache.enable_fused_append()                          # the append rides on the attention launch
 
     # Per-layer views made once, as a model's layers hold them.
-    q_l, k_l, v_l, out_l = ([t[i] for i in range(layers)] for t in (dq, dk, dv, dout))
+    q_l = [dev_in[i, :, :, :r] for i in range(layers)]
+    k_l = [dev_in[i, :, :, r:r + 1] for i in range(layers)]
+    v_l = [dev_in[i, :, :, r + 1:r + 2] for i in range(layers)]
+    out_l = [dout[i] for i in range(layers)]
     host_s = [0.0]
 
     def layer_calls():
@@ -769,9 +775,7 @@ def run_e2e(args, workload, ranks: Ranks):
         # the host's bookkeeping for step t + 1 runs while the GPU works on step t, and its
         # one small copy is ordered behind step t's kernels on the stream.
         t0 = time.perf_counter()
-        dq.copy_(host_q, non_blocking=True)
-        dk.copy_(host_k, non_blocking=True)
-        dv.copy_(host_v, non_blocking=True)
+        dev_in.copy_(host_in, non_blocking=True)
         if graph[0] is None:
             layer_calls()
         else:
@@ -815,14 +819,15 @@ def run_e2e(args, workload, ranks: Ranks):
     g_mean_len = context + 2 * warm + steps + (steps + 1) / 2
     step_bytes = synthetic.kv_bytes_fp16([mean_len] * batch) * layers
     g_bytes = synthetic.kv_bytes_fp16([g_mean_len] * batch) * layers
-    h2d = (host_q.numel() + host_k.numel() + host_v.numel()) * 2 + cache._step_bytes
+    h2d = host_in.numel() * 2 + cache._step_bytes
     d2h = host_out.numel() * 2
     out = {"value": round(world * step_bytes / (ms * 1e-3) / 1e9, 1), "unit": "GB/s",
            "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h),
            "ms_per_step": round(ms, 4), "host_enqueue_ms_per_step": round(host_ms, 4),
-           "steps": steps, "gpu_launches_per_step": 2 * layers,
-           "path": "PagedKVCache.write + paged_decode_attention per layer, eager; PagedKVCache.advance for "
-                   "the next step issued while the GPU works on this one",
+           "steps": steps, "gpu_launches_per_step": layers,
+           "path": "PagedKVCache.write + paged_decode_attention per layer, eager (the cache in fused-append "
+                   "mode: the write rides on the attention launch); PagedKVCache.advance for the next step "
+                   "issued while the GPU works on this one",
            "graph_replay": {"value": round(world * g_bytes / (g_ms * 1e-3) / 1e9, 1), "unit": "GB/s",
                             "ms_per_step": round(g_ms, 4),
                             "host_enqueue_ms_per_step": round(g_host_ms, 4),

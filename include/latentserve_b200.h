@@ -107,6 +107,28 @@ int ls_paged_decode_fp16(const void* q, const void* k_pool, const void* v_pool,
                          int64_t so_b, int64_t so_h, int64_t so_m, float softmax_scale,
                          void* stream);
 
+/* The same launch with the step's KV append riding on it: the new token's K and V rows
+ * (the rows a decode step would first scatter into the pools) are handed to the attention
+ * kernel, which takes the newest row of each sequence's last page from them, stores them to
+ * the pools for the steps to come, and attends as if they had been appended first. One
+ * launch per layer instead of two.
+ * Replaces PagedKVCache.write (cache/paged_cache.py:398-417, two index_copy_) followed by
+ * `paged_decode_fp16` (kernels/cuda/paged_decode_fp16.cu:55-200), as GQAAttention.forward
+ * runs them back to back (model/attention/gqa.py:267, 283-344).
+ *   k_new, v_new fp16 rows [B,H,128] (sn_b, sn_h / svn_b, svn_h), 16-byte aligned; the row of
+ *   sequence b goes to position seq_lens[b] - 1, i.e. block_tables[b][(L-1)/16], row (L-1)%16.
+ *   seq_lens already count the new token. Page bounds are not maintained by this entry
+ *   point (use ls_kv_append_fp16 when the sparse indexer is on). Per-lane copies only
+ *   (LS_LOAD_TMA is ignored). */
+int ls_paged_decode_append_fp16(const void* q, const void* k_new, const void* v_new, void* k_pool,
+                                void* v_pool, const int32_t* block_tables, const int32_t* seq_lens,
+                                float* part_acc, float* part_m, float* part_l, int32_t* seg_range, void* out,
+                                int batch, int kv_heads, int n_rep, int head_dim, int page, int max_pages,
+                                int num_blocks, int num_chunks, int min_chunk, int flags, int64_t sq_b,
+                                int64_t sq_h, int64_t sq_m, int64_t sn_b, int64_t sn_h, int64_t svn_b,
+                                int64_t svn_h, int64_t sk_b, int64_t sk_p, int64_t sk_h, int64_t so_b,
+                                int64_t so_h, int64_t so_m, float softmax_scale, void* stream);
+
 /* Dense fp16 decode for callers that cannot allocate device memory. No
  * counterpart in the reference (its scratch comes from torch's allocator,
  * kernels/gqa/paged_decode.py:501-517, and every caller there has one).

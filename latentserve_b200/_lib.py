@@ -38,6 +38,7 @@ P, I, L, F = c_void_p, c_int, c_int64, c_float
 _PROTOTYPES = {
     "ls_decode_slots": [I, I],
     "ls_paged_decode_fp16": [P, P, P, P, P, P, P, P, P, P] + [I] * 10 + [L] * 9 + [F, P],
+    "ls_paged_decode_append_fp16": [P] * 12 + [I] * 10 + [L] * 13 + [F, P],
     "ls_paged_sparse_fp16": [P, P, P, P, P, P, F, I, P, P, P, P, P] + [I] * 11 + [L] * 11 + [F, P],
     "ls_paged_decode_int8": [P] * 16 + [I] * 11 + [L] * 17 + [F, P],
     "ls_paged_sparse_int8": [P, F, I, I, L, L] + [P] * 16 + [I] * 11 + [L] * 17 + [F, P],

@@ -54,9 +54,13 @@ def build(force: bool = False, verbose: bool = False, ptxas_verbose: bool = Fals
            *ARCH_FLAGS, "-I", str(CSRC)]
     if ptxas_verbose:
         cmd += ["-Xptxas", "-v"]
-    # Developer knob for tuning runs, e.g. LS_NVCC_EXTRA='-DLS_STAGES=2'.
+    # Developer knobs for measurement builds: LS_NVCC_EXTRA adds compiler flags (e.g.
+    # '-DLS_LOADS_ONLY': the decode kernels' pages land and nothing is computed -- the
+    # ceiling of their access pattern), LS_LIB_OUT writes the result elsewhere, to be
+    # loaded through LATENTSERVE_B200_LIB instead of the product library.
     cmd += os.environ.get("LS_NVCC_EXTRA", "").split()
-    cmd += [str(s) for s in sources()] + ["-o", str(LIB)]
+    out = os.environ.get("LS_LIB_OUT") or str(LIB)
+    cmd += [str(s) for s in sources()] + ["-o", out]
     if verbose:
         print(" ".join(cmd), file=sys.stderr)
     res = subprocess.run(cmd, capture_output=True, text=True)
@@ -64,7 +68,7 @@ def build(force: bool = False, verbose: bool = False, ptxas_verbose: bool = Fals
         raise RuntimeError(f"nvcc failed ({res.returncode}):\n{res.stdout}\n{res.stderr}")
     if verbose or ptxas_verbose:
         sys.stderr.write(res.stdout + res.stderr)
-    return LIB
+    return pathlib.Path(out)
 
 
 if __name__ == "__main__":

@@ -343,6 +343,31 @@ class PagedKVCache(_PagedBase):
         self._bounds_on = False
         self.kmin: list = []
         self.kmax: list = []
+        self.fused_append = False
+
+    def enable_fused_append(self) -> None:
+        """Let a decode step's append ride on the attention launch: `write()` of one
+        token per sequence launches nothing and leaves the rows for the next
+        `paged_decode_attention` call on that layer's pools, whose kernel takes the
+        newest row from them and stores them to the pools (`ls_paged_decode_append_fp16`):
+        one launch per layer instead of two. For callers that follow every `write()`
+        with the layer's attention call, as `GQAAttention.forward` does
+        (model/attention/gqa.py:267, 283-344); rows nobody attended are appended by the
+        next `advance()`. Not used while page bounds are kept (the sparse indexer needs
+        the append kernel's bounds update)."""
+        self.fused_append = True
+
+    def _flush_deferred_appends(self) -> None:
+        from latentserve_b200 import paged_decode as pd
+
+        if not self.fused_append:
+            return
+        for layer, pool in enumerate(self.k_pool):
+            pending = pd.take_pending_append(pool)
+            if pending is not None and self._write_slots is not None:
+                k, v = pending
+                kv_write.append_fp16(k, v, self._slot_vec(self._write_slots, k.shape[0]), self._flat_k[layer],
+                                     self._flat_v[layer], None, None, self.block_size)
 
     def reset(self) -> None:
         """Free every sequence; storage and buffer addresses stay."""
@@ -358,6 +383,7 @@ class PagedKVCache(_PagedBase):
 
     def advance(self, n: int, batch_size: Optional[int] = None,
                 slots: Optional[Sequence[int]] = None) -> None:
+        self._flush_deferred_appends()              # rows of the last step nobody attended
         active, starts = self._grow(n, batch_size, slots)
         if n == 1:
             self._ship_decode_slots(active, starts)
@@ -379,6 +405,13 @@ class PagedKVCache(_PagedBase):
         kmin = self.kmin[layer_idx] if self._bounds_on else None
         kmax = self.kmax[layer_idx] if self._bounds_on else None
         if n == 1:
+            if self.fused_append and not self._bounds_on and b == len(self._active):
+                from latentserve_b200 import paged_decode as pd
+                from latentserve_b200 import paged_decode_cuda as pdc
+
+                if pdc.append_rows_ok(k, v, k):
+                    pd.defer_append(self.k_pool[layer_idx], k, v)
+                    return
             kv_write.append_fp16(k, v, self._slot_vec(slots, b), self._flat_k[layer_idx],
                                  self._flat_v[layer_idx], kmin, kmax, self.block_size)
             return

@@ -42,6 +42,10 @@ struct DecodeParams {
     const float* v_zero;
     const __half* k_res;
     const int* res_rows;
+    // fp16 pools: the step's new K / V rows [B, H, 128], appended by this launch (or null)
+    const __half* k_new;
+    const __half* v_new;
+    long long sn_b, sn_h, svn_b, svn_h;
     // sparse page lists
     const int* sel;
     float ratio;

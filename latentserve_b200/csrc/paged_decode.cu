@@ -306,7 +306,7 @@ struct PoolFp16 {
     // takes chunk (l & 15) of rows 2i + (l >> 4), i = 0..7, so a warp-wide copy
     // covers two whole 256-byte rows. Row r lands at r * 256 with its chunks
     // XOR-swizzled by r & 7.
-    static __device__ __forceinline__ int issue(const DecodeParams& p, int, int h,
+    static __device__ __forceinline__ int issue(const DecodeParams& p, int b, int h,
                                                 const PageItem& it, uint32_t stage, int lane,
                                                 uint64_t pol) {
         const int hi = lane >> 4, col = lane & 15;
@@ -316,7 +316,29 @@ struct PoolFp16 {
         const __half* vb = static_cast<const __half*>(p.v_pool) + it.blk * p.sk_b + h * p.sk_h + lane_off;
         const uint32_t dst0 = stage + hi * 256;
         const uint32_t c0 = (uint32_t)(col ^ hi) << 4;      // ((2i + hi) & 7) = (2i & 7) | hi
-        if (it.valid == LS_PAGE) {
+        if (p.k_new != nullptr && (it.last & 1) && it.valid > 0) {
+            // The step's append rides on this launch: the sequence's newest token (the last
+            // valid row of its last page) is not in the pool yet. Its K and V rows come from
+            // the caller's new rows, the older rows from the pool, and the new rows are stored
+            // to the pool for the steps to come. This warp is the only reader of that row in
+            // this launch (a page-head is walked by one warp, and a last page is never shared).
+            const int r_new = it.valid - 1;
+            const __half* kn = p.k_new + b * p.sn_b + h * p.sn_h + col * 8;
+            const __half* vn = p.v_new + b * p.svn_b + h * p.svn_h + col * 8;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const uint32_t dst = dst0 + i * 512 + (c0 ^ (((2 * i) & 7) << 4));
+                const int row = 2 * i + hi;
+                const int nbytes = row <= r_new ? 16 : 0;
+                const bool fresh = row == r_new;
+                cp_async_16(dst, fresh ? kn : (nbytes ? kb + i * row2 : static_cast<const __half*>(p.k_pool)), nbytes);
+                cp_async_16(dst + 4096, fresh ? vn : (nbytes ? vb + i * row2 : static_cast<const __half*>(p.v_pool)),
+                            nbytes);
+            }
+            const uint4 row_bits = *reinterpret_cast<const uint4*>(hi ? vn : kn);
+            __half* pool = static_cast<__half*>(const_cast<void*>(hi ? p.v_pool : p.k_pool));
+            *reinterpret_cast<uint4*>(pool + it.blk * p.sk_b + r_new * p.sk_p + h * p.sk_h + col * 8) = row_bits;
+        } else if (it.valid == LS_PAGE) {
 #pragma unroll
             for (int i = 0; i < 8; ++i) {
                 const uint32_t dst = dst0 + i * 512 + (c0 ^ (((2 * i) & 7) << 4));
@@ -1450,17 +1472,20 @@ extern "C" {
 
 int ls_decode_slots(int batch, int num_chunks) { return batch + num_chunks; }
 
-int ls_paged_decode_fp16(const void* q, const void* k_pool, const void* v_pool,
-                         const int32_t* block_tables, const int32_t* seq_lens, float* part_acc,
-                         float* part_m, float* part_l, int32_t* seg_range, void* out, int batch,
-                         int kv_heads, int n_rep, int head_dim, int page, int max_pages,
-                         int num_blocks, int num_chunks, int min_chunk, int flags, int64_t sq_b,
-                         int64_t sq_h, int64_t sq_m, int64_t sk_b, int64_t sk_p, int64_t sk_h,
-                         int64_t so_b, int64_t so_h, int64_t so_m, float softmax_scale,
-                         void* stream) {
+static int decode_fp16_impl(const void* q, const void* k_new, const void* v_new, int64_t sn_b, int64_t sn_h,
+                            int64_t svn_b, int64_t svn_h, const void* k_pool, const void* v_pool,
+                            const int32_t* block_tables, const int32_t* seq_lens, float* part_acc,
+                            float* part_m, float* part_l, int32_t* seg_range, void* out, int batch,
+                            int kv_heads, int n_rep, int head_dim, int page, int max_pages, int num_blocks,
+                            int num_chunks, int min_chunk, int flags, int64_t sq_b, int64_t sq_h, int64_t sq_m,
+                            int64_t sk_b, int64_t sk_p, int64_t sk_h, int64_t so_b, int64_t so_h, int64_t so_m,
+                            float softmax_scale, void* stream) {
     if (head_dim != LS_HEAD_DIM || page != LS_PAGE) return LS_ERR_UNSUPPORTED;
     DecodeParams p = {};
     p.q = static_cast<const __half*>(q);
+    p.k_new = static_cast<const __half*>(k_new);
+    p.v_new = static_cast<const __half*>(v_new);
+    p.sn_b = sn_b; p.sn_h = sn_h; p.svn_b = svn_b; p.svn_h = svn_h;
     p.k_pool = k_pool;
     p.v_pool = v_pool;
     p.block_tables = block_tables;
@@ -1485,6 +1510,10 @@ int ls_paged_decode_fp16(const void* q, const void* k_pool, const void* v_pool,
     if (rc) return rc;
     rc = check_pool_fp16(p);
     if (rc) return rc;
+    if (k_new != nullptr &&
+        ((reinterpret_cast<uintptr_t>(k_new) & 15) || (reinterpret_cast<uintptr_t>(v_new) & 15) || (sn_b % 8) ||
+         (sn_h % 8) || (svn_b % 8) || (svn_h % 8)))
+        return LS_ERR_MISALIGNED;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     const bool pdl = (flags & LS_LAUNCH_PROGRAMMATIC) != 0;
     const int impl = flags & 0xff;
@@ -1492,7 +1521,8 @@ int ls_paged_decode_fp16(const void* q, const void* k_pool, const void* v_pool,
         return LS_ERR_UNSUPPORTED;
     p.early = (flags & LS_EARLY_PAGES) != 0;
     ls::TmaMaps maps;
-    if (impl == LS_IMPL_MMA && (flags & LS_LOAD_TMA) && build_fp16_maps(p, &maps))
+    // The append rides on the per-lane copies only: a TMA tile always comes whole out of the pool.
+    if (impl == LS_IMPL_MMA && (flags & LS_LOAD_TMA) && k_new == nullptr && build_fp16_maps(p, &maps))
         return ls::launch_decode<ls::MmaFp16Tma, LS_MODE_DENSE, ls::kStages>(p, s, pdl, &maps);
     if (impl == LS_IMPL_SIMT) {
         if (n_rep <= 6)
@@ -1505,6 +1535,35 @@ int ls_paged_decode_fp16(const void* q, const void* k_pool, const void* v_pool,
         return LS_ERR_UNSUPPORTED;
     }
     return rc;
+}
+
+int ls_paged_decode_fp16(const void* q, const void* k_pool, const void* v_pool,
+                         const int32_t* block_tables, const int32_t* seq_lens, float* part_acc,
+                         float* part_m, float* part_l, int32_t* seg_range, void* out, int batch,
+                         int kv_heads, int n_rep, int head_dim, int page, int max_pages,
+                         int num_blocks, int num_chunks, int min_chunk, int flags, int64_t sq_b,
+                         int64_t sq_h, int64_t sq_m, int64_t sk_b, int64_t sk_p, int64_t sk_h,
+                         int64_t so_b, int64_t so_h, int64_t so_m, float softmax_scale,
+                         void* stream) {
+    return decode_fp16_impl(q, nullptr, nullptr, 0, 0, 0, 0, k_pool, v_pool, block_tables, seq_lens, part_acc,
+                            part_m, part_l, seg_range, out, batch, kv_heads, n_rep, head_dim, page, max_pages,
+                            num_blocks, num_chunks, min_chunk, flags, sq_b, sq_h, sq_m, sk_b, sk_p, sk_h, so_b,
+                            so_h, so_m, softmax_scale, stream);
+}
+
+int ls_paged_decode_append_fp16(const void* q, const void* k_new, const void* v_new, void* k_pool,
+                                void* v_pool, const int32_t* block_tables, const int32_t* seq_lens,
+                                float* part_acc, float* part_m, float* part_l, int32_t* seg_range, void* out,
+                                int batch, int kv_heads, int n_rep, int head_dim, int page, int max_pages,
+                                int num_blocks, int num_chunks, int min_chunk, int flags, int64_t sq_b,
+                                int64_t sq_h, int64_t sq_m, int64_t sn_b, int64_t sn_h, int64_t svn_b,
+                                int64_t svn_h, int64_t sk_b, int64_t sk_p, int64_t sk_h, int64_t so_b,
+                                int64_t so_h, int64_t so_m, float softmax_scale, void* stream) {
+    if (!k_new || !v_new) return LS_ERR_NULL_POINTER;
+    return decode_fp16_impl(q, k_new, v_new, sn_b, sn_h, svn_b, svn_h, k_pool, v_pool, block_tables, seq_lens,
+                            part_acc, part_m, part_l, seg_range, out, batch, kv_heads, n_rep, head_dim, page,
+                            max_pages, num_blocks, num_chunks, min_chunk, flags, sq_b, sq_h, sq_m, sk_b, sk_p,
+                            sk_h, so_b, so_h, so_m, softmax_scale, stream);
 }
 
 int ls_paged_sparse_fp16(const void* q, const void* k_pool, const void* v_pool,

@@ -62,6 +62,13 @@ def paged_decode_attention(
     """
     if force_reference:
         raise RuntimeError("latentserve_b200 carries no reference implementation to force")
+    # A cache in fused-append mode has left this layer's new K / V rows here instead of
+    # launching its append: they ride on the attention launch.
+    k_new = v_new = None
+    if _PENDING_APPENDS:
+        pending = _PENDING_APPENDS.pop(k_pool.data_ptr(), None)
+        if pending is not None:
+            k_new, v_new = pending
     # A decode loop makes the same call every step (persistent pools, tables,
     # lengths, projection buffers), so a validated call is remembered by the
     # addresses and layouts of its tensors and repeated as one library call.
@@ -72,7 +79,7 @@ def paged_decode_attention(
            seq_lens.data_ptr(), seq_lens.shape, seq_lens.dtype, softmax_scale, pdc.dense_launch_flags(),
            pdc.loader_flags(),
            _ident(k_scale), _ident(v_scale), _ident(k_zero), _ident(v_zero), _ident(k_residual),
-           _ident(res_rows), _ident(out))
+           _ident(res_rows), _ident(out), _ident(k_new), _ident(v_new))
     plan = _PLANS.get(key)
     if plan is None:
         if not q.is_cuda:
@@ -84,7 +91,7 @@ def paged_decode_attention(
                 "rows per KV head, page 16, fp16 or INT8 pools with 16-byte aligned rows")
         plan = pdc.plan_decode(q, k_pool, v_pool, block_tables, seq_lens, softmax_scale=softmax_scale,
                                k_scale=k_scale, v_scale=v_scale, k_zero=k_zero, v_zero=v_zero,
-                               k_residual=k_residual, res_rows=res_rows, out=out)
+                               k_residual=k_residual, res_rows=res_rows, out=out, k_new=k_new, v_new=v_new)
         if len(_PLANS) >= _PLAN_LIMIT:
             _PLANS.clear()
         _PLANS[key] = plan
@@ -95,6 +102,18 @@ def paged_decode_attention(
 
 _PLANS: dict = {}
 _PLAN_LIMIT = 4096
+# k_pool address -> (k_new, v_new) of a cache.write() whose append was left to the next
+# attention call on that pool (PagedKVCache.enable_fused_append).
+_PENDING_APPENDS: dict = {}
+
+
+def defer_append(k_pool: torch.Tensor, k_new: torch.Tensor, v_new: torch.Tensor) -> None:
+    _PENDING_APPENDS[k_pool.data_ptr()] = (k_new, v_new)
+
+
+def take_pending_append(k_pool: torch.Tensor):
+    """The rows left for `k_pool` by `defer_append`, if no attention call took them."""
+    return _PENDING_APPENDS.pop(k_pool.data_ptr(), None)
 
 
 def _ident(t: Optional[torch.Tensor]):

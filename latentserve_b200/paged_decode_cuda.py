@@ -202,9 +202,21 @@ def paged_decode_cuda(q, k_pool, v_pool, block_tables, seq_lens, max_seq_len: in
     return out if merge else None
 
 
+def append_rows_ok(k_new: torch.Tensor, v_new: torch.Tensor, q: torch.Tensor) -> bool:
+    """Whether the step's new K / V rows ([B, H, 1, 128] or [B, H, 128], fp16) can ride
+    on the attention launch: unit-stride channels, 16-byte aligned rows."""
+    def ok(t):
+        return (t.is_cuda and t.dtype == torch.float16 and t.dim() in (3, 4) and t.shape[0] == q.shape[0]
+                and t.shape[1] == q.shape[1] and t.shape[-1] == 128 and (t.dim() == 3 or t.shape[2] == 1)
+                and t.stride(-1) == 1 and t.data_ptr() % 16 == 0 and t.stride(0) % 8 == 0
+                and t.stride(1) % 8 == 0)
+    return ok(k_new) and ok(v_new)
+
+
 def plan_decode(q, k_pool, v_pool, block_tables, seq_lens, num_splits=None, softmax_scale=None,
                 k_scale=None, v_scale=None, k_zero=None, v_zero=None, k_residual=None, res_rows=None,
-                impl: int = IMPL_MMA, merge: bool = True, out: Optional[torch.Tensor] = None):
+                impl: int = IMPL_MMA, merge: bool = True, out: Optional[torch.Tensor] = None,
+                k_new: Optional[torch.Tensor] = None, v_new: Optional[torch.Tensor] = None):
     """Validate one decode call and bind its arguments: returns (entry point,
     argument tuple without the stream, output tensor, device index). The tuple
     holds raw addresses, so it is valid for as long as the tensors it was built
@@ -251,6 +263,22 @@ def plan_decode(q, k_pool, v_pool, block_tables, seq_lens, num_splits=None, soft
             k_scale.stride(0), k_scale.stride(1),
             v_scale.stride(0), v_scale.stride(1), v_scale.stride(2),
             *res_st, out.stride(0), out.stride(1), out.stride(2), scale)
+    elif k_new is not None:
+        # The step's append rides on the launch (fp16 pools, dense): see the header.
+        if k_scale is not None or k_residual is not None:
+            raise ValueError("fp16 pools take no scales or residual")
+        if v_new is None or not append_rows_ok(k_new, v_new, q):
+            raise ValueError("the new K / V rows must be fp16 [B, H, (1,) 128] with 16-byte aligned rows")
+        fn = lib.ls_paged_decode_append_fp16
+        args = (
+            ptr(q), ptr(k_new), ptr(v_new), ptr(k_pool), ptr(v_pool), ptr(block_tables), ptr(seq_lens),
+            ptr(acc), ptr(m), ptr(l), ptr(seg), out_ptr,
+            b, h_kv, n_rep, d, k_pool.shape[1], block_tables.stride(0), k_pool.shape[0],
+            chunks, MIN_CHUNK_PAGES, impl | dense_launch_flags() | (loader_flags() & ~LOAD_TMA),
+            q.stride(0), q.stride(1), q.stride(2),
+            k_new.stride(0), k_new.stride(1), v_new.stride(0), v_new.stride(1),
+            k_pool.stride(0), k_pool.stride(1), k_pool.stride(2),
+            out.stride(0), out.stride(1), out.stride(2), scale)
     else:
         if k_scale is not None or k_residual is not None:
             raise ValueError("fp16 pools take no scales or residual")

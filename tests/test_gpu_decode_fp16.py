@@ -283,3 +283,90 @@ def test_layout_violations_raise_value_error():
     assert not pdc.eligible(q9, t["k_pool"])
     with pytest.raises(ValueError):
         pd.paged_decode_attention(q9, t["k_pool"], t["v_pool"], t["block_tables"], t["seq_lens"])
+
+
+def _decode_loop(fused: bool, programmatic: bool, graphed: bool, steps: int = 20):
+    """Prefill three sequences, then `steps` decode steps of two layers through
+    PagedKVCache.write + paged_decode_attention; returns every step's outputs and the cache."""
+    from latentserve_b200 import cache as lc
+
+    dev = device()
+    layers, batch = 2, 3
+    spec = lc.KVCacheSpec(num_layers=layers, num_kv_heads=2, head_dim=128, max_seq_len=1024,
+                          max_batch_size=batch, device="cuda")
+    cache = lc.PagedKVCache(spec, num_blocks=3 * 64 + 4)
+    if fused:
+        cache.enable_fused_append()
+    g = torch.Generator(device=dev).manual_seed(91)
+    for i, n in enumerate([700, 47, 15]):        # 47 -> the first step fills a page, the second opens one
+        cache.advance(n, slots=[i])
+        for layer in range(layers):
+            k = torch.randn(1, 2, n, 128, dtype=torch.float16, device=dev, generator=g)
+            v = torch.randn(1, 2, n, 128, dtype=torch.float16, device=dev, generator=g)
+            cache.write(layer, k, v)
+    feed = torch.randn(steps, 3, layers, batch, 2, 6, 128, dtype=torch.float16, device=dev, generator=g)
+    k_in = feed[0, 0, :, :, :, :1].clone()       # [layers, B, H, 1, D]
+    v_in, q_in = feed[0, 1, :, :, :, :1].clone(), feed[0, 2].clone()
+    out = torch.zeros(layers, batch, 2, 6, 128, dtype=torch.float16, device=dev)
+
+    def body():
+        for layer in range(layers):
+            cache.write(layer, k_in[layer], v_in[layer])
+            pd.paged_decode_attention(q_in[layer], cache.k_pool[layer], cache.v_pool[layer],
+                                      cache.block_tables_tensor(batch), cache.seq_lens_tensor(batch),
+                                      max_seq_len=1024, out=out[layer])
+
+    pdc.set_programmatic_launch(programmatic, early_pages=True)
+    pd.set_decode_backend("cuda")
+    outs, graph = [], None
+    try:
+        for s in range(steps):
+            cache.advance(1, batch_size=batch)
+            k_in.copy_(feed[s, 0, :, :, :, :1]); v_in.copy_(feed[s, 1, :, :, :, :1]); q_in.copy_(feed[s, 2])
+            if graphed and graph is None:
+                side = torch.cuda.Stream()
+                side.wait_stream(torch.cuda.current_stream())
+                with torch.cuda.stream(side):
+                    body()
+                torch.cuda.current_stream().wait_stream(side)
+                torch.cuda.synchronize()
+                graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graph):
+                    body()
+            if graph is not None:
+                graph.replay()
+            else:
+                body()
+            outs.append(out.clone())
+        torch.cuda.synchronize()
+    finally:
+        pdc.set_programmatic_launch(False)
+    return outs, cache
+
+
+def test_append_riding_on_the_attention_launch_changes_nothing():
+    """PagedKVCache in fused-append mode: `write()` launches nothing, the attention kernel
+    takes each sequence's newest row from the caller's rows and stores it to the pools.
+    Outputs of every step and the pools afterwards equal the two-launch route bit for
+    bit — eager, replayed from a graph, and with programmatic launch and early page
+    requests; a write nobody attended is appended by the next advance()."""
+    base, c0 = _decode_loop(fused=False, programmatic=False, graphed=False)
+    for programmatic, graphed in [(False, False), (True, False), (True, True)]:
+        got, c1 = _decode_loop(True, programmatic, graphed)
+        for s, (a, b) in enumerate(zip(base, got)):
+            assert torch.equal(a, b), f"step {s} differs (programmatic={programmatic}, graphed={graphed})"
+        for layer in range(2):
+            assert torch.equal(c0.k_pool[layer], c1.k_pool[layer])
+            assert torch.equal(c0.v_pool[layer], c1.v_pool[layer])
+    # Rows written but never attended reach the pool at the next advance().
+    dev = device()
+    g = torch.Generator(device=dev).manual_seed(5)
+    k = torch.randn(3, 2, 1, 128, dtype=torch.float16, device=dev, generator=g)
+    c1.advance(1, batch_size=3)
+    c1.write(0, k, k)
+    slots = [c1.tables[i].slot(c1.tables[i].length - 1) for i in range(3)]
+    c1.advance(1, batch_size=3)
+    torch.cuda.synchronize()
+    flat = c1.k_pool[0].view(-1, 2, 128)
+    for i, slot in enumerate(slots):
+        assert torch.equal(flat[slot], k[i, :, 0])
