@@ -98,10 +98,12 @@ BLOCKS = 5                                  # timed blocks of K steps per worklo
 SUSTAIN_S = 1.0                             # the same load, untimed, between block 1 and the others
 METRIC = "paged decode-attn HBM GB/s"
 FALLBACK_HBM_GBS = 6650.0
-# DRAM bytes per launch of the split-KV kernel on the headline workload: Nsight Compute
-# counted 134.42 MB read + 3.66 MB written on the 134 MB capture (16 x 8 192), and the
-# traffic grows with the pages read, so the 268 MB launch moves twice that.
-NCU_TRAFFIC_BYTES = 273_000_000
+# DRAM bytes a launch of the decode kernel moves, as a multiple of its algorithmic bytes: Nsight
+# Compute counted dram__bytes_read + dram__bytes_write on the small cases (16 x 8 192 fp16:
+# 134.42 MB read + 0.36 MB written for 134.22 MB; 32 x 8 192 INT8: 153.48 + 0.3 MB for 153.09 MB;
+# the selected pages of 8 x 8 192 at 50 %: 33.72 MB for 33.55 MB), and the traffic grows with the
+# pages read, so a full-size launch moves the same multiple.
+NCU_TRAFFIC_RATIO = {"dense": 1.0042, "int8": 1.0045, "sparse": 1.0051}
 
 
 def measured_peak():
@@ -483,7 +485,7 @@ def run_attention(name, args, ranks: Ranks, headline: bool):
     achieved = roof_bytes / (kernel_us * 1e-6) / 1e9
     roofline = {"bound": "hbm", "achieved": round(achieved, 1), "peak": peak, "unit": "GB/s",
                 "frac": round(achieved / peak, 4),
-                "traffic": NCU_TRAFFIC_BYTES if name == HEADLINE else None,
+                "traffic": int(round(roof_bytes * NCU_TRAFFIC_RATIO["sparse" if kind.startswith("sparse") else kind])),
                 "peak_kind": f"of {peak_kind}", "kernel": kernel_name,
                 "kernel_us": round(kernel_us, 2), "algorithmic_bytes_per_launch": roof_bytes,
                 "frac_of_8TBs": round(achieved / 8000.0, 4),

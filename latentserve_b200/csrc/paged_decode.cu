@@ -161,8 +161,9 @@ struct PageWindow {
     __device__ __forceinline__ bool next(const DecodeParams& p, const int* cum, int h, int warp,
                                          int lane, PageItem& it, int& b) {
         if (i == n) {
-            if (n == 0) return false;
-            if (!have_next) prefetch(p, cum, h, warp, lane);
+            // The window after this one was fetched when its last pages were handed out
+            // (below): every non-empty window reaches i + 2 >= n before it reaches i == n.
+            if (n == 0 || !have_next) return false;
             c = nc; n = nn; blk = nblk; vl = nvl;
             have_next = false;
             i = 0;
@@ -1206,8 +1207,8 @@ decode_kernel(const DecodeParams p, const __grid_constant__ TmaMaps maps) {
         if (!Pool::kTma) cp_async_commit();
     };
     auto issue_first = [&]() {                               // STAGES - 1 pages ahead
-#pragma unroll
-        for (int s = 0; s < STAGES - 1; ++s) issue(s);
+#pragma unroll 1
+        for (int s = 0; s < STAGES - 1; ++s) issue(s);       // one copy of the code, not STAGES - 1
     };
     if (early && has_work) issue_first();
     dep_wait();
