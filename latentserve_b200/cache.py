@@ -155,7 +155,11 @@ class _PagedBase:
         self._decode_slots: list = []
         self._capacity_pages = max(1, per_seq)
         dev = self.device
-        self._block_tables_buf = torch.zeros((mb, self._capacity_pages), dtype=torch.int32, device=dev)
+        # The tables, flat, with one spare element behind them: the slot a step's table
+        # patches of sequences that gained no block are aimed at (see _grow).
+        self._block_tables_flat = torch.zeros(mb * self._capacity_pages + 16, dtype=torch.int32, device=dev)
+        self._block_tables_buf = self._block_tables_flat[: mb * self._capacity_pages].view(mb, self._capacity_pages)
+        self._patches: list = []                    # (row, page, block) gained by this advance()
         # Everything a decode step ships besides changed block-table rows lives in ONE
         # device buffer -- lengths and residual rows (int32), write slots, residual slots
         # and the pages to finalise (int64) -- of which the kernels' inputs are typed views, filled by one
@@ -165,7 +169,8 @@ class _PagedBase:
         # rewriting an image whose copy has not run yet.
         off_i64 = -(-(8 * mb) // 16) * 16
         off_state = off_i64 + 32 * mb               # int32 [4]: pages to finalise, arrivals, padding
-        self._step_bytes = off_state + 16
+        off_patch = off_state + 16                  # int64 [mb] flat table indices, then int32 [mb] block ids
+        self._step_bytes = off_patch + 12 * mb
         self._step_dev = torch.zeros(self._step_bytes, dtype=torch.uint8, device=dev)
 
         def views(buf):
@@ -174,10 +179,12 @@ class _PagedBase:
                     buf[off_i64 + 8 * mb: off_i64 + 16 * mb].view(torch.int64),
                     buf[off_i64 + 16 * mb: off_i64 + 24 * mb].view(torch.int64),
                     buf[off_i64 + 24 * mb: off_i64 + 32 * mb].view(torch.int64),
-                    buf[off_state: off_state + 16].view(torch.int32))
+                    buf[off_state: off_state + 16].view(torch.int32),
+                    buf[off_patch: off_patch + 8 * mb].view(torch.int64),
+                    buf[off_patch + 8 * mb: off_patch + 12 * mb].view(torch.int32))
 
         (self._seq_lens_buf, self._res_rows_buf, slots_dev, self._k_res_idx_buf, self._fin_rows_buf,
-         self._fin_ids_buf, self._fin_state_buf) = views(self._step_dev)
+         self._fin_ids_buf, self._fin_state_buf, self._patch_idx_buf, self._patch_val_buf) = views(self._step_dev)
         self._write_slots_buf = slots_dev.view(mb, 1)
         self._step_host = [torch.zeros(self._step_bytes, dtype=torch.uint8).pin_memory() for _ in range(2)]
         self._step_np = [tuple(v.numpy() for v in views(h)) for h in self._step_host]
@@ -254,13 +261,29 @@ class _PagedBase:
             # token's flat slot.
             bs, tables, alloc = self.block_size, self.tables, self.allocator
             starts, slot_list = [], []
-            for i in active:
+            state, cap, patches = self._table_state, self._capacity_pages, self._patches
+            for row, i in enumerate(active):
                 t = tables[i]
                 length, blocks = t.length, t.blocks
                 need = -(-(length + 1) // bs) - len(blocks)
                 if need > 0:
-                    blocks.extend(alloc.allocate(need))
+                    # A sequence whose row on the device is current gains its block as a
+                    # patch of that row (one entry of the step's staging copy) instead of
+                    # a copy of the whole row.
+                    current = need == 1 and state[row] == (i, t.version) and len(blocks) < cap
+                    try:
+                        got = alloc.allocate(need)
+                    except OutOfBlocks:
+                        # Rows patched so far go back to a whole-row copy next time.
+                        for prow, _, _ in patches:
+                            state[prow] = None
+                        patches.clear()
+                        raise
+                    blocks.extend(got)
                     t.version += 1
+                    if current:
+                        patches.append((row, len(blocks) - 1, blocks[-1]))
+                        state[row] = (i, t.version)
                 slot_list.append(blocks[length // bs] * bs + length % bs)
                 t.length = length + 1
                 starts.append(length)
@@ -278,6 +301,9 @@ class _PagedBase:
             state = (i, t.version)
             if self._table_state[row] != state:
                 if len(t.blocks) > self._capacity_pages:
+                    for prow, _, _ in self._patches:     # unshipped: whole-row copies next time
+                        self._table_state[prow] = None
+                    self._patches.clear()
                     raise RuntimeError(f"sequence in slot {i} needs {len(t.blocks)} pages, past the "
                                        f"cache's capacity of {self._capacity_pages}")
                 if t.blocks:
@@ -287,14 +313,27 @@ class _PagedBase:
                     self._block_tables_buf[row, : len(t.blocks)].copy_(src)
                 self._table_state[row] = state
         b = len(active)
-        self._stage()[0][:b] = [self.tables[i].length for i in active]
+        stage = self._stage()
+        stage[0][:b] = [self.tables[i].length for i in active]
+        patches = self._patches
+        if patches:
+            # Rows without a patch aim at the spare element behind the tables.
+            cap = self._capacity_pages
+            stage[7][:b] = len(self.tables) * cap
+            for row, page, blk in patches:
+                stage[7][row] = row * cap + page
+                stage[8][row] = blk
         self._flush_stage()
+        if patches:
+            # Behind the staging copy on the stream, ahead of the step's kernels.
+            self._block_tables_flat.index_copy_(0, self._patch_idx_buf[:b], self._patch_val_buf[:b])
+            patches.clear()
         self._block_tables = self._block_tables_buf[:b]
         self._seq_lens_tensor = self._seq_lens_buf[:b]
 
     def _stage(self):
         """Host image being filled for this advance(): numpy views (lens, res_rows,
-        slots, res_idx, fin_rows, fin_ids, fin_state). Opened on first use; starts as a copy of the last one shipped,
+        slots, res_idx, fin_rows, fin_ids, fin_state, patch_idx, patch_val). Opened on first use; starts as a copy of the last one shipped,
         so fields an advance() does not touch keep their values."""
         if self._step_open is None:
             i = self._step_next
@@ -375,6 +414,7 @@ class PagedKVCache(_PagedBase):
             if t.blocks:
                 t.free()
         self._table_state = [None] * len(self.tables)
+        self._patches.clear()
         self._active = list(range(len(self.tables)))
         self._active_range = None
 
@@ -551,6 +591,7 @@ class Int8PagedKVCache(_PagedBase):
             if t.blocks:
                 t.free()
         self._table_state = [None] * len(self.tables)
+        self._patches.clear()
         self._active = list(range(len(self.tables)))
         self._active_range = None
         self._fin = [0] * len(self.tables)

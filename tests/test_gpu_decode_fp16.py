@@ -370,3 +370,51 @@ def test_append_riding_on_the_attention_launch_changes_nothing():
     flat = c1.k_pool[0].view(-1, 2, 128)
     for i, slot in enumerate(slots):
         assert torch.equal(flat[slot], k[i, :, 0])
+
+
+def test_block_tables_on_the_device_follow_the_host_through_patches_and_row_copies():
+    """A decode step that opens a page ships the new block id as a patch inside the
+    step's one staging copy; a freed and re-admitted slot, a changed active set and a
+    prefill go by whole rows. After every advance() the device rows equal the host's."""
+    from latentserve_b200 import cache as lc
+
+    spec = lc.KVCacheSpec(num_layers=1, num_kv_heads=2, head_dim=128, max_seq_len=256,
+                          max_batch_size=4, device="cuda")
+    cache = lc.PagedKVCache(spec, num_blocks=40)
+
+    def check():
+        tables = cache.block_tables_tensor().cpu()
+        lens = cache.seq_lens_tensor().cpu().tolist()
+        for row, i in enumerate(cache.active_slots()):
+            t = cache.tables[i]
+            assert lens[row] == t.length
+            assert tables[row, :len(t.blocks)].tolist() == t.blocks
+
+    for i, n in enumerate([15, 16, 33, 1]):              # page boundaries at different steps
+        cache.advance(n, slots=[i])
+        check()
+    for step in range(40):
+        cache.advance(1, batch_size=4)
+        check()
+        if step == 17:                                   # slot 1 leaves and comes back shorter
+            cache.free_sequence(1)
+            cache.advance(5, slots=[1])
+            check()
+        if step == 25:                                   # another row order
+            cache.advance(1, slots=[3, 0, 2])
+            check()
+    # Running dry in the middle of a step: the rows patched before the failure were never
+    # shipped, so they go out as whole rows with the next advance().
+    small = lc.PagedKVCache(spec, num_blocks=6)
+    for i in range(4):
+        small.advance(15, slots=[i])
+    small.advance(1, batch_size=4)                       # fills the pages; every row now current
+    with pytest.raises(lc.OutOfBlocks):
+        small.advance(1, batch_size=4)                   # rows 0 and 1 get blocks, row 2 does not
+    assert [t.length for t in small.tables] == [17, 17, 16, 16]
+    small.free_sequence(3)
+    small.advance(1, slots=[0, 1, 2])
+    tables = small.block_tables_tensor().cpu()
+    for row, i in enumerate([0, 1, 2]):
+        assert len(small.tables[i].blocks) == 2
+        assert tables[row, :2].tolist() == small.tables[i].blocks
