@@ -18,8 +18,8 @@ shared prefix blocks are full and read-only).
 What is different is the hot part: `write()` for one token per sequence is one
 launch (`ls_kv_append_fp16` / `ls_int8_decode_write`), INT8 page finalisation
 is one launch per layer (`ls_int8_finalize_blocks`) instead of a dozen torch
-ops, and `advance()` stages the step's indices in pinned host memory and ships
-them with one copy per buffer. Prefill writes (more than one token per
+ops, and `advance()` stages the step's indices and new block ids in pinned host
+memory and ships them with one copy. Prefill writes (more than one token per
 sequence) are set-up, not the hot path; they reuse the same kernels row by row.
 """
 
@@ -160,9 +160,10 @@ class _PagedBase:
         self._block_tables_flat = torch.zeros(mb * self._capacity_pages + 16, dtype=torch.int32, device=dev)
         self._block_tables_buf = self._block_tables_flat[: mb * self._capacity_pages].view(mb, self._capacity_pages)
         self._patches: list = []                    # (row, page, block) gained by this advance()
-        # Everything a decode step ships besides changed block-table rows lives in ONE
-        # device buffer -- lengths and residual rows (int32), write slots, residual slots
-        # and the pages to finalise (int64) -- of which the kernels' inputs are typed views, filled by one
+        # Everything a decode step ships lives in ONE device buffer -- lengths and residual
+        # rows (int32), write slots, residual slots and the pages to finalise (int64), and the
+        # blocks the sequences gained this step as patches of their table rows (whole rows
+        # are copied only when a slot changes hands) -- of which the kernels' inputs are typed views, filled by one
         # asynchronous copy per advance() from one of two pinned host images (the
         # reference makes several small blocking copies per step,
         # cache/paged_cache.py:252-273,337-360). An event per image keeps the host from
