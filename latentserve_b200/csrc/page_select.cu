@@ -14,89 +14,25 @@
 // lane l sums channels 4l..4l+3 left to right starting from 0, then pairwise
 // sums over lanes at distance 16, 8, 4, 2, 1 -- so that scores, and with them
 // the selected indices, are reproducible bit for bit on a CPU. The reference
-// does that with an all-lanes butterfly per value (5 shuffles each); here 32
-// values (4 pages x 8 padded query rows) are reduced together, each step
-// keeping half of the values per lane, which forms exactly the same pairwise
-// sums with 31 shuffles for all 32.
+// does that with a warp per page and an all-lanes butterfly per value. Here a
+// LANE scores a page: the page's bounds wait in shared memory, the thirty-two
+// per-lane partial sums of the reference become thirty-two values of one
+// thread, and the butterfly becomes the same binary tree of additions walked in
+// an order that keeps three partial results alive per query row. Same
+// operands, same operations, no shuffles.
 #include "ls_common.cuh"
 
 namespace ls {
 
-constexpr int kIndexWarps = 4;
-constexpr int kGroup = 4;                    // pages reduced together
-constexpr int kItemGroups = 2;               // groups per pipelined item
-constexpr int kItemPages = kGroup * kItemGroups;
-constexpr int kMaxItems = 3;                 // items a warp stages at once (its span / 8)
+constexpr int kIndexWarps = 4;                 // warp pairs per CTA
+constexpr int kItemPages = 32;               // pages a warp scores at a time: one per lane
 constexpr int kItemBytes = kItemPages * 512; // a page's minimum and maximum rows, 256 bytes each
-static_assert(kMaxItems == 3, "page_index_kernel writes out its three waits");
+constexpr int kQFloats = 8 * 8 * 8 * 4;      // the CTA's query rows as q+ / q- pairs (see stage_query)
+constexpr int kIndexSmem = kIndexWarps * kItemBytes + kQFloats * 4 + kIndexWarps * 8 * 32 * 4;
 #ifndef LS_INDEX_CTAS
-#define LS_INDEX_CTAS 4
+#define LS_INDEX_CTAS 2
 #endif
-constexpr int kIndexCtasPerSm = LS_INDEX_CTAS;   // resident CTAs of the index kernel (registers, 48 KB each)
-
-__device__ __forceinline__ void unpack4h(uint2 raw, float (&f)[4]) {
-    const __half2* h2 = reinterpret_cast<const __half2*>(&raw);
-    const float2 a = __half22float2(h2[0]), b = __half22float2(h2[1]);
-    f[0] = a.x; f[1] = a.y; f[2] = b.x; f[3] = b.y;
-}
-
-// One halving step of the joint reduction: N values per lane in, N/2 out.
-// Lanes with bit OFF clear keep values [0, N/2), the others [N/2, N); each
-// kept value becomes own + partner's, the same two operands the all-lanes
-// butterfly adds at this distance.
-template <int N, int OFF>
-__device__ __forceinline__ void halve(const float (&in)[N], float (&out)[N / 2], int lane) {
-    const bool upper = (lane & OFF) != 0;
-#pragma unroll
-    for (int k = 0; k < N / 2; ++k) {
-        const float keep = upper ? in[k + N / 2] : in[k];
-        const float send = upper ? in[k] : in[k + N / 2];
-        out[k] = __fadd_rn(keep, __shfl_xor_sync(LS_FULL_MASK, send, OFF));
-    }
-}
-
-// Bounds of 8 (padded) query rows x 4 pages. On return lane l holds the
-// complete bound of page (l >> 3) of the group, query row (l & 7).
-// max(q * lo, q * hi) with lo <= hi (a page's channel minimum and maximum) is
-// q * hi for q > 0 and q * lo for q < 0. With q+ = max(q, 0) and q- = min(q, 0)
-// that product is fma(q+, hi, q- * lo), bit for bit: one of the two factors is
-// zero, so one term is a zero and the other is rounded exactly once. No compare,
-// no select -- and rows r, r + 1 go through the two halves of packed fp32
-// instructions, so a term costs 1.5 instructions instead of 4. The per-lane sums
-// run over channels in order, as the reference's do.
-__device__ __forceinline__ float bounds_4x8(const f32x2 (&qp)[4][4], const f32x2 (&qn)[4][4], int n_rep,
-                                            const uint2 (&lo_raw)[kGroup],
-                                            const uint2 (&hi_raw)[kGroup], int lane) {
-    float x[32];
-#pragma unroll
-    for (int pg = 0; pg < kGroup; ++pg) {
-        float lo[4], hi[4];
-        unpack4h(lo_raw[pg], lo);
-        unpack4h(hi_raw[pg], hi);
-        f32x2 lo2[4], hi2[4];
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            lo2[j] = pack2(lo[j], lo[j]);
-            hi2[j] = pack2(hi[j], hi[j]);
-        }
-#pragma unroll
-        for (int rp = 0; rp < 4; ++rp) {
-            f32x2 t = pack2(0.f, 0.f);
-            if (2 * rp < n_rep) {
-#pragma unroll
-                for (int j = 0; j < 4; ++j) t = add2(t, fma2(qp[rp][j], hi2[j], mul2(qn[rp][j], lo2[j])));
-            }
-            unpack2(t, x[pg * 8 + 2 * rp], x[pg * 8 + 2 * rp + 1]);
-        }
-    }
-    float a[16], b[8], c[4], d[2], e[1];
-    halve<32, 16>(x, a, lane);
-    halve<16, 8>(a, b, lane);
-    halve<8, 4>(b, c, lane);
-    halve<4, 2>(c, d, lane);
-    halve<2, 1>(d, e, lane);
-    return e[0];
-}
+constexpr int kIndexCtasPerSm = LS_INDEX_CTAS;   // resident CTAs of the index kernel (256 threads, 76 KB of shared memory each)
 
 // Monotone map from fp32 to uint32: a > b as floats <=> key(a) > key(b).
 // -0 is folded onto +0 first so the two compare equal, as they do as floats.
@@ -403,126 +339,217 @@ __device__ __forceinline__ void select_row(const float* __restrict__ row, int* _
     for (int i = n_keep + tid; i < k; i += THREADS) out[i] = -1;
 }
 
-// grid (ceil(max_pages / (4 * span)), H, B), block 128: a warp scores `span`
-// consecutive pages (8, 16 or 24) of one (sequence, KV head) in items of eight.
-// All of the warp's bounds are requested at once with 8-byte cp.async copies into
-// the warp's own shared memory, one commit group per item, and each item is
-// reduced as soon as its group has landed: one DRAM round trip per warp, and the
-// bounds wait in shared memory instead of 64 registers, which is what lets four
-// CTAs share an SM. Every lane reads back exactly the bytes it copied, so the
-// wait on its own groups is the only synchronisation. The host sizes `span` so
-// that the whole grid is resident at once where the problem allows it.
+// Shared-memory image of the CTA's query rows. max(q * lo, q * hi) with lo <= hi (a
+// page's channel minimum and maximum) is q * hi for q > 0 and q * lo for q < 0. With
+// q+ = max(q, 0) and q- = min(q, 0) that product is fma(q+, hi, q- * lo), bit for bit:
+// one of the two factors is zero, so one term is a zero and the other is rounded
+// exactly once. No compare, no select. The terms of channels c and c + 64 go through
+// the two halves of packed fp32 instructions: c belongs to the reference's lane c / 4
+// and c + 64 to lane c / 4 + 16, the two lanes whose partial sums are added first.
 //
-// Launched programmatically with `early` set, the block ids and the bounds are
+// Step j (0..7) of a page's evaluation covers the reference's lanes j, j + 8, j + 16 and
+// j + 24, i.e. channels 4j + {0..3} + {0, 32, 64, 96}. Its operands for query row r are
+// eight 16-byte entries (pp = 0..7): {q+[c], q+[c + 64], q-[c], q-[c + 64]} with
+// c = 4j + pp for pp < 4 and c = 4j + 32 + (pp - 4) otherwise.
+__device__ __forceinline__ int query_slot(int r, int c) {
+    const int lane_ref = c >> 2, jj = c & 3;
+    const int j = lane_ref & 7, m = lane_ref >> 3;          // reference lane = j + 8 m
+    const int pp = jj + 4 * (m & 1), e = m >> 1;
+    return (((j * 8 + r) * 8 + pp) << 2) + e;               // + 2 for q-
+}
+
+// Barrier of one warp pair (64 threads), with a constant id per pair so that the CTA
+// holds five barriers, not sixteen.
+__device__ __forceinline__ void pair_barrier(int pair) {
+    switch (pair) {
+        case 0: asm volatile("bar.sync 1, 64;\n" ::: "memory"); break;
+        case 1: asm volatile("bar.sync 2, 64;\n" ::: "memory"); break;
+        case 2: asm volatile("bar.sync 3, 64;\n" ::: "memory"); break;
+        default: asm volatile("bar.sync 4, 64;\n" ::: "memory"); break;
+    }
+}
+
+// grid (ceil(max_pages / (4 * span)), H, B), block 256 = four PAIRS of warps: a pair
+// scores `span` consecutive pages of one (sequence, KV head), thirty-two at a time. The
+// bounds of those thirty-two pages are requested at once with 8-byte cp.async copies (a
+// warp-wide copy is one 256-byte row; each warp of the pair requests sixteen of the pages)
+// into the pair's 16 KB of shared memory, chunk u of page k at position u ^ (k & 15) so
+// that the lanes, which then read one page each, hit different banks. Lane l evaluates
+// page l: 128 channels x the group's query rows, the query operands broadcast from shared
+// memory. The two warps of a pair each walk one half of the addition tree (the reference
+// lanes with bit 0 clear / set: the operands of its last butterfly step) and the first warp
+// adds the two halves, so a page's evaluation is two dependent chains of half the length.
+//
+// Launched programmatically with `early` set, the block ids and the first bounds are
 // requested BEFORE the kernel synchronises on its predecessor: the pages whose bounds
 // it reads are never a sequence's last page (page 0 and the `recent` last pages are
 // not scored at all), and only a last page's bounds change between decode steps. The
 // queries, which the predecessor usually wrote, are read after the wait.
 //
-// PER_HEAD = 0: scores [B,H,P]; PER_HEAD = 1: heads [B,H,R,P].
-template <int PER_HEAD>
-__global__ void __launch_bounds__(kIndexWarps * 32, kIndexCtasPerSm)
+// PER_HEAD = 0: scores [B,H,P]; PER_HEAD = 1: heads [B,H,R,P]. NREP: the group size when
+// it is known at compile time (6), else 0 and the rows are tested against n_rep.
+template <int PER_HEAD, int NREP>
+__global__ void __launch_bounds__(kIndexWarps * 64, kIndexCtasPerSm)
 page_index_kernel(const __half* __restrict__ q, const __half* __restrict__ kmin,
                   const __half* __restrict__ kmax, const int* __restrict__ block_tables,
-                  const int* __restrict__ seq_lens, float* __restrict__ out, int n_rep,
+                  const int* __restrict__ seq_lens, float* __restrict__ out, int n_rep_arg,
                   int max_pages, int span, int table_stride, int num_blocks, int recent, int early,
                   long long sq_b, long long sq_h, long long sq_m, long long sb_b, long long sb_h,
                   long long ss_b, long long ss_h, long long ss_r) {
-    __shared__ __align__(16) unsigned char staged[kIndexWarps][kMaxItems][kItemBytes];
+    constexpr int ROWS = NREP ? NREP : 8;
+    const int n_rep = NREP ? NREP : n_rep_arg;
+    extern __shared__ __align__(16) unsigned char index_smem[];
+    float* qs = reinterpret_cast<float*>(index_smem + kIndexWarps * kItemBytes);
+    float* xch = qs + kQFloats;                              // [pair][row][lane]: the second warp's half sums
     const int b = blockIdx.z, h = blockIdx.y;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int first = (blockIdx.x * kIndexWarps + warp) * span;
+    const int pair = warp >> 1, side = warp & 1;
+    const int first = (blockIdx.x * kIndexWarps + pair) * span;
     const int end = min(first + span, max_pages);
     const int items = first < max_pages ? (end - first + kItemPages - 1) / kItemPages : 0;
     if (!early) asm volatile("griddepcontrol.wait;\n" ::: "memory");
     const int L = max(seq_lens[b], 0);
     const int np = min((L + LS_PAGE - 1) / LS_PAGE, table_stride);
+    const uint32_t mine = smem_u32(index_smem + pair * kItemBytes);
+    const long long lane_off = h * sb_h + lane * 4;
 
-    // Lane j fetches the block id of page first + j (-1: nothing to score).
-    int ids = -1;
-    {
-        const int p = first + lane;
+    // Requests this warp's sixteen pages of item `it`; returns the lane's block id for page
+    // `lane` of the item (-1: nothing to score).
+    auto request = [&](int it) -> int {
+        int id = -1;
+        const int p = first + it * kItemPages + lane;
         bool need = p < end && p < np;
         if (!PER_HEAD) need = need && !(p == 0 || p >= np - recent);
         if (need) {
-            const int id = block_tables[(long long)b * table_stride + p];
-            if (id >= 0 && id < num_blocks) ids = id;
+            const int got = block_tables[(long long)b * table_stride + p];
+            if (got >= 0 && got < num_blocks) id = got;
         }
-    }
-    const uint32_t mine = smem_u32(&staged[warp][0][0]) + lane * 8;
-#pragma unroll
-    for (int it = 0; it < kMaxItems; ++it) {
-        if (it < items) {
-#pragma unroll
-            for (int k = 0; k < kItemPages; ++k) {
-                const int blk = __shfl_sync(LS_FULL_MASK, ids, it * kItemPages + k);
-                const long long off = blk >= 0 ? blk * sb_b + h * sb_h + lane * 4 : 0;
-                const uint32_t dst = mine + it * kItemBytes + k * 512;
-                cp_async_8(dst, kmin + off, blk >= 0 ? 8 : 0);          // an unscored page reads as zeros
-                cp_async_8(dst + 256, kmax + off, blk >= 0 ? 8 : 0);
-            }
+#pragma unroll 4
+        for (int kk = 0; kk < kItemPages / 2; ++kk) {
+            const int k = side * (kItemPages / 2) + kk;
+            const int blk = __shfl_sync(LS_FULL_MASK, id, k);
+            const long long off = blk >= 0 ? blk * sb_b + lane_off : 0;
+            const uint32_t dst = mine + k * 512 + ((lane ^ (k & 15)) << 3);
+            cp_async_8(dst, kmin + off, blk >= 0 ? 8 : 0);              // an unscored page reads as zeros
+            cp_async_8(dst + 256, kmax + off, blk >= 0 ? 8 : 0);
         }
         cp_async_commit();
-    }
+        return id;
+    };
+    int id = items > 0 ? request(0) : -1;
     if (early) asm volatile("griddepcontrol.wait;\n" ::: "memory");
 
-    // q+ and q- of rows (2 rp, 2 rp + 1), channel j, packed; rows past n_rep are zero.
-    f32x2 qp[4][4], qn[4][4];
+    // The CTA's query rows, once: threads 0..127 take channel c of rows 0..3, the others of rows 4..7.
+    {
+        const int c = threadIdx.x & 127, r0 = (threadIdx.x >> 7) * 4;
 #pragma unroll
-    for (int rp = 0; rp < 4; ++rp) {
-        float q0[4] = {0.f, 0.f, 0.f, 0.f}, q1[4] = {0.f, 0.f, 0.f, 0.f};
-        if (2 * rp < n_rep)
-            unpack4h(*reinterpret_cast<const uint2*>(q + b * sq_b + h * sq_h + (2 * rp) * sq_m + lane * 4), q0);
-        if (2 * rp + 1 < n_rep)
-            unpack4h(*reinterpret_cast<const uint2*>(q + b * sq_b + h * sq_h + (2 * rp + 1) * sq_m + lane * 4),
-                     q1);
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            qp[rp][j] = pack2(fmaxf(q0[j], 0.f), fmaxf(q1[j], 0.f));
-            qn[rp][j] = pack2(fminf(q0[j], 0.f), fminf(q1[j], 0.f));
+        for (int rr = 0; rr < 4; ++rr) {
+            const int r = r0 + rr;
+            float v = 0.f;
+            if (r < n_rep) v = __half2float(q[b * sq_b + h * sq_h + r * sq_m + c]);
+            const int slot = query_slot(r, c);
+            qs[slot] = fmaxf(v, 0.f);
+            qs[slot + 2] = fminf(v, 0.f);
         }
     }
+    __syncthreads();
 
-    // Reduces group g of item `it` and writes its scores.
-    auto reduce = [&](int it, int g) {
-        uint2 lo_raw[kGroup], hi_raw[kGroup];
-        const unsigned char* src = &staged[warp][it][g * kGroup * 512 + lane * 8];
-#pragma unroll
-        for (int k = 0; k < kGroup; ++k) {
-            lo_raw[k] = *reinterpret_cast<const uint2*>(src + k * 512);
-            hi_raw[k] = *reinterpret_cast<const uint2*>(src + k * 512 + 256);
-        }
-        float s = bounds_4x8(qp, qn, n_rep, lo_raw, hi_raw, lane);
-        const int slot = it * kItemPages + g * kGroup + (lane >> 3);
-        const int p = first + slot, r = lane & 7;
-        const int blk = __shfl_sync(LS_FULL_MASK, ids, slot);
-        if (PER_HEAD) {
-            // Pages past the end get a finite 0: their token count of zero
-            // removes them downstream, and a stale NaN here would not.
-            if (p < end && r < n_rep) out[b * ss_b + h * ss_h + r * ss_r + p] = blk >= 0 ? s : 0.f;
-        } else {
-            if (r >= n_rep || blk < 0) s = neg_inf();
-#pragma unroll
-            for (int off = 1; off < 8; off <<= 1) s = fmaxf(s, __shfl_xor_sync(LS_FULL_MASK, s, off));
-            if (p >= np) s = neg_inf();                                  // past the end: never chosen
-            else if (p == 0 || p >= np - recent) s = pos_inf();          // sink and recent: always kept
-            if (r == 0 && p < end) out[b * ss_b + h * ss_h + p] = s;
-        }
-    };
-    if (items > 0) {
-        cp_async_wait<kMaxItems - 1>();
-#pragma unroll
-        for (int g = 0; g < kItemGroups; ++g) reduce(0, g);
-    }
-    if (items > 1) {
-        cp_async_wait<kMaxItems - 2>();
-#pragma unroll
-        for (int g = 0; g < kItemGroups; ++g) reduce(1, g);
-    }
-    if (items > 2) {
+    const uint32_t page_base = mine + lane * 512;
+    const int sw = lane & 15;
+    for (int it = 0; it < items; ++it) {
         cp_async_wait<0>();
+        pair_barrier(pair);                         // both warps' copies have landed
+        float s4[ROWS];                             // this warp's half of every row's sum
+        float hold3[ROWS];
+#pragma unroll 1
+        for (int half = 0; half < 2; ++half) {
+            // Reference lanes ja and ja + 4 (and + 8, + 16, + 24 of each); this warp's ja: side, side + 2.
+            const int ja = side + 2 * half;
+            float s2a[ROWS];
 #pragma unroll
-        for (int g = 0; g < kItemGroups; ++g) reduce(2, g);
+            for (int sd = 0; sd < 2; ++sd) {
+                const int j = ja + 4 * sd;
+                // Channels 4j + {0..3} + {0, 32, 64, 96}: 8-byte chunks j, j + 8, j + 16, j + 24.
+                f32x2 lo2[8], hi2[8];
+                {
+                    float2 lo[4][2], hi[4][2];
+#pragma unroll
+                    for (int m = 0; m < 4; ++m) {
+                        const uint32_t a = page_base + (((j + 8 * m) ^ sw) << 3);
+                        uint32_t l0, l1, h0, h1;
+                        asm volatile("ld.shared.v2.b32 {%0, %1}, [%2];\n" : "=r"(l0), "=r"(l1) : "r"(a));
+                        asm volatile("ld.shared.v2.b32 {%0, %1}, [%2];\n" : "=r"(h0), "=r"(h1) : "r"(a + 256));
+                        lo[m][0] = __half22float2(*reinterpret_cast<const __half2*>(&l0));
+                        lo[m][1] = __half22float2(*reinterpret_cast<const __half2*>(&l1));
+                        hi[m][0] = __half22float2(*reinterpret_cast<const __half2*>(&h0));
+                        hi[m][1] = __half22float2(*reinterpret_cast<const __half2*>(&h1));
+                    }
+                    // pp < 4: (chunk j, chunk j + 16); pp >= 4: (chunk j + 8, chunk j + 24)
+                    lo2[0] = pack2(lo[0][0].x, lo[2][0].x); hi2[0] = pack2(hi[0][0].x, hi[2][0].x);
+                    lo2[1] = pack2(lo[0][0].y, lo[2][0].y); hi2[1] = pack2(hi[0][0].y, hi[2][0].y);
+                    lo2[2] = pack2(lo[0][1].x, lo[2][1].x); hi2[2] = pack2(hi[0][1].x, hi[2][1].x);
+                    lo2[3] = pack2(lo[0][1].y, lo[2][1].y); hi2[3] = pack2(hi[0][1].y, hi[2][1].y);
+                    lo2[4] = pack2(lo[1][0].x, lo[3][0].x); hi2[4] = pack2(hi[1][0].x, hi[3][0].x);
+                    lo2[5] = pack2(lo[1][0].y, lo[3][0].y); hi2[5] = pack2(hi[1][0].y, hi[3][0].y);
+                    lo2[6] = pack2(lo[1][1].x, lo[3][1].x); hi2[6] = pack2(hi[1][1].x, hi[3][1].x);
+                    lo2[7] = pack2(lo[1][1].y, lo[3][1].y); hi2[7] = pack2(hi[1][1].y, hi[3][1].y);
+                }
+#pragma unroll
+                for (int r = 0; r < ROWS; ++r) {
+                    if (NREP || r < n_rep) {
+                        const float4* qrow = reinterpret_cast<const float4*>(qs + ((j * 8 + r) << 5));
+                        f32x2 acc_a = pack2(0.f, 0.f), acc_b = pack2(0.f, 0.f);
+#pragma unroll
+                        for (int pp = 0; pp < 8; ++pp) {
+                            const float4 qv = qrow[pp];                  // the same address in every lane
+                            const f32x2 t = fma2(pack2(qv.x, qv.y), hi2[pp], mul2(pack2(qv.z, qv.w), lo2[pp]));
+                            if (pp < 4) acc_a = add2(acc_a, t);
+                            else acc_b = add2(acc_b, t);
+                        }
+                        float a0, a1, b0, b1;
+                        unpack2(acc_a, a0, a1);                          // lanes j, j + 16
+                        unpack2(acc_b, b0, b1);                          // lanes j + 8, j + 24
+                        const float s2 = __fadd_rn(__fadd_rn(a0, a1), __fadd_rn(b0, b1));   // distances 16, 8
+                        if (sd == 0) s2a[r] = s2;
+                        else {
+                            const float s3 = __fadd_rn(s2a[r], s2);      // distance 4
+                            if (half == 0) hold3[r] = s3;
+                            else s4[r] = __fadd_rn(hold3[r], s3);        // distance 2
+                        }
+                    }
+                }
+            }
+        }
+        if (side == 1) {
+#pragma unroll
+            for (int r = 0; r < ROWS; ++r)
+                if (NREP || r < n_rep) xch[(pair * 8 + r) * 32 + lane] = s4[r];
+        }
+        pair_barrier(pair);                         // half sums written; bounds read
+        if (side == 0) {
+            const int p = first + it * kItemPages + lane;
+            float s = neg_inf();
+#pragma unroll
+            for (int r = 0; r < ROWS; ++r) {
+                if (NREP || r < n_rep) {
+                    const float total = __fadd_rn(s4[r], xch[(pair * 8 + r) * 32 + lane]);   // distance 1
+                    // Pages past the end get a finite 0 per head: their token count of zero
+                    // removes them downstream, and a stale NaN here would not.
+                    if (PER_HEAD) {
+                        if (p < end) out[b * ss_b + h * ss_h + r * ss_r + p] = id >= 0 ? total : 0.f;
+                    } else {
+                        s = fmaxf(s, total);
+                    }
+                }
+            }
+            if (!PER_HEAD) {
+                if (id < 0) s = neg_inf();
+                if (p >= np) s = neg_inf();                              // past the end: never chosen
+                else if (p == 0 || p >= np - recent) s = pos_inf();      // sink and recent: always kept
+                if (p < end) out[b * ss_b + h * ss_h + p] = s;
+            }
+        }
+        if (it + 1 < items) id = request(it + 1);
     }
     // No early trigger for a programmatic successor: a CTA that has returned counts as
     // having triggered, so the next kernel's CTAs arrive while the last warps here
@@ -576,20 +603,24 @@ static int launch_index(int per_head, const void* q, const void* kmin, const voi
     }
     const long long resident = (long long)ls::kIndexCtasPerSm * sms;
     int span = ls::kItemPages;
-    for (int items = 1; items <= ls::kMaxItems; ++items) {
+    for (int items = 1; items <= 256; ++items) {
         span = items * ls::kItemPages;
         const long long per_row = (max_pages + ls::kIndexWarps * span - 1) / (ls::kIndexWarps * span);
         if (per_row * kv_heads * batch <= resident) break;
     }
     const int per_cta = ls::kIndexWarps * span;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    auto kern = per_head ? ls::page_index_kernel<1> : ls::page_index_kernel<0>;
-    static bool carveout_set[64][2] = {};
+    const bool six = n_rep == 6;
+    auto kern = per_head ? (six ? ls::page_index_kernel<1, 6> : ls::page_index_kernel<1, 0>)
+                         : (six ? ls::page_index_kernel<0, 6> : ls::page_index_kernel<0, 0>);
+    static bool smem_set[64][4] = {};
     const int slot = dev >= 0 && dev < 64 ? dev : 0;
-    const int variant = per_head ? 1 : 0;
-    if (!carveout_set[slot][variant]) {    // four 48 KB CTAs per SM need the large shared-memory split
+    const int variant = (per_head ? 1 : 0) + (six ? 2 : 0);
+    if (!smem_set[slot][variant]) {        // 76 KB of dynamic shared memory per CTA, two CTAs per SM
+        cudaError_t ea = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, ls::kIndexSmem);
+        if (ea != cudaSuccess) return (int)ea;
         cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
-        carveout_set[slot][variant] = dev >= 0 && dev < 64;
+        smem_set[slot][variant] = dev >= 0 && dev < 64;
     }
     // With LS_LAUNCH_PROGRAMMATIC the launch may begin while the previous kernel of the stream
     // drains; with LS_EARLY_PAGES on top of it the bounds are requested before the kernel
@@ -599,7 +630,8 @@ static int launch_index(int per_head, const void* q, const void* kmin, const voi
     const int early = programmatic && (flags & LS_EARLY_PAGES) && !per_head && recent >= 1;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((max_pages + per_cta - 1) / per_cta, kv_heads, batch);
-    cfg.blockDim = dim3(ls::kIndexWarps * 32);
+    cfg.blockDim = dim3(ls::kIndexWarps * 64);
+    cfg.dynamicSmemBytes = ls::kIndexSmem;
     cfg.stream = s;
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;

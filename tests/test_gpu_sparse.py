@@ -77,6 +77,50 @@ def test_indexer_scores_are_bit_exact(lens):
     assert np.array_equal(got.cpu().numpy().view(np.uint32), want.view(np.uint32))
 
 
+@pytest.mark.parametrize("n_rep", [1, 4, 7, 8])
+def test_indexer_scores_are_bit_exact_for_other_group_sizes(n_rep):
+    """Groups other than six query heads per KV head take the kernel's general form
+    (rows tested against the group size at run time); a warp's span of several items too."""
+    case = synthetic.dense_case([2100, 640, 31], n_rep=n_rep, seed=5, page_offset_std=0.5)
+    t = _with_bounds(case)
+    got = ps.page_scores(t["q"], t["kmin"], t["kmax"], t["block_tables"], t["seq_lens"], recent=2)
+    want = orc.page_scores(case["q"], t["kmin"].cpu().numpy(), t["kmax"].cpu().numpy(),
+                           case["block_tables"], case["seq_lens"], recent=2)
+    assert np.array_equal(got.cpu().numpy().view(np.uint32), want.view(np.uint32))
+
+
+def test_indexer_scores_are_bit_exact_when_a_warp_pair_walks_several_items():
+    """More (sequence, head, 128-page) spans than the GPU holds CTAs of the index kernel at
+    once: each warp pair then scores several 32-page items, reusing its shared memory."""
+    dev = device()
+    lens = [20000 - 37 * i for i in range(40)]           # 40 x 2 heads x 10 spans = 800 CTAs at one item each
+    pages = -(-max(lens) // 16)
+    g = torch.Generator(device=dev).manual_seed(77)
+    nb = sum(-(-x // 16) for x in lens) + 3
+    kmin = torch.randn(nb, 2, 128, dtype=torch.float16, device=dev, generator=g) - 1.0
+    kmax = kmin + torch.rand(nb, 2, 128, dtype=torch.float16, device=dev, generator=g) * 3
+    q = torch.randn(len(lens), 2, 6, 128, dtype=torch.float16, device=dev, generator=g)
+    perm = torch.randperm(nb, device=dev, generator=g).to(torch.int32)
+    tables = torch.zeros(len(lens), pages, dtype=torch.int32, device=dev)
+    at = 0
+    for i, x in enumerate(lens):
+        n = -(-x // 16)
+        tables[i, :n] = perm[at:at + n]
+        at += n
+    seq = torch.tensor(lens, dtype=torch.int32, device=dev)
+    got = ps.page_scores(q, kmin, kmax, tables, seq).cpu().numpy()
+    rows = [0, 17, 39]                                    # the oracle on three of the sequences
+    want = orc.page_scores(q[rows].cpu().numpy(), kmin.cpu().numpy(), kmax.cpu().numpy(),
+                           tables[rows].cpu().numpy(), seq[rows].cpu().numpy())
+    assert np.array_equal(got[rows].view(np.uint32), want.view(np.uint32))
+    # The per-head form of the kernel (summed-mass scoring): the same three sequences scored
+    # as part of the big batch and on their own (one item per warp pair) agree bit for bit.
+    mass = ps.page_scores_mass(q, kmin, kmax, tables, seq)[rows].clone()
+    alone = ps.page_scores_mass(q[rows].contiguous(), kmin, kmax, tables[rows].contiguous(),
+                                seq[rows].contiguous())
+    assert torch.equal(mass, alone)
+
+
 def test_indexer_scores_against_the_reference_bounds(golden_dir):
     g = np.load(golden_dir / "sparse.npz")
     lens = [int(x) for x in g["seq_lens"]]
