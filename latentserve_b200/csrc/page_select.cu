@@ -150,6 +150,22 @@ __device__ __forceinline__ int pages_owed(int len, float ratio, int recent, int 
     return min(min(want, np), min(k, n));
 }
 
+// Sum of the per-warp totals tot[0 .. warp) (column c of SelectScratch::warp_tot), by one
+// scan inside the calling warp instead of a chain of dependent shared-memory reads.
+template <int WARPS>
+__device__ __forceinline__ int warps_before(const int (*tot)[2], int c, int warp, int lane) {
+    static_assert(WARPS <= 32, "one lane per warp total");
+    int v = lane < WARPS ? tot[lane][c] : 0;
+#pragma unroll
+    for (int off = 1; off < WARPS; off <<= 1) {
+        const int u = __shfl_up_sync(LS_FULL_MASK, v, off);
+        if (lane >= off) v += u;
+    }
+    const int incl = __shfl_sync(LS_FULL_MASK, v, warp);
+    const int own = __shfl_sync(LS_FULL_MASK, lane < WARPS ? tot[lane][c] : 0, warp);
+    return incl - own;
+}
+
 // One row of scores -> the n_keep best pages in ascending page order, then -1 up to k.
 // Called by all THREADS threads of a CTA; thread i holds keys [i * E, (i + 1) * E).
 //
@@ -274,8 +290,7 @@ __device__ __forceinline__ void select_row(const float* __restrict__ row, int* _
         }
         if (lane == 31) sc.warp_tot[warp][0] = incl;
         __syncthreads();
-        int before = incl - sum;                            // keys in bins above this thread's
-        for (int wq = 0; wq < warp; ++wq) before += sc.warp_tot[wq][0];
+        int before = incl - sum + warps_before<THREADS / 32>(sc.warp_tot, 0, warp, lane);   // keys in bins above this thread's
         if (before < remaining && remaining <= before + sum) {
 #pragma unroll
             for (int j = 0; j < BPT; ++j) {
@@ -321,11 +336,8 @@ __device__ __forceinline__ void select_row(const float* __restrict__ row, int* _
         sc.warp_tot[warp][1] = gt_incl;
     }
     __syncthreads();
-    int eq_before = eq_incl - eq_local, gt_before = gt_incl - gt_local;
-    for (int w = 0; w < warp; ++w) {
-        eq_before += sc.warp_tot[w][0];
-        gt_before += sc.warp_tot[w][1];
-    }
+    int eq_before = eq_incl - eq_local + warps_before<THREADS / 32>(sc.warp_tot, 0, warp, lane);
+    int gt_before = gt_incl - gt_local + warps_before<THREADS / 32>(sc.warp_tot, 1, warp, lane);
     // Position of a kept key = kept keys before it = (above T before it) + min(equal before it, take_eq).
 #pragma unroll
     for (int e = 0; e < E; ++e) {
