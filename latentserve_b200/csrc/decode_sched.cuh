@@ -64,6 +64,9 @@ struct DecodeParams {
     long long vs_b, vs_p, vs_h;    // v_scale strides: block, token, head
     long long sr_r, sr_p, sr_h;    // residual strides: row, token, head
     int early;                     // LS_EARLY_PAGES: old pages may be read before the dependency wait
+    int kv_merged;                 // INT8 TMA loader: a page's K and V tiles come by ONE copy (map `kv`)
+    int k_off;                     // byte offset of the K tile inside a stage (0, or 2048 when the merged
+                                   // copy delivers V first); the V tile sits at 2048 - k_off
     float scale_log2;              // softmax scale * log2(e)
 };
 

@@ -181,6 +181,14 @@ __device__ __forceinline__ void tma_load_4d(uint32_t dst, const void* tmap, uint
         "l"(tmap), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(mbar), "l"(policy)
         : "memory");
 }
+__device__ __forceinline__ void tma_load_5d(uint32_t dst, const void* tmap, uint32_t mbar, int c0,
+                                            int c1, int c2, int c3, int c4, uint64_t policy) {
+    asm volatile(
+        "cp.async.bulk.tensor.5d.shared::cluster.global.tile.mbarrier::complete_tx::bytes"
+        ".L2::cache_hint [%0], [%1, {%2, %3, %4, %5, %6}], [%7], %8;\n" ::"r"(dst),
+        "l"(tmap), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(c4), "r"(mbar), "l"(policy)
+        : "memory");
+}
 // Untiled bulk copy: both addresses 16-byte aligned, bytes a multiple of 16.
 __device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_t bytes,
                                           uint32_t mbar) {

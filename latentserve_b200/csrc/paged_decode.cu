@@ -77,6 +77,7 @@ constexpr int kWarps = 4;
 // Tensor maps of the TMA-loading variants (unused and zero for the others).
 struct TmaMaps {
     CUtensorMap k, v, ks, kz;
+    CUtensorMap kv;                 // INT8: K and V pools as one 5-d tensor (see build_int8_maps)
 };
 constexpr int kMbarSpinLimit = 1 << 22;   // probes of an mbarrier phase before a warp gives up
 constexpr int kStages = LS_STAGES;
@@ -410,7 +411,7 @@ struct MmaFp16T {
     }
 
     __device__ __forceinline__ void compute(const DecodeParams& p, uint32_t stage, int meta,
-                                            int lane) {
+                                            int lane, uint32_t /*scratch*/) {
         float s[4] = {0.f, 0.f, 0.f, 0.f};
         if (TMA && meta < LS_PAGE) {
             // A sequence's last page: the tile's V rows past the end are stale pool
@@ -540,7 +541,7 @@ struct SimtFp16 {
     }
 
     __device__ __forceinline__ void compute(const DecodeParams&, uint32_t stage, int valid,
-                                            int lane) {
+                                            int lane, uint32_t /*scratch*/) {
         const int half_id = lane >> 4, li = lane & 15;
         // Two rounds of four tokens per half keep the score registers modest.
 #pragma unroll
@@ -744,11 +745,15 @@ struct PoolInt8Tma {
                 mbar_expect_tx(mbar, 2048u + (ASYM ? 2u : 1u) * vs_bytes +
                                          (from_res ? 0u : 2048u + (ASYM ? 1024u : 512u)));
                 if (!from_res) {
-                    tma_load_4d(stage, &maps.k, mbar, 0, h, 0, it.blk, pol);
                     tma_load_4d(stage + OFF_KS, &maps.ks, mbar, 0, 0, h, it.blk, pol);
                     if (ASYM) tma_load_4d(stage + OFF_KZ, &maps.kz, mbar, 0, 0, h, it.blk, pol);
                 }
-                tma_load_4d(stage + OFF_V, &maps.v, mbar, 0, h, 0, it.blk, pol);
+                if (!from_res && p.kv_merged) {
+                    tma_load_5d(stage, &maps.kv, mbar, 0, h, 0, it.blk, 0, pol);     // both tiles, 4 KB
+                } else {
+                    if (!from_res) tma_load_4d(stage + p.k_off, &maps.k, mbar, 0, h, 0, it.blk, pol);
+                    tma_load_4d(stage + (2048 - p.k_off), &maps.v, mbar, 0, h, 0, it.blk, pol);
+                }
                 bulk_load(stage + OFF_VS, p.v_scale + it.blk * p.vs_b, vs_bytes, mbar);
                 if (ASYM) bulk_load(stage + OFF_VZ, p.v_zero + it.blk * p.vs_b, vs_bytes, mbar);
             }
@@ -829,15 +834,17 @@ struct MmaInt8 {
     // A full page of a sequence's interior (all 16 tokens, K in the pool) takes the
     // straight-line form: no masks, no residual branch. Anything else -- a last page, a
     // page to skip -- takes the general one.
+    // `scratch`: 320 bytes of the warp's own shared memory that nothing else uses while pages
+    // are being walked (the start of its merge rows).
     __device__ __forceinline__ void compute(const DecodeParams& p, uint32_t stage, int meta,
-                                            int lane) {
-        if (meta == LS_PAGE) compute_page<true>(p, stage, meta, lane);
-        else compute_page<false>(p, stage, meta, lane);
+                                            int lane, uint32_t scratch) {
+        if (meta == LS_PAGE) compute_page<true>(p, stage, meta, lane, scratch);
+        else compute_page<false>(p, stage, meta, lane, scratch);
     }
 
     template <bool FULL>
     __device__ __forceinline__ void compute_page(const DecodeParams& p, uint32_t stage, int meta,
-                                                 int lane) {
+                                                 int lane, uint32_t scratch) {
         const int valid = FULL ? LS_PAGE : (meta & 255);
         const int g = lane >> 2, t = lane & 3;
         float s[4] = {0.f, 0.f, 0.f, 0.f};
@@ -864,16 +871,43 @@ struct MmaInt8 {
             }
         } else {
             // q' = q * fp16(k_scale) in half precision (the query stays in half2 registers:
-            // sixteen fewer than its fp32 form), in this lane's dim order.
+            // sixteen fewer than its fp32 form), in this lane's dim order. The page's 128
+            // scales are rounded to fp16 once per warp -- each lane converts four of them
+            // and leaves them in the warp's scratch, rows of 32 dims 80 bytes apart so that
+            // the four rows the lanes then read together lie in different banks -- instead
+            // of every lane converting the 32 it needs (eight lanes need the same 32).
             uint32_t qk[8][2];
             float zq = 0.f;
+            if (!ASYM) {
+                {
+                    const int row = lane >> 3, ch = lane & 7;
+                    const uint4 sc = lds128(stage + Pool::OFF_KS + ((uint32_t)(8 * row + (ch ^ row)) << 4));
+                    const uint32_t h0 = pack_half2(__uint_as_float(sc.x), __uint_as_float(sc.y));
+                    const uint32_t h1 = pack_half2(__uint_as_float(sc.z), __uint_as_float(sc.w));
+                    asm volatile("st.shared.v2.b32 [%0], {%1, %2};\n" ::"r"(scratch + row * 80 + ch * 8), "r"(h0),
+                                 "r"(h1)
+                                 : "memory");
+                }
+                __syncwarp();
+                // (No second barrier: the loads below feed this page's first MMAs, which no lane
+                // executes before every lane's operands are there; the next page's stores come later.)
 #pragma unroll
-            for (int i = 0; i < 8; ++i) {
-                const uint32_t slot = (uint32_t)(8 * t + (i ^ t)) << 4;   // see PoolInt8::issue
-                const uint4 sc = lds128(stage + Pool::OFF_KS + slot);
-                qk[i][0] = hmul2_u32(qh[2 * i], pack_half2(__uint_as_float(sc.x), __uint_as_float(sc.y)));
-                qk[i][1] = hmul2_u32(qh[2 * i + 1], pack_half2(__uint_as_float(sc.z), __uint_as_float(sc.w)));
-                if (ASYM) {
+                for (int j = 0; j < 4; ++j) {
+                    const uint4 hs = lds128(scratch + t * 80 + j * 16);
+                    qk[2 * j][0] = hmul2_u32(qh[4 * j], hs.x);
+                    qk[2 * j][1] = hmul2_u32(qh[4 * j + 1], hs.y);
+                    qk[2 * j + 1][0] = hmul2_u32(qh[4 * j + 2], hs.z);
+                    qk[2 * j + 1][1] = hmul2_u32(qh[4 * j + 3], hs.w);
+                }
+            } else {
+                // Asymmetric pools: every lane converts the scales it needs and, in the same
+                // pass over its dims, sums q . k_zero (registers are too few for the shared form).
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    const uint32_t slot = (uint32_t)(8 * t + (i ^ t)) << 4;   // see PoolInt8::issue
+                    const uint4 sc = lds128(stage + Pool::OFF_KS + slot);
+                    qk[i][0] = hmul2_u32(qh[2 * i], pack_half2(__uint_as_float(sc.x), __uint_as_float(sc.y)));
+                    qk[i][1] = hmul2_u32(qh[2 * i + 1], pack_half2(__uint_as_float(sc.z), __uint_as_float(sc.w)));
                     const uint4 z = lds128(stage + Pool::OFF_KZ + slot);
                     const float2 qa = __half22float2(*reinterpret_cast<const __half2*>(&qh[2 * i]));
                     const float2 qb = __half22float2(*reinterpret_cast<const __half2*>(&qh[2 * i + 1]));
@@ -883,7 +917,8 @@ struct MmaInt8 {
                     zq = fmaf(qb.y, __uint_as_float(z.w), zq);
                 }
             }
-            const uint32_t r0 = stage + g * 128, r1 = stage + (g + 8) * 128;
+            const uint32_t kt = TMA ? stage + p.k_off : stage;              // the K tile
+            const uint32_t r0 = kt + g * 128, r1 = kt + (g + 8) * 128;
             uint4 w0[2], w1[2];
             w0[0] = lds128(r0 + (((2 * t) ^ g) << 4));
             w0[1] = lds128(r0 + (((2 * t + 1) ^ g) << 4));
@@ -960,7 +995,7 @@ struct MmaInt8 {
         mma_16816(o[8], oneq[0], oneq[1], oneq[2], oneq[3], pb0, pb1);
         const int mi = lane >> 3;                                   // the matrix this lane addresses
         const int vrow = (lane & 7) + (mi & 1) * 8;
-        const uint32_t vaddr = stage + Pool::OFF_V + vrow * 128;
+        const uint32_t vaddr = stage + (TMA ? 2048 - p.k_off : Pool::OFF_V) + vrow * 128;
         const int sw = vrow & 7, hi = mi >> 1;
 #pragma unroll
         for (int q = 0; q < 4; ++q) {
@@ -1164,6 +1199,7 @@ decode_kernel(const DecodeParams p, const __grid_constant__ TmaMaps maps) {
     const bool has_work = g0 < total;
     const int b0 = has_work ? find_seq(cum, p.batch, g0) : 0;
     const uint32_t ring = smem_u32(smem + warp * (STAGES * STAGE_BYTES));
+    const uint32_t warp_scratch = smem_u32(merge_o + warp * p.n_rep * kMergeStride);   // free while pages are walked
 
     // Load side. The dense walk needs nothing the previous kernel may have
     // written; the sparse walk reads the selection, which it usually did write.
@@ -1254,7 +1290,7 @@ decode_kernel(const DecodeParams p, const __grid_constant__ TmaMaps maps) {
                 for (int q = 1; q < STAGES; ++q) meta_now = stage == q ? slot_meta[q] : meta_now;
                 issue(stage == 0 ? STAGES - 1 : stage - 1);          // the slot consumed one page ago
 #ifndef LS_LOADS_ONLY
-                st.compute(p, ring + stage * STAGE_BYTES, meta_now, lane);
+                st.compute(p, ring + stage * STAGE_BYTES, meta_now, lane, warp_scratch);
 #else
                 (void)meta_now;                          // build flag: pages land, nothing is computed
 #endif
@@ -1423,7 +1459,7 @@ bool encode_4d(CUtensorMap* map, CUtensorMapDataType type, const void* base, con
 }
 
 // True if the symmetric INT8 pools have the layout the TMA kernel takes and the maps were built.
-bool build_int8_maps(const ls::DecodeParams& p, ls::TmaMaps* maps) {
+bool build_int8_maps(ls::DecodeParams& p, ls::TmaMaps* maps) {
     // pools [blocks][16][H][128] int8 (any strides that are 16-byte multiples, innermost unit);
     // K scales [blocks][H][128] fp32; V scales [blocks][16][H] fp32 with tokens and heads dense.
     if (p.heads > 8 || p.vs_h != 1 || p.vs_p != p.heads || (p.vs_b % 4) ||
@@ -1440,9 +1476,33 @@ bool build_int8_maps(const ls::DecodeParams& p, ls::TmaMaps* maps) {
         ((reinterpret_cast<uintptr_t>(p.v_zero) & 15) ||
          !encode_4d(&maps->kz, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, p.k_zero, ks_dims, ks_strides, ks_box)))
         return false;                                  // zero points share the scales' layout
-    return encode_4d(&maps->k, CU_TENSOR_MAP_DATA_TYPE_UINT8, p.k_pool, pool_dims, pool_strides, pool_box) &&
-           encode_4d(&maps->v, CU_TENSOR_MAP_DATA_TYPE_UINT8, p.v_pool, pool_dims, pool_strides, pool_box) &&
-           encode_4d(&maps->ks, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, p.k_scale, ks_dims, ks_strides, ks_box);
+    if (!(encode_4d(&maps->k, CU_TENSOR_MAP_DATA_TYPE_UINT8, p.k_pool, pool_dims, pool_strides, pool_box) &&
+          encode_4d(&maps->v, CU_TENSOR_MAP_DATA_TYPE_UINT8, p.v_pool, pool_dims, pool_strides, pool_box) &&
+          encode_4d(&maps->ks, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, p.k_scale, ks_dims, ks_strides, ks_box)))
+        return false;
+    // The two pools seen as ONE tensor [2][blocks][16][H][128] whose outermost stride is the
+    // distance between them: a page's K and V tiles then arrive by a single copy, in address
+    // order (k_off says where the K tile lands). Any two allocations qualify as long as the
+    // distance is a multiple of 16 bytes below the 2^40 a tensor map's strides may hold.
+    p.kv_merged = 0;
+    p.k_off = 0;
+    const uintptr_t ka = reinterpret_cast<uintptr_t>(p.k_pool), va = reinterpret_cast<uintptr_t>(p.v_pool);
+    const uintptr_t lo = ka < va ? ka : va, dist = ka < va ? va - ka : ka - va;
+    if (dist != 0 && (dist % 16) == 0 && dist < (uintptr_t(1) << 40)) {
+        EncodeTiledFn fn = encode_tiled_fn();
+        const cuuint64_t dims5[5] = {128, H, 16, nb, 2};
+        const cuuint64_t strides5[4] = {(cuuint64_t)p.sk_h, (cuuint64_t)p.sk_p, (cuuint64_t)p.sk_b, (cuuint64_t)dist};
+        const cuuint32_t box5[5] = {128, 1, 16, 1, 2};
+        const cuuint32_t ones[5] = {1, 1, 1, 1, 1};
+        if (fn != nullptr &&
+            fn(&maps->kv, CU_TENSOR_MAP_DATA_TYPE_UINT8, 5, reinterpret_cast<void*>(lo), dims5, strides5, box5, ones,
+               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS) {
+            p.kv_merged = 1;
+            p.k_off = ka < va ? 0 : 2048;
+        }
+    }
+    return true;
 }
 
 // fp16 pools [blocks][16][H][128] (strides in elements): tiles of 16 tokens x 64 dims.

@@ -248,6 +248,38 @@ def test_int8_loaders_agree_bit_for_bit():
     assert torch.equal(outs["tma"], outs["cp_async"])
 
 
+
+@pytest.mark.parametrize("order", ["k_first", "v_first"])
+def test_int8_k_and_v_tiles_by_one_copy_whatever_the_pools_address_order(order):
+    """The TMA loader fetches a page's K and V tiles with one copy of a tensor map that spans
+    both pools (outermost stride = their distance). K below V and V below K both give the
+    cp.async form's bits."""
+    lens = [1500, 333, 48, 16, 5]
+    case = _random_int8_case(lens, False, True, seed=29)
+    dev = device()
+    t = {k: torch.from_numpy(np.ascontiguousarray(v)).to(dev) for k, v in case.items()}
+    n = t["k_pool"].numel()
+    gap = 4096
+    arena = torch.zeros(2 * n + gap + 64, dtype=torch.int8, device=dev)
+    base = (-arena.data_ptr()) % 16                           # first 16-byte aligned element
+    lo = arena[base: base + n].view(t["k_pool"].shape)
+    hi = arena[base + n + gap: base + 2 * n + gap].view(t["k_pool"].shape)
+    k_pool, v_pool = (hi, lo) if order == "v_first" else (lo, hi)
+    k_pool.copy_(t["k_pool"])
+    v_pool.copy_(t["v_pool"])
+    outs = {}
+    for name in ("tma", "cp_async"):
+        pdc.set_loader(name)
+        try:
+            outs[name] = pdc.paged_decode_cuda(
+                t["q"], k_pool, v_pool, t["block_tables"], t["seq_lens"], max(lens),
+                k_scale=t["k_scale"], v_scale=t["v_scale"], k_residual=t["k_residual"],
+                res_rows=t["res_rows"]).clone()
+        finally:
+            pdc.set_loader("auto")
+    assert torch.equal(outs["tma"], outs["cp_async"])
+    assert pdc.error_flag(dev, len(lens), tag="cuda_i8") == 0
+
 @pytest.mark.parametrize("ratio", [None, 0.5])
 def test_int8_sparse_decode_matches_the_oracle(ratio, loader):
     """Attention over a page list on INT8 pools (an extension: the reference's sparse
