@@ -54,6 +54,11 @@ extern "C" {
  * the cp.async form runs then). Results are identical. */
 #define LS_LOAD_CP_ASYNC 0x200
 #define LS_LOAD_TMA 0x400
+/* INT8 entry points, TMA loader: a page's K tile and V tile normally arrive by ONE tile
+ * copy, through a tensor map that spans both pools (possible whenever the two allocations
+ * lie less than 2^40 bytes apart). With this flag they are fetched by one copy each, which
+ * is also what happens by itself when the pools are further apart. Results are identical. */
+#define LS_LOAD_TMA_SPLIT_KV 0x1000
 /* With LS_LAUNCH_PROGRAMMATIC on the dense entry points (fp16, INT8): also request
  * the first pages before synchronising on the previous kernel of the stream, except
  * a sequence's LAST page (the one holding token seq_len - 1), which is requested

@@ -40,6 +40,7 @@
 #define LS_LOAD_CP_ASYNC 0x200
 #define LS_LOAD_TMA 0x400
 #define LS_EARLY_PAGES 0x800
+#define LS_LOAD_TMA_SPLIT_KV 0x1000
 #define LS_GEMM_NORM 1
 #define LS_GEMM_SWIGLU 2
 

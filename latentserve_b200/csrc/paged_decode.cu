@@ -1459,7 +1459,7 @@ bool encode_4d(CUtensorMap* map, CUtensorMapDataType type, const void* base, con
 }
 
 // True if the symmetric INT8 pools have the layout the TMA kernel takes and the maps were built.
-bool build_int8_maps(ls::DecodeParams& p, ls::TmaMaps* maps) {
+bool build_int8_maps(ls::DecodeParams& p, ls::TmaMaps* maps, bool merge_kv) {
     // pools [blocks][16][H][128] int8 (any strides that are 16-byte multiples, innermost unit);
     // K scales [blocks][H][128] fp32; V scales [blocks][16][H] fp32 with tokens and heads dense.
     if (p.heads > 8 || p.vs_h != 1 || p.vs_p != p.heads || (p.vs_b % 4) ||
@@ -1488,7 +1488,7 @@ bool build_int8_maps(ls::DecodeParams& p, ls::TmaMaps* maps) {
     p.k_off = 0;
     const uintptr_t ka = reinterpret_cast<uintptr_t>(p.k_pool), va = reinterpret_cast<uintptr_t>(p.v_pool);
     const uintptr_t lo = ka < va ? ka : va, dist = ka < va ? va - ka : ka - va;
-    if (dist != 0 && (dist % 16) == 0 && dist < (uintptr_t(1) << 40)) {
+    if (merge_kv && dist != 0 && (dist % 16) == 0 && dist < (uintptr_t(1) << 40)) {
         EncodeTiledFn fn = encode_tiled_fn();
         const cuuint64_t dims5[5] = {128, H, 16, nb, 2};
         const cuuint64_t strides5[4] = {(cuuint64_t)p.sk_h, (cuuint64_t)p.sk_p, (cuuint64_t)p.sk_b, (cuuint64_t)dist};
@@ -1745,12 +1745,12 @@ static int int8_decode_impl(const int32_t* sel, float ratio, int recent, int num
     if (k_res && ((reinterpret_cast<uintptr_t>(k_res) & 15) || (sr_r % 8) || (sr_p % 8) || (sr_h % 8)))
         return LS_ERR_MISALIGNED;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    if (flags & ~(LS_LAUNCH_PROGRAMMATIC | LS_LOAD_CP_ASYNC | LS_LOAD_TMA | LS_EARLY_PAGES))
+    if (flags & ~(LS_LAUNCH_PROGRAMMATIC | LS_LOAD_CP_ASYNC | LS_LOAD_TMA | LS_EARLY_PAGES | LS_LOAD_TMA_SPLIT_KV))
         return LS_ERR_UNSUPPORTED;
     const bool pdl = (flags & LS_LAUNCH_PROGRAMMATIC) != 0;
     p.early = (flags & LS_EARLY_PAGES) != 0;
     ls::TmaMaps maps;
-    const bool tma = !(flags & LS_LOAD_CP_ASYNC) && build_int8_maps(p, &maps);
+    const bool tma = !(flags & LS_LOAD_CP_ASYNC) && build_int8_maps(p, &maps, !(flags & LS_LOAD_TMA_SPLIT_KV));
     if (sel != nullptr) {
         // Attention over the selected pages only (symmetric pools).
         if (k_zero) return LS_ERR_UNSUPPORTED;

@@ -77,7 +77,7 @@ def paged_decode_attention(
            v_pool.data_ptr(), v_pool.stride(),
            block_tables.data_ptr(), block_tables.shape, block_tables.stride(), block_tables.dtype,
            seq_lens.data_ptr(), seq_lens.shape, seq_lens.dtype, softmax_scale, pdc.dense_launch_flags(),
-           pdc.loader_flags(),
+           pdc.int8_loader_flags(),
            _ident(k_scale), _ident(v_scale), _ident(k_zero), _ident(v_zero), _ident(k_residual),
            _ident(res_rows), _ident(out), _ident(k_new), _ident(v_new))
     plan = _PLANS.get(key)

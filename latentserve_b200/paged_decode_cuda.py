@@ -33,6 +33,7 @@ EARLY_PAGES = 0x800                 # see LS_EARLY_PAGES (dense entry points onl
 # append. Off unless asked for (LATENTSERVE_B200_PDL=1 or set_programmatic_launch).
 _PROGRAMMATIC = {"on": os.environ.get("LATENTSERVE_B200_PDL", "0") == "1"}
 LOAD_CP_ASYNC, LOAD_TMA = 0x200, 0x400   # see LS_LOAD_CP_ASYNC / LS_LOAD_TMA in the header
+LOAD_TMA_SPLIT_KV = 0x1000                # see LS_LOAD_TMA_SPLIT_KV (INT8 entry points)
 # "auto": TMA tile copies for INT8 pools, per-lane cp.async for fp16 pools (the
 # faster form of each); "tma" / "cp_async" force one (same results; for
 # comparison and for the tests).
@@ -66,13 +67,19 @@ def dense_launch_flags() -> int:
 
 
 def set_loader(name: str) -> None:
-    if name not in ("auto", "tma", "cp_async"):
+    if name not in ("auto", "tma", "tma_split_kv", "cp_async"):
         raise ValueError(f"unknown page loader {name!r}")
     _LOADER["name"] = name
 
 
 def loader_flags() -> int:
-    return {"auto": 0, "tma": LOAD_TMA, "cp_async": LOAD_CP_ASYNC}[_LOADER["name"]]
+    return {"auto": 0, "tma": LOAD_TMA, "tma_split_kv": LOAD_TMA, "cp_async": LOAD_CP_ASYNC}[_LOADER["name"]]
+
+
+def int8_loader_flags() -> int:
+    """The loader flags of the INT8 entry points: `tma_split_kv` asks for a page's K and V
+    tiles by one copy each (what pools more than 2^40 bytes apart get by themselves)."""
+    return loader_flags() | (LOAD_TMA_SPLIT_KV if _LOADER["name"] == "tma_split_kv" else 0)
 
 
 def scratch(key, shape, dtype, device, zero: bool = False) -> torch.Tensor:
@@ -257,7 +264,7 @@ def plan_decode(q, k_pool, v_pool, block_tables, seq_lens, num_splits=None, soft
             ptr(acc), ptr(m), ptr(l), ptr(seg), out_ptr,
             b, h_kv, n_rep, d, k_pool.shape[1], block_tables.stride(0), k_pool.shape[0],
             0 if k_residual is None else k_residual.shape[0], chunks, MIN_CHUNK_PAGES,
-            dense_launch_flags() | loader_flags(),
+            dense_launch_flags() | int8_loader_flags(),
             q.stride(0), q.stride(1), q.stride(2),
             k_pool.stride(0), k_pool.stride(1), k_pool.stride(2),
             k_scale.stride(0), k_scale.stride(1),

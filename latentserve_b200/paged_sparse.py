@@ -197,7 +197,7 @@ def sparse_decode(q, k_pool, v_pool, block_tables, seq_lens, sel,
     tag = "sparse_i8" if int8 else "sparse"
     acc, m, l, seg = pdc._partials(q, chunks, tag)
     out = pdc.scratch(tag + "_out", (b, h, n_rep, d), q.dtype, q.device)
-    flags = pdc.launch_flags() | pdc.loader_flags()
+    flags = pdc.launch_flags() | (pdc.int8_loader_flags() if int8 else pdc.loader_flags())
     ratio_f = 0.0 if ratio is None else float(ratio)
     ptr = _lib.ptr
     if int8:

@@ -230,13 +230,14 @@ def test_int8_pools_that_are_views_of_larger_tensors(strided_scales, loader):
 
 
 def test_int8_loaders_agree_bit_for_bit():
-    """TMA tiles and per-lane cp.async feed the same arithmetic."""
+    """TMA tiles (K and V of a page by one copy, or by one each) and per-lane cp.async feed
+    the same arithmetic."""
     lens = [2000, 777, 16, 15, 1]
     case = _random_int8_case(lens, False, True, seed=23)
     dev = device()
     t = {k: torch.from_numpy(np.ascontiguousarray(v)).to(dev) for k, v in case.items()}
     outs = {}
-    for name in ("tma", "cp_async"):
+    for name in ("tma", "tma_split_kv", "cp_async"):
         pdc.set_loader(name)
         try:
             outs[name] = pdc.paged_decode_cuda(
@@ -246,6 +247,7 @@ def test_int8_loaders_agree_bit_for_bit():
         finally:
             pdc.set_loader("auto")
     assert torch.equal(outs["tma"], outs["cp_async"])
+    assert torch.equal(outs["tma_split_kv"], outs["cp_async"])      # K and V tiles by a copy each
 
 
 
