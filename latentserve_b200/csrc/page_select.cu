@@ -138,7 +138,9 @@ struct SelectScratch {
     int n_inf, n_fin;                          // keys that are +inf / finite
     unsigned prefix;
     int remaining;
+    int n_cand, bucket_count;                  // one-pass search: keys in the wanted bucket
 };
+constexpr int kMaxCandidates = 64;            // a wanted bucket with more keys goes to the bit-wise search
 
 // How many pages a sequence attends: the rule of the attention kernel
 // (kernels/cuda/paged_sparse_fp16.cu:242-247 in the reference).
@@ -262,6 +264,82 @@ __device__ __forceinline__ void select_row(const float* __restrict__ row, int* _
         top = 32 - __clz(lo ^ hi);                          // undecided low bits (0: all finite keys equal)
         mask = top >= 32 ? 0u : ~((1u << top) - 1u);        // decided (common) high bits
         prefix = hi & mask;
+        // One pass over 2048 buckets of equal width between the smallest and the largest finite
+        // key usually settles it: the bucket that holds the wanted key rarely holds more than a
+        // handful, and among those the key is found by counting. (The bit-wise search below needs
+        // three passes for scores that straddle a power of two.) Rows whose wanted bucket is
+        // crowded -- many equal or nearly equal scores -- take the bit-wise search instead.
+        if (top > kDigitBits) {
+            const unsigned range = hi - lo;
+            const int bshift = max(0, 32 - __clz(range) - kDigitBits);   // range >> bshift < kBins
+#pragma unroll
+            for (int e = 0; e < E; ++e) {
+                if (key[e] != kPosInf && key[e] != kNegInf && tid * E + e < n)
+                    atomicAdd(&sc.hist[(key[e] - lo) >> bshift], 1);
+            }
+            __syncthreads();
+            int local[BPT], sum = 0;
+#pragma unroll
+            for (int j = 0; j < BPT; ++j) {
+                const int bin = kBins - 1 - (BPT * tid + j);
+                local[j] = sc.hist[bin];
+                sum += local[j];
+            }
+            int incl = sum;
+#pragma unroll
+            for (int off = 1; off < 32; off <<= 1) {
+                const int v = __shfl_up_sync(LS_FULL_MASK, incl, off);
+                if (lane >= off) incl += v;
+            }
+            if (lane == 31) sc.warp_tot[warp][0] = incl;
+            if (tid == 0) sc.n_cand = 0;
+            __syncthreads();
+            int before = incl - sum + warps_before<THREADS / 32>(sc.warp_tot, 0, warp, lane);
+            if (before < remaining && remaining <= before + sum) {
+#pragma unroll
+                for (int j = 0; j < BPT; ++j) {
+                    if (before + local[j] >= remaining) {
+                        sc.prefix = (unsigned)(kBins - 1 - (BPT * tid + j));     // the wanted bucket
+                        sc.remaining = remaining - before;                       // rank inside it, from the top
+                        sc.bucket_count = local[j];
+                        break;
+                    }
+                    before += local[j];
+                }
+            }
+            __syncthreads();
+            const unsigned bucket = sc.prefix;
+            const int want = sc.remaining, crowd = sc.bucket_count;
+            // The histogram is needed again: by the bit-wise search (zeroed), or as the candidates' list.
+            for (int i = tid; i < kBins; i += THREADS) sc.hist[i] = 0;
+            __syncthreads();
+            if (crowd <= kMaxCandidates) {
+                unsigned* cand = reinterpret_cast<unsigned*>(sc.hist);
+#pragma unroll
+                for (int e = 0; e < E; ++e) {
+                    if (key[e] != kPosInf && key[e] != kNegInf && tid * E + e < n &&
+                        ((key[e] - lo) >> bshift) == bucket)
+                        cand[atomicAdd(&sc.n_cand, 1)] = key[e];
+                }
+                __syncthreads();
+                if (tid < crowd) {
+                    const unsigned x = cand[tid];
+                    int gt = 0, ge = 0;
+                    for (int i = 0; i < crowd; ++i) {
+                        gt += cand[i] > x;
+                        ge += cand[i] >= x;
+                    }
+                    if (gt < want && want <= ge) {          // equal candidates all write the same pair
+                        sc.prefix = x;
+                        sc.remaining = want - gt;
+                    }
+                }
+                __syncthreads();
+                prefix = sc.prefix;
+                remaining = sc.remaining;
+                top = 0;                                    // settled: no bit-wise pass
+            }
+        }
     }
 #pragma unroll 1
     while (top > 0) {

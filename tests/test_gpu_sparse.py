@@ -181,6 +181,33 @@ def test_selection_without_the_sort_picks_the_same_pages(n, k, ratio):
             assert (got[b, h, keep:] == -1).all()
 
 
+def test_selection_threshold_search_takes_both_routes():
+    """The wanted score is found in one pass over equal-width buckets when its bucket holds few
+    keys, and by the bit-wise search when the bucket is crowded: rows of well spread scores, of
+    two values only, of one value, and of a tight cluster around a power of two all select
+    exactly the first n entries of the stable sort."""
+    n, k, ratio = 2048, 1024, 0.5
+    rng = np.random.default_rng(99)
+    s = np.empty((5, 2, n), dtype=np.float32)
+    s[0] = rng.standard_normal((2, n)) * 40 + 120                 # spread over two binades
+    s[1] = np.where(rng.random((2, n)) < 0.5, 3.0, 7.0)           # two values: the bucket is crowded
+    s[2] = 1.5                                                    # all equal
+    s[3] = 128.0 + rng.integers(-40, 40, size=(2, n)) * 2.0 ** -17    # a cluster straddling 2^7, many ties
+    s[4] = rng.standard_normal((2, n)).astype(np.float32) * 1e-30     # tiny magnitudes, both signs
+    lens = np.full(5, n * 16, dtype=np.int32)
+    s[:, :, 0] = np.inf
+    s[:, :, n - 2:] = np.inf
+    dev = device()
+    got = ps.select_for_attention(torch.from_numpy(s).to(dev), torch.from_numpy(lens).to(dev), k, ratio)
+    got = got.cpu().numpy()
+    order = orc.select(s, k)
+    keep = int(orc.budgets(lens, ratio)[0])
+    for b in range(5):
+        for h in range(2):
+            assert np.array_equal(got[b, h, :keep], np.sort(order[b, h, :keep])), (b, h)
+            assert (got[b, h, keep:] == -1).all()
+
+
 def test_topk_longest_row_and_one_past_it():
     """8192 pages (a 128K context) is the longest row the sort takes."""
     rng = np.random.default_rng(8192)
