@@ -14,7 +14,10 @@ directory `LATENTSERVE_REFERENCE` names) has its kernel modules patched by
     the reference cache through `update_bounds`, the sparse branch of
     `GQAAttention.forward` against the oracle;
   * `GraphedDecoder.step_greedy` (runtime/cuda_graph.py:307-388): replayed
-    steps against eager steps (cases: tests/test_cuda_decode.py:125-171).
+    steps against eager steps (cases: tests/test_cuda_decode.py:125-171);
+  * `ServingEngine` (runtime/engine.py:59-455) draining a queue of requests with
+    its `PrefixCache` and its graphed decoder switched on, against the same
+    engine without either.
 
 Skipped only where no LatentServe tree (or no `transformers`) is importable.
 """
@@ -274,3 +277,48 @@ def test_reference_graphed_decoder_replays_what_eager_steps_compute(ref, kv_dtyp
         top2 = want_logits[:, agree].topk(2, dim=-1).values
         flipped = got_tokens[:, agree] != want_tokens[:, agree]
         assert ((top2[:, 0] - top2[:, 1])[flipped] <= 6e-2).all()
+
+
+def test_reference_serving_engine_with_prefix_cache_and_graphs(ref):
+    """The reference's `ServingEngine` (runtime/engine.py:59-455) — continuous batching over
+    its own paged cache, its `PrefixCache` sharing full prompt blocks between requests, decode
+    steps replayed by its `GraphedDecoder` — drains a queue of requests with this library
+    under it, and generates what the same engine generates step by step without graphs and
+    without prefix sharing."""
+    calls, _ = ref
+    from runtime.engine import ServingEngine
+    from runtime.request import ServedRequest
+
+    g = torch.Generator().manual_seed(3)
+    shared = torch.randint(0, VOCAB, (48,), generator=g).tolist()          # three full blocks in common
+    prompts = [shared + torch.randint(0, VOCAB, (n,), generator=g).tolist() for n in (21, 5, 40, 13, 30)]
+    new_tokens = 12
+
+    def serve(graphs, prefix):
+        engine = ServingEngine(_model(), max_running=3, max_seq_len=256, use_cuda_graphs=graphs,
+                               prefix_caching=prefix)
+        for i, p in enumerate(prompts):
+            engine.add_request(ServedRequest(i, list(p), max_new_tokens=new_tokens))
+        done = engine.run(max_steps=4000)
+        assert len(done) == len(prompts) and not engine.has_work
+        return engine, {r.request_id: list(r.output_ids) for r in done}
+
+    plain, want = serve(False, False)
+    before = calls["paged_decode_cuda"]
+    engine, got = serve(True, True)
+    assert calls["paged_decode_cuda"] > before                 # captured (and run) through this library
+    assert engine.decoder is not None and engine.decoder.graph_steps > 0
+    assert engine.prefix_hit_tokens >= 48                      # later requests reused the shared blocks
+    agree = total = 0
+    for i in range(len(prompts)):
+        assert len(got[i]) == new_tokens and len(want[i]) == new_tokens
+        assert all(0 <= t < VOCAB for t in got[i])
+        same = 0
+        while same < new_tokens and got[i][same] == want[i][same]:
+            same += 1
+        agree += same
+        total += new_tokens
+    # Same kernels and weights; what differs is how the shared prompt blocks were prefilled
+    # (once, in another batch shape), so a near-tie in the random-init logits may flip a
+    # token, after which that request legitimately goes its own way.
+    assert agree >= total // 2, (agree, total, got, want)
