@@ -88,7 +88,7 @@ extern "C" {
  *                                        before first use.
  * None of it needs filling between calls. `num_chunks` x H is the grid: the
  * fp16 kernels are sized for 2 resident CTAs per SM and the INT8 kernels for
- * 4, so num_chunks = 2*SMs / H (4*SMs / H for INT8) is the natural choice; `min_chunk` (>= 1) is the fewest pages a chunk may hold.
+ * 4, so num_chunks = 2*SMs / H (3*SMs / H for INT8) is the natural choice; `min_chunk` (>= 1) is the fewest pages a chunk may hold.
  * If `out` is non-NULL the same launch also merges the partials — the CTA that
  * delivers a sequence's last partial does it, nobody waits — and `out`
  * receives fp16 [B, H, R, 128] with the given strides; sequences of length 0

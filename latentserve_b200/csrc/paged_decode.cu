@@ -67,11 +67,12 @@ namespace ls {
 #define LS_INT8_STAGES 3            // ring depth of the INT8 kernel (4.6 KB stages, 3 CTAs per SM)
 #endif
 #ifndef LS_INT8_TMA_STAGES
-#define LS_INT8_TMA_STAGES 2        // 5 KB stages of the TMA-loading INT8 kernel
+#define LS_INT8_TMA_STAGES 3        // 5 KB stages of the TMA-loading INT8 kernel (74 KB per CTA, three per SM)
 #endif
 #define LS_INT8_STAGES_ASYM 2       // 5.1 KB stages: a third one would cost the third CTA
+#define LS_INT8_TMA_STAGES_ASYM 2   // 6 KB stages with the zero points: the same
 #ifndef LS_INT8_CTAS
-#define LS_INT8_CTAS 4              // resident CTAs per SM the INT8 kernel is compiled for (128 registers)
+#define LS_INT8_CTAS 3              // resident CTAs per SM the INT8 kernel is compiled for (168 registers)
 #endif
 constexpr int kWarps = 4;
 // Tensor maps of the TMA-loading variants (unused and zero for the others).
@@ -92,6 +93,7 @@ struct PageItem {
     int valid;      // tokens of the page that exist (0 = skip)
     int last;       // bit 0: the sequence's last page; bit 1: a page the step before this
                     // launch may still be writing (never requested ahead of the dependency wait)
+    int vl;         // valid | last << 8: equals LS_PAGE for a full page of a sequence's interior
 };
 
 // Lookahead over a warp's page sequence. Lane j of the warp holds the block id
@@ -172,11 +174,14 @@ struct PageWindow {
         }
         it.blk = __shfl_sync(LS_FULL_MASK, blk, i);
         const int v = __shfl_sync(LS_FULL_MASK, vl, i);
+        it.vl = v;
         it.valid = v & 255;
         it.last = v >> 8;
         b = c.b;
         ++i;
-        if (!have_next && i + 2 >= n) prefetch(p, cum, h, warp, lane);
+        // Once per window, when its last two pages are about to be handed out (i + 2 >= n
+        // for the first time): one compare instead of three tests per page.
+        if (i == max(n - 2, 1)) prefetch(p, cum, h, warp, lane);
         return true;
     }
 };
@@ -732,6 +737,19 @@ struct PoolInt8Tma {
     static __device__ __forceinline__ int issue(const DecodeParams& p, const TmaMaps& maps, int b,
                                                 int h, const PageItem& it, uint32_t stage,
                                                 uint32_t mbar, int lane, uint64_t pol) {
+        if (__builtin_expect(!ASYM && it.vl == LS_PAGE && p.kv_merged, 1)) {
+            // A full page of a sequence's interior, the case almost every page is: one test,
+            // then three copies with nothing to decide.
+            if (lane == 0) {
+                mbar_expect_tx(mbar, 4096u + 512u + 16u * (uint32_t)p.heads * (uint32_t)sizeof(float));
+                tma_load_5d(stage, &maps.kv, mbar, 0, h, 0, it.blk, 0, pol);
+                tma_load_4d(stage + OFF_KS, &maps.ks, mbar, 0, 0, h, it.blk, pol);
+                bulk_load(stage + OFF_VS, p.v_scale + it.blk * p.vs_b, 16u * p.heads * sizeof(float), mbar);
+            }
+            return LS_PAGE;
+        }
+        // Everything else: a last page (K from the residual, rows past the end), a page to skip,
+        // asymmetric pools, pools the merged map cannot span.
         const bool from_res = p.k_res != nullptr && (it.last & 1) && it.valid > 0;
         if (from_res) {
             const int rr = p.res_rows[b];
@@ -1231,7 +1249,7 @@ decode_kernel(const DecodeParams p, const __grid_constant__ TmaMaps maps) {
         PageItem item;
         int lb;
         if (win.next(p, cum, h, warp, lane, item, lb)) {
-            if (item.last) dep_wait();
+            if (item.vl != LS_PAGE && item.last) dep_wait();
             int mt;
             if constexpr (Pool::kTma)
                 mt = Pool::issue(p, maps, lb, h, item, ring + slot * STAGE_BYTES, mbar0 + 8 * slot, lane, pol);
@@ -1760,7 +1778,7 @@ static int int8_decode_impl(const int32_t* sel, float ratio, int recent, int num
         return ls::launch_decode<ls::MmaInt8<0>, LS_MODE_SPARSE, LS_INT8_STAGES>(p, s, pdl);
     }
     if (k_zero && tma)
-        rc = ls::launch_decode<ls::MmaInt8<1, true>, LS_MODE_DENSE, LS_INT8_TMA_STAGES>(p, s, pdl, &maps);
+        rc = ls::launch_decode<ls::MmaInt8<1, true>, LS_MODE_DENSE, LS_INT8_TMA_STAGES_ASYM>(p, s, pdl, &maps);
     else if (k_zero)
         rc = ls::launch_decode<ls::MmaInt8<1>, LS_MODE_DENSE, LS_INT8_STAGES_ASYM>(p, s, pdl);
     else if (tma)

@@ -42,7 +42,7 @@ ROWS_PER_PARTIAL = 8                # query rows a partial holds (GQA ratio <= 8
 MIN_CHUNK_PAGES = 8                 # never cut the page axis finer than this
 CTAS_PER_SM = 2                     # resident CTAs per SM the kernels are sized for
 # ... and for the INT8 kernel (must match LS_INT8_CTAS the library was built with)
-INT8_CTAS_PER_SM = int(os.environ.get("LATENTSERVE_B200_INT8_CTAS", "4"))
+INT8_CTAS_PER_SM = int(os.environ.get("LATENTSERVE_B200_INT8_CTAS", "3"))
 MAX_BATCH = 1024
 
 _SCRATCH: dict = {}
