@@ -323,7 +323,15 @@ struct PoolFp16 {
         const __half* vb = static_cast<const __half*>(p.v_pool) + it.blk * p.sk_b + h * p.sk_h + lane_off;
         const uint32_t dst0 = stage + hi * 256;
         const uint32_t c0 = (uint32_t)(col ^ hi) << 4;      // ((2i + hi) & 7) = (2i & 7) | hi
-        if (p.k_new != nullptr && (it.last & 1) && it.valid > 0) {
+        if (__builtin_expect(it.vl == LS_PAGE, 1)) {
+            // A full page of a sequence's interior, the case almost every page is: one test.
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const uint32_t dst = dst0 + i * 512 + (c0 ^ (((2 * i) & 7) << 4));
+                cp_async_16_stream(dst, kb + i * row2, pol);
+                cp_async_16_stream(dst + 4096, vb + i * row2, pol);
+            }
+        } else if (p.k_new != nullptr && (it.last & 1) && it.valid > 0) {
             // The step's append rides on this launch: the sequence's newest token (the last
             // valid row of its last page) is not in the pool yet. Its K and V rows come from
             // the caller's new rows, the older rows from the pool, and the new rows are stored
