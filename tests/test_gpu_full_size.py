@@ -6,8 +6,8 @@ that wrap thousands of times — through properties that need no CPU pass over
 hundreds of megabytes: one sequence (or one head of it) against the CPU oracle,
 invariance under moving every page to another physical block, the two page
 loaders agreeing bit for bit, and a clean error flag. Shapes: 32 sequences of
-8K-32K tokens over INT8 pools written by the quantize-on-write kernels, and
-8 x 32 768 tokens at a 50 % page budget (cases follow the reference's
+8K-32K tokens over INT8 pools written by the quantize-on-write kernels,
+8 x 32 768 tokens at a 50 % page budget, and that budget over INT8 pools (cases follow the reference's
 tests/test_cuda_decode.py:174-212 and tests/test_phase14_sparse_kernels.py:110-147).
 """
 
@@ -116,3 +116,57 @@ def test_sparse_attention_at_8_by_32k_half_budget():
     full = ps.sparse_attention(q, k, v, tables, lens, kmin, kmax, ratio=1.0, max_seq_len=context)
     dense = pdc.paged_decode_cuda(q, k, v, tables, lens, context)
     assert torch.equal(full, dense)
+
+
+def test_int8_sparse_attention_at_8_by_32k_half_budget():
+    """The decode kernel's page-list mode on INT8 pools (a combination the reference never
+    built) at the sparse workload's size: 8 sequences of up to 32 768 tokens over pools written
+    by the quantize-on-write kernels, each (sequence, head) attending its own half of the pages."""
+    dev = device()
+    lens = [32768, 32768 - 7, 30001, 32768, 16400, 32768, 9000, 32768]
+    w = synthetic.int8_pools_on_device(lens, 1, dev, seed=13)
+    L = w["layers"][0]
+    q, tables, seq = w["q"][0], w["block_tables"], w["seq_lens"]
+    pages = -(-max(lens) // 16)
+    keep = pages // 2
+    g = torch.Generator(device=dev).manual_seed(5)
+    sel = torch.full((len(lens), 2, keep), -1, dtype=torch.int32, device=dev)
+    for b, n in enumerate(lens):
+        np_ = -(-n // 16)
+        for h in range(2):                                # page 0, the two last pages, a random rest
+            take = min(keep, np_)
+            mid = torch.randperm(np_ - 3, device=dev, generator=g)[: take - 3] + 1
+            picked = torch.cat([torch.tensor([0, np_ - 2, np_ - 1], device=dev), mid]).sort().values
+            sel[b, h, :take] = picked.to(torch.int32)
+    extra = dict(k_scale=L["k_scale"], v_scale=L["v_scale"], k_residual=L["k_residual"], res_rows=w["res_rows"])
+    outs = {}
+    for name in ("tma", "cp_async"):
+        pdc.set_loader(name)
+        try:
+            outs[name] = ps.sparse_decode(q, L["k_pool"], L["v_pool"], tables, seq, sel, **extra).clone()
+        finally:
+            pdc.set_loader("auto")
+    torch.cuda.synchronize()
+    got = outs["tma"]
+    assert torch.isfinite(got).all()
+    assert torch.equal(outs["tma"], outs["cp_async"])
+    # One long and one short sequence against masked softmax over the dequantised rows, on
+    # their own pages only.
+    for b in (2, 6):
+        np_ = -(-lens[b] // 16)
+        blocks = tables[b, :np_].long()
+        row = int(w["res_rows"][b])
+        want = orc.sparse_decode(
+            q[b:b + 1].cpu().numpy(), L["k_pool"][blocks].cpu().numpy(), L["v_pool"][blocks].cpu().numpy(),
+            np.arange(np_, dtype=np.int32)[None], np.asarray([lens[b]], dtype=np.int32),
+            sel[b:b + 1].cpu().numpy(), k_scale=L["k_scale"][blocks].cpu().numpy(),
+            v_scale=L["v_scale"][blocks].cpu().numpy(),
+            k_residual=L["k_residual"][row:row + 1].cpu().numpy(), res_rows=np.zeros(1, dtype=np.int32))
+        close(got[b:b + 1], want)
+    # Every page selected, in order: the dense INT8 kernel's result (the lists of the shorter
+    # sequences carry entries past their end, so the page axis is cut elsewhere and the partial
+    # sums meet in another order: equal to rounding, not to the bit).
+    full = torch.arange(pages, dtype=torch.int32, device=dev).expand(len(lens), 2, pages).contiguous()
+    dense = pdc.paged_decode_cuda(q, L["k_pool"], L["v_pool"], tables, seq, max(lens), **extra)
+    everything = ps.sparse_decode(q, L["k_pool"], L["v_pool"], tables, seq, full, **extra)
+    assert (everything.float() - dense.float()).abs().max() <= 2e-3
