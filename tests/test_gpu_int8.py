@@ -556,3 +556,36 @@ def test_int8_programmatic_launch_with_early_pages_across_page_finalisation(load
         k_scale=c0.k_scale_pool[layer].cpu().numpy(), v_scale=c0.v_scale_pool[layer].cpu().numpy(),
         k_residual=c0.residual(layer).cpu().numpy(), res_rows=c0.residual_rows_tensor(4).cpu().numpy())
     close(base[-1][layer], want)
+
+
+def test_int8_asymmetric_pools_at_long_contexts():
+    """Asymmetric pools (zero points) at contexts where every CTA walks hundreds of pages and
+    chunks span sequences: both loaders agree bit for bit, one sequence against the oracle,
+    and a clean error flag."""
+    lens = [8192, 5000, 8192 - 3, 300]
+    case = _random_int8_case(lens, True, True, seed=31)
+    dev = device()
+    t = {k: torch.from_numpy(np.ascontiguousarray(v)).to(dev) for k, v in case.items()}
+    outs = {}
+    for name in ("tma", "cp_async"):
+        pdc.set_loader(name)
+        try:
+            outs[name] = pdc.paged_decode_cuda(
+                t["q"], t["k_pool"], t["v_pool"], t["block_tables"], t["seq_lens"], max(lens),
+                k_scale=t["k_scale"], v_scale=t["v_scale"], k_zero=t["k_zero"], v_zero=t["v_zero"],
+                k_residual=t["k_residual"], res_rows=t["res_rows"]).clone()
+        finally:
+            pdc.set_loader("auto")
+    assert torch.equal(outs["tma"], outs["cp_async"])
+    assert pdc.error_flag(dev, len(lens), tag="cuda_i8") == 0
+    b = 1
+    pages = -(-lens[b] // 16)
+    blocks = case["block_tables"][b, :pages]
+    row = int(case["res_rows"][b])
+    want = orc.paged_decode(
+        case["q"][b:b + 1], case["k_pool"][blocks], case["v_pool"][blocks],
+        np.arange(pages, dtype=np.int32)[None], np.asarray([lens[b]], dtype=np.int32),
+        k_scale=case["k_scale"][blocks], v_scale=case["v_scale"][blocks], k_zero=case["k_zero"][blocks],
+        v_zero=case["v_zero"][blocks], k_residual=case["k_residual"][row:row + 1],
+        res_rows=np.zeros(1, dtype=np.int32))
+    close(outs["tma"][b:b + 1], want)
