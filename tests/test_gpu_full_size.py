@@ -170,3 +170,62 @@ def test_int8_sparse_attention_at_8_by_32k_half_budget():
     dense = pdc.paged_decode_cuda(q, L["k_pool"], L["v_pool"], tables, seq, max(lens), **extra)
     everything = ps.sparse_decode(q, L["k_pool"], L["v_pool"], tables, seq, full, **extra)
     assert (everything.float() - dense.float()).abs().max() <= 2e-3
+
+
+def test_append_riding_on_the_attention_launch_at_16_by_16k():
+    """The fused-append cache mode at the benchmark's size: three decode steps of 16 sequences
+    at ~16 384 tokens (one of them opening a new page), two layers, through
+    `PagedKVCache.write` + `paged_decode_attention` with the append riding on the attention
+    launch and with a launch of its own: same outputs and same pools, bit for bit."""
+    import random
+
+    from latentserve_b200 import cache as lc
+    from latentserve_b200 import paged_decode as pd
+
+    dev = device()
+    batch, context, layers = 16, 16384 - 1, 2            # the second step opens page 1024
+    spec = lc.KVCacheSpec(num_layers=layers, num_kv_heads=2, head_dim=128, max_seq_len=context + 64,
+                          max_batch_size=batch, device="cuda")
+    need = -(-(context + 64) // 16)
+    g = torch.Generator(device=dev).manual_seed(3)
+    seed_pools = [(torch.randn(int(1.1 * batch * need), 16, 2, 128, dtype=torch.float16, device=dev, generator=g),
+                   torch.randn(int(1.1 * batch * need), 16, 2, 128, dtype=torch.float16, device=dev, generator=g))
+                  for _ in range(layers)]
+    feed = torch.randn(3, layers, batch, 2, 8, 128, dtype=torch.float16, device=dev, generator=g)
+
+    def run(fused):
+        cache = lc.PagedKVCache(spec, num_blocks=int(1.1 * batch * need))
+        for layer in range(layers):
+            cache.k_pool[layer].copy_(seed_pools[layer][0])
+            cache.v_pool[layer].copy_(seed_pools[layer][1])
+        random.Random(0).shuffle(cache.allocator._free)
+        for i in range(batch):
+            cache.tables[i].append(context - (i % 3))    # lengths differ by a token or two
+        if fused:
+            cache.enable_fused_append()
+        outs = []
+        pd.set_decode_backend("cuda")
+        pdc.set_programmatic_launch(True, early_pages=True)
+        try:
+            for step in range(3):
+                cache.advance(1, batch_size=batch)
+                for layer in range(layers):
+                    x = feed[step, layer]
+                    cache.write(layer, x[:, :, 6:7], x[:, :, 7:8])
+                    outs.append(pd.paged_decode_attention(
+                        x[:, :, :6], cache.k_pool[layer], cache.v_pool[layer], cache.block_tables_tensor(batch),
+                        cache.seq_lens_tensor(batch), max_seq_len=cache.max_len).clone())
+            cache.advance(1, batch_size=batch)           # flushes rows nobody attended (none here)
+            torch.cuda.synchronize()
+        finally:
+            pdc.set_programmatic_launch(False)
+        return outs, cache
+
+    plain_outs, plain = run(False)
+    fused_outs, fused = run(True)
+    for a, b in zip(plain_outs, fused_outs):
+        assert torch.equal(a, b)
+    for layer in range(layers):
+        assert torch.equal(plain.k_pool[layer], fused.k_pool[layer])
+        assert torch.equal(plain.v_pool[layer], fused.v_pool[layer])
+    assert torch.equal(plain.block_tables_tensor(batch), fused.block_tables_tensor(batch))
