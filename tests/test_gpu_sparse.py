@@ -208,6 +208,51 @@ def test_selection_threshold_search_takes_both_routes():
             assert (got[b, h, keep:] == -1).all()
 
 
+@pytest.mark.parametrize("seed", range(6))
+def test_selection_on_seeded_random_rows_and_budgets(seed):
+    """Rows of random length, score distribution and budget (spread, heavy ties, clusters around
+    powers of two, both signs, tiny and huge magnitudes): the kept pages are the first n of
+    the stable descending sort, in ascending page order."""
+    rng = np.random.default_rng(1000 + seed)
+    n = int(rng.integers(40, 8193))
+    batch = 6
+    s = np.empty((batch, 2, n), dtype=np.float32)
+    for b in range(batch):
+        for h in range(2):
+            kind = rng.integers(0, 5)
+            x = rng.standard_normal(n)
+            if kind == 0:
+                v = x * 30 + 100
+            elif kind == 1:
+                v = np.round(x * 3) / 2                                # heavy ties
+            elif kind == 2:
+                v = 2.0 ** rng.integers(-3, 9) + x * 2.0 ** -12        # a cluster around a power of two
+            elif kind == 3:
+                v = x * 1e-20
+            else:
+                v = x * 1e20 * (rng.random(n) < 0.5)                   # half of them exactly zero
+            s[b, h] = v.astype(np.float32)
+    lens = rng.integers(1, n * 16 + 1, size=batch).astype(np.int32)
+    lens[0] = n * 16
+    for b, L in enumerate(lens):
+        np_ = -(-int(L) // 16)
+        s[b, :, np_:] = -np.inf
+        s[b, :, 0] = np.inf
+        s[b, :, max(0, np_ - 2):np_] = np.inf
+    ratio = float(rng.choice([0.0625, 0.25, 0.5, 0.75]))
+    k = max(3, int(np.ceil(ratio * n)))
+    dev = device()
+    got = ps.select_for_attention(torch.from_numpy(s).to(dev), torch.from_numpy(lens).to(dev), k, ratio)
+    got = got.cpu().numpy()
+    order = orc.select(s, k)
+    counts = orc.budgets(lens, ratio)
+    for b in range(batch):
+        keep = int(min(counts[b], -(-int(lens[b]) // 16), k))
+        for h in range(2):
+            assert np.array_equal(got[b, h, :keep], np.sort(order[b, h, :keep])), (seed, b, h)
+            assert (got[b, h, keep:] == -1).all()
+
+
 def test_topk_longest_row_and_one_past_it():
     """8192 pages (a 128K context) is the longest row the sort takes."""
     rng = np.random.default_rng(8192)
