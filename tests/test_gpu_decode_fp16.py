@@ -41,6 +41,31 @@ def test_matches_the_oracle_on_ragged_lengths(impl, splits):
     close(_run(on_device(case), impl, splits), want)
 
 
+@pytest.mark.parametrize("seed", range(6))
+def test_matches_the_oracle_on_seeded_random_batches(seed):
+    """Batches of random size and lengths (empty sequences, single tokens, page edges, a few
+    long ones): wherever the page axis happens to be cut, the result is the oracle's, with
+    either loader and with the split count capped or free."""
+    rng = np.random.default_rng(500 + seed)
+    batch = int(rng.integers(1, 41))
+    lens = rng.integers(0, 600, size=batch)
+    lens[rng.integers(0, batch)] = int(rng.integers(2000, 6000))       # one long sequence
+    for edge in (16, 17, 31, 32, 1):
+        lens[rng.integers(0, batch)] = edge
+    case = synthetic.dense_case([int(x) for x in lens], seed=seed)
+    want = orc.paged_decode(case["q"], case["k_pool"], case["v_pool"], case["block_tables"],
+                            case["seq_lens"])
+    t = on_device(case)
+    for loader in ("cp_async", "tma"):
+        pdc.set_loader(loader)
+        try:
+            close(_run(t, pdc.IMPL_MMA, None), want)
+            close(_run(t, pdc.IMPL_MMA, int(rng.integers(1, 9))), want)
+        finally:
+            pdc.set_loader("auto")
+    assert pdc.error_flag(device(), batch) == 0
+
+
 @pytest.mark.parametrize("impl", IMPLS)
 @pytest.mark.parametrize("name,make", [
     ("dense_ragged", lambda: synthetic.dense_case([1024, 300, 61, 17, 1], seed=0)),

@@ -198,6 +198,33 @@ def test_int8_decode_matches_the_oracle(asym, residual, splits, loader):
     assert pdc.error_flag(dev, len(lens), tag="cuda_i8") == 0
 
 
+@pytest.mark.parametrize("seed", range(4))
+def test_int8_decode_on_seeded_random_batches(seed, loader):
+    """Random batch sizes and lengths over symmetric and asymmetric pools with residuals:
+    the oracle's result wherever the page axis is cut."""
+    rng = np.random.default_rng(700 + seed)
+    batch = int(rng.integers(1, 25))
+    lens = rng.integers(0, 500, size=batch)
+    lens[rng.integers(0, batch)] = int(rng.integers(1500, 4000))
+    for edge in (16, 17, 32, 1):
+        lens[rng.integers(0, batch)] = edge
+    lens = [int(x) for x in lens]
+    asym = bool(seed % 2)
+    case = _random_int8_case(lens, asym, True, seed=seed + 50)
+    extra = {k: case[k] for k in ("k_scale", "v_scale", "k_zero", "v_zero", "k_residual", "res_rows")
+             if k in case}
+    want = orc.paged_decode(case["q"], case["k_pool"], case["v_pool"], case["block_tables"],
+                            case["seq_lens"], **extra)
+    dev = device()
+    t = {k: torch.from_numpy(np.ascontiguousarray(v)).to(dev) for k, v in case.items()}
+    got = pdc.paged_decode_cuda(
+        t["q"], t["k_pool"], t["v_pool"], t["block_tables"], t["seq_lens"], max(max(lens), 1),
+        k_scale=t["k_scale"], v_scale=t["v_scale"], k_zero=t.get("k_zero"), v_zero=t.get("v_zero"),
+        k_residual=t["k_residual"], res_rows=t["res_rows"])
+    close(got, want)
+    assert pdc.error_flag(dev, batch, tag="cuda_i8") == 0
+
+
 @pytest.mark.parametrize("strided_scales", [False, True])
 def test_int8_pools_that_are_views_of_larger_tensors(strided_scales, loader):
     """Pools with head stride 128 inside a 3-head allocation (tensor maps describe them;
